@@ -1,0 +1,220 @@
+/*
+ * rwkv7_b200 -- C ABI of the sm_100a RWKV-7 forward library (librwkv7_b200.so).
+ *
+ * This is the boundary a host program binds instead of the reference's C++ backend class
+ * `rwkv7_server::ModelBackend` (include/rwkv_server_backend.hpp:104-147 of the reference) and,
+ * for the op-level entry points, instead of the launchers declared in the reference's
+ * cuda/rwkv7_fast_v4_kernels.cuh.  Every citation below is a path inside the reference project.
+ *
+ * Conventions
+ *   - every function returns an int status (RWKV7_B200_OK == 0); on failure
+ *     rwkv7_b200_last_error() returns a thread-local message.  Nothing exits or aborts.
+ *   - `stream` is a cudaStream_t passed as void*; NULL is the legacy default stream.
+ *   - pointers are device pointers unless the name ends in _host.
+ *   - half tensors are IEEE binary16 passed as uint16_t bit patterns.
+ *   - activations are row-major [B*T, C] (b major, then t); C = 64 * H.
+ *   - functions only enqueue work; they synchronise only where stated.
+ */
+#ifndef RWKV7_B200_H
+#define RWKV7_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define RWKV7_B200_OK 0
+#define RWKV7_B200_BAD_ARG 1
+#define RWKV7_B200_SHAPE 2
+#define RWKV7_B200_PRECISION 3   /* state precision does not match the model (fp16 vs fp32 WKV state) */
+#define RWKV7_B200_CUDA 4
+#define RWKV7_B200_NCCL 5
+#define RWKV7_B200_TIMEOUT 6
+#define RWKV7_B200_NOT_READY 7   /* model not finalised / tensor missing */
+
+/* weight formats of the large matrices (att r/k/v/o, ffn key/value, head) */
+#define RWKV7_B200_FMT_F16 0
+#define RWKV7_B200_FMT_W8A16 1   /* int8, per output channel, symmetric, fp16 scale */
+#define RWKV7_B200_FMT_W4A16 2   /* int4, group 128 along K, asymmetric, fp16 scale and zero */
+
+/* element types accepted by rwkv7_b200_model_set_tensor */
+#define RWKV7_B200_DT_F16 0
+#define RWKV7_B200_DT_BF16 1
+
+/* input activations / epilogues of rwkv7_b200_linear_* */
+#define RWKV7_B200_ACT_NONE 0
+#define RWKV7_B200_ACT_TANH 1
+#define RWKV7_B200_ACT_SIGMOID 2
+#define RWKV7_B200_EPI_NONE 0
+#define RWKV7_B200_EPI_RELU2 1
+#define RWKV7_B200_EPI_F32 3
+
+const char* rwkv7_b200_last_error(void);
+/* Compiled-in facts a binding can check at load time: head size (64) and ABI version. */
+int rwkv7_b200_abi_version(void);
+
+/* ------------------------------------------------------------------------------------------
+ * Model-level entry points (replace rwkv7_server::ModelBackend)
+ * ---------------------------------------------------------------------------------------- */
+
+typedef struct rwkv7_b200_model rwkv7_b200_model;
+
+typedef struct {
+  int layers, channels, ffn, vocab;      /* heads = channels / 64 */
+  int rank_w, rank_a, rank_v, rank_g;    /* LoRA ranks, multiples of 8, <= 512 */
+  int weight_format;                     /* RWKV7_B200_FMT_* ; large matrices are quantised at finalize */
+  int wkv32;                             /* 1: fp32 WKV state (the reference's --wkv32), 0: fp16 */
+  int device;                            /* CUDA device ordinal; -1 = current device */
+  int tp_rank, tp_size;                  /* head-sharded tensor parallelism; 0/1 = off */
+} rwkv7_b200_config;
+
+typedef struct {
+  size_t free_vram_bytes, total_vram_bytes, reserve_vram_bytes, bytes_per_batch;
+  int max_batch_size;
+} rwkv7_b200_capacity;
+
+/* Replaces ModelBackend::ModelBackend (src/rwkv7_fast_v4.cu:1364-1365): creates an empty model. */
+int rwkv7_b200_model_create(const rwkv7_b200_config* cfg, rwkv7_b200_model** out);
+
+/* Replaces the per-tensor upload of load_model_weights (src/rwkv7_fast_v4.cu:630-701).
+ * `name` is the checkpoint tensor name (emb.weight, blocks.N.att.key.weight, ln_out.weight,
+ * head.weight, ...; full list in src/rwkv7_fast_v4.cu:574-596).  `data` holds `count` elements of
+ * `dtype`, on the host (on_device = 0) or on this model's device (1); it is copied and may be
+ * freed on return.  bf16 is converted as half_rn(float(bf16)) like cuda/rwkv7_v3a_ops.cu:79-88.
+ * The pseudo-tensor "emb_ln0" ([vocab, channels] fp16) may be given instead of emb.weight +
+ * blocks.0.ln0.{weight,bias}. */
+int rwkv7_b200_model_set_tensor(rwkv7_b200_model* m, const char* name, const void* data, int dtype,
+                                long long count, int on_device);
+
+/* Builds device layouts (LoRA transposes, emb+LN0 table as cuda/rwkv7_v3a_ops.cu:153-187,
+ * quantisation) and frees staging copies.  Synchronises the device. */
+int rwkv7_b200_model_finalize(rwkv7_b200_model* m);
+int rwkv7_b200_model_destroy(rwkv7_b200_model* m);
+int rwkv7_b200_vocab_size(const rwkv7_b200_model* m);   /* ModelBackend::vocab_size, src/rwkv7_fast_v4.cu:1582 */
+
+/* Element counts of the three state buffers of a batch of B sequences, laid out exactly like
+ * GenerationState (include/rwkv_server_backend.hpp:45-58, src/rwkv7_fast_v4.cu:1177-1185,1381-1390):
+ *   shift   half  [layers][2][B][channels]
+ *   wkv     half or float [layers][B][heads][64][64]   (element size 2, or 4 when wkv32)
+ *   elapsed int32 [B] */
+int rwkv7_b200_state_sizes(const rwkv7_b200_model* m, int B, size_t* shift_elems, size_t* wkv_elems,
+                           size_t* elapsed_elems);
+/* Zero-initialises caller-allocated state buffers (ModelBackend::create_state, :1373-1400). */
+int rwkv7_b200_state_init(const rwkv7_b200_model* m, int B, void* shift, void* wkv, int* elapsed, void* stream);
+
+/* Replaces run_backend_forward / forward_prefill / forward_decode (src/rwkv7_fast_v4.cu:1046-1345,
+ * 1402-1419).  tokens_host is [B][T] row-major on the host (decode: T = 1); the state is updated
+ * in place; logits receives fp32 [B][vocab] of the last token of every sequence.  Token ids are
+ * validated on the host before anything is enqueued (BAD_ARG, state untouched).  Asynchronous:
+ * the logits are valid once `stream` has completed; tokens_host may be reused on return. */
+int rwkv7_b200_forward(rwkv7_b200_model* m, const int64_t* tokens_host, int B, int T, void* shift, void* wkv,
+                       int* elapsed, float* logits, void* stream);
+
+/* Same call for a host program that keeps no device buffers for the result: additionally copies
+ * the logits to logits_host (pinned memory recommended) and synchronises `stream`. */
+int rwkv7_b200_forward_to_host(rwkv7_b200_model* m, const int64_t* tokens_host, int B, int T, void* shift,
+                               void* wkv, int* elapsed, float* logits, float* logits_host, void* stream);
+
+/* Replaces ModelBackend::copy_state_slice (src/rwkv7_fast_v4.cu:1421-1504): copies `count`
+ * sequences from a state of batch size src_B (starting at src_offset) into a state of batch size
+ * dst_B (starting at dst_offset).  Enqueued on `stream`. */
+int rwkv7_b200_copy_state_slice(const rwkv7_b200_model* m, const void* src_shift, const void* src_wkv,
+                                const int* src_elapsed, int src_B, int src_offset, void* dst_shift,
+                                void* dst_wkv, int* dst_elapsed, int dst_B, int dst_offset, int count,
+                                void* stream);
+
+/* Replaces ModelBackend::query_prefill_capacity (src/rwkv7_fast_v4.cu:1534-1580). */
+int rwkv7_b200_query_capacity(const rwkv7_b200_model* m, int prefill_chunk_size, rwkv7_b200_capacity* out);
+
+/* Number of kernels enqueued by forward calls since the model was created (for benchmarks). */
+long long rwkv7_b200_kernel_launches(const rwkv7_b200_model* m);
+
+/* ------------------------------------------------------------------------------------------
+ * Op-level entry points (replace launchers of cuda/rwkv7_fast_v4_kernels.cuh)
+ * ---------------------------------------------------------------------------------------- */
+
+/* rwkv7_wkv_fp16_seq_launch (cuda/rwkv7_wkv_fp16_v2.cu:676-742): w holds the decay pre-activation. */
+int rwkv7_b200_wkv_fp16_seq(void* stream, int B, int T, int C, int H, uint16_t* state, const uint16_t* r,
+                            const uint16_t* w, const uint16_t* k, const uint16_t* v, const uint16_t* a,
+                            const uint16_t* b, uint16_t* y, const int* elapsed);
+/* rwkv7_wkv_fp16_seq_w0_launch (cuda/rwkv7_wkv_fp16_v2.cu:744-830): w0 [C] added in fp32 inside. */
+int rwkv7_b200_wkv_fp16_seq_w0(void* stream, int B, int T, int C, int H, uint16_t* state, const uint16_t* r,
+                               const uint16_t* w, const uint16_t* w0, const uint16_t* k, const uint16_t* v,
+                               const uint16_t* a, const uint16_t* b, uint16_t* y, const int* elapsed);
+/* rwkv7_wkv_fp32io16_launch (cuda/rwkv7_wkv_fp32_v2.cu:237-294), mode 0. */
+int rwkv7_b200_wkv_fp32io16(void* stream, int B, int T, int C, int H, float* state, const uint16_t* r,
+                            const uint16_t* w, const uint16_t* k, const uint16_t* v, const uint16_t* a,
+                            const uint16_t* b, uint16_t* y);
+
+/* rwkv7_tmix_mix6_launch (cuda/rwkv7_fast_ops_fp16.cu:831-860); mix/out are arrays of 6 device pointers
+ * in the order r, w, k, v, a, g; shift [B,C] is consumed and replaced by the last row. */
+int rwkv7_b200_tmix_mix6(void* stream, int B, int T, int C, const uint16_t* x, uint16_t* shift,
+                         const uint16_t* const* mix, uint16_t* const* out);
+/* rwkv7_cmix_mix_launch (cuda/rwkv7_fast_ops_fp16.cu:924-940) */
+int rwkv7_b200_cmix_mix(void* stream, int B, int T, int C, const uint16_t* x, uint16_t* shift,
+                        const uint16_t* x_k, uint16_t* out);
+/* rwkv7_tmix_kk_a_gate_launch (cuda/rwkv7_fast_ops_fp16.cu:862-884) */
+int rwkv7_b200_tmix_kk_a_gate(void* stream, int B, int T, int C, int H, const uint16_t* k, const uint16_t* k_k,
+                              const uint16_t* a0, const uint16_t* a12, const uint16_t* k_a, uint16_t* new_k,
+                              uint16_t* neg_kk, uint16_t* kka);
+/* rwkv7_tmix_lnx_rkvres_xg_launch (cuda/rwkv7_fast_ops_fp16.cu:886-906) */
+int rwkv7_b200_tmix_lnx_rkvres_xg(void* stream, int B, int T, int C, int H, const uint16_t* x, const uint16_t* r,
+                                  const uint16_t* k, const uint16_t* v, const uint16_t* r_k, const uint16_t* weight,
+                                  const uint16_t* bias, const uint16_t* g, uint16_t* out);
+/* rwkv7_tmix_vres_gate_launch (cuda/rwkv7_fast_ops_fp16.cu:908-922) */
+int rwkv7_b200_tmix_vres_gate(void* stream, int B, int T, int C, const uint16_t* v, const uint16_t* v_first,
+                              const uint16_t* v0, const uint16_t* v12, uint16_t* out);
+/* rwkv7_v3a_layer_norm_f16_launch (cuda/rwkv7_v3a_ops.cu:2123-2140) */
+int rwkv7_b200_layer_norm_f16(void* stream, int rows, int C, const uint16_t* x, const uint16_t* weight,
+                              const uint16_t* bias, uint16_t* y, float eps);
+/* rwkv7_v3a_add_layer_norm_f16_launch (cuda/rwkv7_v3a_ops.cu:2142-2160) */
+int rwkv7_b200_add_layer_norm_f16(void* stream, int rows, int C, const uint16_t* x, const uint16_t* residual,
+                                  const uint16_t* weight, const uint16_t* bias, uint16_t* x_out, uint16_t* y,
+                                  float eps);
+/* rwkv7_v3a_add_last_layer_norm_f16_launch (cuda/rwkv7_v3a_ops.cu:2162-2182) */
+int rwkv7_b200_add_last_layer_norm_f16(void* stream, int B, int T, int C, const uint16_t* x,
+                                       const uint16_t* residual, const uint16_t* weight, const uint16_t* bias,
+                                       uint16_t* y, float eps);
+/* rwkv7_v3a_add_layer_norm_cmix_mix_f16_launch (cuda/rwkv7_v3a_ops.cu:2184-2196), for any T */
+int rwkv7_b200_add_layer_norm_cmix_mix_f16(void* stream, int B, int T, int C, const uint16_t* x,
+                                           const uint16_t* residual, uint16_t* shift, const uint16_t* weight,
+                                           const uint16_t* bias, const uint16_t* x_k, uint16_t* x_out,
+                                           uint16_t* mixed, float eps);
+/* rwkv7_v3a_add_layer_norm_tmix_mix6_f16_launch (cuda/rwkv7_v3a_ops.cu:2198-2215), for any B and T */
+int rwkv7_b200_add_layer_norm_tmix_mix6_f16(void* stream, int B, int T, int C, const uint16_t* x,
+                                            const uint16_t* residual, uint16_t* shift, const uint16_t* weight,
+                                            const uint16_t* bias, const uint16_t* const* mix, uint16_t* x_out,
+                                            uint16_t* const* out, float eps);
+/* rwkv7_v4_emb_ln0_bf16_to_f16_launch (cuda/rwkv7_v3a_ops.cu:2101-2115); dtype RWKV7_B200_DT_* */
+int rwkv7_b200_emb_ln0(void* stream, int V, int C, const void* emb, const void* weight, const void* bias,
+                       int dtype, uint16_t* out, float eps);
+/* rwkv7_relu_square_launch (cuda/rwkv7_fast_ops_fp16.cu:942-950) */
+int rwkv7_b200_relu_square(void* stream, const uint16_t* x, uint16_t* out, long long elems);
+/* rwkv7_v3a_advance_i32_launch (cuda/rwkv7_v3a_ops.cu:2117-2121) */
+int rwkv7_b200_advance_i32(void* stream, int* x, int amount, long long elems);
+
+/* rwkv7_v3a_linear_f16_orig_launch / linear_orig_rows_* / linear_t_act_* (cuda/rwkv7_v3a_ops.cu:2270-2302,
+ * 2370-2507): y[M,N] = epi(act(x[M,K]) W^T), W [N,K] row-major fp16.  With RWKV7_B200_EPI_F32 y is
+ * float [M,N] holding float(half(acc)) like the lm-head + rwkv7_v4_f16_to_f32_launch pair
+ * (src/rwkv7_fast_v4.cu:1321-1342). */
+int rwkv7_b200_linear_f16_orig(void* stream, int M, int K, int N, const uint16_t* x, const uint16_t* weight,
+                               int in_act, int epilogue, void* y);
+/* No counterpart in the reference (it has no quantised weights): the same layer on W8A16 / W4A16
+ * weights in the formats written down in oracle/rwkv7_oracle.c and csrc/quant.cu. */
+int rwkv7_b200_linear_w8a16(void* stream, int M, int K, int N, const uint16_t* x, const int8_t* q,
+                            const uint16_t* scale, int epilogue, void* y);
+int rwkv7_b200_linear_w4a16(void* stream, int M, int K, int N, const uint16_t* x, const uint8_t* q,
+                            const uint16_t* scale, const uint16_t* zero, int epilogue, void* y);
+int rwkv7_b200_quant_pack_w8(void* stream, int N, int K, const uint16_t* W, int8_t* q, uint16_t* scale);
+int rwkv7_b200_quant_unpack_w8(void* stream, int N, int K, const int8_t* q, const uint16_t* scale, uint16_t* W);
+int rwkv7_b200_quant_pack_w4(void* stream, int N, int K, const uint16_t* W, uint8_t* q, uint16_t* scale,
+                             uint16_t* zero);
+int rwkv7_b200_quant_unpack_w4(void* stream, int N, int K, const uint8_t* q, const uint16_t* scale,
+                               const uint16_t* zero, uint16_t* W);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RWKV7_B200_H */

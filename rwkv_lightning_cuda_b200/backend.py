@@ -1,0 +1,202 @@
+"""Python mirror of the reference's ``rwkv7_server::ModelBackend`` on top of the C ABI.
+
+Same method names, argument meaning and error behaviour as the reference class
+(include/rwkv_server_backend.hpp:72-147, src/rwkv7_fast_v4.cu:1373-1592): argument errors raise
+(``Rwkv7B200Error`` here, ``std::runtime_error`` there) with the same messages; ``forward_*`` is
+synchronous on return.  torch is used only to own device memory and streams.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+from typing import Dict, Optional, Sequence
+
+import torch
+
+from . import lib as L
+
+
+@dataclass
+class ModelDims:
+    """Mirror of rwkv7_fast_v4::ModelDims (include/rwkv7_fast_v4_common.hpp:29-36) plus LoRA ranks."""
+    layers: int
+    channels: int
+    ffn: int
+    vocab: int
+    rank_w: int = 64
+    rank_a: int = 64
+    rank_v: int = 32
+    rank_g: int = 128
+
+    @property
+    def heads(self) -> int:
+        return self.channels // 64
+
+
+class GenerationState:
+    """Mirror of rwkv7_server::GenerationState: the four device buffers and their layouts."""
+
+    def __init__(self, batch_size: int, wkv32: bool, shift: torch.Tensor, wkv: torch.Tensor, elapsed: torch.Tensor):
+        self.batch_size = batch_size
+        self.wkv32 = wkv32
+        self.shift = shift        # half  [L, 2, B, C]
+        self.wkv_state = wkv      # half or float [L, B, H, 64, 64]
+        self.elapsed = elapsed    # int32 [B]
+
+
+class DeviceLogits:
+    """Mirror of rwkv7_server::DeviceLogits: fp32 [rows, vocab] on the device."""
+
+    def __init__(self):
+        self.rows = 0
+        self.vocab_size = 0
+        self.values: Optional[torch.Tensor] = None
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else C.c_void_p(t.data_ptr())
+
+
+class ModelBackend:
+    """Drop-in counterpart of the reference ``ModelBackend`` (weights given as named tensors)."""
+
+    def __init__(self, dims: ModelDims, tensors: Dict[str, torch.Tensor], use_wkv32: bool = False,
+                 weight_format: int = L.FMT_F16, device: Optional[int] = None, model_path: str = "<synthetic>"):
+        self._lib = L.load_library()
+        self.dims = dims
+        self.use_wkv32 = bool(use_wkv32)
+        self._model_path = model_path
+        self.device = torch.cuda.current_device() if device is None else device
+        cfg = L.Config(dims.layers, dims.channels, dims.ffn, dims.vocab, dims.rank_w, dims.rank_a, dims.rank_v,
+                       dims.rank_g, weight_format, int(self.use_wkv32), self.device, 0, 1)
+        handle = C.c_void_p()
+        L.check(self._lib.rwkv7_b200_model_create(C.byref(cfg), C.byref(handle)))
+        self._h = handle
+        for name, t in tensors.items():
+            self.set_tensor(name, t)
+        L.check(self._lib.rwkv7_b200_model_finalize(self._h))
+        self._pinned: Dict[int, torch.Tensor] = {}
+
+    def set_tensor(self, name: str, t: torch.Tensor) -> None:
+        if t.dtype == torch.float16:
+            dt = L.DT_F16
+        elif t.dtype == torch.bfloat16:
+            dt = L.DT_BF16
+        else:
+            raise TypeError(f"{name}: dtype {t.dtype} not supported (float16 or bfloat16)")
+        t = t.contiguous()
+        L.check(self._lib.rwkv7_b200_model_set_tensor(self._h, name.encode(), _ptr(t), dt, t.numel(), int(t.is_cuda)))
+
+    # ---- IModelBackend surface -------------------------------------------------------------
+    def create_state(self, batch_size: int) -> GenerationState:
+        ns, nw, ne = C.c_size_t(), C.c_size_t(), C.c_size_t()
+        L.check(self._lib.rwkv7_b200_state_sizes(self._h, batch_size, C.byref(ns), C.byref(nw), C.byref(ne)))
+        d = self.dims
+        dev = torch.device("cuda", self.device)
+        shift = torch.empty((d.layers, 2, batch_size, d.channels), dtype=torch.float16, device=dev)
+        wkv = torch.empty((d.layers, batch_size, d.heads, 64, 64), dtype=torch.float32 if self.use_wkv32 else torch.float16, device=dev)
+        elapsed = torch.empty((batch_size,), dtype=torch.int32, device=dev)
+        assert shift.numel() == ns.value and wkv.numel() == nw.value and elapsed.numel() == ne.value
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        L.check(self._lib.rwkv7_b200_state_init(self._h, batch_size, _ptr(shift), _ptr(wkv), _ptr(elapsed), C.c_void_p(stream)))
+        torch.cuda.synchronize(dev)
+        return GenerationState(batch_size, self.use_wkv32, shift, wkv, elapsed)
+
+    def _forward(self, tokens: torch.Tensor, state: GenerationState, logits: DeviceLogits, sync: bool) -> None:
+        B, T = tokens.shape
+        if state.batch_size != B:
+            raise L.Rwkv7B200Error(1, "state batch size mismatch")
+        if state.wkv32 != self.use_wkv32:
+            raise L.Rwkv7B200Error(3, "state wkv precision mismatch")
+        dev = torch.device("cuda", self.device)
+        if logits.values is None or logits.values.numel() < B * self.dims.vocab:
+            logits.values = torch.empty((B, self.dims.vocab), dtype=torch.float32, device=dev)
+        logits.rows, logits.vocab_size = B, self.dims.vocab
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        L.check(self._lib.rwkv7_b200_forward(self._h, C.c_void_p(tokens.data_ptr()), B, T, _ptr(state.shift), _ptr(state.wkv_state),
+                                             _ptr(state.elapsed), _ptr(logits.values), C.c_void_p(stream)))
+        if sync:
+            torch.cuda.current_stream(dev).synchronize()
+
+    @staticmethod
+    def _as_tokens(token_batches) -> torch.Tensor:
+        if isinstance(token_batches, torch.Tensor):
+            t = token_batches.to(dtype=torch.int64, device="cpu").contiguous()
+        else:
+            if len(token_batches) == 0:
+                raise L.Rwkv7B200Error(1, "token_batches must not be empty")
+            n = len(token_batches[0])
+            if n == 0:
+                raise L.Rwkv7B200Error(1, "token batch length must be positive")
+            if any(len(b) != n for b in token_batches):
+                raise L.Rwkv7B200Error(1, "all token batches must share the same length")
+            t = torch.tensor(token_batches, dtype=torch.int64)
+        return t
+
+    def forward_prefill(self, token_batches: Sequence[Sequence[int]], state: GenerationState, logits: DeviceLogits,
+                        sync: bool = True) -> None:
+        self._forward(self._as_tokens(token_batches), state, logits, sync)
+
+    def forward_decode(self, token_batch: Sequence[int], state: GenerationState, logits: DeviceLogits, sync: bool = True) -> None:
+        t = self._as_tokens(token_batch) if isinstance(token_batch, torch.Tensor) else torch.tensor(list(token_batch), dtype=torch.int64)
+        if t.numel() == 0:
+            raise L.Rwkv7B200Error(1, "token_batches must not be empty")
+        self._forward(t.reshape(-1, 1), state, logits, sync)
+
+    def forward_to_host(self, tokens: torch.Tensor, state: GenerationState, logits: DeviceLogits, out_host: torch.Tensor) -> None:
+        """Host-buffer call: token ids from host memory in, fp32 logits in (pinned) host memory out."""
+        B, T = tokens.shape
+        dev = torch.device("cuda", self.device)
+        if logits.values is None or logits.values.numel() < B * self.dims.vocab:
+            logits.values = torch.empty((B, self.dims.vocab), dtype=torch.float32, device=dev)
+        logits.rows, logits.vocab_size = B, self.dims.vocab
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        L.check(self._lib.rwkv7_b200_forward_to_host(self._h, C.c_void_p(tokens.data_ptr()), B, T, _ptr(state.shift),
+                                                     _ptr(state.wkv_state), _ptr(state.elapsed), _ptr(logits.values),
+                                                     C.c_void_p(out_host.data_ptr()), C.c_void_p(stream)))
+
+    def copy_state_slice(self, src: GenerationState, src_offset: int, dst: GenerationState, dst_offset: int, count: int) -> None:
+        if src.wkv32 != dst.wkv32 or src.wkv32 != self.use_wkv32:
+            raise L.Rwkv7B200Error(3, "state slice wkv precision mismatch")
+        dev = torch.device("cuda", self.device)
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        L.check(self._lib.rwkv7_b200_copy_state_slice(
+            self._h, _ptr(src.shift), _ptr(src.wkv_state), _ptr(src.elapsed), src.batch_size, src_offset,
+            _ptr(dst.shift), _ptr(dst.wkv_state), _ptr(dst.elapsed), dst.batch_size, dst_offset, count, C.c_void_p(stream)))
+        torch.cuda.current_stream(dev).synchronize()
+
+    def copy_logits_slice(self, src: DeviceLogits, src_offset: int, dst: DeviceLogits, dst_offset: int, count: int) -> None:
+        if src_offset < 0 or dst_offset < 0 or count <= 0:
+            raise L.Rwkv7B200Error(1, "invalid backend logits slice range")
+        if src.rows <= 0 or src.vocab_size <= 0 or src.values is None:
+            raise L.Rwkv7B200Error(1, "logits slice requires non-empty source")
+        if dst.rows <= 0 or dst.vocab_size != src.vocab_size or dst.values is None:
+            raise L.Rwkv7B200Error(1, "logits slice destination shape mismatch")
+        if src_offset + count > src.rows or dst_offset + count > dst.rows:
+            raise L.Rwkv7B200Error(1, "logits slice range exceeds row count")
+        dst.values[dst_offset:dst_offset + count].copy_(src.values[src_offset:src_offset + count])
+
+    def query_prefill_capacity(self, prefill_chunk_size: int) -> L.Capacity:
+        cap = L.Capacity()
+        L.check(self._lib.rwkv7_b200_query_capacity(self._h, prefill_chunk_size, C.byref(cap)))
+        return cap
+
+    def vocab_size(self) -> int:
+        return self._lib.rwkv7_b200_vocab_size(self._h)
+
+    def model_path(self) -> str:
+        return self._model_path
+
+    def kernel_launches(self) -> int:
+        return int(self._lib.rwkv7_b200_kernel_launches(self._h))
+
+    def close(self) -> None:
+        if getattr(self, "_h", None):
+            self._lib.rwkv7_b200_model_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

@@ -1,0 +1,83 @@
+// Host-callable launchers of the sm_100a kernels (C++ linkage, used by the engine and by the
+// C ABI's op-level exports).  All pointers are device pointers; every function enqueues work on
+// `stream` and returns an rk::Status code without synchronising.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "common.cuh"
+
+namespace rk {
+
+// ---- wkv7.cu
+int wkv7_fp16(cudaStream_t stream, int B, int T, int C, int H, half* state, const half* r, const half* w,
+              const half* w0, int w_mode, const half* k, const half* v, const half* a, const half* b,
+              half* y, const int* elapsed);
+int wkv7_fp32(cudaStream_t stream, int B, int T, int C, int H, float* state, const half* r, const half* w,
+              const half* w0, const half* k, const half* v, const half* a, const half* b, half* y);
+
+// ---- rowops.cu : LayerNorm / residual / token-shift fusions, one CTA per activation row
+struct RowOpArgs {
+  int B = 0, T = 0, C = 0;
+  float eps = 1e-5f;
+  // source: either an embedding gather or x (+ residual)
+  const int64_t* tokens = nullptr;  // [B*T] device, with `table`
+  const half* table = nullptr;      // [V,C] embedding with LN0 folded in
+  int vocab = 0;
+  const half* x = nullptr;          // [B*T,C]
+  const half* residual = nullptr;   // optional, added to x in fp32
+  half* x_out = nullptr;            // optional: half(x + residual) or the gathered row
+  // normalisation
+  const half* ln_w = nullptr;
+  const half* ln_b = nullptr;
+  half* n_out = nullptr;            // optional: half(LN(.)) per row
+  // token shift on the normalised rows
+  half* shift = nullptr;            // [B,C] previous-token row, replaced by the last row
+  int n_mix = 0;                    // 0, 1 (channel mix) or 6 (time mix)
+  const half* mix[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+  half* mix_out[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+  // last_only: only row T-1 of each sequence is normalised, n_out is [B,C]
+  bool identity_norm = false;        // token shift on the rows as given, no LayerNorm
+  bool last_only = false;
+  int* bad_token_flag = nullptr;    // set to 1 if a token id is outside [0, vocab)
+};
+int row_op(cudaStream_t stream, const RowOpArgs& args);
+
+int tmix_kk_a_gate(cudaStream_t stream, int rows, int C, const half* k, const half* k_k, const half* a0,
+                   const half* a12, const half* k_a, half* new_k, half* neg_kk, half* kka);
+int tmix_lnx_rkvres_xg(cudaStream_t stream, int rows, int C, const half* y, const half* r, const half* k,
+                       const half* v, const half* r_k, const half* w, const half* b, const half* g, half* out);
+int tmix_vres_gate(cudaStream_t stream, int rows, int C, const half* v, const half* v_first, const half* v0,
+                   const half* v12, half* out);
+int advance_i32(cudaStream_t stream, int* x, int amount, int n);
+int relu_square(cudaStream_t stream, const half* x, half* out, long long n);
+int bf16_to_f16(cudaStream_t stream, const uint16_t* src, half* dst, long long n);
+int transpose_f16(cudaStream_t stream, const half* src, half* dst, int rows, int cols);
+int emb_ln0(cudaStream_t stream, int V, int C, const void* emb, const void* w, const void* b, int src_is_bf16,
+            half* out, float eps);
+
+// ---- linear.cu : y = act(x) W^T with W [N,K] row-major ("orig" layout of the checkpoint)
+struct LinearArgs {
+  int M = 0, K = 0, N = 0;
+  const half* x = nullptr;   // [M,K]
+  int ldx = 0;               // row stride of x in elements (0 = K)
+  const void* w = nullptr;   // fp16 [N,K] | int8 [N,K] | packed int4 [N,K/2]
+  int fmt = 0;               // 0 fp16, 1 W8A16, 2 W4A16 (group 128)
+  const half* scale = nullptr;  // W8: [N]; W4: [N,K/128]
+  const half* zero = nullptr;   // W4: [N,K/128]
+  int in_act = kActNone;
+  int epi = kEpiNone;
+  EpiArgs ea;
+  void* y = nullptr;         // half [M,N], or float [M,N] for kEpiF32
+};
+int linear(cudaStream_t stream, const LinearArgs& args);
+
+// ---- quant.cu
+int quant_pack_w8(cudaStream_t stream, int N, int K, const half* W, int8_t* q, half* scale);
+int quant_unpack_w8(cudaStream_t stream, int N, int K, const int8_t* q, const half* scale, half* W);
+int quant_pack_w4(cudaStream_t stream, int N, int K, const half* W, uint8_t* q, half* scale, half* zero);
+int quant_unpack_w4(cudaStream_t stream, int N, int K, const uint8_t* q, const half* scale, const half* zero, half* W);
+
+}  // namespace rk

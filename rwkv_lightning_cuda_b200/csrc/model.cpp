@@ -1,0 +1,487 @@
+// Host-side engine: see model.h.  The launch order follows the reference's
+// run_backend_forward (src/rwkv7_fast_v4.cu:1158-1342) but with persistent workspaces, the
+// embedding table on the device, fused row kernels and a captured CUDA graph per decode shape
+// instead of per-call allocation, a host gather and ~14 separate launches per layer.
+#include "model.h"
+
+#include <algorithm>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <limits>
+
+namespace rk {
+
+// ------------------------------------------------------------------ errors
+namespace {
+thread_local char g_error[512] = "";
+thread_local long long g_launches = 0;
+}  // namespace
+
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, ap);
+  va_end(ap);
+}
+const char* last_error() { return g_error; }
+long long& launch_counter() { return g_launches; }
+
+int cuda_status(cudaError_t err, const char* what) {
+  if (err == cudaSuccess) return kOk;
+  set_error("CUDA error in %s: %s", what, cudaGetErrorString(err));
+  return kCuda;
+}
+
+// ------------------------------------------------------------------ buffers
+int DevBuf::alloc(size_t n) {
+  release();
+  if (n == 0) return kOk;
+  RK_CUDA(cudaMalloc(&p, n));
+  bytes = n;
+  return kOk;
+}
+void DevBuf::release() {
+  if (p) cudaFree(p);
+  p = nullptr;
+  bytes = 0;
+}
+Workspace::~Workspace() {
+  if (tokens_pinned) cudaFreeHost(tokens_pinned);
+  if (tokens_copied) cudaEventDestroy(tokens_copied);
+}
+
+// ------------------------------------------------------------------ model
+Model::Model(const rwkv7_b200_config& cfg) : cfg_(cfg) {
+  H_ = cfg.channels / kHead;
+  layers_.resize(static_cast<size_t>(cfg.layers));
+}
+Model::~Model() {
+  for (auto& kv : graphs_)
+    if (kv.second.exec) cudaGraphExecDestroy(kv.second.exec);
+}
+
+int Model::use_device() const {
+  if (cfg_.device >= 0) RK_CUDA(cudaSetDevice(cfg_.device));
+  return kOk;
+}
+
+int Model::upload(DevBuf& dst, const void* data, int dtype, long long count, int on_device, long long expect) {
+  RK_REQUIRE(count == expect, kShape, "set_tensor: got %lld elements, expected %lld", count, expect);
+  RK_REQUIRE(dtype == RWKV7_B200_DT_F16 || dtype == RWKV7_B200_DT_BF16, kBadArg, "set_tensor: unknown dtype %d", dtype);
+  const size_t bytes = static_cast<size_t>(count) * 2;
+  int s = dst.alloc(bytes);
+  if (s != kOk) return s;
+  const cudaMemcpyKind kind = on_device ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice;
+  if (dtype == RWKV7_B200_DT_F16) {
+    RK_CUDA(cudaMemcpy(dst.p, data, bytes, kind));
+  } else {
+    DevBuf tmp;
+    s = tmp.alloc(bytes);
+    if (s != kOk) return s;
+    RK_CUDA(cudaMemcpy(tmp.p, data, bytes, kind));
+    s = bf16_to_f16(nullptr, tmp.as<uint16_t>(), dst.as<half>(), count);
+    if (s != kOk) return s;
+    RK_CUDA(cudaDeviceSynchronize());
+  }
+  return kOk;
+}
+
+int Model::upload_matrix(Matrix& m, int N, int K, const void* data, int dtype, long long count, int on_device) {
+  m.N = N;
+  m.K = K;
+  m.fmt = RWKV7_B200_FMT_F16;
+  return upload(m.w, data, dtype, count, on_device, static_cast<long long>(N) * K);
+}
+
+int Model::set_tensor(const char* name, const void* data, int dtype, long long count, int on_device) {
+  RK_REQUIRE(name && data, kBadArg, "set_tensor: null argument");
+  RK_REQUIRE(!finalized_, kBadArg, "set_tensor: model already finalised");
+  int s = use_device();
+  if (s != kOk) return s;
+  const long long C = cfg_.channels, F = cfg_.ffn, V = cfg_.vocab;
+  const std::string n(name);
+  if (n == "emb_ln0") return upload(emb_ln0_, data, dtype, count, on_device, V * C);
+  if (n == "emb.weight") {
+    // kept in its source type: LN0 is evaluated from the checkpoint values, not from rounded halves
+    RK_REQUIRE(count == V * C, kShape, "set_tensor: emb.weight has %lld elements, expected %lld", count, V * C);
+    emb_dtype_ = dtype;
+    s = emb_raw_.alloc(static_cast<size_t>(count) * 2);
+    if (s != kOk) return s;
+    RK_CUDA(cudaMemcpy(emb_raw_.p, data, static_cast<size_t>(count) * 2, on_device ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice));
+    return kOk;
+  }
+  if (n == "ln_out.weight") return upload(ln_out_w_, data, dtype, count, on_device, C);
+  if (n == "ln_out.bias") return upload(ln_out_b_, data, dtype, count, on_device, C);
+  if (n == "head.weight") return upload_matrix(head_, static_cast<int>(V), static_cast<int>(C), data, dtype, count, on_device);
+
+  int layer = -1, off = 0;
+  if (sscanf(name, "blocks.%d.%n", &layer, &off) < 1 || layer < 0 || layer >= cfg_.layers || off == 0) {
+    set_error("set_tensor: unknown tensor name '%s'", name);
+    return kBadArg;
+  }
+  const std::string key(name + off);
+  LayerWeights& L = layers_[static_cast<size_t>(layer)];
+  if (key == "ln0.weight" || key == "ln0.bias") {
+    RK_REQUIRE(layer == 0 && count == C, kShape, "set_tensor: bad ln0 tensor");
+    RK_REQUIRE(emb_dtype_ < 0 || emb_dtype_ == dtype, kBadArg, "set_tensor: ln0 and emb.weight must share a dtype");
+    DevBuf& dst = key == "ln0.weight" ? ln0_w_raw_ : ln0_b_raw_;
+    s = dst.alloc(static_cast<size_t>(count) * 2);
+    if (s != kOk) return s;
+    RK_CUDA(cudaMemcpy(dst.p, data, static_cast<size_t>(count) * 2, on_device ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice));
+    if (emb_dtype_ < 0) emb_dtype_ = dtype;
+    return kOk;
+  }
+  struct VecSlot { const char* key; DevBuf* buf; long long n; };
+  const VecSlot vecs[] = {
+      {"ln1.weight", &L.ln1_w, C}, {"ln1.bias", &L.ln1_b, C}, {"ln2.weight", &L.ln2_w, C}, {"ln2.bias", &L.ln2_b, C},
+      {"att.x_r", &L.mix[0], C}, {"att.x_w", &L.mix[1], C}, {"att.x_k", &L.mix[2], C}, {"att.x_v", &L.mix[3], C},
+      {"att.x_a", &L.mix[4], C}, {"att.x_g", &L.mix[5], C}, {"att.w0", &L.w0, C}, {"att.a0", &L.a0, C},
+      {"att.v0", &L.v0, C}, {"att.k_k", &L.k_k, C}, {"att.k_a", &L.k_a, C}, {"att.r_k", &L.r_k, C},
+      {"att.ln_x.weight", &L.lnx_w, C}, {"att.ln_x.bias", &L.lnx_b, C}, {"ffn.x_k", &L.ffn_x_k, C},
+  };
+  for (const VecSlot& v : vecs)
+    if (key == v.key) return upload(*v.buf, data, dtype, count, on_device, v.n);
+  if (key == "att.receptance.weight") return upload_matrix(L.Wr, C, C, data, dtype, count, on_device);
+  if (key == "att.key.weight") return upload_matrix(L.Wk, C, C, data, dtype, count, on_device);
+  if (key == "att.value.weight") return upload_matrix(L.Wv, C, C, data, dtype, count, on_device);
+  if (key == "att.output.weight") return upload_matrix(L.Wo, C, C, data, dtype, count, on_device);
+  if (key == "ffn.key.weight") return upload_matrix(L.Wkey, F, C, data, dtype, count, on_device);
+  if (key == "ffn.value.weight") return upload_matrix(L.Wval, C, F, data, dtype, count, on_device);
+  struct LoraSlot { const char* key; long long n; };
+  const LoraSlot loras[] = {
+      {"att.w1", C * cfg_.rank_w}, {"att.w2", C * cfg_.rank_w}, {"att.a1", C * cfg_.rank_a}, {"att.a2", C * cfg_.rank_a},
+      {"att.g1", C * cfg_.rank_g}, {"att.g2", C * cfg_.rank_g}, {"att.v1", C * cfg_.rank_v}, {"att.v2", C * cfg_.rank_v},
+  };
+  for (const LoraSlot& l : loras)
+    if (key == l.key) return upload(lora_raw_[n], data, dtype, count, on_device, l.n);
+  set_error("set_tensor: unknown tensor name '%s'", name);
+  return kBadArg;
+}
+
+int Model::transpose_into(DevBuf& dst, const DevBuf& src, int rows, int cols) {
+  RK_REQUIRE(src.p && src.bytes == static_cast<size_t>(rows) * cols * 2, kNotReady, "finalize: LoRA tensor missing");
+  int s = dst.alloc(src.bytes);
+  if (s != kOk) return s;
+  return transpose_f16(nullptr, src.as<half>(), dst.as<half>(), rows, cols);
+}
+
+int Model::quantize(Matrix& m) {
+  if (cfg_.weight_format == RWKV7_B200_FMT_F16) return kOk;
+  RK_REQUIRE(m.w.p, kNotReady, "finalize: matrix missing");
+  DevBuf q;
+  int s;
+  if (cfg_.weight_format == RWKV7_B200_FMT_W8A16) {
+    if ((s = q.alloc(static_cast<size_t>(m.N) * m.K)) != kOk) return s;
+    if ((s = m.scale.alloc(static_cast<size_t>(m.N) * 2)) != kOk) return s;
+    if ((s = quant_pack_w8(nullptr, m.N, m.K, m.w.as<half>(), q.as<int8_t>(), m.scale.as<half>())) != kOk) return s;
+  } else {
+    RK_REQUIRE(m.K % 128 == 0, kShape, "finalize: W4A16 needs K %% 128 == 0 (K=%d)", m.K);
+    const size_t groups = static_cast<size_t>(m.N) * (m.K / 128);
+    if ((s = q.alloc(static_cast<size_t>(m.N) * m.K / 2)) != kOk) return s;
+    if ((s = m.scale.alloc(groups * 2)) != kOk) return s;
+    if ((s = m.zero.alloc(groups * 2)) != kOk) return s;
+    if ((s = quant_pack_w4(nullptr, m.N, m.K, m.w.as<half>(), q.as<uint8_t>(), m.scale.as<half>(), m.zero.as<half>())) != kOk) return s;
+  }
+  RK_CUDA(cudaDeviceSynchronize());
+  m.w = std::move(q);
+  m.fmt = cfg_.weight_format;
+  return kOk;
+}
+
+int Model::finalize() {
+  RK_REQUIRE(!finalized_, kBadArg, "finalize: called twice");
+  int s = use_device();
+  if (s != kOk) return s;
+  const int C = cfg_.channels, V = cfg_.vocab;
+  if (!emb_ln0_.p) {
+    RK_REQUIRE(emb_raw_.p && ln0_w_raw_.p && ln0_b_raw_.p, kNotReady, "finalize: need emb_ln0 or emb.weight + blocks.0.ln0.*");
+    if ((s = emb_ln0_.alloc(static_cast<size_t>(V) * C * 2)) != kOk) return s;
+    if ((s = emb_ln0(nullptr, V, C, emb_raw_.p, ln0_w_raw_.p, ln0_b_raw_.p, emb_dtype_ == RWKV7_B200_DT_BF16,
+                     emb_ln0_.as<half>(), 1e-5f)) != kOk) return s;
+    RK_CUDA(cudaDeviceSynchronize());
+  }
+  emb_raw_.release(); ln0_w_raw_.release(); ln0_b_raw_.release();
+  RK_REQUIRE(ln_out_w_.p && ln_out_b_.p && head_.w.p, kNotReady, "finalize: ln_out / head missing");
+
+  for (int li = 0; li < cfg_.layers; ++li) {
+    LayerWeights& L = layers_[static_cast<size_t>(li)];
+    const std::string pre = "blocks." + std::to_string(li) + ".att.";
+    struct T { const char* key; DevBuf* dst; int rows, cols; };
+    // checkpoint: x1 [C,R] (down), x2 [R,C] (up); device: down [R,C], up [C,R]
+    const T ts[] = {
+        {"w1", &L.w1t, C, cfg_.rank_w}, {"w2", &L.w2t, cfg_.rank_w, C}, {"a1", &L.a1t, C, cfg_.rank_a},
+        {"a2", &L.a2t, cfg_.rank_a, C}, {"g1", &L.g1t, C, cfg_.rank_g}, {"g2", &L.g2t, cfg_.rank_g, C},
+        {"v1", &L.v1t, C, cfg_.rank_v}, {"v2", &L.v2t, cfg_.rank_v, C},
+    };
+    for (const T& t : ts) {
+      if (li == 0 && t.key[0] == 'v') continue;  // layer 0 has no value residual
+      auto it = lora_raw_.find(pre + t.key);
+      RK_REQUIRE(it != lora_raw_.end(), kNotReady, "finalize: %s%s missing", pre.c_str(), t.key);
+      if ((s = transpose_into(*t.dst, it->second, t.rows, t.cols)) != kOk) return s;
+    }
+    const DevBuf* need[] = {&L.ln1_w, &L.ln1_b, &L.ln2_w, &L.ln2_b, &L.mix[0], &L.mix[1], &L.mix[2], &L.mix[3], &L.mix[4],
+                            &L.mix[5], &L.w0, &L.a0, &L.k_k, &L.k_a, &L.r_k, &L.lnx_w, &L.lnx_b, &L.ffn_x_k,
+                            &L.Wr.w, &L.Wk.w, &L.Wv.w, &L.Wo.w, &L.Wkey.w, &L.Wval.w};
+    for (const DevBuf* b : need) RK_REQUIRE(b->p, kNotReady, "finalize: a tensor of layer %d is missing", li);
+    RK_REQUIRE(li == 0 || L.v0.p, kNotReady, "finalize: att.v0 of layer %d missing", li);
+    for (Matrix* m : {&L.Wr, &L.Wk, &L.Wv, &L.Wo, &L.Wkey, &L.Wval})
+      if ((s = quantize(*m)) != kOk) return s;
+  }
+  RK_CUDA(cudaDeviceSynchronize());
+  lora_raw_.clear();
+  if ((s = quantize(head_)) != kOk) return s;
+  finalized_ = true;
+  return kOk;
+}
+
+int Model::state_sizes(int B, size_t* shift_elems, size_t* wkv_elems, size_t* elapsed_elems) const {
+  RK_REQUIRE(B > 0, kBadArg, "batch_size must be positive");
+  if (shift_elems) *shift_elems = static_cast<size_t>(cfg_.layers) * 2 * B * cfg_.channels;
+  if (wkv_elems) *wkv_elems = static_cast<size_t>(cfg_.layers) * B * H_ * kHead * kHead;
+  if (elapsed_elems) *elapsed_elems = static_cast<size_t>(B);
+  return kOk;
+}
+
+int Model::state_init(int B, void* shift, void* wkv, int* elapsed, cudaStream_t stream) const {
+  size_t ns, nw, ne;
+  int s = state_sizes(B, &ns, &nw, &ne);
+  if (s != kOk) return s;
+  RK_REQUIRE(shift && wkv && elapsed, kBadArg, "state_init: null state buffer");
+  if ((s = use_device()) != kOk) return s;
+  RK_CUDA(cudaMemsetAsync(shift, 0, ns * 2, stream));
+  RK_CUDA(cudaMemsetAsync(wkv, 0, nw * (cfg_.wkv32 ? 4 : 2), stream));
+  RK_CUDA(cudaMemsetAsync(elapsed, 0, ne * sizeof(int), stream));
+  return kOk;
+}
+
+int Model::copy_state_slice(const void* src_shift, const void* src_wkv, const int* src_elapsed, int src_B, int src_off,
+                            void* dst_shift, void* dst_wkv, int* dst_elapsed, int dst_B, int dst_off, int count,
+                            cudaStream_t stream) const {
+  RK_REQUIRE(src_off >= 0 && dst_off >= 0 && count > 0, kBadArg, "invalid backend state slice range");
+  RK_REQUIRE(src_B > 0 && dst_B > 0, kBadArg, "state slice requires non-empty source and destination");
+  RK_REQUIRE(src_off + count <= src_B && dst_off + count <= dst_B, kBadArg, "state slice range exceeds batch size");
+  RK_REQUIRE(src_shift && src_wkv && src_elapsed && dst_shift && dst_wkv && dst_elapsed, kBadArg, "state slice: null buffer");
+  int s = use_device();
+  if (s != kOk) return s;
+  const size_t C = static_cast<size_t>(cfg_.channels);
+  const size_t lane = static_cast<size_t>(H_) * kHead * kHead * (cfg_.wkv32 ? 4 : 2);
+  // one strided copy per buffer: [layers*2] rows of count*C halves, [layers] rows of count*lane bytes
+  RK_CUDA(cudaMemcpy2DAsync(static_cast<char*>(dst_shift) + static_cast<size_t>(dst_off) * C * 2, static_cast<size_t>(dst_B) * C * 2,
+                            static_cast<const char*>(src_shift) + static_cast<size_t>(src_off) * C * 2, static_cast<size_t>(src_B) * C * 2,
+                            static_cast<size_t>(count) * C * 2, static_cast<size_t>(cfg_.layers) * 2, cudaMemcpyDeviceToDevice, stream));
+  RK_CUDA(cudaMemcpy2DAsync(static_cast<char*>(dst_wkv) + static_cast<size_t>(dst_off) * lane, static_cast<size_t>(dst_B) * lane,
+                            static_cast<const char*>(src_wkv) + static_cast<size_t>(src_off) * lane, static_cast<size_t>(src_B) * lane,
+                            static_cast<size_t>(count) * lane, static_cast<size_t>(cfg_.layers), cudaMemcpyDeviceToDevice, stream));
+  RK_CUDA(cudaMemcpyAsync(dst_elapsed + dst_off, src_elapsed + src_off, static_cast<size_t>(count) * sizeof(int),
+                          cudaMemcpyDeviceToDevice, stream));
+  return kOk;
+}
+
+namespace {
+size_t workspace_halves(const rwkv7_b200_config& c, size_t rows, size_t B) {
+  const size_t C = c.channels;
+  return rows * C * 25 + rows * static_cast<size_t>(c.ffn) + rows * 512 * 4 + B * C + 1024;
+}
+}  // namespace
+
+int Model::query_capacity(int chunk, rwkv7_b200_capacity* out) const {
+  RK_REQUIRE(chunk > 0, kBadArg, "prefill chunk size must be positive");
+  RK_REQUIRE(out, kBadArg, "query_capacity: null output");
+  int s = use_device();
+  if (s != kOk) return s;
+  RK_CUDA(cudaMemGetInfo(&out->free_vram_bytes, &out->total_vram_bytes));
+  const size_t L = cfg_.layers, C = cfg_.channels;
+  const size_t state = L * 2 * C * 2 + L * H_ * kHead * kHead * (cfg_.wkv32 ? 4 : 2) + sizeof(int);
+  const size_t arena = workspace_halves(cfg_, static_cast<size_t>(chunk), 1) * 2 + static_cast<size_t>(chunk) * 8;
+  out->bytes_per_batch = state + arena + static_cast<size_t>(cfg_.vocab) * 4;
+  out->reserve_vram_bytes = std::max<size_t>(static_cast<size_t>(512) << 20, out->free_vram_bytes / 10);
+  const size_t usable = out->free_vram_bytes > out->reserve_vram_bytes ? out->free_vram_bytes - out->reserve_vram_bytes : 0;
+  out->max_batch_size = static_cast<int>(std::min<size_t>(usable / out->bytes_per_batch, std::numeric_limits<int>::max()));
+  return kOk;
+}
+
+Workspace* Model::workspace(int B, int T) {
+  auto key = std::make_pair(B, T);
+  auto it = workspaces_.find(key);
+  if (it != workspaces_.end()) return it->second.get();
+  auto ws = std::make_unique<Workspace>();
+  const size_t rows = static_cast<size_t>(B) * T, C = cfg_.channels, F = cfg_.ffn;
+  ws->rows = static_cast<int>(rows);
+  ws->B = B;
+  const size_t halves = workspace_halves(cfg_, rows, B);
+  if (ws->arena.alloc(halves * 2 + rows * 8 + 256) != kOk) return nullptr;
+  half* p = ws->arena.as<half>();
+  auto take = [&](size_t n) { half* q = p; p += (n + 7) & ~static_cast<size_t>(7); return q; };
+  const size_t RC = rows * C;
+  ws->xA = take(RC); ws->xB = take(RC);
+  for (int i = 0; i < 6; ++i) ws->xm[i] = take(RC);
+  ws->r = take(RC); ws->k = take(RC); ws->v = take(RC); ws->vfirst = take(RC); ws->vout = take(RC);
+  ws->w12 = take(RC); ws->a12 = take(RC); ws->g = take(RC); ws->k2 = take(RC); ws->nkk = take(RC); ws->kka = take(RC);
+  ws->y = take(RC); ws->y2 = take(RC); ws->att = take(RC); ws->mixed = take(RC); ws->ffn = take(RC);
+  ws->hid = take(rows * F);
+  for (int i = 0; i < 4; ++i) ws->l1[i] = take(rows * 512);
+  ws->xf = take(static_cast<size_t>(B) * C);
+  ws->tokens = reinterpret_cast<int64_t*>(take(rows * 4 + 8));
+  if (cudaMallocHost(&ws->tokens_pinned, rows * sizeof(int64_t)) != cudaSuccess) return nullptr;
+  if (cudaEventCreateWithFlags(&ws->tokens_copied, cudaEventDisableTiming) != cudaSuccess) return nullptr;
+  Workspace* raw = ws.get();
+  workspaces_[key] = std::move(ws);
+  return raw;
+}
+
+int Model::lin(cudaStream_t s, int M, const Matrix& W, const half* x, void* y, int epi) {
+  LinearArgs a;
+  a.M = M; a.K = W.K; a.N = W.N; a.x = x; a.w = W.w.p; a.fmt = W.fmt;
+  a.scale = W.scale.as<half>(); a.zero = W.zero.as<half>(); a.epi = epi; a.y = y;
+  return linear(s, a);
+}
+
+int Model::lin16(cudaStream_t s, int M, int K, int N, const half* x, const half* w, half* y, int in_act, int epi,
+                 const EpiArgs& ea) {
+  LinearArgs a;
+  a.M = M; a.K = K; a.N = N; a.x = x; a.w = w; a.fmt = RWKV7_B200_FMT_F16; a.in_act = in_act; a.epi = epi; a.ea = ea; a.y = y;
+  return linear(s, a);
+}
+
+#define RK_TRY(expr)            \
+  do {                          \
+    int _s = (expr);            \
+    if (_s != kOk) return _s;   \
+  } while (0)
+
+int Model::enqueue(Workspace& ws, int B, int T, half* shift, void* wkv, int* elapsed, float* logits, cudaStream_t st) {
+  const int C = cfg_.channels, L = cfg_.layers, rows = B * T;
+  const EpiArgs none;
+  {
+    RowOpArgs a;
+    a.B = B; a.T = T; a.C = C; a.tokens = ws.tokens; a.table = emb_ln0_.as<half>(); a.vocab = cfg_.vocab;
+    a.x_out = ws.xA; a.ln_w = layers_[0].ln1_w.as<half>(); a.ln_b = layers_[0].ln1_b.as<half>();
+    a.shift = shift; a.n_mix = 6;
+    for (int i = 0; i < 6; ++i) { a.mix[i] = layers_[0].mix[i].as<half>(); a.mix_out[i] = ws.xm[i]; }
+    RK_TRY(row_op(st, a));
+  }
+  for (int li = 0; li < L; ++li) {
+    const LayerWeights& W = layers_[static_cast<size_t>(li)];
+    half* shift0 = shift + static_cast<size_t>(li) * 2 * B * C;
+    half* shift1 = shift0 + static_cast<size_t>(B) * C;
+    half *xr = ws.xm[0], *xw = ws.xm[1], *xk = ws.xm[2], *xv = ws.xm[3], *xa = ws.xm[4], *xg = ws.xm[5];
+    half* v_lin = li == 0 ? ws.vfirst : ws.v;
+    RK_TRY(lin(st, rows, W.Wr, xr, ws.r, kEpiNone));
+    RK_TRY(lin(st, rows, W.Wk, xk, ws.k, kEpiNone));
+    RK_TRY(lin(st, rows, W.Wv, xv, v_lin, kEpiNone));
+    RK_TRY(lin16(st, rows, C, cfg_.rank_w, xw, W.w1t.as<half>(), ws.l1[0], kActNone, kEpiNone, none));
+    RK_TRY(lin16(st, rows, C, cfg_.rank_a, xa, W.a1t.as<half>(), ws.l1[1], kActNone, kEpiNone, none));
+    RK_TRY(lin16(st, rows, C, cfg_.rank_g, xg, W.g1t.as<half>(), ws.l1[2], kActNone, kEpiNone, none));
+    RK_TRY(lin16(st, rows, cfg_.rank_w, C, ws.l1[0], W.w2t.as<half>(), ws.w12, kActTanh, kEpiNone, none));
+    RK_TRY(lin16(st, rows, cfg_.rank_a, C, ws.l1[1], W.a2t.as<half>(), ws.a12, kActNone, kEpiNone, none));
+    RK_TRY(lin16(st, rows, cfg_.rank_g, C, ws.l1[2], W.g2t.as<half>(), ws.g, kActSigmoid, kEpiNone, none));
+    const half* v_use = ws.vfirst;
+    if (li > 0) {
+      RK_TRY(lin16(st, rows, C, cfg_.rank_v, xv, W.v1t.as<half>(), ws.l1[3], kActNone, kEpiNone, none));
+      EpiArgs ea;
+      ea.v = ws.v; ea.v_first = ws.vfirst; ea.v0 = W.v0.as<half>();
+      RK_TRY(lin16(st, rows, cfg_.rank_v, C, ws.l1[3], W.v2t.as<half>(), ws.vout, kActNone, kEpiVres, ea));
+      v_use = ws.vout;
+    }
+    RK_TRY(tmix_kk_a_gate(st, rows, C, ws.k, W.k_k.as<half>(), W.a0.as<half>(), ws.a12, W.k_a.as<half>(), ws.k2, ws.nkk, ws.kka));
+    const size_t wkv_off = static_cast<size_t>(li) * B * H_ * kHead * kHead;
+    if (cfg_.wkv32) {
+      RK_TRY(wkv7_fp32(st, B, T, C, H_, static_cast<float*>(wkv) + wkv_off, ws.r, ws.w12, W.w0.as<half>(), ws.k2, v_use,
+                       ws.nkk, ws.kka, ws.y));
+    } else {
+      // the reference adds w0 in fp32 inside the kernel for T <= 16 and pre-rounds the sum otherwise
+      RK_TRY(wkv7_fp16(st, B, T, C, H_, static_cast<half*>(wkv) + wkv_off, ws.r, ws.w12, W.w0.as<half>(), T <= 16 ? 1 : 2,
+                       ws.k2, v_use, ws.nkk, ws.kka, ws.y, elapsed));
+    }
+    RK_TRY(tmix_lnx_rkvres_xg(st, rows, C, ws.y, ws.r, ws.k2, v_use, W.r_k.as<half>(), W.lnx_w.as<half>(), W.lnx_b.as<half>(),
+                              ws.g, ws.y2));
+    RK_TRY(lin(st, rows, W.Wo, ws.y2, ws.att, kEpiNone));
+    {
+      RowOpArgs a;
+      a.B = B; a.T = T; a.C = C; a.x = ws.xA; a.residual = ws.att; a.x_out = ws.xB;
+      a.ln_w = W.ln2_w.as<half>(); a.ln_b = W.ln2_b.as<half>(); a.shift = shift1; a.n_mix = 1;
+      a.mix[0] = W.ffn_x_k.as<half>(); a.mix_out[0] = ws.mixed;
+      RK_TRY(row_op(st, a));
+    }
+    RK_TRY(lin(st, rows, W.Wkey, ws.mixed, ws.hid, kEpiRelu2));
+    RK_TRY(lin(st, rows, W.Wval, ws.hid, ws.ffn, kEpiNone));
+    RowOpArgs a;
+    a.B = B; a.T = T; a.C = C; a.x = ws.xB; a.residual = ws.ffn;
+    if (li + 1 < L) {
+      const LayerWeights& Nx = layers_[static_cast<size_t>(li) + 1];
+      a.x_out = ws.xA; a.ln_w = Nx.ln1_w.as<half>(); a.ln_b = Nx.ln1_b.as<half>();
+      a.shift = shift + static_cast<size_t>(li + 1) * 2 * B * C; a.n_mix = 6;
+      for (int i = 0; i < 6; ++i) { a.mix[i] = Nx.mix[i].as<half>(); a.mix_out[i] = ws.xm[i]; }
+    } else {
+      a.ln_w = ln_out_w_.as<half>(); a.ln_b = ln_out_b_.as<half>(); a.n_out = ws.xf; a.last_only = true;
+    }
+    RK_TRY(row_op(st, a));
+  }
+  RK_TRY(advance_i32(st, elapsed, T, B));
+  RK_TRY(lin(st, B, head_, ws.xf, logits, kEpiF32));
+  return kOk;
+}
+
+int Model::forward(const int64_t* tokens_host, int B, int T, void* shift, void* wkv, int* elapsed, float* logits,
+                   cudaStream_t stream) {
+  RK_REQUIRE(finalized_, kNotReady, "forward: model not finalised");
+  RK_REQUIRE(B > 0, kBadArg, "token_batches must not be empty");
+  RK_REQUIRE(T > 0, kBadArg, "token batch length must be positive");
+  RK_REQUIRE(tokens_host && shift && wkv && elapsed && logits, kBadArg, "forward: null pointer");
+  const long long rows = static_cast<long long>(B) * T;
+  for (long long i = 0; i < rows; ++i)
+    RK_REQUIRE(tokens_host[i] >= 0 && tokens_host[i] < cfg_.vocab, kBadArg, "token id out of range");
+  int s = use_device();
+  if (s != kOk) return s;
+
+  std::lock_guard<std::mutex> lock(mu_);
+  Workspace* ws = workspace(B, T);
+  RK_REQUIRE(ws, kCuda, "forward: workspace allocation failed for B=%d T=%d", B, T);
+  // the pinned staging buffer may still be the source of the previous call's copy
+  RK_CUDA(cudaEventSynchronize(ws->tokens_copied));
+  std::memcpy(ws->tokens_pinned, tokens_host, static_cast<size_t>(rows) * sizeof(int64_t));
+  RK_CUDA(cudaMemcpyAsync(ws->tokens, ws->tokens_pinned, static_cast<size_t>(rows) * sizeof(int64_t), cudaMemcpyHostToDevice, stream));
+  RK_CUDA(cudaEventRecord(ws->tokens_copied, stream));
+
+  if (T != 1 || stream == nullptr) {
+    const long long before = launch_counter();
+    s = enqueue(*ws, B, T, static_cast<half*>(shift), wkv, elapsed, logits, stream);
+    launches_ += launch_counter() - before;
+    return s;
+  }
+  // Decode step: replay a captured graph (key: batch and the caller's buffers).
+  const GraphKey key{B, shift, wkv, elapsed, logits};
+  auto it = graphs_.find(key);
+  if (it == graphs_.end()) {
+    if (graphs_.size() >= 16) {  // evict the least recently used
+      auto victim = graphs_.begin();
+      for (auto g = graphs_.begin(); g != graphs_.end(); ++g)
+        if (g->second.last_use < victim->second.last_use) victim = g;
+      cudaGraphExecDestroy(victim->second.exec);
+      graphs_.erase(victim);
+    }
+    GraphEntry e;
+    cudaGraph_t graph = nullptr;
+    RK_CUDA(cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal));
+    const long long before = launch_counter();
+    s = enqueue(*ws, B, T, static_cast<half*>(shift), wkv, elapsed, logits, stream);
+    e.launches = launch_counter() - before;
+    const cudaError_t ce = cudaStreamEndCapture(stream, &graph);
+    if (s != kOk) {
+      if (graph) cudaGraphDestroy(graph);
+      return s;
+    }
+    RK_CUDA(ce);
+    const cudaError_t ie = cudaGraphInstantiate(&e.exec, graph, 0);
+    cudaGraphDestroy(graph);
+    RK_CUDA(ie);
+    it = graphs_.emplace(key, e).first;
+  }
+  it->second.last_use = ++tick_;
+  RK_CUDA(cudaGraphLaunch(it->second.exec, stream));
+  launches_ += it->second.launches;
+  return kOk;
+}
+
+}  // namespace rk

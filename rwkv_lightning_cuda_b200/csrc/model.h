@@ -1,0 +1,126 @@
+// Host-side engine of the sm_100a RWKV-7 forward: weight storage, activation workspaces,
+// the per-layer launch sequence and the CUDA-graph cache for decode steps.
+#pragma once
+
+#include <map>
+#include <memory>
+#include <mutex>
+#include <string>
+#include <tuple>
+#include <unordered_map>
+#include <vector>
+
+#include "../../include/rwkv7_b200.h"
+#include "kernels.h"
+
+namespace rk {
+
+struct DevBuf {
+  void* p = nullptr;
+  size_t bytes = 0;
+  DevBuf() = default;
+  DevBuf(const DevBuf&) = delete;
+  DevBuf& operator=(const DevBuf&) = delete;
+  DevBuf(DevBuf&& o) noexcept : p(o.p), bytes(o.bytes) { o.p = nullptr; o.bytes = 0; }
+  DevBuf& operator=(DevBuf&& o) noexcept {
+    if (this != &o) { release(); p = o.p; bytes = o.bytes; o.p = nullptr; o.bytes = 0; }
+    return *this;
+  }
+  ~DevBuf() { release(); }
+  int alloc(size_t n);
+  void release();
+  template <typename T> T* as() const { return static_cast<T*>(p); }
+};
+
+// One large matrix in its device format.
+struct Matrix {
+  int N = 0, K = 0, fmt = RWKV7_B200_FMT_F16;
+  DevBuf w, scale, zero;
+};
+
+struct LayerWeights {
+  DevBuf ln1_w, ln1_b, ln2_w, ln2_b;
+  DevBuf mix[6];  // x_r, x_w, x_k, x_v, x_a, x_g
+  Matrix Wr, Wk, Wv, Wo, Wkey, Wval;
+  DevBuf w0, a0, v0;
+  DevBuf w1t, a1t, g1t, v1t;  // LoRA down, transposed to [R,C]
+  DevBuf w2t, a2t, g2t, v2t;  // LoRA up, transposed to [C,R]
+  DevBuf k_k, k_a, r_k, lnx_w, lnx_b, ffn_x_k;
+};
+
+// Activation buffers for one forward of `rows` = B*T rows.
+struct Workspace {
+  int rows = 0, B = 0;
+  DevBuf arena;
+  half *xA, *xB, *xm[6], *r, *k, *v, *vfirst, *vout, *w12, *a12, *g, *k2, *nkk, *kka, *y, *y2, *att, *mixed, *ffn;
+  half *hid, *l1[4], *xf;
+  int64_t* tokens;
+  int64_t* tokens_pinned = nullptr;  // host staging for the token ids
+  cudaEvent_t tokens_copied = nullptr;  // recorded after the staging buffer has been read
+  ~Workspace();
+};
+
+class Model {
+ public:
+  explicit Model(const rwkv7_b200_config& cfg);
+  ~Model();
+
+  int set_tensor(const char* name, const void* data, int dtype, long long count, int on_device);
+  int finalize();
+  int forward(const int64_t* tokens_host, int B, int T, void* shift, void* wkv, int* elapsed, float* logits,
+              cudaStream_t stream);
+  int state_sizes(int B, size_t* shift_elems, size_t* wkv_elems, size_t* elapsed_elems) const;
+  int state_init(int B, void* shift, void* wkv, int* elapsed, cudaStream_t stream) const;
+  int copy_state_slice(const void* src_shift, const void* src_wkv, const int* src_elapsed, int src_B, int src_off,
+                       void* dst_shift, void* dst_wkv, int* dst_elapsed, int dst_B, int dst_off, int count,
+                       cudaStream_t stream) const;
+  int query_capacity(int chunk, rwkv7_b200_capacity* out) const;
+
+  const rwkv7_b200_config& cfg() const { return cfg_; }
+  long long launches() const { return launches_; }
+
+ private:
+  struct GraphKey {
+    int B;
+    const void *shift, *wkv, *elapsed, *logits;
+    bool operator<(const GraphKey& o) const {
+      return std::tie(B, shift, wkv, elapsed, logits) < std::tie(o.B, o.shift, o.wkv, o.elapsed, o.logits);
+    }
+  };
+  struct GraphEntry {
+    cudaGraphExec_t exec = nullptr;
+    long long launches = 0;
+    unsigned long long last_use = 0;
+  };
+
+  int use_device() const;
+  int upload(DevBuf& dst, const void* data, int dtype, long long count, int on_device, long long expect);
+  int upload_matrix(Matrix& m, int N, int K, const void* data, int dtype, long long count, int on_device);
+  int transpose_into(DevBuf& dst, const DevBuf& src, int rows, int cols);
+  int quantize(Matrix& m);
+  Workspace* workspace(int B, int T);
+  int enqueue(Workspace& ws, int B, int T, half* shift, void* wkv, int* elapsed, float* logits, cudaStream_t s);
+  int lin(cudaStream_t s, int M, const Matrix& W, const half* x, void* y, int epi);
+  int lin16(cudaStream_t s, int M, int K, int N, const half* x, const half* w, half* y, int in_act, int epi,
+            const EpiArgs& ea);
+
+  rwkv7_b200_config cfg_;
+  int H_ = 0;
+  bool finalized_ = false;
+  std::vector<LayerWeights> layers_;
+  DevBuf emb_ln0_, ln_out_w_, ln_out_b_;
+  Matrix head_;
+  // staging until finalize
+  DevBuf emb_raw_, ln0_w_raw_, ln0_b_raw_;
+  int emb_dtype_ = -1;
+  std::unordered_map<std::string, DevBuf> lora_raw_;  // checkpoint-orientation LoRA matrices
+
+  std::mutex mu_;
+  std::map<std::pair<int, int>, std::unique_ptr<Workspace>> workspaces_;
+  std::map<GraphKey, GraphEntry> graphs_;
+  unsigned long long tick_ = 0;
+  long long launches_ = 0;
+  long long counting_ = 0;  // launches counted while enqueueing
+};
+
+}  // namespace rk

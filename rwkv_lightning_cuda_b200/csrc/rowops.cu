@@ -1,0 +1,385 @@
+// Row-wise fusions of the RWKV-7 forward: embedding gather, residual add, LayerNorm and the
+// token-shift interpolations, plus the small per-head gates around the WKV recurrence.
+//
+// One kernel (row_op_kernel) covers what the reference spreads over
+//   layer_norm_f16 / add_layer_norm_f16 / add_last_layer_norm_f16        cuda/rwkv7_v3a_ops.cu:1272-1351,1800-1931
+//   add_layer_norm_cmix_mix_f16 / add_layer_norm_tmix_mix6_f16 (T=1)     cuda/rwkv7_v3a_ops.cu:1515-2060
+//   tmix_mix6 / cmix_mix / update_shift_state_last                       cuda/rwkv7_fast_ops_fp16.cu:53-127,393-419
+// for every T: a CTA normalises its own row and, when t > 0, re-normalises row t-1 as the
+// "previous token" instead of waiting for another CTA; the CTA of t = 0 alone reads and then
+// replaces the shift state, so no second launch is needed.
+// Rounding points follow the reference: the sum x + residual and the LayerNorm output are each
+// rounded to half once, the interpolation reads the rounded LayerNorm output.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace rk {
+namespace {
+
+constexpr int kRowThreads = 256;
+
+struct RowOpDev {
+  int B, T, C, vocab, n_mix, last_only, identity;
+  float eps;
+  const int64_t* tokens;
+  const half* table;
+  const half* x;
+  const half* residual;
+  half* x_out;
+  const half* ln_w;
+  const half* ln_b;
+  half* n_out;
+  half* shift;
+  const half* mix[6];
+  half* mix_out[6];
+  int* bad_token_flag;
+};
+
+// Loads row (b,t) as fp32 into buf; optionally stores the rounded sum.
+__device__ __forceinline__ void load_row(const RowOpDev& p, int b, int t, float* buf, bool store_x) {
+  const size_t row = static_cast<size_t>(b) * p.T + t;
+  const int pairs = p.C >> 1;
+  if (p.table) {
+    long long tok = p.tokens[row];
+    if (tok < 0 || tok >= p.vocab) {
+      if (threadIdx.x == 0 && p.bad_token_flag) *p.bad_token_flag = 1;
+      tok = 0;
+    }
+    const __half2* src = reinterpret_cast<const __half2*>(p.table + static_cast<size_t>(tok) * p.C);
+    for (int q = threadIdx.x; q < pairs; q += kRowThreads) {
+      const __half2 h2 = src[q];
+      const float2 f = __half22float2(h2);
+      buf[2 * q] = f.x;
+      buf[2 * q + 1] = f.y;
+      if (store_x && p.x_out) reinterpret_cast<__half2*>(p.x_out + row * p.C)[q] = h2;
+    }
+  } else {
+    const __half2* xs = reinterpret_cast<const __half2*>(p.x + row * p.C);
+    const __half2* rs = p.residual ? reinterpret_cast<const __half2*>(p.residual + row * p.C) : nullptr;
+    for (int q = threadIdx.x; q < pairs; q += kRowThreads) {
+      float2 f = __half22float2(xs[q]);
+      if (rs) {
+        const float2 g = __half22float2(rs[q]);
+        f.x += g.x;
+        f.y += g.y;
+      }
+      buf[2 * q] = f.x;
+      buf[2 * q + 1] = f.y;
+      if (store_x && p.x_out) reinterpret_cast<__half2*>(p.x_out + row * p.C)[q] = __floats2half2_rn(f.x, f.y);
+    }
+  }
+}
+
+// In place: buf[c] <- float(half(LN(buf)[c])).  Two-pass statistics in fp32.
+__device__ __forceinline__ void ln_row(const RowOpDev& p, float* buf, float* scratch) {
+  if (p.identity) return;  // plain token shift: the row is used as it is
+  float s = 0.f;
+  for (int c = threadIdx.x; c < p.C; c += kRowThreads) s += buf[c];
+  const float inv_c = 1.0f / static_cast<float>(p.C);
+  const float mean = block_sum<kRowThreads>(s, scratch) * inv_c;
+  float sv = 0.f;
+  for (int c = threadIdx.x; c < p.C; c += kRowThreads) {
+    const float d = buf[c] - mean;
+    sv += d * d;
+  }
+  const float rstd = rsqrtf(block_sum<kRowThreads>(sv, scratch) * inv_c + p.eps);
+  for (int c = threadIdx.x; c < p.C; c += kRowThreads) {
+    const float wv = __half2float(p.ln_w[c]), bv = __half2float(p.ln_b[c]);
+    buf[c] = __half2float(__float2half_rn((buf[c] - mean) * rstd * wv + bv));
+  }
+}
+
+__global__ void __launch_bounds__(kRowThreads) row_op_kernel(const RowOpDev p) {
+  extern __shared__ __align__(16) float smem[];
+  float* cur = smem;
+  float* prev = smem + p.C;
+  __shared__ float scratch[kRowThreads / 32];
+
+  int b, t;
+  if (p.last_only) {
+    b = blockIdx.x;
+    t = p.T - 1;
+  } else {
+    b = blockIdx.x / p.T;
+    t = blockIdx.x - b * p.T;
+  }
+  const size_t row = static_cast<size_t>(b) * p.T + t;
+
+  load_row(p, b, t, cur, true);
+  __syncthreads();
+  if (!p.ln_w && !p.identity) return;
+  ln_row(p, cur, scratch);  // each thread rewrites only the channels it later reads
+  if (p.n_out) {
+    half* dst = p.n_out + (p.last_only ? static_cast<size_t>(b) : row) * p.C;
+    for (int c = threadIdx.x; c < p.C; c += kRowThreads) dst[c] = __float2half_rn(cur[c]);
+  }
+  if (p.n_mix == 0) return;
+
+  if (t == 0) {
+    for (int c = threadIdx.x; c < p.C; c += kRowThreads) prev[c] = __half2float(p.shift[static_cast<size_t>(b) * p.C + c]);
+  } else {
+    __syncthreads();
+    load_row(p, b, t - 1, prev, false);
+    __syncthreads();
+    ln_row(p, prev, scratch);
+  }
+  for (int c = threadIdx.x; c < p.C; c += kRowThreads) {
+    const float n = cur[c];
+    const float dx = prev[c] - n;
+#pragma unroll
+    for (int m = 0; m < 6; ++m)
+      if (m < p.n_mix) p.mix_out[m][row * p.C + c] = __float2half_rn(n + dx * __half2float(p.mix[m][c]));
+  }
+  if (t == 0) {
+    // this CTA is the only one that touches shift[b]: it has consumed the old row above
+    if (p.T == 1) {
+      for (int c = threadIdx.x; c < p.C; c += kRowThreads) p.shift[static_cast<size_t>(b) * p.C + c] = __float2half_rn(cur[c]);
+    } else {
+      __syncthreads();
+      load_row(p, b, p.T - 1, prev, false);
+      __syncthreads();
+      ln_row(p, prev, scratch);
+      for (int c = threadIdx.x; c < p.C; c += kRowThreads) p.shift[static_cast<size_t>(b) * p.C + c] = __float2half_rn(prev[c]);
+    }
+  }
+}
+
+// kk = normalize(k * k_k) per head, a = sigmoid(a0 + a12), k' = k (1 + (a - 1) k_a);
+// emits k', -kk and kk*a (the WKV "a" and "b" operands).  One warp per (row, head).
+// Reference: tmix_kk_a_gate_kernel, cuda/rwkv7_fast_ops_fp16.cu:129-172.
+__global__ void __launch_bounds__(128) kk_a_gate_kernel(
+    int H, long long n_heads_total, const half* __restrict__ k, const half* __restrict__ k_k,
+    const half* __restrict__ a0, const half* __restrict__ a12, const half* __restrict__ k_a,
+    half* __restrict__ new_k, half* __restrict__ neg_kk, half* __restrict__ kka) {
+  const long long bth = static_cast<long long>(blockIdx.x) * 4 + (threadIdx.x >> 5);
+  if (bth >= n_heads_total) return;
+  const int lane = threadIdx.x & 31;
+  const int h = static_cast<int>(bth % H);
+  const long long idx = bth * kHead + lane * 2;
+  const int c = h * kHead + lane * 2;
+  const float2 kv = __half22float2(*reinterpret_cast<const __half2*>(k + idx));
+  const float2 ks = __half22float2(*reinterpret_cast<const __half2*>(k_k + c));
+  const float u0 = kv.x * ks.x, u1 = kv.y * ks.y;
+  const float total = warp_sum(u0 * u0 + u1 * u1);
+  const float inv_d = 1.0f / fmaxf(sqrtf(total), 1.0e-12f);
+  const float kk0 = u0 * inv_d, kk1 = u1 * inv_d;
+  const float2 a0v = __half22float2(*reinterpret_cast<const __half2*>(a0 + c));
+  const float2 a12v = __half22float2(*reinterpret_cast<const __half2*>(a12 + idx));
+  const float av0 = sigmoid_fast(a0v.x + a12v.x), av1 = sigmoid_fast(a0v.y + a12v.y);
+  const float2 ka = __half22float2(*reinterpret_cast<const __half2*>(k_a + c));
+  *reinterpret_cast<__half2*>(new_k + idx) =
+      __floats2half2_rn(kv.x * fmaf(av0, ka.x, 1.0f - ka.x), kv.y * fmaf(av1, ka.y, 1.0f - ka.y));
+  *reinterpret_cast<__half2*>(neg_kk + idx) = __floats2half2_rn(-kk0, -kk1);
+  *reinterpret_cast<__half2*>(kka + idx) = __floats2half2_rn(kk0 * av0, kk1 * av1);
+}
+
+// out = (GroupNorm_64(y; eps 64e-5) * w + b + (sum_j r k r_k) v) * g.  One warp per (row, head).
+// Reference: tmix_lnx_rkvres_xg_kernel, cuda/rwkv7_fast_ops_fp16.cu:174-237.
+__global__ void __launch_bounds__(128) lnx_rkvres_xg_kernel(
+    int H, long long n_heads_total, const half* __restrict__ y, const half* __restrict__ r,
+    const half* __restrict__ k, const half* __restrict__ v, const half* __restrict__ r_k,
+    const half* __restrict__ w, const half* __restrict__ b, const half* __restrict__ g,
+    half* __restrict__ out) {
+  const long long bth = static_cast<long long>(blockIdx.x) * 4 + (threadIdx.x >> 5);
+  if (bth >= n_heads_total) return;
+  const int lane = threadIdx.x & 31;
+  const int h = static_cast<int>(bth % H);
+  const long long idx = bth * kHead + lane * 2;
+  const int c = h * kHead + lane * 2;
+  const float2 yv = __half22float2(*reinterpret_cast<const __half2*>(y + idx));
+  const float mean = warp_sum(yv.x + yv.y) * (1.0f / 64.0f);
+  const float d0 = yv.x - mean, d1 = yv.y - mean;
+  const float var = warp_sum(d0 * d0 + d1 * d1) * (1.0f / 64.0f);
+  const float rstd = rsqrtf(var + 64.0e-5f);
+  const float2 rv = __half22float2(*reinterpret_cast<const __half2*>(r + idx));
+  const float2 kv = __half22float2(*reinterpret_cast<const __half2*>(k + idx));
+  const float2 vv = __half22float2(*reinterpret_cast<const __half2*>(v + idx));
+  const float2 rk = __half22float2(*reinterpret_cast<const __half2*>(r_k + c));
+  const float rkv = warp_sum(rv.x * kv.x * rk.x + rv.y * kv.y * rk.y);
+  const float2 wv = __half22float2(*reinterpret_cast<const __half2*>(w + c));
+  const float2 bv = __half22float2(*reinterpret_cast<const __half2*>(b + c));
+  const float2 gv = __half22float2(*reinterpret_cast<const __half2*>(g + idx));
+  *reinterpret_cast<__half2*>(out + idx) = __floats2half2_rn(
+      (d0 * rstd * wv.x + bv.x + rkv * vv.x) * gv.x, (d1 * rstd * wv.y + bv.y + rkv * vv.y) * gv.y);
+}
+
+// Reference: tmix_vres_gate_kernel, cuda/rwkv7_fast_ops_fp16.cu:239-255.
+__global__ void vres_gate_kernel(int C, long long total, const half* __restrict__ v,
+                                 const half* __restrict__ v_first, const half* __restrict__ v0,
+                                 const half* __restrict__ v12, half* __restrict__ out) {
+  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const int c = static_cast<int>(i % C);
+  const float vv = __half2float(v[i]);
+  const float gate = sigmoid_fast(__half2float(v0[c]) + __half2float(v12[i]));
+  out[i] = __float2half_rn(fmaf(__half2float(v_first[i]) - vv, gate, vv));
+}
+
+__global__ void advance_i32_kernel(int* x, int amount, int n) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) x[i] += amount;
+}
+
+__global__ void relu_square_kernel(const half* __restrict__ x, half* __restrict__ out, long long n) {
+  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const float t = fmaxf(__half2float(x[i]), 0.f);
+  out[i] = __float2half_rn(t * t);
+}
+
+__device__ __forceinline__ float bf16_bits_to_float(uint16_t b) { return __uint_as_float(static_cast<uint32_t>(b) << 16); }
+
+// fp16 = round_to_nearest(float(bf16)): the canonical device value of a checkpoint weight
+// (reference: bf16_to_f16_kernel, cuda/rwkv7_v3a_ops.cu:79-88).
+__global__ void bf16_to_f16_kernel(const uint16_t* __restrict__ src, half* __restrict__ dst, long long n) {
+  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i < n) dst[i] = __float2half_rn(bf16_bits_to_float(src[i]));
+}
+
+__global__ void transpose_f16_kernel(const half* __restrict__ src, half* __restrict__ dst, int rows, int cols) {
+  __shared__ half tile[32][33];
+  const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
+  for (int dy = threadIdx.y; dy < 32; dy += blockDim.y) {
+    const int rr = r0 + dy, cc = c0 + threadIdx.x;
+    if (rr < rows && cc < cols) tile[dy][threadIdx.x] = src[static_cast<size_t>(rr) * cols + cc];
+  }
+  __syncthreads();
+  for (int dy = threadIdx.y; dy < 32; dy += blockDim.y) {
+    const int cc = c0 + dy, rr = r0 + threadIdx.x;
+    if (rr < rows && cc < cols) dst[static_cast<size_t>(cc) * rows + rr] = tile[threadIdx.x][dy];
+  }
+}
+
+// Embedding table with LN0 folded in, from bf16 or fp16 checkpoint values, statistics in fp32
+// (reference: emb_ln0_bf16_to_f16_kernel, cuda/rwkv7_v3a_ops.cu:153-187).
+template <bool kBf16>
+__global__ void __launch_bounds__(256) emb_ln0_kernel(int C, const uint16_t* __restrict__ emb,
+                                                      const uint16_t* __restrict__ w, const uint16_t* __restrict__ b,
+                                                      half* __restrict__ out, float eps) {
+  __shared__ float scratch[8];
+  auto cvt = [](uint16_t bits) {
+    return kBf16 ? bf16_bits_to_float(bits) : __half2float(__ushort_as_half(bits));
+  };
+  const uint16_t* er = emb + static_cast<size_t>(blockIdx.x) * C;
+  float s = 0.f;
+  for (int c = threadIdx.x; c < C; c += 256) s += cvt(er[c]);
+  const float mean = block_sum<256>(s, scratch) / static_cast<float>(C);
+  float sv = 0.f;
+  for (int c = threadIdx.x; c < C; c += 256) {
+    const float d = cvt(er[c]) - mean;
+    sv += d * d;
+  }
+  const float rstd = rsqrtf(block_sum<256>(sv, scratch) / static_cast<float>(C) + eps);
+  half* yr = out + static_cast<size_t>(blockIdx.x) * C;
+  for (int c = threadIdx.x; c < C; c += 256) yr[c] = __float2half_rn((cvt(er[c]) - mean) * rstd * cvt(w[c]) + cvt(b[c]));
+}
+
+}  // namespace
+
+int row_op(cudaStream_t stream, const RowOpArgs& a) {
+  RK_REQUIRE(a.B > 0 && a.T > 0 && a.C > 0 && (a.C & 1) == 0, kShape, "row_op: need B,T > 0 and even C");
+  RK_REQUIRE((a.table && a.tokens && a.vocab > 0) || a.x, kBadArg, "row_op: no source");
+  RK_REQUIRE(a.n_mix == 0 || a.n_mix == 1 || a.n_mix == 6, kBadArg, "row_op: n_mix must be 0, 1 or 6");
+  RK_REQUIRE(a.n_mix == 0 || (a.shift && (a.ln_w || a.identity_norm) && !a.last_only), kBadArg,
+             "row_op: token shift needs shift state and LayerNorm weights");
+  RK_REQUIRE(!a.ln_w || a.ln_b, kBadArg, "row_op: LayerNorm bias missing");
+  RK_REQUIRE(!(a.ln_w && a.identity_norm), kBadArg, "row_op: identity_norm excludes LayerNorm weights");
+  RowOpDev p;
+  p.B = a.B; p.T = a.T; p.C = a.C; p.vocab = a.vocab; p.n_mix = a.n_mix; p.last_only = a.last_only ? 1 : 0; p.identity = a.identity_norm ? 1 : 0;
+  p.eps = a.eps; p.tokens = a.tokens; p.table = a.table; p.x = a.x; p.residual = a.residual; p.x_out = a.x_out;
+  p.ln_w = a.ln_w; p.ln_b = a.ln_b; p.n_out = a.n_out; p.shift = a.shift; p.bad_token_flag = a.bad_token_flag;
+  for (int m = 0; m < 6; ++m) {
+    p.mix[m] = a.mix[m];
+    p.mix_out[m] = a.mix_out[m];
+    RK_REQUIRE(m >= a.n_mix || (a.mix[m] && a.mix_out[m]), kBadArg, "row_op: mix tensor %d missing", m);
+  }
+  const int grid = a.last_only ? a.B : a.B * a.T;
+  const size_t smem = sizeof(float) * 2 * static_cast<size_t>(a.C);
+  RK_REQUIRE(smem <= 200 * 1024, kShape, "row_op: C too large");
+  if (smem > 48 * 1024) {
+    static bool raised = false;  // idempotent attribute; a benign race at worst repeats the call
+    if (!raised) {
+      RK_CUDA(cudaFuncSetAttribute(row_op_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+      raised = true;
+    }
+  }
+  row_op_kernel<<<grid, kRowThreads, smem, stream>>>(p);
+  RK_LAUNCH_CHECK("row_op launch");
+  return kOk;
+}
+
+int tmix_kk_a_gate(cudaStream_t stream, int rows, int C, const half* k, const half* k_k, const half* a0,
+                   const half* a12, const half* k_a, half* new_k, half* neg_kk, half* kka) {
+  RK_REQUIRE(rows > 0 && C > 0 && C % kHead == 0, kShape, "kk_a_gate: C must be a multiple of 64");
+  RK_REQUIRE(k && k_k && a0 && a12 && k_a && new_k && neg_kk && kka, kBadArg, "kk_a_gate: null pointer");
+  const int H = C / kHead;
+  const long long total = static_cast<long long>(rows) * H;
+  kk_a_gate_kernel<<<static_cast<unsigned>((total + 3) / 4), 128, 0, stream>>>(H, total, k, k_k, a0, a12, k_a, new_k, neg_kk, kka);
+  RK_LAUNCH_CHECK("kk_a_gate launch");
+  return kOk;
+}
+
+int tmix_lnx_rkvres_xg(cudaStream_t stream, int rows, int C, const half* y, const half* r, const half* k,
+                       const half* v, const half* r_k, const half* w, const half* b, const half* g, half* out) {
+  RK_REQUIRE(rows > 0 && C > 0 && C % kHead == 0, kShape, "lnx_rkvres_xg: C must be a multiple of 64");
+  RK_REQUIRE(y && r && k && v && r_k && w && b && g && out, kBadArg, "lnx_rkvres_xg: null pointer");
+  const int H = C / kHead;
+  const long long total = static_cast<long long>(rows) * H;
+  lnx_rkvres_xg_kernel<<<static_cast<unsigned>((total + 3) / 4), 128, 0, stream>>>(H, total, y, r, k, v, r_k, w, b, g, out);
+  RK_LAUNCH_CHECK("lnx_rkvres_xg launch");
+  return kOk;
+}
+
+int tmix_vres_gate(cudaStream_t stream, int rows, int C, const half* v, const half* v_first, const half* v0,
+                   const half* v12, half* out) {
+  RK_REQUIRE(rows > 0 && C > 0, kShape, "vres_gate: empty");
+  RK_REQUIRE(v && v_first && v0 && v12 && out, kBadArg, "vres_gate: null pointer");
+  const long long total = static_cast<long long>(rows) * C;
+  vres_gate_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, stream>>>(C, total, v, v_first, v0, v12, out);
+  RK_LAUNCH_CHECK("vres_gate launch");
+  return kOk;
+}
+
+int advance_i32(cudaStream_t stream, int* x, int amount, int n) {
+  RK_REQUIRE(x && n > 0, kBadArg, "advance_i32: bad argument");
+  advance_i32_kernel<<<(n + 255) / 256, 256, 0, stream>>>(x, amount, n);
+  RK_LAUNCH_CHECK("advance_i32 launch");
+  return kOk;
+}
+
+int relu_square(cudaStream_t stream, const half* x, half* out, long long n) {
+  RK_REQUIRE(x && out && n > 0, kBadArg, "relu_square: bad argument");
+  relu_square_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, stream>>>(x, out, n);
+  RK_LAUNCH_CHECK("relu_square launch");
+  return kOk;
+}
+
+int bf16_to_f16(cudaStream_t stream, const uint16_t* src, half* dst, long long n) {
+  RK_REQUIRE(src && dst && n > 0, kBadArg, "bf16_to_f16: bad argument");
+  bf16_to_f16_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, stream>>>(src, dst, n);
+  RK_LAUNCH_CHECK("bf16_to_f16 launch");
+  return kOk;
+}
+
+int transpose_f16(cudaStream_t stream, const half* src, half* dst, int rows, int cols) {
+  RK_REQUIRE(src && dst && rows > 0 && cols > 0, kBadArg, "transpose_f16: bad argument");
+  const dim3 grid((cols + 31) / 32, (rows + 31) / 32), block(32, 8);
+  transpose_f16_kernel<<<grid, block, 0, stream>>>(src, dst, rows, cols);
+  RK_LAUNCH_CHECK("transpose_f16 launch");
+  return kOk;
+}
+
+int emb_ln0(cudaStream_t stream, int V, int C, const void* emb, const void* w, const void* b, int src_is_bf16,
+            half* out, float eps) {
+  RK_REQUIRE(V > 0 && C > 0 && emb && w && b && out, kBadArg, "emb_ln0: bad argument");
+  if (src_is_bf16)
+    emb_ln0_kernel<true><<<V, 256, 0, stream>>>(C, static_cast<const uint16_t*>(emb), static_cast<const uint16_t*>(w),
+                                               static_cast<const uint16_t*>(b), out, eps);
+  else
+    emb_ln0_kernel<false><<<V, 256, 0, stream>>>(C, static_cast<const uint16_t*>(emb), static_cast<const uint16_t*>(w),
+                                                static_cast<const uint16_t*>(b), out, eps);
+  RK_LAUNCH_CHECK("emb_ln0 launch");
+  return kOk;
+}
+
+}  // namespace rk

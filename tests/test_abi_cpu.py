@@ -1,0 +1,64 @@
+"""CPU-only checks of the drop-in boundary: the library loads, exports exactly what
+include/rwkv7_b200.h declares, and rejects bad arguments with a status code before touching CUDA."""
+import ctypes as C
+import os
+import re
+
+import pytest
+
+from tests.helpers import ROOT
+
+
+def declared_functions():
+    text = open(os.path.join(ROOT, "include", "rwkv7_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(rwkv7_b200_[a-z0-9_]+)\s*\(", text)))
+
+
+@pytest.fixture(scope="module")
+def lib():
+    from rwkv_lightning_cuda_b200 import build, lib as L
+    build.build()
+    return L.load_library()
+
+
+def test_every_declared_symbol_is_exported_and_bound(lib):
+    from rwkv_lightning_cuda_b200 import lib as L
+    names = declared_functions()
+    assert len(names) >= 35
+    for n in names:
+        assert hasattr(lib, n), f"{n} declared in the header but not exported"
+    assert sorted(L.SIGNATURES) == names, "python binding table and header disagree"
+    assert lib.rwkv7_b200_abi_version() == 1
+
+
+def test_bad_config_is_rejected_without_a_gpu(lib):
+    from rwkv_lightning_cuda_b200 import lib as L
+    h = C.c_void_p()
+    good = dict(layers=2, channels=128, ffn=512, vocab=64, rank_w=32, rank_a=32, rank_v=16, rank_g=64,
+                weight_format=0, wkv32=0, device=-1, tp_rank=0, tp_size=1)
+    for patch, status in ((dict(channels=100), 2), (dict(layers=0), 2), (dict(rank_g=520), 2), (dict(weight_format=7), 1),
+                          (dict(weight_format=2, channels=192), 2)):
+        cfg = L.Config(**{**good, **patch})
+        assert lib.rwkv7_b200_model_create(C.byref(cfg), C.byref(h)) == status
+        assert lib.rwkv7_b200_last_error()
+    assert lib.rwkv7_b200_model_create(None, C.byref(h)) == 1
+    cfg = L.Config(**good)
+    assert lib.rwkv7_b200_model_create(C.byref(cfg), C.byref(h)) == 0
+    ns, nw, ne = C.c_size_t(), C.c_size_t(), C.c_size_t()
+    assert lib.rwkv7_b200_state_sizes(h, 3, C.byref(ns), C.byref(nw), C.byref(ne)) == 0
+    # GenerationState layout: shift [L][2][B][C], wkv [L][B][H][64][64], elapsed [B]
+    assert (ns.value, nw.value, ne.value) == (2 * 2 * 3 * 128, 2 * 3 * 2 * 64 * 64, 3)
+    assert lib.rwkv7_b200_state_sizes(h, 0, None, None, None) == 1
+    assert b"positive" in lib.rwkv7_b200_last_error()
+    # forward before finalize / with bad shapes fails with a status, it never exits the process
+    assert lib.rwkv7_b200_forward(h, None, 1, 1, None, None, None, None, None) == 7
+    assert lib.rwkv7_b200_model_destroy(h) == 0
+
+
+def test_missing_library_fails_loudly(monkeypatch, tmp_path):
+    from rwkv_lightning_cuda_b200 import lib as L
+    monkeypatch.setattr(L, "_LIB", None)
+    monkeypatch.setattr(L, "_HERE", str(tmp_path))
+    with pytest.raises(ImportError, match="no CPU fallback"):
+        L.load_library()

@@ -1,0 +1,237 @@
+"""GPU parity tests of the op-level C-ABI entry points against the CPU oracle, and (when the
+reference build under oracle/_ref is present) against the reference's own kernels on the same GPU.
+
+Tolerances: integer/byte work (quant pack/unpack) bit-exact; fp16 outputs within 2 fp16 ulp of
+the oracle with at least 97 % of the elements identical (the oracle sums in double, the kernels
+in fp32, so results on a rounding boundary may differ by one ulp); the fp16-state WKV must equal
+the reference's kernel bit for bit."""
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle as orc
+from tests.helpers import h16, pattern_value, ref_lib, ulp_diff16, wkv_inputs
+
+pytestmark = pytest.mark.gpu
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def host(t):
+    torch.cuda.synchronize()
+    return t.cpu().numpy()
+
+
+def assert_close16(got, want, max_ulp=2, min_exact=0.97, what=""):
+    d = ulp_diff16(got, want)
+    exact = float((d == 0).mean())
+    print(f"[parity] {what}: max ulp {int(d.max())}, exact {exact:.4f}")
+    assert d.max() <= max_ulp, f"{what}: max ulp diff {d.max()}"
+    assert exact >= min_exact, f"{what}: only {exact:.3f} of the elements identical"
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from rwkv_lightning_cuda_b200 import ops as o
+    return o
+
+
+def _p(t):
+    return C.c_void_p(t.data_ptr())
+
+
+@pytest.mark.parametrize("rows,Cc", [(1, 768), (3, 2560), (2, 4096), (5, 64)])
+def test_layer_norm_family(ops, rows, Cc):
+    idx = np.arange(rows * Cc)
+    x = h16(pattern_value(idx, 0.75, 0.05)).reshape(rows, Cc)
+    res = h16(pattern_value(idx + 17, 0.5, -0.03)).reshape(rows, Cc)
+    w = h16(pattern_value(np.arange(Cc) + 3, 0.25, 1.0))
+    b = h16(pattern_value(np.arange(Cc) + 5, 0.1, 0.0))
+    assert_close16(host(ops.layer_norm_f16(dev(x), dev(w), dev(b))), orc.layer_norm(x, w, b), what="layer_norm")
+    xo, y = ops.add_layer_norm_f16(dev(x), dev(res), dev(w), dev(b))
+    oxo, oy = orc.add_layer_norm(x, res, w, b)
+    assert (host(xo) == oxo).all()
+    assert_close16(host(y), oy, what="add_layer_norm")
+    # the reference test's own acceptance level (test/cuda_non4096_kernels_test.cpp:283-339)
+    np.testing.assert_allclose(host(y).astype(np.float32), oy.astype(np.float32), atol=2.5e-2)
+    last = ops.add_last_layer_norm_f16(1, rows, dev(x), dev(res), dev(w), dev(b))
+    assert_close16(host(last), orc.add_last_layer_norm(1, rows, x, res, w, b), what="add_last_layer_norm")
+
+
+@pytest.mark.parametrize("B,T,Cc", [(1, 1, 768), (2, 1, 2560), (1, 5, 768), (3, 4, 128), (2, 17, 256)])
+def test_token_shift_fusions(ops, B, T, Cc):
+    rng = np.random.default_rng(B * 100 + T)
+    rows = B * T
+    x = h16(rng.standard_normal((rows, Cc)))
+    res = h16(rng.standard_normal((rows, Cc)) * 0.5)
+    w = h16(1 + 0.1 * rng.standard_normal(Cc)); b = h16(0.1 * rng.standard_normal(Cc))
+    mixes = [h16(rng.uniform(0, 1, Cc)) for _ in range(6)]
+    shift0 = h16(rng.standard_normal((B, Cc)))
+
+    # plain token shifts
+    sh = dev(shift0.copy()); osh = shift0.copy()
+    outs = ops.tmix_mix6(B, T, dev(x), sh, [dev(m) for m in mixes])
+    oouts = orc.tmix_mix6(B, T, x, osh, mixes)
+    for g, o in zip(outs, oouts):
+        assert_close16(host(g), o, max_ulp=1, what="tmix_mix6")
+    assert (host(sh) == osh).all()
+    sh = dev(shift0.copy()); osh = shift0.copy()
+    assert_close16(host(ops.cmix_mix(B, T, dev(x), sh, dev(mixes[0]))), orc.cmix_mix(B, T, x, osh, mixes[0]), max_ulp=1, what="cmix_mix")
+    assert (host(sh) == osh).all()
+
+    # residual + LayerNorm + shift, for every T (the reference fuses these for T == 1 only)
+    oxo, on = orc.add_layer_norm(x, res, w, b)
+    osh = shift0.copy()
+    omixed = orc.cmix_mix(B, T, on, osh, mixes[2])
+    sh = dev(shift0.copy())
+    xo, mixed = ops.add_layer_norm_cmix_mix_f16(B, T, dev(x), dev(res), sh, dev(w), dev(b), dev(mixes[2]))
+    assert (host(xo) == oxo).all()
+    assert_close16(host(mixed), omixed, max_ulp=3, min_exact=0.9, what="add_ln_cmix_mix")
+    assert_close16(host(sh), osh, what="shift after add_ln_cmix_mix")
+    osh = shift0.copy()
+    oouts = orc.tmix_mix6(B, T, on, osh, mixes)
+    sh = dev(shift0.copy())
+    xo, outs = ops.add_layer_norm_tmix_mix6_f16(B, T, dev(x), dev(res), sh, dev(w), dev(b), [dev(m) for m in mixes])
+    assert (host(xo) == oxo).all()
+    for g, o in zip(outs, oouts):
+        assert_close16(host(g), o, max_ulp=3, min_exact=0.9, what="add_ln_tmix_mix6")
+    assert_close16(host(sh), osh, what="shift after add_ln_tmix_mix6")
+
+
+@pytest.mark.parametrize("rows,H", [(1, 12), (7, 2), (3, 40)])
+def test_head_gates(ops, rows, H):
+    rng = np.random.default_rng(rows + H)
+    Cc = H * 64
+    k = h16(rng.standard_normal((rows, Cc))); a12 = h16(rng.standard_normal((rows, Cc)))
+    k_k = h16(rng.uniform(0.5, 1.5, Cc)); a0 = h16(rng.standard_normal(Cc)); k_a = h16(rng.uniform(0, 1, Cc))
+    got = ops.tmix_kk_a_gate(rows, 1, H, dev(k), dev(k_k), dev(a0), dev(a12), dev(k_a))
+    want = orc.kk_a_gate(k, k_k, a0, a12, k_a)
+    for g, o, n in zip(got, want, ("new_k", "neg_kk", "kka")):
+        assert_close16(host(g), o, what="kk_a_gate " + n)
+    y = h16(rng.standard_normal((rows, Cc)) * 3); r = h16(rng.standard_normal((rows, Cc)))
+    v = h16(rng.standard_normal((rows, Cc))); g = h16(rng.standard_normal((rows, Cc)))
+    r_k = h16(rng.standard_normal(Cc) * 0.1); lw = h16(1 + 0.1 * rng.standard_normal(Cc)); lb = h16(0.1 * rng.standard_normal(Cc))
+    got = ops.tmix_lnx_rkvres_xg(rows, 1, H, dev(y), dev(r), dev(k), dev(v), dev(r_k), dev(lw), dev(lb), dev(g))
+    assert_close16(host(got), orc.lnx_rkvres_xg(y, r, k, v, r_k, lw, lb, g), what="lnx_rkvres_xg")
+    vf = h16(rng.standard_normal((rows, Cc))); v0 = h16(rng.standard_normal(Cc)); v12 = h16(rng.standard_normal((rows, Cc)))
+    assert_close16(host(ops.tmix_vres_gate(rows, 1, dev(v), dev(vf), dev(v0), dev(v12))), orc.vres_gate(v, vf, v0, v12), what="vres_gate")
+    assert (host(ops.relu_square(dev(y))) == h16(np.maximum(y.astype(np.float32), 0) ** 2)).all()
+
+
+@pytest.mark.parametrize("M,K,N", [(1, 768, 768), (2, 2560, 96), (4, 64, 768), (3, 4096, 130), (1, 3072, 768), (6, 256, 64)])
+def test_linear_fp16(ops, M, K, N):
+    from rwkv_lightning_cuda_b200 import lib as L
+    rng = np.random.default_rng(M * 7 + N)
+    x = h16(rng.standard_normal((M, K))); W = h16(rng.standard_normal((N, K)) * 0.02)
+    assert_close16(host(ops.linear_f16_orig(dev(x), dev(W))), orc.linear_orig(x, W), max_ulp=1, what="linear")
+    assert_close16(host(ops.linear_f16_orig(dev(x), dev(W), epilogue=L.EPI_RELU2)), orc.linear_orig(x, W, epi=orc.EPI_RELU2), max_ulp=2, what="linear relu2")
+    for act in (L.ACT_TANH, L.ACT_SIGMOID):
+        assert_close16(host(ops.linear_f16_orig(dev(x), dev(W), in_act=act)), orc.linear_orig(x, W, in_act=act), max_ulp=2, min_exact=0.9, what="linear act")
+    lg = host(ops.linear_f16_orig(dev(x), dev(W), epilogue=L.EPI_F32))
+    assert lg.dtype == np.float32
+    assert_close16(lg.astype(np.float16), orc.linear_orig(x, W), max_ulp=1, what="linear f32 out")
+    assert (lg == lg.astype(np.float16).astype(np.float32)).all()   # logits are fp16 values widened
+
+
+@pytest.mark.parametrize("N,K", [(64, 256), (5, 1024), (130, 128)])
+def test_quant_pack_bit_exact_and_linear(ops, N, K):
+    rng = np.random.default_rng(N + K)
+    W = h16(rng.standard_normal((N, K)) * 0.02)
+    W[0, :128] = 0                                     # all-zero group / edge case
+    W[1 % N, :] = np.float16(0.01)                     # constant row
+    q8, s8 = ops.quant_pack_w8(dev(W)); oq8, os8 = orc.quant_pack_w8(W)
+    assert (host(q8) == oq8).all() and (host(s8).view(np.uint16) == os8.view(np.uint16)).all()
+    assert (host(ops.quant_unpack_w8(q8, s8)).view(np.uint16) == orc.quant_unpack_w8(oq8, os8).view(np.uint16)).all()
+    q4, s4, z4 = ops.quant_pack_w4(dev(W)); oq4, os4, oz4 = orc.quant_pack_w4(W)
+    assert (host(q4) == oq4).all() and (host(s4).view(np.uint16) == os4.view(np.uint16)).all() and (host(z4) == oz4).all()
+    Wd = host(ops.quant_unpack_w4(q4, s4, z4))
+    assert (Wd.view(np.uint16) == orc.quant_unpack_w4(oq4, os4, oz4).view(np.uint16)).all()
+    # unpack . pack is idempotent on the quantised grid
+    q4b, s4b, z4b = ops.quant_pack_w4(dev(Wd))
+    assert (host(ops.quant_unpack_w4(q4b, s4b, z4b)).view(np.uint16) == Wd.view(np.uint16)).all()
+    for M in (1, 3):
+        x = h16(rng.standard_normal((M, K)))
+        assert_close16(host(ops.linear_w8a16(dev(x), q8, s8)), orc.linear_w8a16(x, oq8, os8), max_ulp=1, what="linear_w8a16")
+        assert_close16(host(ops.linear_w4a16(dev(x), q4, s4, z4)), orc.linear_w4a16(x, oq4, os4, oz4), max_ulp=1, what="linear_w4a16")
+
+
+@pytest.mark.parametrize("B,T,H", [(1, 128, 12), (3, 1, 2), (2, 7, 3), (1, 1, 64)])
+def test_wkv_fp32(ops, B, T, H):
+    r, w, k, v, a, b = wkv_inputs(B, T, H, seed=B * 10 + T)
+    rng = np.random.default_rng(9)
+    s0 = (rng.standard_normal((B, H, 64, 64)) * (0.0 if T == 128 else 0.5)).astype(np.float32)
+    os_ = s0.copy()
+    oy = orc.wkv_fp32(B, T, H, os_, r, w, k, v, a, b)
+    st = dev(s0.copy())
+    y = ops.wkv_fp32io16(B, T, H, st, *(dev(t) for t in (r, w, k, v, a, b)))
+    gs = host(st)
+    rel = np.abs(gs - os_).max() / max(np.abs(os_).max(), 1e-6)
+    print(f"[parity] wkv_fp32 B={B} T={T} H={H}: state rel err {rel:.2e}")
+    assert rel < 1e-4          # the stated tolerance for the fp32 state
+    assert_close16(host(y), oy, max_ulp=2, min_exact=0.9, what="wkv_fp32 y")
+
+
+@pytest.mark.parametrize("B,T,H,use_w0", [(1, 128, 12, False), (2, 1, 3, True), (3, 9, 2, True), (1, 16, 4, False)])
+def test_wkv_fp16(ops, B, T, H, use_w0):
+    r, w, k, v, a, b = wkv_inputs(B, T, H, seed=B * 10 + T)
+    rng = np.random.default_rng(11)
+    s0 = h16(rng.standard_normal((B, H, 64, 64)) * (0.0 if T == 128 else 0.5))
+    elapsed = np.arange(B, dtype=np.int32) * 977 + 5
+    w0 = h16(rng.uniform(-1, 1, H * 64)) if use_w0 else None
+    os_ = s0.copy()
+    oy = orc.wkv_fp16(B, T, H, os_, r, w, w0, k, v, a, b, elapsed)
+    st = dev(s0.copy())
+    y = ops.wkv_fp16_seq(B, T, H, st, *(dev(t) for t in (r, w, k, v, a, b)), dev(elapsed), w0=None if w0 is None else dev(w0))
+    gy, gs = host(y), host(st)
+    # vs the CPU oracle: identical half arithmetic; only the decay (exp2 / reciprocal approximations on
+    # the GPU) can differ by one fp16 ulp on a rounding boundary, which then spreads through the row
+    dy = np.abs(gy.astype(np.float32) - oy.astype(np.float32))
+    print(f"[parity] wkv_fp16 B={B} T={T}: y exact {(gy.view(np.uint16) == oy.view(np.uint16)).mean():.4f} max abs {dy.max():.3e}; "
+          f"state exact {(gs.view(np.uint16) == os_.view(np.uint16)).mean():.4f}")
+    assert dy.max() <= 2e-2 * max(1.0, float(np.abs(oy.astype(np.float32)).max()))
+    ref = ref_lib()
+    if ref is not None:
+        st2 = dev(s0.copy()); y2 = torch.empty_like(y)
+        args = [_p(dev(t)) for t in (r, w)]
+        tens = {n: dev(t) for n, t in zip("rwkvab", (r, w, k, v, a, b))}
+        el = dev(elapsed)
+        if w0 is None:
+            rc = ref.ref_wkv_fp16_seq(B, T, H * 64, H, _p(st2), _p(tens["r"]), _p(tens["w"]), _p(tens["k"]), _p(tens["v"]),
+                                      _p(tens["a"]), _p(tens["b"]), _p(y2), _p(el))
+        else:
+            w0d = dev(w0)
+            rc = ref.ref_wkv_fp16_seq_w0(B, T, H * 64, H, _p(st2), _p(tens["r"]), _p(tens["w"]), _p(w0d), _p(tens["k"]), _p(tens["v"]),
+                                         _p(tens["a"]), _p(tens["b"]), _p(y2), _p(el))
+        assert rc == 0, ref.ref_last_error()
+        assert (host(y2).view(np.uint16) == gy.view(np.uint16)).all(), "fp16 WKV output differs from the reference kernel"
+        assert (host(st2).view(np.uint16) == gs.view(np.uint16)).all(), "fp16 WKV state differs from the reference kernel"
+
+
+def test_emb_ln0_and_advance(ops):
+    rng = np.random.default_rng(12)
+    V, Cc = 50, 768
+    emb = torch.from_numpy(rng.standard_normal((V, Cc)).astype(np.float32) * 0.02).to(torch.bfloat16)
+    w = torch.from_numpy(1 + 0.02 * rng.standard_normal(Cc).astype(np.float32)).to(torch.bfloat16)
+    b = torch.from_numpy(0.02 * rng.standard_normal(Cc).astype(np.float32)).to(torch.bfloat16)
+    got = host(ops.emb_ln0(emb.cuda(), w.cuda(), b.cuda()))
+    want = orc.emb_ln0(emb.float().numpy(), w.float().numpy(), b.float().numpy())
+    assert_close16(got, want, what="emb_ln0")
+    np.testing.assert_allclose(got.astype(np.float32), want.astype(np.float32), atol=3e-2)  # reference test level
+    e = torch.arange(5, dtype=torch.int32).cuda()
+    ops.advance_i32(e, 7)
+    assert host(e).tolist() == [7, 8, 9, 10, 11]
+
+
+def test_bad_arguments_return_status_not_abort(ops):
+    from rwkv_lightning_cuda_b200 import lib as L
+    x = torch.zeros((1, 100), dtype=torch.float16).cuda()
+    W = torch.zeros((4, 100), dtype=torch.float16).cuda()
+    with pytest.raises(L.Rwkv7B200Error) as e:
+        ops.linear_f16_orig(x, W)          # K not a multiple of 8
+    assert e.value.status == 2
+    with pytest.raises(L.Rwkv7B200Error):
+        ops.wkv_fp32io16(1, 1, 0, torch.zeros(1).cuda(), *([x] * 6))
