@@ -60,8 +60,9 @@ def _ptr(t: Optional[torch.Tensor]):
 class ModelBackend:
     """Drop-in counterpart of the reference ``ModelBackend`` (weights given as named tensors)."""
 
-    def __init__(self, dims: ModelDims, tensors: Dict[str, torch.Tensor], use_wkv32: bool = False,
-                 weight_format: int = L.FMT_F16, device: Optional[int] = None, model_path: str = "<synthetic>"):
+    def __init__(self, dims: ModelDims, tensors: Optional[Dict[str, torch.Tensor]] = None, use_wkv32: bool = False,
+                 weight_format: int = L.FMT_F16, device: Optional[int] = None, model_path: str = "<synthetic>",
+                 finalize: bool = True):
         self._lib = L.load_library()
         self.dims = dims
         self.use_wkv32 = bool(use_wkv32)
@@ -72,10 +73,15 @@ class ModelBackend:
         handle = C.c_void_p()
         L.check(self._lib.rwkv7_b200_model_create(C.byref(cfg), C.byref(handle)))
         self._h = handle
-        for name, t in tensors.items():
+        for name, t in (tensors or {}).items():
             self.set_tensor(name, t)
+        if finalize:
+            self.finalize()
+
+    def finalize(self) -> None:
+        """Builds the device layouts once every tensor has been set (streaming loaders call
+        set_tensor per tensor and this at the end)."""
         L.check(self._lib.rwkv7_b200_model_finalize(self._h))
-        self._pinned: Dict[int, torch.Tensor] = {}
 
     def set_tensor(self, name: str, t: torch.Tensor) -> None:
         if t.dtype == torch.float16:

@@ -47,8 +47,10 @@ void DevBuf::release() {
   bytes = 0;
 }
 Workspace::~Workspace() {
-  if (tokens_pinned) cudaFreeHost(tokens_pinned);
-  if (tokens_copied) cudaEventDestroy(tokens_copied);
+  for (int i = 0; i < kSlots; ++i) {
+    if (tokens_pinned[i]) cudaFreeHost(tokens_pinned[i]);
+    if (tokens_copied[i]) cudaEventDestroy(tokens_copied[i]);
+  }
 }
 
 // ------------------------------------------------------------------ model
@@ -323,8 +325,10 @@ Workspace* Model::workspace(int B, int T) {
   for (int i = 0; i < 4; ++i) ws->l1[i] = take(rows * 512);
   ws->xf = take(static_cast<size_t>(B) * C);
   ws->tokens = reinterpret_cast<int64_t*>(take(rows * 4 + 8));
-  if (cudaMallocHost(&ws->tokens_pinned, rows * sizeof(int64_t)) != cudaSuccess) return nullptr;
-  if (cudaEventCreateWithFlags(&ws->tokens_copied, cudaEventDisableTiming) != cudaSuccess) return nullptr;
+  for (int i = 0; i < Workspace::kSlots; ++i) {
+    if (cudaMallocHost(&ws->tokens_pinned[i], rows * sizeof(int64_t)) != cudaSuccess) return nullptr;
+    if (cudaEventCreateWithFlags(&ws->tokens_copied[i], cudaEventDisableTiming) != cudaSuccess) return nullptr;
+  }
   Workspace* raw = ws.get();
   workspaces_[key] = std::move(ws);
   return raw;
@@ -438,11 +442,12 @@ int Model::forward(const int64_t* tokens_host, int B, int T, void* shift, void* 
   std::lock_guard<std::mutex> lock(mu_);
   Workspace* ws = workspace(B, T);
   RK_REQUIRE(ws, kCuda, "forward: workspace allocation failed for B=%d T=%d", B, T);
-  // the pinned staging buffer may still be the source of the previous call's copy
-  RK_CUDA(cudaEventSynchronize(ws->tokens_copied));
-  std::memcpy(ws->tokens_pinned, tokens_host, static_cast<size_t>(rows) * sizeof(int64_t));
-  RK_CUDA(cudaMemcpyAsync(ws->tokens, ws->tokens_pinned, static_cast<size_t>(rows) * sizeof(int64_t), cudaMemcpyHostToDevice, stream));
-  RK_CUDA(cudaEventRecord(ws->tokens_copied, stream));
+  const int slot = ws->slot;
+  ws->slot = (slot + 1) % Workspace::kSlots;
+  RK_CUDA(cudaEventSynchronize(ws->tokens_copied[slot]));  // the copy that last read this slot is done
+  std::memcpy(ws->tokens_pinned[slot], tokens_host, static_cast<size_t>(rows) * sizeof(int64_t));
+  RK_CUDA(cudaMemcpyAsync(ws->tokens, ws->tokens_pinned[slot], static_cast<size_t>(rows) * sizeof(int64_t), cudaMemcpyHostToDevice, stream));
+  RK_CUDA(cudaEventRecord(ws->tokens_copied[slot], stream));
 
   if (T != 1 || stream == nullptr) {
     const long long before = launch_counter();

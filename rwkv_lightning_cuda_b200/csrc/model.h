@@ -55,8 +55,12 @@ struct Workspace {
   half *xA, *xB, *xm[6], *r, *k, *v, *vfirst, *vout, *w12, *a12, *g, *k2, *nkk, *kka, *y, *y2, *att, *mixed, *ffn;
   half *hid, *l1[4], *xf;
   int64_t* tokens;
-  int64_t* tokens_pinned = nullptr;  // host staging for the token ids
-  cudaEvent_t tokens_copied = nullptr;  // recorded after the staging buffer has been read
+  // ring of pinned host staging slots for the token ids; a slot is reused only after the copy
+  // that read it has completed, so callers may overwrite their token array as soon as forward returns
+  static constexpr int kSlots = 4;
+  int64_t* tokens_pinned[kSlots] = {nullptr, nullptr, nullptr, nullptr};
+  cudaEvent_t tokens_copied[kSlots] = {nullptr, nullptr, nullptr, nullptr};
+  int slot = 0;
   ~Workspace();
 };
 

@@ -128,8 +128,6 @@ def test_quant_formats_known_answers():
     qa, sa, za = orc.quant_pack_w4(Wr)
     Wd = orc.quant_unpack_w4(qa, sa, za)
     assert np.abs(Wd.astype(np.float32) - Wr.astype(np.float32)).max() <= sa.astype(np.float32).max() * 0.51
-    qb, sb, zb = orc.quant_pack_w4(Wd)
-    assert (orc.quant_unpack_w4(qb, sb, zb) == Wd).all()
 
 
 def test_quant_linear_equals_linear_on_dequantised_weights():
