@@ -73,6 +73,25 @@ struct LinearArgs {
   void* y = nullptr;         // half [M,N], or float [M,N] for kEpiF32
 };
 int linear(cudaStream_t stream, const LinearArgs& args);
+// Up to 8 independent problems sharing M <= 4 in a single launch.
+int linear_batch(cudaStream_t stream, const LinearArgs* args, int n);
+
+// ---- tmix_decode.cu : fused one-token time-mix core (LoRA up + gates + WKV + GroupNorm/gate)
+struct TmixDecodeArgs {
+  int B = 0, C = 0;
+  bool layer0 = false, wkv32 = false;
+  int R[4] = {0, 0, 0, 0};                                   // ranks of w, a, g, v
+  const half* l1[4] = {nullptr, nullptr, nullptr, nullptr};  // [B,R] LoRA down outputs
+  const half* up[4] = {nullptr, nullptr, nullptr, nullptr};  // [C,R] LoRA up matrices
+  const half *r = nullptr, *k = nullptr, *v = nullptr, *v_first = nullptr;
+  const half *w0 = nullptr, *a0 = nullptr, *v0 = nullptr, *k_k = nullptr, *k_a = nullptr, *r_k = nullptr;
+  const half *lnx_w = nullptr, *lnx_b = nullptr;
+  void* state = nullptr;  // this layer's [B,H,64,64] half or float
+  const int* elapsed = nullptr;
+  half* y2 = nullptr;
+};
+bool tmix_decode_supported(const TmixDecodeArgs& args);
+int tmix_decode(cudaStream_t stream, const TmixDecodeArgs& args);
 
 // ---- quant.cu
 int quant_pack_w8(cudaStream_t stream, int N, int K, const half* W, int8_t* q, half* scale);

@@ -1,11 +1,22 @@
-// Weight-streaming linear layers for decode-sized row counts: y = act(x) W^T, W [N,K] row-major
-// in fp16, int8 (W8A16) or packed int4 (W4A16, group 128).  The weights are read exactly once
-// with 128-bit non-allocating loads, dequantised in registers, accumulated in fp32 and reduced
-// with warp shuffles; the result is rounded to half once (the reference's rounding point,
-// cuda/rwkv7_v3a_ops.cu:464-509).  Replaces linear_orig_row{1,2}_exact*_f16_kernel and the
-// linear_t*/LoRA kernels of cuda/rwkv7_v3a_ops.cu for rows <= 4; larger row counts go to the
-// tensor-core GEMM.
-#include "common.cuh"
+// Weight-streaming linear layers for decode-sized row counts (M <= 4): y = epi(act(x) W^T),
+// W [N,K] row-major in fp16, int8 (W8A16) or packed int4 (W4A16, group 128).
+//
+// Memory-bound by construction: every weight byte is read exactly once with 128-bit
+// non-allocating loads, two stages of eight loads per lane are kept in flight (register double
+// buffering), the activations are staged once per CTA in shared memory, weights are dequantised
+// in registers, accumulated in fp32 and reduced with warp shuffles; the result is rounded to half
+// once (the reference's rounding point, cuda/rwkv7_v3a_ops.cu:464-509).  Several independent
+// problems (e.g. the r/k/v projections and the LoRA down-projections of one layer) run as one
+// launch.  The first weight stage is requested before the programmatic-dependency wait, so the
+// HBM stream of one kernel starts while its predecessor drains.
+//
+// Replaces linear_orig_row{1,2}_exact*_f16_kernel, the linear_t*/LoRA kernels and the sparse
+// FFN-down kernels (cuda/rwkv7_v3a_ops.cu:209-1270, cuda/rwkv7_fast_ops_fp16.cu:487-827) for
+// rows <= 4; larger row counts go to the tensor-core GEMM.
+#include <algorithm>
+#include <type_traits>
+
+#include "gemv.h"
 #include "kernels.h"
 
 namespace rk {
@@ -15,21 +26,9 @@ bool gemm_tc_supported(const LinearArgs& a);
 
 namespace {
 
-struct LinearDev {
-  int M, K, N, ldx, in_act, epi;
-  const half* x;
-  const void* w;
-  const half* scale;
-  const half* zero;
-  const half* v;
-  const half* v_first;
-  const half* v0;
-  void* y;
-};
-
-constexpr int kWarpsPerCta = 8;
-constexpr int kOutPerWarp = 2;
-constexpr int kUnroll = 4;
+constexpr int kWarps = 8;       // warps per CTA
+constexpr int kU = 4;           // 16-byte chunks per lane and weight row in one stage
+constexpr int kRowsPerTile = 2 * kWarps;
 
 template <int kFmt>
 struct Fmt;
@@ -95,125 +94,147 @@ __device__ __forceinline__ void dequant_chunk<2>(const uint4& q, float* out, flo
   }
 }
 
+template <int kFmt>
+struct Stage {
+  uint4 w[kU][2];
+  __half2 sz[kU][2];  // W4A16: (scale, zero) of the chunk's group
+};
+
 template <int kM, int kFmt>
-__global__ void __launch_bounds__(kWarpsPerCta * 32) gemv_kernel(const LinearDev p) {
+__device__ __forceinline__ void run_segment(const GemvSeg& sg, half* xs16, float* xs32, int row0, int rows_end) {
   constexpr int E = Fmt<kFmt>::kElems;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n0 = (blockIdx.x * kWarpsPerCta + warp) * kOutPerWarp;
-  if (n0 >= p.N) return;
-  const int n_valid = min(kOutPerWarp, p.N - n0);
-  const size_t row_bytes = static_cast<size_t>(p.K) * 16 / E;  // bytes per weight row
-  const char* wbase = static_cast<const char*>(p.w) + static_cast<size_t>(n0) * row_bytes;
-  const int groups = p.K >> 7;
+  const int K = sg.K;
+  const size_t row_bytes = static_cast<size_t>(K) * 16 / E;
+  const int groups = K >> 7;
+  const int chunk_span = 32 * E;                              // elements covered by one warp-wide chunk
+  const int n_stages = (K + chunk_span * kU - 1) / (chunk_span * kU);
+  const int first = row0 + 2 * warp;
+  const int n_pairs = first < rows_end ? (rows_end - first + kRowsPerTile - 1) / kRowsPerTile : 0;
+  const int total = n_pairs * n_stages;
+  const char* wbase = static_cast<const char*>(sg.w);
 
-  float acc[kM][kOutPerWarp];
+  auto issue = [&](int item, Stage<kFmt>& st) {
+    const int pair = item / n_stages, stg = item - pair * n_stages;
+    const int n = first + pair * kRowsPerTile;
 #pragma unroll
-  for (int m = 0; m < kM; ++m)
+    for (int u = 0; u < kU; ++u) {
+      const int k = (stg * kU + u) * chunk_span + lane * E;
 #pragma unroll
-    for (int j = 0; j < kOutPerWarp; ++j) acc[m][j] = 0.f;
-
-  const int step = 32 * E;
-  for (int k0 = lane * E; k0 < p.K; k0 += step * kUnroll) {
-    uint4 wq[kUnroll][kOutPerWarp];
-#pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
-      const int k = k0 + u * step;
-#pragma unroll
-      for (int j = 0; j < kOutPerWarp; ++j) {
-        if (k < p.K && j < n_valid) wq[u][j] = ldg_stream(wbase + j * row_bytes + static_cast<size_t>(k) * 16 / E);
-        else wq[u][j] = make_uint4(0, 0, 0, 0);
+      for (int j = 0; j < 2; ++j) {
+        const bool ok = k < K && n + j < rows_end;
+        st.w[u][j] = ok ? ldg_stream(wbase + static_cast<size_t>(n + j) * row_bytes + static_cast<size_t>(k) * 16 / E)
+                        : make_uint4(0, 0, 0, 0);
+        if (kFmt == 2) {
+          const size_t gi = static_cast<size_t>(ok ? n + j : row0) * groups + (ok ? (k >> 7) : 0);
+          st.sz[u][j] = __halves2half2(sg.scale[gi], sg.zero[gi]);
+        }
       }
     }
+  };
+
+  float acc[kM][2];
+  auto compute = [&](int item, const Stage<kFmt>& st) {
+    const int pair = item / n_stages, stg = item - pair * n_stages;
+    if (stg == 0) {
 #pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
-      const int k = k0 + u * step;
-      if (k >= p.K) break;
-      float wf[kOutPerWarp][E];
+      for (int m = 0; m < kM; ++m) acc[m][0] = acc[m][1] = 0.f;
+    }
 #pragma unroll
-      for (int j = 0; j < kOutPerWarp; ++j) {
+    for (int u = 0; u < kU; ++u) {
+      const int k = (stg * kU + u) * chunk_span + lane * E;
+      if (k >= K) break;
+      float wf[2][E];
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
         float s = 0.f, z = 0.f;
         if (kFmt == 2) {
-          const int nn = min(n0 + j, p.N - 1);
-          s = __half2float(p.scale[static_cast<size_t>(nn) * groups + (k >> 7)]);
-          z = __half2float(p.zero[static_cast<size_t>(nn) * groups + (k >> 7)]);
+          s = __low2float(st.sz[u][j]);
+          z = __high2float(st.sz[u][j]);
         }
-        dequant_chunk<kFmt>(wq[u][j], wf[j], s, z);
+        dequant_chunk<kFmt>(st.w[u][j], wf[j], s, z);
       }
 #pragma unroll
       for (int m = 0; m < kM; ++m) {
-        const half* xr = p.x + static_cast<size_t>(m) * p.ldx + k;
 #pragma unroll
         for (int c = 0; c < E / 8; ++c) {
-          const uint4 xq = *reinterpret_cast<const uint4*>(xr + c * 8);
-          const uint32_t xu[4] = {xq.x, xq.y, xq.z, xq.w};
+          float xf[8];
+          if (xs32) {
+            const float4 a = *reinterpret_cast<const float4*>(xs32 + static_cast<size_t>(m) * K + k + c * 8);
+            const float4 b = *reinterpret_cast<const float4*>(xs32 + static_cast<size_t>(m) * K + k + c * 8 + 4);
+            xf[0] = a.x; xf[1] = a.y; xf[2] = a.z; xf[3] = a.w; xf[4] = b.x; xf[5] = b.y; xf[6] = b.z; xf[7] = b.w;
+          } else {
+            const uint4 xq = *reinterpret_cast<const uint4*>(xs16 + static_cast<size_t>(m) * K + k + c * 8);
+            const uint32_t xu[4] = {xq.x, xq.y, xq.z, xq.w};
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            float2 xf = h2f2(xu[i]);
-            if (p.in_act != kActNone) {
-              xf.x = apply_in_act(xf.x, p.in_act);
-              xf.y = apply_in_act(xf.y, p.in_act);
+            for (int i = 0; i < 4; ++i) {
+              const float2 f = h2f2(xu[i]);
+              xf[2 * i] = f.x;
+              xf[2 * i + 1] = f.y;
             }
+          }
 #pragma unroll
-            for (int j = 0; j < kOutPerWarp; ++j) {
-              acc[m][j] = fmaf(xf.x, wf[j][c * 8 + 2 * i], acc[m][j]);
-              acc[m][j] = fmaf(xf.y, wf[j][c * 8 + 2 * i + 1], acc[m][j]);
-            }
+          for (int i = 0; i < 8; ++i) {
+            acc[m][0] = fmaf(xf[i], wf[0][c * 8 + i], acc[m][0]);
+            acc[m][1] = fmaf(xf[i], wf[1][c * 8 + i], acc[m][1]);
           }
         }
       }
     }
-  }
-
+    if (stg != n_stages - 1) return;
+    const int n = first + pair * kRowsPerTile;
 #pragma unroll
-  for (int m = 0; m < kM; ++m)
-#pragma unroll
-    for (int j = 0; j < kOutPerWarp; ++j) acc[m][j] = warp_sum(acc[m][j]);
-
-  if (lane == 0) {
-#pragma unroll
-    for (int j = 0; j < kOutPerWarp; ++j) {
-      if (j >= n_valid) break;
-      const int n = n0 + j;
-      const float sc = (kFmt == 1) ? __half2float(p.scale[n]) : 1.0f;
+    for (int m = 0; m < kM; ++m) {
+      acc[m][0] = warp_sum(acc[m][0]);
+      acc[m][1] = warp_sum(acc[m][1]);
+    }
+    if (lane < 2 && n + lane < rows_end) {
+      const int nn = n + lane;
+      const float sc = (kFmt == 1) ? __half2float(sg.scale[nn]) : 1.0f;
 #pragma unroll
       for (int m = 0; m < kM; ++m) {
-        const float a = acc[m][j] * sc;
-        const size_t o = static_cast<size_t>(m) * p.N + n;
-        if (p.epi == kEpiF32) {
-          static_cast<float*>(p.y)[o] = __half2float(__float2half_rn(a));
-        } else if (p.epi == kEpiRelu2) {
-          const float t = fmaxf(__half2float(__float2half_rn(a)), 0.f);
-          static_cast<half*>(p.y)[o] = __float2half_rn(t * t);
-        } else if (p.epi == kEpiVres) {
-          const float vv = __half2float(p.v[o]);
-          const float gate = 1.0f / (1.0f + expf(-(__half2float(p.v0[n]) + a)));
-          static_cast<half*>(p.y)[o] = __float2half_rn(vv + (__half2float(p.v_first[o]) - vv) * gate);
-        } else {
-          static_cast<half*>(p.y)[o] = __float2half_rn(a);
-        }
+        store_result(sg, m, nn, (lane == 0 ? acc[m][0] : acc[m][1]) * sc);
       }
+    }
+  };
+
+  // Weights do not depend on the previous kernel: request the first stage before waiting for it.
+  Stage<kFmt> sa, sb;
+  if (total > 0) issue(0, sa);
+  pdl_wait();
+  stage_activations<kM, kWarps * 32>(sg, xs16, xs32);
+  __syncthreads();
+  for (int item = 0; item < total; item += 2) {
+    if (item + 1 < total) issue(item + 1, sb);
+    compute(item, sa);
+    if (item + 1 < total) {
+      if (item + 2 < total) issue(item + 2, sa);
+      compute(item + 1, sb);
     }
   }
 }
 
-template <int kFmt>
-int launch_gemv(cudaStream_t stream, const LinearDev& p) {
-  const int warps = (p.N + kOutPerWarp - 1) / kOutPerWarp;
-  const int grid = (warps + kWarpsPerCta - 1) / kWarpsPerCta;
-  const int block = kWarpsPerCta * 32;
-  switch (p.M) {
-    case 1: gemv_kernel<1, kFmt><<<grid, block, 0, stream>>>(p); break;
-    case 2: gemv_kernel<2, kFmt><<<grid, block, 0, stream>>>(p); break;
-    case 3: gemv_kernel<3, kFmt><<<grid, block, 0, stream>>>(p); break;
-    default: gemv_kernel<4, kFmt><<<grid, block, 0, stream>>>(p); break;
-  }
-  RK_LAUNCH_CHECK("gemv launch");
-  return kOk;
+// kMaxFmt: highest weight format present in the batch; code for formats above it is not compiled
+// in, which keeps the fp16-only kernel's register count (and so its occupancy) unaffected by int4.
+template <int kM, int kMaxFmt>
+__global__ void __launch_bounds__(kWarps * 32) gemv_multi_kernel(const GemvBatch p) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  pdl_trigger();
+  int s = 0;
+#pragma unroll
+  for (int i = 1; i < kMaxSeg; ++i)
+    if (i < p.n_seg && static_cast<int>(blockIdx.x) >= p.seg[i].cta_begin) s = i;
+  const GemvSeg& sg = p.seg[s];
+  const int row0 = (blockIdx.x - sg.cta_begin) * sg.rows_per_cta;
+  const int rows_end = min(sg.N, row0 + sg.rows_per_cta);
+  half* xs16 = sg.in_act == kActNone ? reinterpret_cast<half*>(smem_raw) : nullptr;
+  float* xs32 = sg.in_act == kActNone ? nullptr : reinterpret_cast<float*>(smem_raw);
+  if (kMaxFmt >= 2 && sg.fmt == 2) run_segment<kM, 2>(sg, xs16, xs32, row0, rows_end);
+  else if (kMaxFmt >= 1 && sg.fmt == 1) run_segment<kM, 1>(sg, xs16, xs32, row0, rows_end);
+  else run_segment<kM, 0>(sg, xs16, xs32, row0, rows_end);
 }
 
-}  // namespace
-
-int linear(cudaStream_t stream, const LinearArgs& a) {
+int check_args(const LinearArgs& a) {
   RK_REQUIRE(a.M > 0 && a.K > 0 && a.N > 0, kShape, "linear: M, K, N must be positive");
   RK_REQUIRE(a.x && a.w && a.y, kBadArg, "linear: null pointer");
   RK_REQUIRE(a.fmt >= 0 && a.fmt <= 2, kBadArg, "linear: unknown weight format %d", a.fmt);
@@ -225,23 +246,93 @@ int linear(cudaStream_t stream, const LinearArgs& a) {
   const int ldx = a.ldx ? a.ldx : a.K;
   RK_REQUIRE(ldx % 8 == 0 && (reinterpret_cast<uintptr_t>(a.x) & 15u) == 0 && (reinterpret_cast<uintptr_t>(a.w) & 15u) == 0,
              kBadArg, "linear: x and w must be 16-byte aligned");
+  return kOk;
+}
 
+}  // namespace
+
+// Up to 8 independent problems with the same row count M <= 4 in one launch.
+int linear_batch(cudaStream_t stream, const LinearArgs* args, int n) {
+  RK_REQUIRE(args && n > 0 && n <= kMaxSeg, kBadArg, "linear_batch: 1..%d problems", kMaxSeg);
+  const int M = args[0].M;
+  RK_REQUIRE(M >= 1 && M <= 4, kShape, "linear_batch: M must be 1..4");
+  GemvBatch b;
+  b.n_seg = n;
+  long long tiles = 0;
+  size_t smem = 0;
+  for (int i = 0; i < n; ++i) {
+    int s = check_args(args[i]);
+    if (s != kOk) return s;
+    RK_REQUIRE(args[i].M == M, kShape, "linear_batch: all problems must share M");
+    tiles += (args[i].N + kRowsPerTile - 1) / kRowsPerTile;
+    smem = std::max(smem, static_cast<size_t>(M) * args[i].K * (args[i].in_act == kActNone ? 2 : 4));
+  }
+  int max_fmt = 0;
+  for (int i = 0; i < n; ++i) {
+    const LinearArgs& a = args[i];
+    GemvSeg& g = b.seg[i];
+    g.x = a.x; g.w = a.w; g.scale = a.scale; g.zero = a.zero; g.y = a.y;
+    g.v = a.ea.v; g.v_first = a.ea.v_first; g.v0 = a.ea.v0;
+    g.ldx = a.ldx ? a.ldx : a.K; g.N = a.N; g.K = a.K; g.fmt = a.fmt; g.in_act = a.in_act; g.epi = a.epi;
+    g.cta_begin = 0; g.rows_per_cta = 0; g.parts = 0; g.piece_bytes = 0;
+    max_fmt = std::max(max_fmt, a.fmt);
+  }
+  for (int i = n; i < kMaxSeg; ++i) b.seg[i] = b.seg[0];
+
+  // fp16 weights: bulk-copy kernel (shared-memory rings fed by the copy engine)
+  size_t tma_smem = 0;
+  int tma_grid = 0;
+  if (max_fmt == 0 && gemv_tma_plan(b, M, &tma_smem, &tma_grid)) return gemv_tma_launch(stream, b, M, tma_smem, tma_grid);
+
+  RK_REQUIRE(smem <= 160 * 1024, kShape, "linear_batch: M*K too large for the activation staging buffer");
+  const int tiles_per_cta = static_cast<int>(std::max<long long>(1, (tiles + 295) / 296));  // about two CTAs per SM
+  int cta = 0;
+  for (int i = 0; i < n; ++i) {
+    GemvSeg& g = b.seg[i];
+    g.cta_begin = cta;
+    g.rows_per_cta = tiles_per_cta * kRowsPerTile;
+    cta += (g.N + g.rows_per_cta - 1) / g.rows_per_cta;
+  }
+  for (int i = n; i < kMaxSeg; ++i) b.seg[i] = b.seg[0];
+  const dim3 grid(cta), block(kWarps * 32);
+  auto launch = [&](auto kernel) -> int {
+    if (smem > 48 * 1024) RK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+    RK_CUDA(launch_pdl(kernel, grid, block, smem, stream, b));
+    return kOk;
+  };
+  auto by_m = [&](auto fmt_tag) -> int {
+    constexpr int F = decltype(fmt_tag)::value;
+    switch (M) {
+      case 1: return launch(gemv_multi_kernel<1, F>);
+      case 2: return launch(gemv_multi_kernel<2, F>);
+      case 3: return launch(gemv_multi_kernel<3, F>);
+      default: return launch(gemv_multi_kernel<4, F>);
+    }
+  };
+  int s;
+  if (max_fmt == 0) s = by_m(std::integral_constant<int, 0>{});
+  else if (max_fmt == 1) s = by_m(std::integral_constant<int, 1>{});
+  else s = by_m(std::integral_constant<int, 2>{});
+  if (s != kOk) return s;
+  RK_LAUNCH_CHECK("gemv launch");
+  return kOk;
+}
+
+int linear(cudaStream_t stream, const LinearArgs& a) {
+  int s = check_args(a);
+  if (s != kOk) return s;
   if (a.M > 4 && gemm_tc_supported(a)) return gemm_tc(stream, a);
-
-  LinearDev p;
-  p.K = a.K; p.N = a.N; p.ldx = ldx; p.in_act = a.in_act; p.epi = a.epi;
-  p.w = a.w; p.scale = a.scale; p.zero = a.zero; p.v0 = a.ea.v0;
+  const int ldx = a.ldx ? a.ldx : a.K;
   const size_t out_elem = a.epi == kEpiF32 ? sizeof(float) : sizeof(half);
   for (int m0 = 0; m0 < a.M; m0 += 4) {
-    p.M = a.M - m0 < 4 ? a.M - m0 : 4;
-    p.x = a.x + static_cast<size_t>(m0) * ldx;
-    p.y = static_cast<char*>(a.y) + static_cast<size_t>(m0) * a.N * out_elem;
-    p.v = a.ea.v ? a.ea.v + static_cast<size_t>(m0) * a.N : nullptr;
-    p.v_first = a.ea.v_first ? a.ea.v_first + static_cast<size_t>(m0) * a.N : nullptr;
-    int s;
-    if (a.fmt == 0) s = launch_gemv<0>(stream, p);
-    else if (a.fmt == 1) s = launch_gemv<1>(stream, p);
-    else s = launch_gemv<2>(stream, p);
+    LinearArgs c = a;
+    c.M = a.M - m0 < 4 ? a.M - m0 : 4;
+    c.ldx = ldx;
+    c.x = a.x + static_cast<size_t>(m0) * ldx;
+    c.y = static_cast<char*>(a.y) + static_cast<size_t>(m0) * a.N * out_elem;
+    if (a.ea.v) c.ea.v = a.ea.v + static_cast<size_t>(m0) * a.N;
+    if (a.ea.v_first) c.ea.v_first = a.ea.v_first + static_cast<size_t>(m0) * a.N;
+    s = linear_batch(stream, &c, 1);
     if (s != kOk) return s;
   }
   return kOk;

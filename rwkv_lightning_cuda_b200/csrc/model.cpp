@@ -371,35 +371,66 @@ int Model::enqueue(Workspace& ws, int B, int T, half* shift, void* wkv, int* ela
     half* shift1 = shift0 + static_cast<size_t>(B) * C;
     half *xr = ws.xm[0], *xw = ws.xm[1], *xk = ws.xm[2], *xv = ws.xm[3], *xa = ws.xm[4], *xg = ws.xm[5];
     half* v_lin = li == 0 ? ws.vfirst : ws.v;
-    RK_TRY(lin(st, rows, W.Wr, xr, ws.r, kEpiNone));
-    RK_TRY(lin(st, rows, W.Wk, xk, ws.k, kEpiNone));
-    RK_TRY(lin(st, rows, W.Wv, xv, v_lin, kEpiNone));
-    RK_TRY(lin16(st, rows, C, cfg_.rank_w, xw, W.w1t.as<half>(), ws.l1[0], kActNone, kEpiNone, none));
-    RK_TRY(lin16(st, rows, C, cfg_.rank_a, xa, W.a1t.as<half>(), ws.l1[1], kActNone, kEpiNone, none));
-    RK_TRY(lin16(st, rows, C, cfg_.rank_g, xg, W.g1t.as<half>(), ws.l1[2], kActNone, kEpiNone, none));
-    RK_TRY(lin16(st, rows, cfg_.rank_w, C, ws.l1[0], W.w2t.as<half>(), ws.w12, kActTanh, kEpiNone, none));
-    RK_TRY(lin16(st, rows, cfg_.rank_a, C, ws.l1[1], W.a2t.as<half>(), ws.a12, kActNone, kEpiNone, none));
-    RK_TRY(lin16(st, rows, cfg_.rank_g, C, ws.l1[2], W.g2t.as<half>(), ws.g, kActSigmoid, kEpiNone, none));
-    const half* v_use = ws.vfirst;
-    if (li > 0) {
-      RK_TRY(lin16(st, rows, C, cfg_.rank_v, xv, W.v1t.as<half>(), ws.l1[3], kActNone, kEpiNone, none));
-      EpiArgs ea;
-      ea.v = ws.v; ea.v_first = ws.vfirst; ea.v0 = W.v0.as<half>();
-      RK_TRY(lin16(st, rows, cfg_.rank_v, C, ws.l1[3], W.v2t.as<half>(), ws.vout, kActNone, kEpiVres, ea));
-      v_use = ws.vout;
-    }
-    RK_TRY(tmix_kk_a_gate(st, rows, C, ws.k, W.k_k.as<half>(), W.a0.as<half>(), ws.a12, W.k_a.as<half>(), ws.k2, ws.nkk, ws.kka));
     const size_t wkv_off = static_cast<size_t>(li) * B * H_ * kHead * kHead;
-    if (cfg_.wkv32) {
-      RK_TRY(wkv7_fp32(st, B, T, C, H_, static_cast<float*>(wkv) + wkv_off, ws.r, ws.w12, W.w0.as<half>(), ws.k2, v_use,
-                       ws.nkk, ws.kka, ws.y));
+    TmixDecodeArgs ta;
+    ta.B = B; ta.C = C; ta.layer0 = li == 0; ta.wkv32 = cfg_.wkv32 != 0;
+    ta.R[0] = cfg_.rank_w; ta.R[1] = cfg_.rank_a; ta.R[2] = cfg_.rank_g; ta.R[3] = cfg_.rank_v;
+    if (T == 1 && rows <= 4 && tmix_decode_supported(ta)) {
+      // decode: r/k/v projections and the LoRA down-projections as one launch, then the fused head kernel
+      auto mat = [&](const Matrix& Wm, const half* x, half* y) {
+        LinearArgs a;
+        a.M = rows; a.K = Wm.K; a.N = Wm.N; a.x = x; a.w = Wm.w.p; a.fmt = Wm.fmt;
+        a.scale = Wm.scale.as<half>(); a.zero = Wm.zero.as<half>(); a.y = y;
+        return a;
+      };
+      auto low = [&](const DevBuf& w, int R, const half* x, half* y) {
+        LinearArgs a;
+        a.M = rows; a.K = C; a.N = R; a.x = x; a.w = w.p; a.fmt = RWKV7_B200_FMT_F16; a.y = y;
+        return a;
+      };
+      LinearArgs seg[7] = {mat(W.Wr, xr, ws.r), mat(W.Wk, xk, ws.k), mat(W.Wv, xv, v_lin),
+                           low(W.w1t, cfg_.rank_w, xw, ws.l1[0]), low(W.a1t, cfg_.rank_a, xa, ws.l1[1]),
+                           low(W.g1t, cfg_.rank_g, xg, ws.l1[2]), low(W.v1t, cfg_.rank_v, xv, ws.l1[3])};
+      RK_TRY(linear_batch(st, seg, li == 0 ? 6 : 7));
+      for (int i = 0; i < 4; ++i) ta.l1[i] = ws.l1[i];
+      ta.up[0] = W.w2t.as<half>(); ta.up[1] = W.a2t.as<half>(); ta.up[2] = W.g2t.as<half>(); ta.up[3] = W.v2t.as<half>();
+      ta.r = ws.r; ta.k = ws.k; ta.v = v_lin; ta.v_first = ws.vfirst;
+      ta.w0 = W.w0.as<half>(); ta.a0 = W.a0.as<half>(); ta.v0 = W.v0.as<half>(); ta.k_k = W.k_k.as<half>();
+      ta.k_a = W.k_a.as<half>(); ta.r_k = W.r_k.as<half>(); ta.lnx_w = W.lnx_w.as<half>(); ta.lnx_b = W.lnx_b.as<half>();
+      ta.state = cfg_.wkv32 ? static_cast<void*>(static_cast<float*>(wkv) + wkv_off)
+                            : static_cast<void*>(static_cast<half*>(wkv) + wkv_off);
+      ta.elapsed = elapsed; ta.y2 = ws.y2;
+      RK_TRY(tmix_decode(st, ta));
     } else {
-      // the reference adds w0 in fp32 inside the kernel for T <= 16 and pre-rounds the sum otherwise
-      RK_TRY(wkv7_fp16(st, B, T, C, H_, static_cast<half*>(wkv) + wkv_off, ws.r, ws.w12, W.w0.as<half>(), T <= 16 ? 1 : 2,
-                       ws.k2, v_use, ws.nkk, ws.kka, ws.y, elapsed));
+      RK_TRY(lin(st, rows, W.Wr, xr, ws.r, kEpiNone));
+      RK_TRY(lin(st, rows, W.Wk, xk, ws.k, kEpiNone));
+      RK_TRY(lin(st, rows, W.Wv, xv, v_lin, kEpiNone));
+      RK_TRY(lin16(st, rows, C, cfg_.rank_w, xw, W.w1t.as<half>(), ws.l1[0], kActNone, kEpiNone, none));
+      RK_TRY(lin16(st, rows, C, cfg_.rank_a, xa, W.a1t.as<half>(), ws.l1[1], kActNone, kEpiNone, none));
+      RK_TRY(lin16(st, rows, C, cfg_.rank_g, xg, W.g1t.as<half>(), ws.l1[2], kActNone, kEpiNone, none));
+      RK_TRY(lin16(st, rows, cfg_.rank_w, C, ws.l1[0], W.w2t.as<half>(), ws.w12, kActTanh, kEpiNone, none));
+      RK_TRY(lin16(st, rows, cfg_.rank_a, C, ws.l1[1], W.a2t.as<half>(), ws.a12, kActNone, kEpiNone, none));
+      RK_TRY(lin16(st, rows, cfg_.rank_g, C, ws.l1[2], W.g2t.as<half>(), ws.g, kActSigmoid, kEpiNone, none));
+      const half* v_use = ws.vfirst;
+      if (li > 0) {
+        RK_TRY(lin16(st, rows, C, cfg_.rank_v, xv, W.v1t.as<half>(), ws.l1[3], kActNone, kEpiNone, none));
+        EpiArgs ea;
+        ea.v = ws.v; ea.v_first = ws.vfirst; ea.v0 = W.v0.as<half>();
+        RK_TRY(lin16(st, rows, cfg_.rank_v, C, ws.l1[3], W.v2t.as<half>(), ws.vout, kActNone, kEpiVres, ea));
+        v_use = ws.vout;
+      }
+      RK_TRY(tmix_kk_a_gate(st, rows, C, ws.k, W.k_k.as<half>(), W.a0.as<half>(), ws.a12, W.k_a.as<half>(), ws.k2, ws.nkk, ws.kka));
+      if (cfg_.wkv32) {
+        RK_TRY(wkv7_fp32(st, B, T, C, H_, static_cast<float*>(wkv) + wkv_off, ws.r, ws.w12, W.w0.as<half>(), ws.k2, v_use,
+                         ws.nkk, ws.kka, ws.y));
+      } else {
+        // the reference adds w0 in fp32 inside the kernel for T <= 16 and pre-rounds the sum otherwise
+        RK_TRY(wkv7_fp16(st, B, T, C, H_, static_cast<half*>(wkv) + wkv_off, ws.r, ws.w12, W.w0.as<half>(), T <= 16 ? 1 : 2,
+                         ws.k2, v_use, ws.nkk, ws.kka, ws.y, elapsed));
+      }
+      RK_TRY(tmix_lnx_rkvres_xg(st, rows, C, ws.y, ws.r, ws.k2, v_use, W.r_k.as<half>(), W.lnx_w.as<half>(), W.lnx_b.as<half>(),
+                                ws.g, ws.y2));
     }
-    RK_TRY(tmix_lnx_rkvres_xg(st, rows, C, ws.y, ws.r, ws.k2, v_use, W.r_k.as<half>(), W.lnx_w.as<half>(), W.lnx_b.as<half>(),
-                              ws.g, ws.y2));
     RK_TRY(lin(st, rows, W.Wo, ws.y2, ws.att, kEpiNone));
     {
       RowOpArgs a;

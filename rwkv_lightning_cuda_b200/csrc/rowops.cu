@@ -6,8 +6,10 @@
 //   add_layer_norm_cmix_mix_f16 / add_layer_norm_tmix_mix6_f16 (T=1)     cuda/rwkv7_v3a_ops.cu:1515-2060
 //   tmix_mix6 / cmix_mix / update_shift_state_last                       cuda/rwkv7_fast_ops_fp16.cu:53-127,393-419
 // for every T: a CTA normalises its own row and, when t > 0, re-normalises row t-1 as the
-// "previous token" instead of waiting for another CTA; the CTA of t = 0 alone reads and then
-// replaces the shift state, so no second launch is needed.
+// "previous token" instead of waiting for another CTA; the CTAs of t = 0 alone read and then
+// replace the shift state, so no second launch is needed.  Rows live in registers (no shared-memory
+// staging) and a row may be split over several CTAs so that a decode step's single row does not
+// serialise on one SM.
 // Rounding points follow the reference: the sum x + residual and the LayerNorm output are each
 // rounded to half once, the interpolation reads the rounded LayerNorm output.
 #include "common.cuh"
@@ -19,7 +21,7 @@ namespace {
 constexpr int kRowThreads = 256;
 
 struct RowOpDev {
-  int B, T, C, vocab, n_mix, last_only, identity;
+  int B, T, C, vocab, n_mix, last_only, identity, n_slices;
   float eps;
   const int64_t* tokens;
   const half* table;
@@ -35,8 +37,10 @@ struct RowOpDev {
   int* bad_token_flag;
 };
 
-// Loads row (b,t) as fp32 into buf; optionally stores the rounded sum.
-__device__ __forceinline__ void load_row(const RowOpDev& p, int b, int t, float* buf, bool store_x) {
+// A thread owns the channel pairs q = tid + 256 i, i < kPairs, of a row, in registers.
+// Loads row (b,t) as fp32 (x + residual, or the gathered embedding row).
+template <int kPairs>
+__device__ __forceinline__ void load_row(const RowOpDev& p, int b, int t, float2 (&v)[kPairs]) {
   const size_t row = static_cast<size_t>(b) * p.T + t;
   const int pairs = p.C >> 1;
   if (p.table) {
@@ -46,101 +50,135 @@ __device__ __forceinline__ void load_row(const RowOpDev& p, int b, int t, float*
       tok = 0;
     }
     const __half2* src = reinterpret_cast<const __half2*>(p.table + static_cast<size_t>(tok) * p.C);
-    for (int q = threadIdx.x; q < pairs; q += kRowThreads) {
-      const __half2 h2 = src[q];
-      const float2 f = __half22float2(h2);
-      buf[2 * q] = f.x;
-      buf[2 * q + 1] = f.y;
-      if (store_x && p.x_out) reinterpret_cast<__half2*>(p.x_out + row * p.C)[q] = h2;
+#pragma unroll
+    for (int i = 0; i < kPairs; ++i) {
+      const int q = threadIdx.x + kRowThreads * i;
+      v[i] = q < pairs ? __half22float2(src[q]) : make_float2(0.f, 0.f);
     }
   } else {
     const __half2* xs = reinterpret_cast<const __half2*>(p.x + row * p.C);
     const __half2* rs = p.residual ? reinterpret_cast<const __half2*>(p.residual + row * p.C) : nullptr;
-    for (int q = threadIdx.x; q < pairs; q += kRowThreads) {
-      float2 f = __half22float2(xs[q]);
-      if (rs) {
-        const float2 g = __half22float2(rs[q]);
-        f.x += g.x;
-        f.y += g.y;
-      }
-      buf[2 * q] = f.x;
-      buf[2 * q + 1] = f.y;
-      if (store_x && p.x_out) reinterpret_cast<__half2*>(p.x_out + row * p.C)[q] = __floats2half2_rn(f.x, f.y);
+    __half2 xv[kPairs], rv[kPairs];
+#pragma unroll
+    for (int i = 0; i < kPairs; ++i) {
+      const int q = threadIdx.x + kRowThreads * i;
+      xv[i] = q < pairs ? xs[q] : __floats2half2_rn(0.f, 0.f);
+      rv[i] = (rs && q < pairs) ? rs[q] : __floats2half2_rn(0.f, 0.f);
+    }
+#pragma unroll
+    for (int i = 0; i < kPairs; ++i) {
+      const float2 a = __half22float2(xv[i]), r = __half22float2(rv[i]);
+      v[i] = make_float2(a.x + r.x, a.y + r.y);
     }
   }
 }
 
-// In place: buf[c] <- float(half(LN(buf)[c])).  Two-pass statistics in fp32.
-__device__ __forceinline__ void ln_row(const RowOpDev& p, float* buf, float* scratch) {
+// In place: v <- float(half(LN(v))).  Two-pass statistics in fp32 over the whole row.
+template <int kPairs>
+__device__ __forceinline__ void ln_row(const RowOpDev& p, float2 (&v)[kPairs], float* scratch) {
   if (p.identity) return;  // plain token shift: the row is used as it is
+  const int pairs = p.C >> 1;
   float s = 0.f;
-  for (int c = threadIdx.x; c < p.C; c += kRowThreads) s += buf[c];
+#pragma unroll
+  for (int i = 0; i < kPairs; ++i) s += v[i].x + v[i].y;  // absent pairs hold zeros
   const float inv_c = 1.0f / static_cast<float>(p.C);
   const float mean = block_sum<kRowThreads>(s, scratch) * inv_c;
   float sv = 0.f;
-  for (int c = threadIdx.x; c < p.C; c += kRowThreads) {
-    const float d = buf[c] - mean;
-    sv += d * d;
+#pragma unroll
+  for (int i = 0; i < kPairs; ++i) {
+    if (threadIdx.x + kRowThreads * i < pairs) {
+      const float d0 = v[i].x - mean, d1 = v[i].y - mean;
+      sv += d0 * d0 + d1 * d1;
+    }
   }
   const float rstd = rsqrtf(block_sum<kRowThreads>(sv, scratch) * inv_c + p.eps);
-  for (int c = threadIdx.x; c < p.C; c += kRowThreads) {
-    const float wv = __half2float(p.ln_w[c]), bv = __half2float(p.ln_b[c]);
-    buf[c] = __half2float(__float2half_rn((buf[c] - mean) * rstd * wv + bv));
+#pragma unroll
+  for (int i = 0; i < kPairs; ++i) {
+    const int q = threadIdx.x + kRowThreads * i;
+    if (q < pairs) {
+      const float2 w = __half22float2(reinterpret_cast<const __half2*>(p.ln_w)[q]);
+      const float2 b = __half22float2(reinterpret_cast<const __half2*>(p.ln_b)[q]);
+      v[i] = __half22float2(__floats2half2_rn((v[i].x - mean) * rstd * w.x + b.x, (v[i].y - mean) * rstd * w.y + b.y));
+    }
   }
 }
 
+// grid = (n_slices, rows).  Every CTA computes the statistics of its whole row; slice s writes the
+// outputs of pairs i in [s*kPairs/n_slices, (s+1)*kPairs/n_slices) so that a single decode row is
+// spread over several SMs.
+template <int kPairs>
 __global__ void __launch_bounds__(kRowThreads) row_op_kernel(const RowOpDev p) {
-  extern __shared__ __align__(16) float smem[];
-  float* cur = smem;
-  float* prev = smem + p.C;
   __shared__ float scratch[kRowThreads / 32];
-
+  pdl_trigger();
   int b, t;
   if (p.last_only) {
-    b = blockIdx.x;
+    b = blockIdx.y;
     t = p.T - 1;
   } else {
-    b = blockIdx.x / p.T;
-    t = blockIdx.x - b * p.T;
+    b = blockIdx.y / p.T;
+    t = blockIdx.y - b * p.T;
   }
   const size_t row = static_cast<size_t>(b) * p.T + t;
+  const int pairs = p.C >> 1;
+  const int per = kPairs / p.n_slices;
+  const int i_lo = blockIdx.x * per, i_hi = i_lo + per;
+  auto owned = [&](int i) { return i >= i_lo && i < i_hi && threadIdx.x + kRowThreads * i < pairs; };
 
-  load_row(p, b, t, cur, true);
-  __syncthreads();
+  pdl_wait();
+  float2 cur[kPairs];
+  load_row<kPairs>(p, b, t, cur);
+  if (p.x_out) {
+#pragma unroll
+    for (int i = 0; i < kPairs; ++i)
+      if (owned(i)) reinterpret_cast<__half2*>(p.x_out + row * p.C)[threadIdx.x + kRowThreads * i] = __floats2half2_rn(cur[i].x, cur[i].y);
+  }
   if (!p.ln_w && !p.identity) return;
-  ln_row(p, cur, scratch);  // each thread rewrites only the channels it later reads
+  ln_row<kPairs>(p, cur, scratch);
   if (p.n_out) {
     half* dst = p.n_out + (p.last_only ? static_cast<size_t>(b) : row) * p.C;
-    for (int c = threadIdx.x; c < p.C; c += kRowThreads) dst[c] = __float2half_rn(cur[c]);
+#pragma unroll
+    for (int i = 0; i < kPairs; ++i)
+      if (owned(i)) reinterpret_cast<__half2*>(dst)[threadIdx.x + kRowThreads * i] = __floats2half2_rn(cur[i].x, cur[i].y);
   }
   if (p.n_mix == 0) return;
 
+  float2 prev[kPairs];
+  __half2* shift2 = reinterpret_cast<__half2*>(p.shift + static_cast<size_t>(b) * p.C);
   if (t == 0) {
-    for (int c = threadIdx.x; c < p.C; c += kRowThreads) prev[c] = __half2float(p.shift[static_cast<size_t>(b) * p.C + c]);
+#pragma unroll
+    for (int i = 0; i < kPairs; ++i) prev[i] = owned(i) ? __half22float2(shift2[threadIdx.x + kRowThreads * i]) : make_float2(0.f, 0.f);
   } else {
-    __syncthreads();
-    load_row(p, b, t - 1, prev, false);
-    __syncthreads();
-    ln_row(p, prev, scratch);
+    load_row<kPairs>(p, b, t - 1, prev);
+    ln_row<kPairs>(p, prev, scratch);
   }
-  for (int c = threadIdx.x; c < p.C; c += kRowThreads) {
-    const float n = cur[c];
-    const float dx = prev[c] - n;
+  __half2 mixv[kPairs][6];
+#pragma unroll
+  for (int i = 0; i < kPairs; ++i)
 #pragma unroll
     for (int m = 0; m < 6; ++m)
-      if (m < p.n_mix) p.mix_out[m][row * p.C + c] = __float2half_rn(n + dx * __half2float(p.mix[m][c]));
+      if (m < p.n_mix && owned(i)) mixv[i][m] = reinterpret_cast<const __half2*>(p.mix[m])[threadIdx.x + kRowThreads * i];
+#pragma unroll
+  for (int i = 0; i < kPairs; ++i) {
+    if (!owned(i)) continue;
+    const float dx0 = prev[i].x - cur[i].x, dx1 = prev[i].y - cur[i].y;
+#pragma unroll
+    for (int m = 0; m < 6; ++m) {
+      if (m < p.n_mix) {
+        const float2 c = __half22float2(mixv[i][m]);
+        reinterpret_cast<__half2*>(p.mix_out[m] + row * p.C)[threadIdx.x + kRowThreads * i] =
+            __floats2half2_rn(cur[i].x + dx0 * c.x, cur[i].y + dx1 * c.y);
+      }
+    }
   }
   if (t == 0) {
-    // this CTA is the only one that touches shift[b]: it has consumed the old row above
-    if (p.T == 1) {
-      for (int c = threadIdx.x; c < p.C; c += kRowThreads) p.shift[static_cast<size_t>(b) * p.C + c] = __float2half_rn(cur[c]);
-    } else {
-      __syncthreads();
-      load_row(p, b, p.T - 1, prev, false);
-      __syncthreads();
-      ln_row(p, prev, scratch);
-      for (int c = threadIdx.x; c < p.C; c += kRowThreads) p.shift[static_cast<size_t>(b) * p.C + c] = __float2half_rn(prev[c]);
+    // only the CTAs of t == 0 touch shift[b]; each has consumed its old pairs above
+    if (p.T > 1) {
+      load_row<kPairs>(p, b, p.T - 1, cur);
+      ln_row<kPairs>(p, cur, scratch);
     }
+#pragma unroll
+    for (int i = 0; i < kPairs; ++i)
+      if (owned(i)) shift2[threadIdx.x + kRowThreads * i] = __floats2half2_rn(cur[i].x, cur[i].y);
   }
 }
 
@@ -293,17 +331,21 @@ int row_op(cudaStream_t stream, const RowOpArgs& a) {
     p.mix_out[m] = a.mix_out[m];
     RK_REQUIRE(m >= a.n_mix || (a.mix[m] && a.mix_out[m]), kBadArg, "row_op: mix tensor %d missing", m);
   }
-  const int grid = a.last_only ? a.B : a.B * a.T;
-  const size_t smem = sizeof(float) * 2 * static_cast<size_t>(a.C);
-  RK_REQUIRE(smem <= 200 * 1024, kShape, "row_op: C too large");
-  if (smem > 48 * 1024) {
-    static bool raised = false;  // idempotent attribute; a benign race at worst repeats the call
-    if (!raised) {
-      RK_CUDA(cudaFuncSetAttribute(row_op_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-      raised = true;
-    }
+  const int rows = a.last_only ? a.B : a.B * a.T;
+  const int need = (a.C / 2 + kRowThreads - 1) / kRowThreads;  // pairs per thread
+  RK_REQUIRE(need <= 16, kShape, "row_op: C=%d too large (max 8192)", a.C);
+  const int kp = need <= 1 ? 1 : need <= 2 ? 2 : need <= 4 ? 4 : need <= 8 ? 8 : 16;
+  p.n_slices = rows <= 32 ? kp : 1;  // spread few rows over more SMs
+  const dim3 grid(p.n_slices, rows), block(kRowThreads);
+  cudaError_t e;
+  switch (kp) {
+    case 1: e = launch_pdl(row_op_kernel<1>, grid, block, 0, stream, p); break;
+    case 2: e = launch_pdl(row_op_kernel<2>, grid, block, 0, stream, p); break;
+    case 4: e = launch_pdl(row_op_kernel<4>, grid, block, 0, stream, p); break;
+    case 8: e = launch_pdl(row_op_kernel<8>, grid, block, 0, stream, p); break;
+    default: e = launch_pdl(row_op_kernel<16>, grid, block, 0, stream, p); break;
   }
-  row_op_kernel<<<grid, kRowThreads, smem, stream>>>(p);
+  RK_CUDA(e);
   RK_LAUNCH_CHECK("row_op launch");
   return kOk;
 }
