@@ -133,9 +133,46 @@ __device__ __forceinline__ void cp_async_wait() {
 }
 
 // Programmatic dependent launch: a kernel may start while its predecessor drains.
-// wait() blocks until the predecessor's memory is visible; trigger() lets the successor start.
+// wait() blocks until the predecessor has completed and its memory is visible; trigger() lets the
+// successor be scheduled.  Kernels here call trigger() only after wait(): then the successor cannot
+// start before the predecessor's predecessor has completed, so what a kernel reads before its own
+// wait() may be anything except the output of its immediate predecessor.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;"); }
+
+// ---- mbarrier + bulk-copy (TMA engine) primitives
+constexpr uint32_t kSpinLimit = 1u << 24;
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait: gives up after kSpinLimit polls instead of hanging the GPU; callers record the
+// failure in a device flag and return.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  for (uint32_t i = 0; i < kSpinLimit; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
+  return false;
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
 
 __device__ __forceinline__ float2 h2f2(uint32_t u) {
   return __half22float2(*reinterpret_cast<const __half2*>(&u));

@@ -70,7 +70,7 @@ __device__ __forceinline__ void stage_activations(const GemvSeg& sg, half* xs16,
 #endif
 
 // gemv_tma.cu: fp16 weights fetched with per-warp rings of bulk copies (cp.async.bulk + mbarrier).
-bool gemv_tma_plan(GemvBatch& b, int M, size_t* smem_bytes, int* grid);
-int gemv_tma_launch(cudaStream_t stream, const GemvBatch& b, int M, size_t smem_bytes, int grid);
+bool gemv_tma_plan(GemvBatch& b, int M, size_t* smem_bytes, int* grid, int* n_slots, int* slot_stride);
+int gemv_tma_launch(cudaStream_t stream, const GemvBatch& b, int M, size_t smem_bytes, int grid, int n_slots, int slot_stride);
 
 }  // namespace rk

@@ -15,48 +15,26 @@ namespace rk {
 namespace {
 
 constexpr int kWarps = 8;
-constexpr int kSlots = 3;
+constexpr int kMaxSlots = 6;
 constexpr int kPieceCap = 4096;  // bytes
-constexpr uint32_t kSpinLimit = 1u << 24;
 
 __device__ int g_gemv_timeout = 0;  // set when a bounded mbarrier wait gives up
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-// Bounded wait: gives up after kSpinLimit polls instead of hanging the GPU.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-  for (uint32_t i = 0; i < kSpinLimit; ++i)
-    if (mbar_try_wait(bar, parity)) return true;
-  return false;
-}
-__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
-               : "memory");
+// One 16-byte weight chunk (8 halves) against 8 fp32 activations from shared memory.
+__device__ __forceinline__ void fma_chunk(const uint4& q, const float* x, float& a0, float& a1) {
+  const float4 xa = *reinterpret_cast<const float4*>(x);
+  const float4 xb = *reinterpret_cast<const float4*>(x + 4);
+  const float2 w0 = h2f2(q.x), w1 = h2f2(q.y), w2 = h2f2(q.z), w3 = h2f2(q.w);
+  a0 = fmaf(xa.x, w0.x, a0); a1 = fmaf(xa.y, w0.y, a1);
+  a0 = fmaf(xa.z, w1.x, a0); a1 = fmaf(xa.w, w1.y, a1);
+  a0 = fmaf(xb.x, w2.x, a0); a1 = fmaf(xb.y, w2.y, a1);
+  a0 = fmaf(xb.z, w3.x, a0); a1 = fmaf(xb.w, w3.y, a1);
 }
 
 template <int kM>
-__global__ void __launch_bounds__(kWarps * 32) gemv_tma_kernel(const GemvBatch p, int x_bytes) {
+__global__ void __launch_bounds__(kWarps * 32) gemv_tma_kernel(const GemvBatch p, int x_bytes, int n_slots, int slot_stride) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
-  __shared__ __align__(8) uint64_t bars[kWarps][kSlots];
-  pdl_trigger();
+  __shared__ __align__(8) uint64_t bars[kWarps][kMaxSlots];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   int s = 0;
 #pragma unroll
@@ -65,98 +43,88 @@ __global__ void __launch_bounds__(kWarps * 32) gemv_tma_kernel(const GemvBatch p
   const GemvSeg& sg = p.seg[s];
   const int row0 = (blockIdx.x - sg.cta_begin) * sg.rows_per_cta;
   const int rows_end = min(sg.N, row0 + sg.rows_per_cta);
-  const int rows_cta = max(rows_end - row0, 0);
-  const int rpw = (rows_cta + kWarps - 1) / kWarps;
+  const int rpw = sg.rows_per_cta / kWarps;  // rows_per_cta is a multiple of the warp count
   const int r_begin = row0 + warp * rpw;
   const int r_end = min(rows_end, r_begin + rpw);
   const int parts = sg.parts, piece = sg.piece_bytes;
   const int total = r_end > r_begin ? (r_end - r_begin) * parts : 0;
-  const size_t row_bytes = static_cast<size_t>(sg.K) * 2;
-  const char* stream = static_cast<const char*>(sg.w) + static_cast<size_t>(r_begin) * row_bytes;
+  const int K = sg.K;
+  const char* stream = static_cast<const char*>(sg.w) + static_cast<size_t>(r_begin) * K * 2;
 
-  half* xs16 = sg.in_act == kActNone ? reinterpret_cast<half*>(smem_raw) : nullptr;
-  float* xs32 = sg.in_act == kActNone ? nullptr : reinterpret_cast<float*>(smem_raw);
-  unsigned char* ring = smem_raw + x_bytes + static_cast<size_t>(warp) * kSlots * kPieceCap;
+  float* xs = reinterpret_cast<float*>(smem_raw);  // activations, fp32, input activation applied
+  unsigned char* ring = smem_raw + x_bytes + static_cast<size_t>(warp) * n_slots * slot_stride;
+  // pieces of a row are visited in a per-warp rotated order so that the warps' streams do not march
+  // through the same low address bits (and hence the same memory channels) in lock step
+  const int rot = (blockIdx.x * kWarps + warp) % parts;
 
   if (lane == 0) {
 #pragma unroll
-    for (int i = 0; i < kSlots; ++i) mbar_init(smem_u32(&bars[warp][i]), 1);
+    for (int i = 0; i < kMaxSlots; ++i) mbar_init(smem_u32(&bars[warp][i]), 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncwarp();
-  auto issue = [&](int pc) {
+  // producer state (lane 0): next piece to request, as (row, rotated part, slot)
+  int q_row = 0, q_pp = rot, q_slot = 0, q_left = total;
+  auto issue = [&]() {
     if (lane == 0) {
-      const int slot = pc % kSlots;
-      const uint32_t bar = smem_u32(&bars[warp][slot]);
+      const uint32_t bar = smem_u32(&bars[warp][q_slot]);
       mbar_expect_tx(bar, piece);
-      bulk_g2s(smem_u32(ring + slot * kPieceCap), stream + static_cast<size_t>(pc) * piece, piece, bar);
+      bulk_g2s(smem_u32(ring + q_slot * slot_stride), stream + (static_cast<size_t>(q_row) * parts + q_pp) * piece, piece, bar);
     }
+    --q_left;
+    if (++q_slot == n_slots) q_slot = 0;
+    if (++q_pp == parts) q_pp = 0;
+    if (q_pp == rot) ++q_row;
   };
   // weights do not depend on the previous kernel: fill the ring before waiting for it
-  for (int pc = 0; pc < kSlots && pc < total; ++pc) issue(pc);
+  for (int i = 0; i < n_slots && q_left > 0; ++i) issue();
 
   pdl_wait();
-  stage_activations<kM, kWarps * 32>(sg, xs16, xs32);
+  pdl_trigger();  // after the wait: at most this kernel and its successor are ever in flight together
+  stage_activations<kM, kWarps * 32>(sg, nullptr, xs);
   __syncthreads();
 
   const int chunks = piece >> 4;  // 16-byte chunks per piece
-  float acc[kM];
+  float acc0[kM], acc1[kM];
+#pragma unroll
+  for (int m = 0; m < kM; ++m) acc0[m] = acc1[m] = 0.f;
+  int slot = 0, phase = 0, pp = rot, part = 0, row = r_begin;
   for (int pc = 0; pc < total; ++pc) {
-    const int slot = pc % kSlots;
-    const int row = pc / parts, part = pc - row * parts;
-    if (!mbar_wait(smem_u32(&bars[warp][slot]), (pc / kSlots) & 1)) {
+    const uint32_t bar = smem_u32(&bars[warp][slot]);
+    if (!mbar_try_wait(bar, phase) && !mbar_wait(bar, phase)) {
       if (lane == 0) atomicExch(&g_gemv_timeout, 1);
       return;
     }
-    if (part == 0) {
+    const uint4* wsm = reinterpret_cast<const uint4*>(ring + slot * slot_stride) + lane;
+    const float* xk = xs + pp * (piece >> 1) + lane * 8;
+    if (piece == kPieceCap) {
+      uint4 q[8];
 #pragma unroll
-      for (int m = 0; m < kM; ++m) acc[m] = 0.f;
-    }
-    const uint4* wsm = reinterpret_cast<const uint4*>(ring + slot * kPieceCap);
-    const int k0 = part * (piece >> 1);
+      for (int it = 0; it < 8; ++it) q[it] = wsm[it * 32];
 #pragma unroll
-    for (int it = 0; it < kPieceCap / 16 / 32; ++it) {
-      const int c = it * 32 + lane;
-      if (c < chunks) {
-        const uint4 q = wsm[c];
-        const uint32_t wu[4] = {q.x, q.y, q.z, q.w};
-        float wf[8];
+      for (int it = 0; it < 8; ++it)
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const float2 f = h2f2(wu[i]);
-          wf[2 * i] = f.x;
-          wf[2 * i + 1] = f.y;
-        }
+        for (int m = 0; m < kM; ++m) fma_chunk(q[it], xk + m * K + it * 256, acc0[m], acc1[m]);
+    } else {
+      for (int c = lane; c < chunks; c += 32) {
+        const uint4 q = wsm[c - lane];
 #pragma unroll
-        for (int m = 0; m < kM; ++m) {
-          float xf[8];
-          if (xs32) {
-            const float4 a = *reinterpret_cast<const float4*>(xs32 + static_cast<size_t>(m) * sg.K + k0 + c * 8);
-            const float4 b = *reinterpret_cast<const float4*>(xs32 + static_cast<size_t>(m) * sg.K + k0 + c * 8 + 4);
-            xf[0] = a.x; xf[1] = a.y; xf[2] = a.z; xf[3] = a.w; xf[4] = b.x; xf[5] = b.y; xf[6] = b.z; xf[7] = b.w;
-          } else {
-            const uint4 xq = *reinterpret_cast<const uint4*>(xs16 + static_cast<size_t>(m) * sg.K + k0 + c * 8);
-            const uint32_t xu[4] = {xq.x, xq.y, xq.z, xq.w};
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const float2 f = h2f2(xu[i]);
-              xf[2 * i] = f.x;
-              xf[2 * i + 1] = f.y;
-            }
-          }
-#pragma unroll
-          for (int i = 0; i < 8; ++i) acc[m] = fmaf(xf[i], wf[i], acc[m]);
-        }
+        for (int m = 0; m < kM; ++m) fma_chunk(q, xk + m * K + (c - lane) * 8, acc0[m], acc1[m]);
       }
     }
     __syncwarp();  // every lane has read the slot: it may be overwritten
-    if (pc + kSlots < total) issue(pc + kSlots);
-    if (part == parts - 1) {
+    if (q_left > 0) issue();
+    if (++slot == n_slots) { slot = 0; phase ^= 1; }
+    if (++pp == parts) pp = 0;
+    if (++part == parts) {
+      part = 0;
 #pragma unroll
       for (int m = 0; m < kM; ++m) {
-        const float a = warp_sum(acc[m]);
-        if (lane == 0) store_result(sg, m, r_begin + row, a);
+        const float a = warp_sum(acc0[m] + acc1[m]);
+        if (lane == 0) store_result(sg, m, row, a);
+        acc0[m] = acc1[m] = 0.f;
       }
+      ++row;
     }
   }
 }
@@ -165,7 +133,7 @@ __global__ void __launch_bounds__(kWarps * 32) gemv_tma_kernel(const GemvBatch p
 
 // Fills cta_begin / rows_per_cta / parts / piece_bytes for the bulk-copy kernel.  Returns false when
 // a problem does not fit it (non-fp16 weights, or a row that cannot be cut into 16-byte multiples).
-bool gemv_tma_plan(GemvBatch& b, int M, size_t* smem_bytes, int* grid) {
+bool gemv_tma_plan(GemvBatch& b, int M, size_t* smem_bytes, int* grid, int* n_slots, int* slot_stride) {
   size_t x_bytes = 0;
   double total_bytes = 0;
   for (int i = 0; i < b.n_seg; ++i) {
@@ -177,35 +145,55 @@ bool gemv_tma_plan(GemvBatch& b, int M, size_t* smem_bytes, int* grid) {
     if (parts > 64) return false;
     g.parts = parts;
     g.piece_bytes = row_bytes / parts;
-    x_bytes = std::max(x_bytes, static_cast<size_t>(M) * g.K * (g.in_act == kActNone ? 2 : 4));
+    x_bytes = std::max(x_bytes, static_cast<size_t>(M) * g.K * 4);
     total_bytes += static_cast<double>(g.N) * row_bytes;
   }
   x_bytes = (x_bytes + 127) & ~static_cast<size_t>(127);
-  const size_t smem = x_bytes + static_cast<size_t>(kWarps) * kSlots * kPieceCap;
-  if (smem > 200 * 1024) return false;
-  // two CTAs per SM when the shared memory allows it, CTAs shared out by weight bytes
-  const int per_sm = smem <= 110 * 1024 ? 2 : 1;
+  // Bytes in flight decide the achieved HBM rate (the loaded latency is several microseconds):
+  // two CTAs per SM with 3-slot rings when the activations are small (192 KiB in flight per SM),
+  // else one CTA per SM with rings as deep as the shared memory allows.
+  const int cap = kPieceCap;
+  int per_sm = 2, slots = 3;
+  if (x_bytes + static_cast<size_t>(kWarps) * 3 * cap > 112 * 1024) {
+    per_sm = 1;
+    slots = static_cast<int>((200 * 1024 - x_bytes) / (static_cast<size_t>(kWarps) * cap));
+    slots = std::min(slots, kMaxSlots);
+    if (slots < 2) return false;
+  }
+  for (int i = 0; i < b.n_seg; ++i) {
+    GemvSeg& g = b.seg[i];
+    const int row_bytes = g.K * 2;
+    int parts = (row_bytes + cap - 1) / cap;
+    while (parts <= 256 && (row_bytes % (parts * 16) != 0)) ++parts;
+    if (parts > 256) return false;
+    g.parts = parts;
+    g.piece_bytes = row_bytes / parts;
+  }
+  const size_t smem = x_bytes + static_cast<size_t>(kWarps) * slots * cap;
+  // CTAs are shared out by weight bytes; every warp of a problem gets the same number of rows
   const int budget = 148 * per_sm;
   int cta = 0;
   for (int i = 0; i < b.n_seg; ++i) {
     GemvSeg& g = b.seg[i];
     const double share = static_cast<double>(g.N) * g.K * 2 / total_bytes;
-    int n = static_cast<int>(share * budget + 0.5);
-    n = std::max(1, std::min(n, (g.N + kWarps - 1) / kWarps));
-    g.rows_per_cta = (g.N + n - 1) / n;
+    const int n = std::max(1, static_cast<int>(share * budget + 0.5));
+    const int rpw = std::max(1, (g.N + n * kWarps - 1) / (n * kWarps));
+    g.rows_per_cta = rpw * kWarps;
     g.cta_begin = cta;
     cta += (g.N + g.rows_per_cta - 1) / g.rows_per_cta;
   }
   *smem_bytes = smem;
   *grid = cta;
+  *n_slots = slots;
+  *slot_stride = cap;
   return true;
 }
 
-int gemv_tma_launch(cudaStream_t stream, const GemvBatch& b, int M, size_t smem_bytes, int grid) {
-  const int x_bytes = static_cast<int>(smem_bytes - static_cast<size_t>(kWarps) * kSlots * kPieceCap);
+int gemv_tma_launch(cudaStream_t stream, const GemvBatch& b, int M, size_t smem_bytes, int grid, int n_slots, int slot_stride) {
+  const int x_bytes = static_cast<int>(smem_bytes - static_cast<size_t>(kWarps) * n_slots * slot_stride);
   auto launch = [&](auto kernel) -> int {
     RK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-    RK_CUDA(launch_pdl(kernel, dim3(grid), dim3(kWarps * 32), smem_bytes, stream, b, x_bytes));
+    RK_CUDA(launch_pdl(kernel, dim3(grid), dim3(kWarps * 32), smem_bytes, stream, b, x_bytes, n_slots, slot_stride));
     return kOk;
   };
   int s;

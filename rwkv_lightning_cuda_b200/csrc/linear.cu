@@ -202,6 +202,7 @@ __device__ __forceinline__ void run_segment(const GemvSeg& sg, half* xs16, float
   Stage<kFmt> sa, sb;
   if (total > 0) issue(0, sa);
   pdl_wait();
+  pdl_trigger();
   stage_activations<kM, kWarps * 32>(sg, xs16, xs32);
   __syncthreads();
   for (int item = 0; item < total; item += 2) {
@@ -219,7 +220,6 @@ __device__ __forceinline__ void run_segment(const GemvSeg& sg, half* xs16, float
 template <int kM, int kMaxFmt>
 __global__ void __launch_bounds__(kWarps * 32) gemv_multi_kernel(const GemvBatch p) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  pdl_trigger();
   int s = 0;
 #pragma unroll
   for (int i = 1; i < kMaxSeg; ++i)
@@ -281,8 +281,9 @@ int linear_batch(cudaStream_t stream, const LinearArgs* args, int n) {
 
   // fp16 weights: bulk-copy kernel (shared-memory rings fed by the copy engine)
   size_t tma_smem = 0;
-  int tma_grid = 0;
-  if (max_fmt == 0 && gemv_tma_plan(b, M, &tma_smem, &tma_grid)) return gemv_tma_launch(stream, b, M, tma_smem, tma_grid);
+  int tma_grid = 0, tma_slots = 0, tma_stride = 0;
+  if (max_fmt == 0 && gemv_tma_plan(b, M, &tma_smem, &tma_grid, &tma_slots, &tma_stride))
+    return gemv_tma_launch(stream, b, M, tma_smem, tma_grid, tma_slots, tma_stride);
 
   RK_REQUIRE(smem <= 160 * 1024, kShape, "linear_batch: M*K too large for the activation staging buffer");
   const int tiles_per_cta = static_cast<int>(std::max<long long>(1, (tiles + 295) / 296));  // about two CTAs per SM

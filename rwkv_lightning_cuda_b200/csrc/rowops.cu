@@ -74,8 +74,11 @@ __device__ __forceinline__ void load_row(const RowOpDev& p, int b, int t, float2
 }
 
 // In place: v <- float(half(LN(v))).  Two-pass statistics in fp32 over the whole row.
+// Statistics cover the whole row; only the pairs i in [i_lo, i_hi) (whose weights lw/lb were
+// prefetched) are normalised, the others are left as they are and not used afterwards.
 template <int kPairs>
-__device__ __forceinline__ void ln_row(const RowOpDev& p, float2 (&v)[kPairs], float* scratch) {
+__device__ __forceinline__ void ln_row(const RowOpDev& p, float2 (&v)[kPairs], float* scratch,
+                                       const __half2 (&lw)[kPairs], const __half2 (&lb)[kPairs], int i_lo, int i_hi) {
   if (p.identity) return;  // plain token shift: the row is used as it is
   const int pairs = p.C >> 1;
   float s = 0.f;
@@ -95,9 +98,9 @@ __device__ __forceinline__ void ln_row(const RowOpDev& p, float2 (&v)[kPairs], f
 #pragma unroll
   for (int i = 0; i < kPairs; ++i) {
     const int q = threadIdx.x + kRowThreads * i;
-    if (q < pairs) {
-      const float2 w = __half22float2(reinterpret_cast<const __half2*>(p.ln_w)[q]);
-      const float2 b = __half22float2(reinterpret_cast<const __half2*>(p.ln_b)[q]);
+    if (q < pairs && i >= i_lo && i < i_hi) {
+      const float2 w = __half22float2(lw[i]);
+      const float2 b = __half22float2(lb[i]);
       v[i] = __half22float2(__floats2half2_rn((v[i].x - mean) * rstd * w.x + b.x, (v[i].y - mean) * rstd * w.y + b.y));
     }
   }
@@ -109,7 +112,6 @@ __device__ __forceinline__ void ln_row(const RowOpDev& p, float2 (&v)[kPairs], f
 template <int kPairs>
 __global__ void __launch_bounds__(kRowThreads) row_op_kernel(const RowOpDev p) {
   __shared__ float scratch[kRowThreads / 32];
-  pdl_trigger();
   int b, t;
   if (p.last_only) {
     b = blockIdx.y;
@@ -124,7 +126,26 @@ __global__ void __launch_bounds__(kRowThreads) row_op_kernel(const RowOpDev p) {
   const int i_lo = blockIdx.x * per, i_hi = i_lo + per;
   auto owned = [&](int i) { return i >= i_lo && i < i_hi && threadIdx.x + kRowThreads * i < pairs; };
 
+  // Weights, and the shift row (last written one step ago), are requested before the dependency wait.
+  __half2 lw[kPairs], lb[kPairs], mixv[kPairs][6];
+  float2 prev[kPairs];
+  __half2* shift2 = p.shift ? reinterpret_cast<__half2*>(p.shift + static_cast<size_t>(b) * p.C) : nullptr;
+#pragma unroll
+  for (int i = 0; i < kPairs; ++i) {
+    const int q = threadIdx.x + kRowThreads * i;
+    prev[i] = make_float2(0.f, 0.f);
+    if (!owned(i)) continue;
+    if (p.ln_w) {
+      lw[i] = reinterpret_cast<const __half2*>(p.ln_w)[q];
+      lb[i] = reinterpret_cast<const __half2*>(p.ln_b)[q];
+    }
+#pragma unroll
+    for (int m = 0; m < 6; ++m)
+      if (m < p.n_mix) mixv[i][m] = reinterpret_cast<const __half2*>(p.mix[m])[q];
+    if (p.n_mix && t == 0) prev[i] = __half22float2(shift2[q]);
+  }
   pdl_wait();
+  pdl_trigger();
   float2 cur[kPairs];
   load_row<kPairs>(p, b, t, cur);
   if (p.x_out) {
@@ -133,7 +154,7 @@ __global__ void __launch_bounds__(kRowThreads) row_op_kernel(const RowOpDev p) {
       if (owned(i)) reinterpret_cast<__half2*>(p.x_out + row * p.C)[threadIdx.x + kRowThreads * i] = __floats2half2_rn(cur[i].x, cur[i].y);
   }
   if (!p.ln_w && !p.identity) return;
-  ln_row<kPairs>(p, cur, scratch);
+  ln_row<kPairs>(p, cur, scratch, lw, lb, i_lo, i_hi);
   if (p.n_out) {
     half* dst = p.n_out + (p.last_only ? static_cast<size_t>(b) : row) * p.C;
 #pragma unroll
@@ -142,21 +163,10 @@ __global__ void __launch_bounds__(kRowThreads) row_op_kernel(const RowOpDev p) {
   }
   if (p.n_mix == 0) return;
 
-  float2 prev[kPairs];
-  __half2* shift2 = reinterpret_cast<__half2*>(p.shift + static_cast<size_t>(b) * p.C);
-  if (t == 0) {
-#pragma unroll
-    for (int i = 0; i < kPairs; ++i) prev[i] = owned(i) ? __half22float2(shift2[threadIdx.x + kRowThreads * i]) : make_float2(0.f, 0.f);
-  } else {
+  if (t != 0) {
     load_row<kPairs>(p, b, t - 1, prev);
-    ln_row<kPairs>(p, prev, scratch);
+    ln_row<kPairs>(p, prev, scratch, lw, lb, i_lo, i_hi);
   }
-  __half2 mixv[kPairs][6];
-#pragma unroll
-  for (int i = 0; i < kPairs; ++i)
-#pragma unroll
-    for (int m = 0; m < 6; ++m)
-      if (m < p.n_mix && owned(i)) mixv[i][m] = reinterpret_cast<const __half2*>(p.mix[m])[threadIdx.x + kRowThreads * i];
 #pragma unroll
   for (int i = 0; i < kPairs; ++i) {
     if (!owned(i)) continue;
@@ -174,7 +184,7 @@ __global__ void __launch_bounds__(kRowThreads) row_op_kernel(const RowOpDev p) {
     // only the CTAs of t == 0 touch shift[b]; each has consumed its old pairs above
     if (p.T > 1) {
       load_row<kPairs>(p, b, p.T - 1, cur);
-      ln_row<kPairs>(p, cur, scratch);
+      ln_row<kPairs>(p, cur, scratch, lw, lb, i_lo, i_hi);
     }
 #pragma unroll
     for (int i = 0; i < kPairs; ++i)

@@ -20,6 +20,8 @@ constexpr float kTwoNeg41 = 4.547473508864641e-13f;
 constexpr float kNegExpHalfLog2e = -0.8750387749145276f;
 constexpr float kNegLog2e = -1.4426950408889634f;
 
+__device__ int g_tmix_timeout = 0;  // set when the bounded wait for the weight rows gives up
+
 struct TmixDev {
   int C, H, layer0;
   int R[4];               // ranks of w, a, g, v
@@ -39,8 +41,8 @@ __global__ void __launch_bounds__(256) tmix_decode_kernel(const TmixDev p) {
   __shared__ float res[4][kHead];
   __shared__ __align__(16) half hv[8][kHead];  // r, d, k', a, b, v, g, y
   __shared__ float red[4];
+  __shared__ __align__(8) uint64_t wbar;
 
-  pdl_trigger();
   const int bh = blockIdx.x;
   const int b_id = bh / p.H;
   const int h = bh - b_id * p.H;
@@ -48,19 +50,30 @@ __global__ void __launch_bounds__(256) tmix_decode_kernel(const TmixDev p) {
   const size_t tok = static_cast<size_t>(b_id) * p.C + static_cast<size_t>(h) * kHead;
 
   // ---- requests that do not depend on the previous kernel: up-projection rows and the state
+  // Thread j owns up-projection row j (matrix j/64, channel j%64 of this head).  The rows are fetched
+  // by the bulk-copy engine, one request per row, into rows padded by 16 bytes so that the 32 lanes
+  // of a warp later read their own rows without bank conflicts.
   uint4* tile = reinterpret_cast<uint4*>(smem_raw);             // fp16 state tile, 8 KiB (unused for fp32)
-  half* wsm = reinterpret_cast<half*>(smem_raw + (kWkv32 ? 0 : 8192));
-  int seg_off[5];
-  seg_off[0] = 0;
-#pragma unroll
-  for (int s = 0; s < 4; ++s) seg_off[s + 1] = seg_off[s] + ((p.layer0 && s == 3) ? 0 : kHead * p.R[s]);
+  unsigned char* wsm = smem_raw + (kWkv32 ? 0 : 8192);
+  const int my_seg = tid >> 6, my_ch = tid & 63;
+  const bool has_row = !(p.layer0 && my_seg == 3);
+  int my_off = 0, total_bytes = 0;
 #pragma unroll
   for (int s = 0; s < 4; ++s) {
-    if (p.layer0 && s == 3) continue;
-    const half* src = p.up[s] + static_cast<size_t>(h) * kHead * p.R[s];
-    const int n16 = kHead * p.R[s] / 8;
-    for (int i = tid; i < n16; i += 256) cp_async16(wsm + seg_off[s] + i * 8, src + i * 8);
+    const int seg_bytes = (p.layer0 && s == 3) ? 0 : kHead * (p.R[s] * 2 + 16);
+    if (s < my_seg) my_off += seg_bytes;
+    if (!(p.layer0 && s == 3)) total_bytes += kHead * p.R[s] * 2;
   }
+  const int my_R = p.R[my_seg];
+  const unsigned char* my_row = wsm + my_off + my_ch * (my_R * 2 + 16);
+  if (tid == 0) {
+    mbar_init(smem_u32(&wbar), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    mbar_expect_tx(smem_u32(&wbar), total_bytes);
+  }
+  __syncthreads();
+  if (has_row)
+    bulk_g2s(smem_u32(my_row), p.up[my_seg] + (static_cast<size_t>(h) * kHead + my_ch) * my_R, my_R * 2, smem_u32(&wbar));
   float4 S32[4];
   if (kWkv32) {
     const float4* sb = reinterpret_cast<const float4*>(static_cast<float*>(p.state) + static_cast<size_t>(bh) * (kHead * kHead));
@@ -78,6 +91,7 @@ __global__ void __launch_bounds__(256) tmix_decode_kernel(const TmixDev p) {
   cp_async_commit();
 
   pdl_wait();
+  pdl_trigger();
   // ---- LoRA inputs with their activations, kept in fp32
 #pragma unroll
   for (int s = 0; s < 4; ++s) {
@@ -98,27 +112,26 @@ __global__ void __launch_bounds__(256) tmix_decode_kernel(const TmixDev p) {
   }
   cp_async_wait<0>();
   __syncthreads();
+  if (!mbar_wait(smem_u32(&wbar), 0)) {  // uniform: every thread waits on the same barrier
+    if (tid == 0) atomicExch(&g_tmix_timeout, 1);
+    return;
+  }
 
-  // ---- up-projections: 4 x 64 dot products, one per warp iteration, rows interleaved over warps
-  for (int j = warp; j < 4 * kHead; j += 8) {
-    const int s = j >> 6, ch = j & 63;
-    if (p.layer0 && s == 3) continue;
-    const int R = p.R[s];
-    const half* wrow = wsm + seg_off[s] + ch * R;
-    const float* xa = acts + s * 512;
+  // ---- up-projections: thread j computes the dot product of its row with the activated LoRA input
+  if (has_row) {
+    const float* xa = acts + my_seg * 512;
     float acc = 0.f;
-    for (int c = lane * 8; c < R; c += 256) {
-      const uint4 q = *reinterpret_cast<const uint4*>(wrow + c);
-      const uint32_t u[4] = {q.x, q.y, q.z, q.w};
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const float2 f = h2f2(u[e]);
-        acc = fmaf(xa[c + 2 * e], f.x, acc);
-        acc = fmaf(xa[c + 2 * e + 1], f.y, acc);
-      }
+    for (int c = 0; c < my_R; c += 8) {
+      const uint4 q = *reinterpret_cast<const uint4*>(my_row + c * 2);
+      const float4 x0 = *reinterpret_cast<const float4*>(xa + c);
+      const float4 x1 = *reinterpret_cast<const float4*>(xa + c + 4);
+      const float2 f0 = h2f2(q.x), f1 = h2f2(q.y), f2 = h2f2(q.z), f3 = h2f2(q.w);
+      acc = fmaf(x0.x, f0.x, acc); acc = fmaf(x0.y, f0.y, acc);
+      acc = fmaf(x0.z, f1.x, acc); acc = fmaf(x0.w, f1.y, acc);
+      acc = fmaf(x1.x, f2.x, acc); acc = fmaf(x1.y, f2.y, acc);
+      acc = fmaf(x1.z, f3.x, acc); acc = fmaf(x1.w, f3.y, acc);
     }
-    acc = warp_sum(acc);
-    if (lane == 0) res[s][ch] = acc;
+    res[my_seg][my_ch] = acc;
   }
   __syncthreads();
 
@@ -283,7 +296,7 @@ __global__ void __launch_bounds__(256) tmix_decode_kernel(const TmixDev p) {
 
 bool tmix_decode_supported(const TmixDecodeArgs& a) {
   const int sum_r = a.R[0] + a.R[1] + a.R[2] + (a.layer0 ? 0 : a.R[3]);
-  const size_t smem = static_cast<size_t>(kHead) * sum_r * 2 + (a.wkv32 ? 0 : 8192);
+  const size_t smem = static_cast<size_t>(kHead) * (sum_r * 2 + 64) + (a.wkv32 ? 0 : 8192);
   for (int s = 0; s < 4; ++s)
     if (a.R[s] > 512 || a.R[s] % 8 != 0) return false;
   return smem <= 200 * 1024;
@@ -300,7 +313,7 @@ int tmix_decode(cudaStream_t stream, const TmixDecodeArgs& a) {
   p.w0 = a.w0; p.a0 = a.a0; p.v0 = a.v0; p.k_k = a.k_k; p.k_a = a.k_a; p.r_k = a.r_k; p.lnx_w = a.lnx_w; p.lnx_b = a.lnx_b;
   p.state = a.state; p.elapsed = a.elapsed; p.y2 = a.y2;
   const int sum_r = a.R[0] + a.R[1] + a.R[2] + (a.layer0 ? 0 : a.R[3]);
-  const size_t smem = static_cast<size_t>(kHead) * sum_r * 2 + (a.wkv32 ? 0 : 8192);
+  const size_t smem = static_cast<size_t>(kHead) * (sum_r * 2 + 64) + (a.wkv32 ? 0 : 8192);
   const dim3 grid(a.B * p.H), block(256);
   if (a.wkv32) {
     if (smem > 48 * 1024) RK_CUDA(cudaFuncSetAttribute(tmix_decode_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));

@@ -62,3 +62,16 @@ def test_missing_library_fails_loudly(monkeypatch, tmp_path):
     monkeypatch.setattr(L, "_HERE", str(tmp_path))
     with pytest.raises(ImportError, match="no CPU fallback"):
         L.load_library()
+
+
+def test_adapter_compiles_against_the_unmodified_reference_headers():
+    """The C++ IModelBackend adapter must build against the reference's own headers (drop-in proof)."""
+    import shutil
+    import subprocess
+    ref = "/root/reference/include"
+    if not os.path.isdir(ref) or shutil.which("g++") is None:
+        pytest.skip("reference tree or g++ not present")
+    cmd = ["g++", "-std=c++17", "-fsyntax-only", "-I" + ref, "-I/usr/local/cuda/include", "-I" + os.path.join(ROOT, "include"),
+           os.path.join(ROOT, "rwkv_lightning_cuda_b200", "adapter", "b200_model_backend.cpp")]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    assert res.returncode == 0, res.stderr

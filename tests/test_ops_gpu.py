@@ -125,12 +125,13 @@ def test_head_gates(ops, rows, H):
     assert (host(ops.relu_square(dev(y))) == h16(np.maximum(y.astype(np.float32), 0) ** 2)).all()
 
 
-@pytest.mark.parametrize("M,K,N", [(1, 768, 768), (2, 2560, 96), (4, 64, 768), (3, 4096, 130), (1, 3072, 768), (6, 256, 64)])
+@pytest.mark.parametrize("M,K,N", [(1, 768, 768), (2, 2560, 96), (4, 64, 768), (3, 4096, 130), (1, 3072, 768), (6, 256, 64),
+                                   (128, 768, 768), (300, 1024, 640), (17, 96, 96), (256, 4096, 256)])
 def test_linear_fp16(ops, M, K, N):
     from rwkv_lightning_cuda_b200 import lib as L
     rng = np.random.default_rng(M * 7 + N)
     x = h16(rng.standard_normal((M, K))); W = h16(rng.standard_normal((N, K)) * 0.02)
-    assert_close16(host(ops.linear_f16_orig(dev(x), dev(W))), orc.linear_orig(x, W), max_ulp=1, what="linear")
+    assert_close16(host(ops.linear_f16_orig(dev(x), dev(W))), orc.linear_orig(x, W), max_ulp=1 if M <= 4 else 2, what="linear")
     assert_close16(host(ops.linear_f16_orig(dev(x), dev(W), epilogue=L.EPI_RELU2)), orc.linear_orig(x, W, epi=orc.EPI_RELU2), max_ulp=2, what="linear relu2")
     for act in (L.ACT_TANH, L.ACT_SIGMOID):
         assert_close16(host(ops.linear_f16_orig(dev(x), dev(W), in_act=act)), orc.linear_orig(x, W, in_act=act), max_ulp=2, min_exact=0.9, what="linear act")
