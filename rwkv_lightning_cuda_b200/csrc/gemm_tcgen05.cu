@@ -14,9 +14,7 @@
 // reaches its final barrier, frees its tensor memory and returns.
 #include <cuda.h>
 
-#include <map>
-#include <mutex>
-#include <tuple>
+#include <algorithm>
 
 #include "common.cuh"
 #include "kernels.h"
@@ -32,6 +30,8 @@ __device__ int g_gemm_timeout = 0;
 
 struct GemmDev {
   int M, N, K, Nt, stages, epi;
+  int splits, kb_per_split;  // split-K: grid.z CTAs share an output tile, kb_per_split K blocks each
+  float* partial;            // [splits, M, N] fp32 partial sums (scratch), used when splits > 1
   void* y;
   const half* scale;    // optional per-output-channel factor applied to the accumulator
   const half* v;        // kEpiVres
@@ -75,6 +75,23 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
       : "r"(taddr));
 }
 
+// Applies the epilogue to one fp32 result: the layer's single rounding to half.
+__device__ __forceinline__ void emit(const GemmDev& p, int m, int n, float a) {
+  const size_t o = static_cast<size_t>(m) * p.N + n;
+  if (p.epi == kEpiF32) {
+    static_cast<float*>(p.y)[o] = __half2float(__float2half_rn(a));
+  } else if (p.epi == kEpiRelu2) {
+    const float t = fmaxf(__half2float(__float2half_rn(a)), 0.f);
+    static_cast<half*>(p.y)[o] = __float2half_rn(t * t);
+  } else if (p.epi == kEpiVres) {
+    const float vv = __half2float(p.v[o]);
+    const float gate = 1.0f / (1.0f + expf(-(__half2float(p.v0[n]) + a)));
+    static_cast<half*>(p.y)[o] = __float2half_rn(vv + (__half2float(p.v_first[o]) - vv) * gate);
+  } else {
+    static_cast<half*>(p.y)[o] = __float2half_rn(a);
+  }
+}
+
 __global__ void __launch_bounds__(kThreads) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,
                                                            const __grid_constant__ CUtensorMap map_x, const GemmDev p) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -84,7 +101,9 @@ __global__ void __launch_bounds__(kThreads) gemm_tc_kernel(const __grid_constant
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * kBM, m0 = blockIdx.y * p.Nt;
-  const int kblocks = (p.K + kBK - 1) / kBK;
+  const int kb_total = (p.K + kBK - 1) / kBK;
+  const int kb_begin = blockIdx.z * p.kb_per_split;
+  const int kblocks = min(kb_total - kb_begin, p.kb_per_split);  // >= 1 by construction of the grid
   const uint32_t stage_bytes = kBM * 128 + p.Nt * 128;
   // the dynamic window is 1024-byte aligned by the launch (required by the 128-byte swizzle)
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -121,8 +140,8 @@ __global__ void __launch_bounds__(kThreads) gemm_tc_kernel(const __grid_constant
         const uint32_t bar = smem_u32(&full_bar[s]);
         const uint32_t a = smem_base + s * stage_bytes;
         mbar_expect_tx(bar, stage_bytes);
-        tma_load_2d(a, &map_w, bar, kb * kBK, n0);
-        tma_load_2d(a + kBM * 128, &map_x, bar, kb * kBK, m0);
+        tma_load_2d(a, &map_w, bar, (kb_begin + kb) * kBK, n0);
+        tma_load_2d(a + kBM * 128, &map_x, bar, (kb_begin + kb) * kBK, m0);
       }
     }
   } else if (warp == 1) {
@@ -163,20 +182,8 @@ __global__ void __launch_bounds__(kThreads) gemm_tc_kernel(const __grid_constant
           for (int j = 0; j < 16; ++j) {
             const int m = m0 + c0 + j;
             if (m >= p.M) break;
-            const float a = __uint_as_float(r[j]) * sc;
-            const size_t o = static_cast<size_t>(m) * p.N + n;
-            if (p.epi == kEpiF32) {
-              static_cast<float*>(p.y)[o] = __half2float(__float2half_rn(a));
-            } else if (p.epi == kEpiRelu2) {
-              const float t = fmaxf(__half2float(__float2half_rn(a)), 0.f);
-              static_cast<half*>(p.y)[o] = __float2half_rn(t * t);
-            } else if (p.epi == kEpiVres) {
-              const float vv = __half2float(p.v[o]);
-              const float gate = 1.0f / (1.0f + expf(-(__half2float(p.v0[n]) + a)));
-              static_cast<half*>(p.y)[o] = __float2half_rn(vv + (__half2float(p.v_first[o]) - vv) * gate);
-            } else {
-              static_cast<half*>(p.y)[o] = __float2half_rn(a);
-            }
+            if (p.splits == 1) emit(p, m, n, __uint_as_float(r[j]) * sc);
+            else p.partial[(static_cast<size_t>(blockIdx.z) * p.M + m) * p.N + n] = __uint_as_float(r[j]);
           }
         }
       }
@@ -190,6 +197,27 @@ __global__ void __launch_bounds__(kThreads) gemm_tc_kernel(const __grid_constant
   if (warp == 1) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"(tmem_cols) : "memory");
   }
+}
+
+// Second pass of a split-K GEMM: adds the fp32 partial sums in split order (the result does not
+// depend on which CTA finished first) and applies the epilogue.  One thread per four output channels.
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(const GemmDev p) {
+  pdl_wait();
+  pdl_trigger();
+  const int n4 = p.N >> 2;
+  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= static_cast<long long>(p.M) * n4) return;
+  const int m = static_cast<int>(i / n4), n = static_cast<int>(i - static_cast<long long>(m) * n4) * 4;
+  const size_t plane = static_cast<size_t>(p.M) * p.N;
+  const float* src = p.partial + static_cast<size_t>(m) * p.N + n;
+  float4 acc = __ldcg(reinterpret_cast<const float4*>(src));
+  for (int z = 1; z < p.splits; ++z) {
+    const float4 t = __ldcg(reinterpret_cast<const float4*>(src + z * plane));
+    acc.x += t.x; acc.y += t.y; acc.z += t.z; acc.w += t.w;
+  }
+  const float v[4] = {acc.x, acc.y, acc.z, acc.w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) emit(p, m, n + j, v[j] * (p.scale ? __half2float(p.scale[n + j]) : 1.0f));
 }
 
 }  // namespace
@@ -258,9 +286,29 @@ int gemm_tc(cudaStream_t stream, const LinearArgs& a) {
   s = make_map(&map_x, a.x, a.M, a.K, ldx, p.Nt);
   if (s != kOk) return s;
   RK_CUDA(cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 201 * 1024 + 1024));
-  const dim3 grid((a.N + kBM - 1) / kBM, (a.M + p.Nt - 1) / p.Nt), block(kThreads);
+  // Split K over grid.z until the grid covers the SMs: a tile of 128 output channels per CTA alone
+  // leaves most of them idle for the narrow layers (C x C projections, LoRA).  Needs scratch for the
+  // fp32 partial sums (a second small kernel adds them in split order); without it the kernel runs unsplit.
+  const int tiles = ((a.N + kBM - 1) / kBM) * ((a.M + p.Nt - 1) / p.Nt);
+  const int kb_total = (a.K + kBK - 1) / kBK;
+  int splits = 1;
+  if (a.scratch && tiles < 120 && a.N % 4 == 0) {
+    splits = std::min({(148 + tiles - 1) / tiles, std::max(1, kb_total / 2), 32});
+    const size_t per_split = static_cast<size_t>(a.M) * a.N * sizeof(float);
+    splits = static_cast<int>(std::min<size_t>(splits, a.scratch_bytes / per_split));
+    splits = std::max(splits, 1);
+  }
+  p.kb_per_split = (kb_total + splits - 1) / splits;
+  p.splits = (kb_total + p.kb_per_split - 1) / p.kb_per_split;  // no empty split
+  p.partial = a.scratch;
+  const dim3 grid((a.N + kBM - 1) / kBM, (a.M + p.Nt - 1) / p.Nt, p.splits), block(kThreads);
   RK_CUDA(launch_pdl(gemm_tc_kernel, grid, block, smem, stream, map_w, map_x, p));
   RK_LAUNCH_CHECK("gemm_tc launch");
+  if (p.splits > 1) {
+    const long long work = static_cast<long long>(a.M) * (a.N / 4);
+    RK_CUDA(launch_pdl(splitk_reduce_kernel, dim3(static_cast<unsigned>((work + 255) / 256)), dim3(256), 0, stream, p));
+    RK_LAUNCH_CHECK("splitk_reduce launch");
+  }
   return kOk;
 }
 

@@ -53,6 +53,7 @@ int tmix_vres_gate(cudaStream_t stream, int rows, int C, const half* v, const ha
                    const half* v12, half* out);
 int advance_i32(cudaStream_t stream, int* x, int amount, int n);
 int relu_square(cudaStream_t stream, const half* x, half* out, long long n);
+int activate(cudaStream_t stream, const half* x, half* out, long long n, int act);  // half(tanh(x)) / half(sigmoid(x))
 int bf16_to_f16(cudaStream_t stream, const uint16_t* src, half* dst, long long n);
 int transpose_f16(cudaStream_t stream, const half* src, half* dst, int rows, int cols);
 int emb_ln0(cudaStream_t stream, int V, int C, const void* emb, const void* w, const void* b, int src_is_bf16,
@@ -71,6 +72,10 @@ struct LinearArgs {
   int epi = kEpiNone;
   EpiArgs ea;
   void* y = nullptr;         // half [M,N], or float [M,N] for kEpiF32
+  // optional scratch for the tensor-core path's split-K (rows > 4): fp32 partial sums [splits, M, N];
+  // calls sharing it must not overlap on the GPU
+  float* scratch = nullptr;
+  size_t scratch_bytes = 0;
 };
 int linear(cudaStream_t stream, const LinearArgs& args);
 // Up to 8 independent problems sharing M <= 4 in a single launch.

@@ -325,6 +325,10 @@ Workspace* Model::workspace(int B, int T) {
   for (int i = 0; i < 4; ++i) ws->l1[i] = take(rows * 512);
   ws->xf = take(static_cast<size_t>(B) * C);
   ws->tokens = reinterpret_cast<int64_t*>(take(rows * 4 + 8));
+  if (rows > 4) {
+    const size_t want = std::min<size_t>(static_cast<size_t>(256) << 20, rows * C * sizeof(float) * 8);
+    if (ws->gemm_scratch.alloc(want) != kOk) return nullptr;
+  }
   for (int i = 0; i < Workspace::kSlots; ++i) {
     if (cudaMallocHost(&ws->tokens_pinned[i], rows * sizeof(int64_t)) != cudaSuccess) return nullptr;
     if (cudaEventCreateWithFlags(&ws->tokens_copied[i], cudaEventDisableTiming) != cudaSuccess) return nullptr;
@@ -338,6 +342,7 @@ int Model::lin(cudaStream_t s, int M, const Matrix& W, const half* x, void* y, i
   LinearArgs a;
   a.M = M; a.K = W.K; a.N = W.N; a.x = x; a.w = W.w.p; a.fmt = W.fmt;
   a.scale = W.scale.as<half>(); a.zero = W.zero.as<half>(); a.epi = epi; a.y = y;
+  if (cur_) { a.scratch = cur_->gemm_scratch.as<float>(); a.scratch_bytes = cur_->gemm_scratch.bytes; }
   return linear(s, a);
 }
 
@@ -345,6 +350,7 @@ int Model::lin16(cudaStream_t s, int M, int K, int N, const half* x, const half*
                  const EpiArgs& ea) {
   LinearArgs a;
   a.M = M; a.K = K; a.N = N; a.x = x; a.w = w; a.fmt = RWKV7_B200_FMT_F16; a.in_act = in_act; a.epi = epi; a.ea = ea; a.y = y;
+  if (cur_) { a.scratch = cur_->gemm_scratch.as<float>(); a.scratch_bytes = cur_->gemm_scratch.bytes; }
   return linear(s, a);
 }
 
@@ -357,6 +363,7 @@ int Model::lin16(cudaStream_t s, int M, int K, int N, const half* x, const half*
 int Model::enqueue(Workspace& ws, int B, int T, half* shift, void* wkv, int* elapsed, float* logits, cudaStream_t st) {
   const int C = cfg_.channels, L = cfg_.layers, rows = B * T;
   const EpiArgs none;
+  cur_ = &ws;
   {
     RowOpArgs a;
     a.B = B; a.T = T; a.C = C; a.tokens = ws.tokens; a.table = emb_ln0_.as<half>(); a.vocab = cfg_.vocab;
@@ -408,15 +415,25 @@ int Model::enqueue(Workspace& ws, int B, int T, half* shift, void* wkv, int* ela
       RK_TRY(lin16(st, rows, C, cfg_.rank_w, xw, W.w1t.as<half>(), ws.l1[0], kActNone, kEpiNone, none));
       RK_TRY(lin16(st, rows, C, cfg_.rank_a, xa, W.a1t.as<half>(), ws.l1[1], kActNone, kEpiNone, none));
       RK_TRY(lin16(st, rows, C, cfg_.rank_g, xg, W.g1t.as<half>(), ws.l1[2], kActNone, kEpiNone, none));
-      RK_TRY(lin16(st, rows, cfg_.rank_w, C, ws.l1[0], W.w2t.as<half>(), ws.w12, kActTanh, kEpiNone, none));
+      const bool big = rows > 4;  // the reference rounds tanh/sigmoid and the v LoRA output to half for larger row counts
+      if (big) {
+        RK_TRY(activate(st, ws.l1[0], ws.l1[0], static_cast<long long>(rows) * cfg_.rank_w, kActTanh));
+        RK_TRY(activate(st, ws.l1[2], ws.l1[2], static_cast<long long>(rows) * cfg_.rank_g, kActSigmoid));
+      }
+      RK_TRY(lin16(st, rows, cfg_.rank_w, C, ws.l1[0], W.w2t.as<half>(), ws.w12, big ? kActNone : kActTanh, kEpiNone, none));
       RK_TRY(lin16(st, rows, cfg_.rank_a, C, ws.l1[1], W.a2t.as<half>(), ws.a12, kActNone, kEpiNone, none));
-      RK_TRY(lin16(st, rows, cfg_.rank_g, C, ws.l1[2], W.g2t.as<half>(), ws.g, kActSigmoid, kEpiNone, none));
+      RK_TRY(lin16(st, rows, cfg_.rank_g, C, ws.l1[2], W.g2t.as<half>(), ws.g, big ? kActNone : kActSigmoid, kEpiNone, none));
       const half* v_use = ws.vfirst;
       if (li > 0) {
         RK_TRY(lin16(st, rows, C, cfg_.rank_v, xv, W.v1t.as<half>(), ws.l1[3], kActNone, kEpiNone, none));
-        EpiArgs ea;
-        ea.v = ws.v; ea.v_first = ws.vfirst; ea.v0 = W.v0.as<half>();
-        RK_TRY(lin16(st, rows, cfg_.rank_v, C, ws.l1[3], W.v2t.as<half>(), ws.vout, kActNone, kEpiVres, ea));
+        if (big) {
+          RK_TRY(lin16(st, rows, cfg_.rank_v, C, ws.l1[3], W.v2t.as<half>(), ws.y, kActNone, kEpiNone, none));
+          RK_TRY(tmix_vres_gate(st, rows, C, ws.v, ws.vfirst, W.v0.as<half>(), ws.y, ws.vout));
+        } else {
+          EpiArgs ea;
+          ea.v = ws.v; ea.v_first = ws.vfirst; ea.v0 = W.v0.as<half>();
+          RK_TRY(lin16(st, rows, cfg_.rank_v, C, ws.l1[3], W.v2t.as<half>(), ws.vout, kActNone, kEpiVres, ea));
+        }
         v_use = ws.vout;
       }
       RK_TRY(tmix_kk_a_gate(st, rows, C, ws.k, W.k_k.as<half>(), W.a0.as<half>(), ws.a12, W.k_a.as<half>(), ws.k2, ws.nkk, ws.kka));

@@ -55,6 +55,7 @@ struct Workspace {
   half *xA, *xB, *xm[6], *r, *k, *v, *vfirst, *vout, *w12, *a12, *g, *k2, *nkk, *kka, *y, *y2, *att, *mixed, *ffn;
   half *hid, *l1[4], *xf;
   int64_t* tokens;
+  DevBuf gemm_scratch;  // split-K partial sums of the tensor-core GEMM (rows > 4)
   // ring of pinned host staging slots for the token ids; a slot is reused only after the copy
   // that read it has completed, so callers may overwrite their token array as soon as forward returns
   static constexpr int kSlots = 4;
@@ -124,7 +125,7 @@ class Model {
   std::map<GraphKey, GraphEntry> graphs_;
   unsigned long long tick_ = 0;
   long long launches_ = 0;
-  long long counting_ = 0;  // launches counted while enqueueing
+  Workspace* cur_ = nullptr;  // workspace of the forward being enqueued (guarded by mu_)
 };
 
 }  // namespace rk

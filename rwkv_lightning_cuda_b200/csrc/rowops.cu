@@ -268,6 +268,13 @@ __global__ void advance_i32_kernel(int* x, int amount, int n) {
   if (i < n) x[i] += amount;
 }
 
+// out = half(act(x)): the rounded tanh / sigmoid of a LoRA intermediate that the reference materialises
+// for more than four rows (act_tanh_kernel / act_sigmoid_kernel, cuda/rwkv7_fast_ops_fp16.cu:437-470).
+__global__ void act_kernel(const half* __restrict__ x, half* __restrict__ out, long long n, int act) {
+  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i < n) out[i] = __float2half_rn(apply_in_act(__half2float(x[i]), act));
+}
+
 __global__ void relu_square_kernel(const half* __restrict__ x, half* __restrict__ out, long long n) {
   const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (i >= n) return;
@@ -396,6 +403,13 @@ int advance_i32(cudaStream_t stream, int* x, int amount, int n) {
   RK_REQUIRE(x && n > 0, kBadArg, "advance_i32: bad argument");
   advance_i32_kernel<<<(n + 255) / 256, 256, 0, stream>>>(x, amount, n);
   RK_LAUNCH_CHECK("advance_i32 launch");
+  return kOk;
+}
+
+int activate(cudaStream_t stream, const half* x, half* out, long long n, int act) {
+  RK_REQUIRE(x && out && n > 0 && (act == kActTanh || act == kActSigmoid), kBadArg, "activate: bad argument");
+  act_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, stream>>>(x, out, n, act);
+  RK_LAUNCH_CHECK("activate launch");
   return kOk;
 }
 

@@ -42,7 +42,7 @@ def run_both(d, om, gm, wkv32, B, chunks, n_decode, seed=1):
     worst = 0.0
     for T in chunks:
         toks = rng.integers(0, d.vocab, (B, T))
-        want = om.forward(toks, shift, wkv, elapsed)
+        want = om.forward(toks, shift, wkv, elapsed, lora_round_act=int(B * T > 4))
         gm.forward_prefill(toks.tolist(), st, lg)
         got = lg.values.cpu().numpy()
         worst = max(worst, np.abs(got - want).max() / (np.abs(want).max() if wkv32 else 1.0))
@@ -50,7 +50,7 @@ def run_both(d, om, gm, wkv32, B, chunks, n_decode, seed=1):
     agree = []
     for _ in range(n_decode):
         agree.append((ids_o == ids_g).all())
-        want = om.forward(ids_o[:, None], shift, wkv, elapsed)
+        want = om.forward(ids_o[:, None], shift, wkv, elapsed, lora_round_act=int(B > 4))
         gm.forward_decode(ids_o.tolist(), st, lg)
         got = lg.values.cpu().numpy()
         worst = max(worst, np.abs(got - want).max() / (np.abs(want).max() if wkv32 else 1.0))
