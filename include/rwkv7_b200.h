@@ -201,6 +201,18 @@ int rwkv7_b200_advance_i32(void* stream, int* x, int amount, long long elems);
  * (src/rwkv7_fast_v4.cu:1321-1342). */
 int rwkv7_b200_linear_f16_orig(void* stream, int M, int K, int N, const uint16_t* x, const uint16_t* weight,
                                int in_act, int epilogue, void* y);
+/* No counterpart in the reference.  The same layer as rwkv7_b200_linear_f16_orig for M > 4 rows, for host
+ * programs that cannot allocate device memory around the call -- for instance a serving loop that runs under a
+ * fixed memory budget and has closed its allocator once the model is resident, or a plugin host that forbids
+ * cudaMalloc inside its callbacks.  The tensor-core kernel splits K over several CTAs and needs room for fp32 partial sums; this variant
+ * keeps that room in a fixed 16 MiB device array inside the library image (held by every GPU that loads the
+ * library until the process exits) and calls no cudaMalloc/cudaFree or allocating library routine.
+ * Limits: M > 4, N % 4 == 0, M*N <= 2,097,152 (SHAPE otherwise).  The first call on a device looks the array's
+ * device address up (cudaGetSymbolAddress) and should therefore be made before any stream capture.  All calls
+ * share the array: nothing in it has to be cleared (every partial sum that is read is written by the same call), but
+ * two calls whose kernels overlap on the GPU (different streams) race on it. */
+int rwkv7_b200_linear_f16_orig_static(void* stream, int M, int K, int N, const uint16_t* x, const uint16_t* weight,
+                                      int epilogue, void* y);
 /* No counterpart in the reference (it has no quantised weights): the same layer on W8A16 / W4A16
  * weights in the formats written down in oracle/rwkv7_oracle.c and csrc/quant.cu. */
 int rwkv7_b200_linear_w8a16(void* stream, int M, int K, int N, const uint16_t* x, const int8_t* q,

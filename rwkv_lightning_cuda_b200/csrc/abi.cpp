@@ -9,6 +9,7 @@
 
 namespace rk {
 const char* last_error();
+int gemm_tc_static_scratch(cudaStream_t stream, const LinearArgs& a);
 }
 
 using rk::kBadArg;
@@ -219,6 +220,15 @@ static int linear_common(void* stream, int M, int K, int N, const uint16_t* x, c
 int rwkv7_b200_linear_f16_orig(void* stream, int M, int K, int N, const uint16_t* x, const uint16_t* weight, int in_act,
                                int epilogue, void* y) {
   return linear_common(stream, M, K, N, x, weight, RWKV7_B200_FMT_F16, nullptr, nullptr, in_act, epilogue, y);
+}
+int rwkv7_b200_linear_f16_orig_static(void* stream, int M, int K, int N, const uint16_t* x, const uint16_t* weight,
+                                      int epilogue, void* y) {
+  RK_REQUIRE(epilogue == RWKV7_B200_EPI_NONE || epilogue == RWKV7_B200_EPI_RELU2 || epilogue == RWKV7_B200_EPI_F32, kBadArg,
+             "linear: unknown epilogue %d", epilogue);
+  RK_REQUIRE(M > 0 && K > 0 && N > 0 && x && weight && y, kBadArg, "linear (static scratch): bad argument");
+  rk::LinearArgs a;
+  a.M = M; a.K = K; a.N = N; a.x = h(x); a.w = weight; a.fmt = RWKV7_B200_FMT_F16; a.epi = epilogue; a.y = y;
+  return rk::gemm_tc_static_scratch(st(stream), a);
 }
 int rwkv7_b200_linear_w8a16(void* stream, int M, int K, int N, const uint16_t* x, const int8_t* q, const uint16_t* scale,
                             int epilogue, void* y) {

@@ -15,6 +15,7 @@
 #include <cuda.h>
 
 #include <algorithm>
+#include <mutex>
 
 #include "common.cuh"
 #include "kernels.h"
@@ -310,6 +311,43 @@ int gemm_tc(cudaStream_t stream, const LinearArgs& a) {
     RK_LAUNCH_CHECK("splitk_reduce launch");
   }
   return kOk;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Split-K GEMM for callers that must not allocate: the fp32 partial sums go to a fixed device array
+// that is part of the loaded library image (every GPU that loads the library holds these 16 MiB
+// until the process exits).
+constexpr size_t kStaticScratchFloats = static_cast<size_t>(4) << 20;  // 16 MiB
+static __device__ __align__(256) float g_static_scratch[kStaticScratchFloats];
+
+int gemm_tc_static_scratch(cudaStream_t stream, const LinearArgs& a) {
+  RK_REQUIRE(gemm_tc_supported(a), kShape, "linear (static scratch): needs more than 4 rows, fp16 weights, K %% 8 == 0");
+  RK_REQUIRE(a.N % 4 == 0, kShape, "linear (static scratch): N must be a multiple of 4");
+  // at least two K splits must fit: 2 * M * N floats
+  RK_REQUIRE(static_cast<size_t>(a.M) * a.N * 2 <= kStaticScratchFloats, kShape,
+             "linear (static scratch): M*N = %lld exceeds the built-in scratch (max %lld elements)",
+             static_cast<long long>(a.M) * a.N, static_cast<long long>(kStaticScratchFloats / 2));
+  // In host code the array's name is only a stand-in; the device address is looked up once per device
+  // (with that device current, as it is here) and cached.
+  static float* dev_ptr[64] = {nullptr};
+  static std::mutex mu;
+  int dev = 0;
+  RK_CUDA(cudaGetDevice(&dev));
+  RK_REQUIRE(dev >= 0 && dev < 64, kBadArg, "linear (static scratch): device ordinal out of range");
+  float* ptr;
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (!dev_ptr[dev]) {
+      void* p = nullptr;
+      RK_CUDA(cudaGetSymbolAddress(&p, g_static_scratch));
+      dev_ptr[dev] = static_cast<float*>(p);
+    }
+    ptr = dev_ptr[dev];
+  }
+  LinearArgs b = a;
+  b.scratch = ptr;
+  b.scratch_bytes = kStaticScratchFloats * sizeof(float);
+  return gemm_tc(stream, b);
 }
 
 int gemm_timeout_flag() {

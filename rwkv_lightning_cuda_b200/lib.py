@@ -69,6 +69,7 @@ SIGNATURES = {
     "rwkv7_b200_relu_square": [_vp, _vp, _vp, _ll],
     "rwkv7_b200_advance_i32": [_vp, _vp, _i, _ll],
     "rwkv7_b200_linear_f16_orig": [_vp, _i, _i, _i, _vp, _vp, _i, _i, _vp],
+    "rwkv7_b200_linear_f16_orig_static": [_vp, _i, _i, _i, _vp, _vp, _i, _vp],
     "rwkv7_b200_linear_w8a16": [_vp, _i, _i, _i, _vp, _vp, _vp, _i, _vp],
     "rwkv7_b200_linear_w4a16": [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _vp],
     "rwkv7_b200_quant_pack_w8": [_vp, _i, _i, _vp, _vp, _vp],

@@ -134,6 +134,15 @@ def linear_f16_orig(x, weight, in_act=L.ACT_NONE, epilogue=L.EPI_NONE):
     return y
 
 
+def linear_f16_orig_static(x, weight, epilogue=L.EPI_NONE, out=None):
+    """linear_f16_orig for more than four rows through the entry point that allocates nothing itself
+    (its split-K scratch is a fixed device array inside the library).  Pass `out` to avoid the
+    allocation of the result tensor as well."""
+    y = _out(x, weight.shape[0], epilogue) if out is None else out
+    L.check(L.load_library().rwkv7_b200_linear_f16_orig_static(_s(), x.shape[0], x.shape[1], weight.shape[0], _p(x), _p(weight), epilogue, _p(y)))
+    return y
+
+
 def linear_w8a16(x, q, scale, epilogue=L.EPI_NONE):
     y = _out(x, q.shape[0], epilogue)
     L.check(L.load_library().rwkv7_b200_linear_w8a16(_s(), x.shape[0], x.shape[1], q.shape[0], _p(x), _p(q), _p(scale), epilogue, _p(y)))
