@@ -20,6 +20,24 @@ struct GemvSeg {
   int ldx, N, K, fmt, in_act, epi;
   int cta_begin, rows_per_cta;  // CTAs [cta_begin, ...) own rows_per_cta consecutive output rows each
   int parts, piece_bytes;       // bulk-copy path: a weight row is fetched as `parts` pieces
+  // Optional fused prologue for decode rows (one token per sequence, K == channels): the activations
+  // are x' = half(n + (shift - n) * mix) with n = half(LayerNorm(x + res)), computed by every CTA from
+  // the residual stream instead of being read from memory.  The first CTA of the problem also stores
+  // half(x + res) to x_out and n to n_out (a later kernel moves n_out into the shift state, which all
+  // CTAs of this kernel are still reading).
+  const half* res;
+  const half* ln_w;
+  const half* ln_b;
+  const half* shift;
+  const half* mix;
+  half* x_out;
+  half* n_out;
+  float eps;
+  // Optional small copy done by the first CTA after the dependency wait (moves a previous kernel's
+  // n_out into the shift state).
+  const half* copy_src;
+  half* copy_dst;
+  int copy_n;
 };
 
 struct GemvBatch {
@@ -64,6 +82,89 @@ __device__ __forceinline__ void stage_activations(const GemvSeg& sg, half* xs16,
       }
     } else {
       *reinterpret_cast<uint4*>(xs16 + static_cast<size_t>(m) * sg.K + kv * 8) = q;
+    }
+  }
+}
+// Fused prologue (see GemvSeg): residual add + LayerNorm + token shift for kM decode rows, result as
+// fp32 in xs [kM, K].  Rounding points as in the separate row kernel: half(x + res), half(LN), half(mix).
+// A thread owns the channel pairs q = tid + kThreads*i, i < kLnPairs (K <= 2*kThreads*kLnPairs); the
+// LayerNorm weights, the mix coefficients and the first row's shift values are requested before the
+// dependency wait (LnPrefetch), the row itself stays in registers between the passes.
+constexpr int kLnPairs = 8;
+
+struct LnPrefetch {
+  __half2 w[kLnPairs], b[kLnPairs], mix[kLnPairs], shift0[kLnPairs];
+};
+
+template <int kThreads>
+__device__ __forceinline__ void ln_prefetch(const GemvSeg& sg, LnPrefetch& pf) {
+  const int pairs = sg.K >> 1;
+#pragma unroll
+  for (int i = 0; i < kLnPairs; ++i) {
+    const int q = threadIdx.x + kThreads * i;
+    if (q < pairs) {
+      pf.w[i] = reinterpret_cast<const __half2*>(sg.ln_w)[q];
+      pf.b[i] = reinterpret_cast<const __half2*>(sg.ln_b)[q];
+      if (sg.mix) {
+        pf.mix[i] = reinterpret_cast<const __half2*>(sg.mix)[q];
+        pf.shift0[i] = reinterpret_cast<const __half2*>(sg.shift)[q];  // written one step ago
+      }
+    }
+  }
+}
+
+template <int kM, int kThreads>
+__device__ __forceinline__ void stage_ln_mix(const GemvSeg& sg, float* xs, float* scratch, bool writer, const LnPrefetch& pf) {
+  const int K = sg.K, pairs = K >> 1;
+#pragma unroll
+  for (int m = 0; m < kM; ++m) {
+    const __half2* xg = reinterpret_cast<const __half2*>(sg.x + static_cast<size_t>(m) * sg.ldx);
+    const __half2* rg = sg.res ? reinterpret_cast<const __half2*>(sg.res + static_cast<size_t>(m) * K) : nullptr;
+    __half2 xv[kLnPairs], rv[kLnPairs], sh[kLnPairs];
+#pragma unroll
+    for (int i = 0; i < kLnPairs; ++i) {
+      const int q = threadIdx.x + kThreads * i;
+      const bool ok = q < pairs;
+      xv[i] = ok ? xg[q] : __floats2half2_rn(0.f, 0.f);
+      rv[i] = (ok && rg) ? rg[q] : __floats2half2_rn(0.f, 0.f);
+      if (sg.mix) sh[i] = (m == 0) ? pf.shift0[i] : (ok ? reinterpret_cast<const __half2*>(sg.shift + static_cast<size_t>(m) * K)[q] : pf.shift0[i]);
+    }
+    float2 v[kLnPairs];
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < kLnPairs; ++i) {
+      const float2 a = __half22float2(xv[i]), r = __half22float2(rv[i]);
+      v[i] = make_float2(a.x + r.x, a.y + r.y);
+      s += v[i].x + v[i].y;
+    }
+    const float inv_k = 1.0f / static_cast<float>(K);
+    const float mean = block_sum<kThreads>(s, scratch) * inv_k;
+    float sv = 0.f;
+#pragma unroll
+    for (int i = 0; i < kLnPairs; ++i) {
+      if (threadIdx.x + kThreads * i < pairs) {
+        const float d0 = v[i].x - mean, d1 = v[i].y - mean;
+        sv += d0 * d0 + d1 * d1;
+      }
+    }
+    const float rstd = rsqrtf(block_sum<kThreads>(sv, scratch) * inv_k + sg.eps);
+    float* row = xs + static_cast<size_t>(m) * K;
+#pragma unroll
+    for (int i = 0; i < kLnPairs; ++i) {
+      const int q = threadIdx.x + kThreads * i;
+      if (q >= pairs) continue;
+      const float2 w = __half22float2(pf.w[i]), b = __half22float2(pf.b[i]);
+      const __half2 nh = __floats2half2_rn((v[i].x - mean) * rstd * w.x + b.x, (v[i].y - mean) * rstd * w.y + b.y);
+      if (writer) {
+        if (sg.x_out) reinterpret_cast<__half2*>(sg.x_out + static_cast<size_t>(m) * K)[q] = __floats2half2_rn(v[i].x, v[i].y);
+        if (sg.n_out) reinterpret_cast<__half2*>(sg.n_out + static_cast<size_t>(m) * K)[q] = nh;
+      }
+      float2 n = __half22float2(nh);
+      if (sg.mix) {
+        const float2 p = __half22float2(sh[i]), c = __half22float2(pf.mix[i]);
+        n = __half22float2(__floats2half2_rn(n.x + (p.x - n.x) * c.x, n.y + (p.y - n.y) * c.y));
+      }
+      *reinterpret_cast<float2*>(row + 2 * q) = n;
     }
   }
 }

@@ -7,6 +7,7 @@
 // programmatic-dependency wait, so a kernel's weight stream starts while its predecessor drains.
 // Same arithmetic and rounding as the register-staged kernel in linear.cu.
 #include <algorithm>
+#include <cstdlib>
 
 #include "gemv.h"
 #include "kernels.h"
@@ -35,6 +36,7 @@ template <int kM>
 __global__ void __launch_bounds__(kWarps * 32) gemv_tma_kernel(const GemvBatch p, int x_bytes, int n_slots, int slot_stride) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   __shared__ __align__(8) uint64_t bars[kWarps][kMaxSlots];
+  __shared__ float red_scratch[kWarps];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   int s = 0;
 #pragma unroll
@@ -79,9 +81,16 @@ __global__ void __launch_bounds__(kWarps * 32) gemv_tma_kernel(const GemvBatch p
   // weights do not depend on the previous kernel: fill the ring before waiting for it
   for (int i = 0; i < n_slots && q_left > 0; ++i) issue();
 
+  LnPrefetch pf;
+  if (sg.ln_w) ln_prefetch<kWarps * 32>(sg, pf);
   pdl_wait();
   pdl_trigger();  // after the wait: at most this kernel and its successor are ever in flight together
-  stage_activations<kM, kWarps * 32>(sg, nullptr, xs);
+  const bool first_cta = static_cast<int>(blockIdx.x) == sg.cta_begin;
+  if (first_cta && sg.copy_src)
+    for (int i = threadIdx.x; i < (sg.copy_n >> 1); i += kWarps * 32)
+      reinterpret_cast<__half2*>(sg.copy_dst)[i] = reinterpret_cast<const __half2*>(sg.copy_src)[i];
+  if (sg.ln_w) stage_ln_mix<kM, kWarps * 32>(sg, xs, red_scratch, first_cta, pf);
+  else stage_activations<kM, kWarps * 32>(sg, nullptr, xs);
   __syncthreads();
 
   const int chunks = piece >> 4;  // 16-byte chunks per piece
@@ -152,14 +161,21 @@ bool gemv_tma_plan(GemvBatch& b, int M, size_t* smem_bytes, int* grid, int* n_sl
   // Bytes in flight decide the achieved HBM rate (the loaded latency is several microseconds):
   // two CTAs per SM with 3-slot rings when the activations are small (192 KiB in flight per SM),
   // else one CTA per SM with rings as deep as the shared memory allows.
-  const int cap = kPieceCap;
+  int cap = kPieceCap;
   int per_sm = 2, slots = 3;
+  static const int env_slots = getenv("RWKV7_B200_GEMV_SLOTS") ? atoi(getenv("RWKV7_B200_GEMV_SLOTS")) : 0;  // tuning aids
+  static const int env_per_sm = getenv("RWKV7_B200_GEMV_PER_SM") ? atoi(getenv("RWKV7_B200_GEMV_PER_SM")) : 0;
+  static const int env_cap = getenv("RWKV7_B200_GEMV_PIECE") ? atoi(getenv("RWKV7_B200_GEMV_PIECE")) : 0;
+  if (env_cap >= 512 && env_cap <= kPieceCap) cap = env_cap;
   if (x_bytes + static_cast<size_t>(kWarps) * 3 * cap > 112 * 1024) {
     per_sm = 1;
     slots = static_cast<int>((200 * 1024 - x_bytes) / (static_cast<size_t>(kWarps) * cap));
     slots = std::min(slots, kMaxSlots);
     if (slots < 2) return false;
   }
+  if (env_per_sm > 0) per_sm = env_per_sm;
+  if (env_slots > 0) slots = std::min(env_slots, kMaxSlots);
+  if (x_bytes + static_cast<size_t>(kWarps) * slots * cap > 200 * 1024) return false;
   for (int i = 0; i < b.n_seg; ++i) {
     GemvSeg& g = b.seg[i];
     const int row_bytes = g.K * 2;

@@ -76,6 +76,18 @@ struct LinearArgs {
   // calls sharing it must not overlap on the GPU
   float* scratch = nullptr;
   size_t scratch_bytes = 0;
+  // optional fused prologue of the decode GEMV (M <= 4, fp16 weights, K == channels): see GemvSeg in gemv.h
+  const half* res = nullptr;
+  const half* ln_w = nullptr;
+  const half* ln_b = nullptr;
+  const half* shift = nullptr;
+  const half* mix = nullptr;
+  half* x_out = nullptr;
+  half* n_out = nullptr;
+  float eps = 1e-5f;
+  const half* copy_src = nullptr;
+  half* copy_dst = nullptr;
+  int copy_n = 0;
 };
 int linear(cudaStream_t stream, const LinearArgs& args);
 // Up to 8 independent problems sharing M <= 4 in a single launch.
@@ -94,6 +106,8 @@ struct TmixDecodeArgs {
   void* state = nullptr;  // this layer's [B,H,64,64] half or float
   const int* elapsed = nullptr;
   half* y2 = nullptr;
+  const half* shift_src = nullptr;  // optional: [B,C] rows copied into shift_dst (the layer's time-mix shift state)
+  half* shift_dst = nullptr;
 };
 bool tmix_decode_supported(const TmixDecodeArgs& args);
 int tmix_decode(cudaStream_t stream, const TmixDecodeArgs& args);

@@ -268,6 +268,7 @@ int linear_batch(cudaStream_t stream, const LinearArgs* args, int n) {
     smem = std::max(smem, static_cast<size_t>(M) * args[i].K * (args[i].in_act == kActNone ? 2 : 4));
   }
   int max_fmt = 0;
+  bool fused = false;
   for (int i = 0; i < n; ++i) {
     const LinearArgs& a = args[i];
     GemvSeg& g = b.seg[i];
@@ -275,6 +276,9 @@ int linear_batch(cudaStream_t stream, const LinearArgs* args, int n) {
     g.v = a.ea.v; g.v_first = a.ea.v_first; g.v0 = a.ea.v0;
     g.ldx = a.ldx ? a.ldx : a.K; g.N = a.N; g.K = a.K; g.fmt = a.fmt; g.in_act = a.in_act; g.epi = a.epi;
     g.cta_begin = 0; g.rows_per_cta = 0; g.parts = 0; g.piece_bytes = 0;
+    g.res = a.res; g.ln_w = a.ln_w; g.ln_b = a.ln_b; g.shift = a.shift; g.mix = a.mix; g.x_out = a.x_out; g.n_out = a.n_out;
+    g.eps = a.eps; g.copy_src = a.copy_src; g.copy_dst = a.copy_dst; g.copy_n = a.copy_n;
+    fused = fused || a.ln_w || a.copy_src;
     max_fmt = std::max(max_fmt, a.fmt);
   }
   for (int i = n; i < kMaxSeg; ++i) b.seg[i] = b.seg[0];
@@ -285,6 +289,7 @@ int linear_batch(cudaStream_t stream, const LinearArgs* args, int n) {
   if (max_fmt == 0 && gemv_tma_plan(b, M, &tma_smem, &tma_grid, &tma_slots, &tma_stride))
     return gemv_tma_launch(stream, b, M, tma_smem, tma_grid, tma_slots, tma_stride);
 
+  RK_REQUIRE(!fused, kShape, "linear_batch: the fused LayerNorm prologue needs fp16 weights and a row size the bulk-copy kernel accepts");
   RK_REQUIRE(smem <= 160 * 1024, kShape, "linear_batch: M*K too large for the activation staging buffer");
   const int tiles_per_cta = static_cast<int>(std::max<long long>(1, (tiles + 295) / 296));  // about two CTAs per SM
   int cta = 0;

@@ -283,7 +283,7 @@ int Model::copy_state_slice(const void* src_shift, const void* src_wkv, const in
 namespace {
 size_t workspace_halves(const rwkv7_b200_config& c, size_t rows, size_t B) {
   const size_t C = c.channels;
-  return rows * C * 25 + rows * static_cast<size_t>(c.ffn) + rows * 512 * 4 + B * C + 1024;
+  return rows * C * 27 + rows * static_cast<size_t>(c.ffn) + rows * 512 * 4 + B * C + 1024;
 }
 }  // namespace
 
@@ -324,6 +324,7 @@ Workspace* Model::workspace(int B, int T) {
   ws->hid = take(rows * F);
   for (int i = 0; i < 4; ++i) ws->l1[i] = take(rows * 512);
   ws->xf = take(static_cast<size_t>(B) * C);
+  ws->n1 = take(RC); ws->n2 = take(RC);
   ws->tokens = reinterpret_cast<int64_t*>(take(rows * 4 + 8));
   if (rows > 4) {
     const size_t want = std::min<size_t>(static_cast<size_t>(256) << 20, rows * C * sizeof(float) * 8);
@@ -360,10 +361,94 @@ int Model::lin16(cudaStream_t s, int M, int K, int N, const half* x, const half*
     if (_s != kOk) return _s;   \
   } while (0)
 
+// Decode step for up to four sequences with fp16 weights: five launches per layer.  The residual
+// add + LayerNorm + token shift in front of the r/k/v (+LoRA down) projections, of ffn.key and of
+// the lm-head run as the prologue of those GEMV kernels; the shift states are updated by the kernel
+// that follows (the fused head kernel, the ffn.value GEMV).
+int Model::enqueue_decode(Workspace& ws, int B, half* shift, void* wkv, int* elapsed, float* logits, cudaStream_t st) {
+  const int C = cfg_.channels, L = cfg_.layers, rows = B;
+  auto mat = [&](const Matrix& Wm, const half* x, void* y, int epi) {
+    LinearArgs a;
+    a.M = rows; a.K = Wm.K; a.N = Wm.N; a.x = x; a.w = Wm.w.p; a.fmt = Wm.fmt; a.epi = epi; a.y = y;
+    return a;
+  };
+  auto low = [&](const DevBuf& w, int R, const half* x, half* y) {
+    LinearArgs a;
+    a.M = rows; a.K = C; a.N = R; a.x = x; a.w = w.p; a.fmt = RWKV7_B200_FMT_F16; a.y = y;
+    return a;
+  };
+  {
+    RowOpArgs a;
+    a.B = B; a.T = 1; a.C = C; a.tokens = ws.tokens; a.table = emb_ln0_.as<half>(); a.vocab = cfg_.vocab;
+    a.x_out = ws.xA; a.ln_w = layers_[0].ln1_w.as<half>(); a.ln_b = layers_[0].ln1_b.as<half>();
+    a.shift = shift; a.n_mix = 6;
+    for (int i = 0; i < 6; ++i) { a.mix[i] = layers_[0].mix[i].as<half>(); a.mix_out[i] = ws.xm[i]; }
+    RK_TRY(row_op(st, a));
+  }
+  for (int li = 0; li < L; ++li) {
+    const LayerWeights& W = layers_[static_cast<size_t>(li)];
+    half* shift0 = shift + static_cast<size_t>(li) * 2 * B * C;
+    half* shift1 = shift0 + static_cast<size_t>(B) * C;
+    half* v_lin = li == 0 ? ws.vfirst : ws.v;
+    // time mix: inputs are xm[] for layer 0, otherwise computed in the prologue from xB + ffn
+    const half* xin[6];
+    for (int i = 0; i < 6; ++i) xin[i] = li == 0 ? ws.xm[i] : ws.xB;
+    LinearArgs seg[7] = {mat(W.Wr, xin[0], ws.r, kEpiNone), mat(W.Wk, xin[2], ws.k, kEpiNone), mat(W.Wv, xin[3], v_lin, kEpiNone),
+                         low(W.w1t, cfg_.rank_w, xin[1], ws.l1[0]), low(W.a1t, cfg_.rank_a, xin[4], ws.l1[1]),
+                         low(W.g1t, cfg_.rank_g, xin[5], ws.l1[2]), low(W.v1t, cfg_.rank_v, xin[3], ws.l1[3])};
+    if (li > 0) {
+      const int mix_of[7] = {0, 2, 3, 1, 4, 5, 3};  // x_r, x_k, x_v, x_w, x_a, x_g, x_v
+      for (int i = 0; i < 7; ++i) {
+        seg[i].res = ws.ffn; seg[i].ln_w = W.ln1_w.as<half>(); seg[i].ln_b = W.ln1_b.as<half>();
+        seg[i].shift = shift0; seg[i].mix = W.mix[mix_of[i]].as<half>();
+      }
+      seg[0].x_out = ws.xA; seg[0].n_out = ws.n1;
+    }
+    RK_TRY(linear_batch(st, seg, li == 0 ? 6 : 7));
+    TmixDecodeArgs ta;
+    ta.B = B; ta.C = C; ta.layer0 = li == 0; ta.wkv32 = cfg_.wkv32 != 0;
+    ta.R[0] = cfg_.rank_w; ta.R[1] = cfg_.rank_a; ta.R[2] = cfg_.rank_g; ta.R[3] = cfg_.rank_v;
+    for (int i = 0; i < 4; ++i) ta.l1[i] = ws.l1[i];
+    ta.up[0] = W.w2t.as<half>(); ta.up[1] = W.a2t.as<half>(); ta.up[2] = W.g2t.as<half>(); ta.up[3] = W.v2t.as<half>();
+    ta.r = ws.r; ta.k = ws.k; ta.v = v_lin; ta.v_first = ws.vfirst;
+    ta.w0 = W.w0.as<half>(); ta.a0 = W.a0.as<half>(); ta.v0 = W.v0.as<half>(); ta.k_k = W.k_k.as<half>();
+    ta.k_a = W.k_a.as<half>(); ta.r_k = W.r_k.as<half>(); ta.lnx_w = W.lnx_w.as<half>(); ta.lnx_b = W.lnx_b.as<half>();
+    const size_t wkv_off = static_cast<size_t>(li) * B * H_ * kHead * kHead;
+    ta.state = cfg_.wkv32 ? static_cast<void*>(static_cast<float*>(wkv) + wkv_off)
+                          : static_cast<void*>(static_cast<half*>(wkv) + wkv_off);
+    ta.elapsed = elapsed; ta.y2 = ws.y2;
+    if (li > 0) { ta.shift_src = ws.n1; ta.shift_dst = shift0; }
+    RK_TRY(tmix_decode(st, ta));
+    LinearArgs wo = mat(W.Wo, ws.y2, ws.att, kEpiNone);
+    RK_TRY(linear_batch(st, &wo, 1));
+    // channel mix: x <- xA + att, LN2, token shift, ffn.key with relu^2
+    LinearArgs key = mat(W.Wkey, ws.xA, ws.hid, kEpiRelu2);
+    key.res = ws.att; key.ln_w = W.ln2_w.as<half>(); key.ln_b = W.ln2_b.as<half>(); key.shift = shift1;
+    key.mix = W.ffn_x_k.as<half>(); key.x_out = ws.xB; key.n_out = ws.n2;
+    RK_TRY(linear_batch(st, &key, 1));
+    LinearArgs val = mat(W.Wval, ws.hid, ws.ffn, kEpiNone);
+    val.copy_src = ws.n2; val.copy_dst = shift1; val.copy_n = B * C;
+    RK_TRY(linear_batch(st, &val, 1));
+  }
+  RK_TRY(advance_i32(st, elapsed, 1, B));
+  LinearArgs head = mat(head_, ws.xB, logits, kEpiF32);
+  head.res = ws.ffn; head.ln_w = ln_out_w_.as<half>(); head.ln_b = ln_out_b_.as<half>();
+  RK_TRY(linear_batch(st, &head, 1));
+  return kOk;
+}
+
 int Model::enqueue(Workspace& ws, int B, int T, half* shift, void* wkv, int* elapsed, float* logits, cudaStream_t st) {
   const int C = cfg_.channels, L = cfg_.layers, rows = B * T;
   const EpiArgs none;
   cur_ = &ws;
+  {
+    TmixDecodeArgs probe;
+    probe.B = B; probe.C = C; probe.wkv32 = cfg_.wkv32 != 0;
+    probe.R[0] = cfg_.rank_w; probe.R[1] = cfg_.rank_a; probe.R[2] = cfg_.rank_g; probe.R[3] = cfg_.rank_v;
+    if (T == 1 && rows <= 4 && cfg_.weight_format == RWKV7_B200_FMT_F16 && tmix_decode_supported(probe) && C <= 4096 &&
+        C % 8 == 0)
+      return enqueue_decode(ws, B, shift, wkv, elapsed, logits, st);
+  }
   {
     RowOpArgs a;
     a.B = B; a.T = T; a.C = C; a.tokens = ws.tokens; a.table = emb_ln0_.as<half>(); a.vocab = cfg_.vocab;

@@ -53,7 +53,7 @@ struct Workspace {
   int rows = 0, B = 0;
   DevBuf arena;
   half *xA, *xB, *xm[6], *r, *k, *v, *vfirst, *vout, *w12, *a12, *g, *k2, *nkk, *kka, *y, *y2, *att, *mixed, *ffn;
-  half *hid, *l1[4], *xf;
+  half *hid, *l1[4], *xf, *n1, *n2;
   int64_t* tokens;
   DevBuf gemm_scratch;  // split-K partial sums of the tensor-core GEMM (rows > 4)
   // ring of pinned host staging slots for the token ids; a slot is reused only after the copy
@@ -105,6 +105,7 @@ class Model {
   int quantize(Matrix& m);
   Workspace* workspace(int B, int T);
   int enqueue(Workspace& ws, int B, int T, half* shift, void* wkv, int* elapsed, float* logits, cudaStream_t s);
+  int enqueue_decode(Workspace& ws, int B, half* shift, void* wkv, int* elapsed, float* logits, cudaStream_t s);
   int lin(cudaStream_t s, int M, const Matrix& W, const half* x, void* y, int epi);
   int lin16(cudaStream_t s, int M, int K, int N, const half* x, const half* w, half* y, int in_act, int epi,
             const EpiArgs& ea);

@@ -32,6 +32,8 @@ struct TmixDev {
   void* state;
   const int* elapsed;
   half* y2;
+  const half* shift_src;  // optional [B,C] rows to move into the time-mix shift state (this head's 64 channels)
+  half* shift_dst;
 };
 
 template <bool kWkv32>
@@ -92,6 +94,8 @@ __global__ void __launch_bounds__(256) tmix_decode_kernel(const TmixDev p) {
 
   pdl_wait();
   pdl_trigger();
+  if (p.shift_src && tid < kHead / 2)
+    reinterpret_cast<__half2*>(p.shift_dst + tok)[tid] = reinterpret_cast<const __half2*>(p.shift_src + tok)[tid];
   // ---- LoRA inputs with their activations, kept in fp32
 #pragma unroll
   for (int s = 0; s < 4; ++s) {
@@ -311,7 +315,7 @@ int tmix_decode(cudaStream_t stream, const TmixDecodeArgs& a) {
   for (int s = 0; s < 4; ++s) { p.R[s] = a.R[s]; p.l1[s] = a.l1[s]; p.up[s] = a.up[s]; }
   p.r = a.r; p.k = a.k; p.v = a.v; p.v_first = a.v_first;
   p.w0 = a.w0; p.a0 = a.a0; p.v0 = a.v0; p.k_k = a.k_k; p.k_a = a.k_a; p.r_k = a.r_k; p.lnx_w = a.lnx_w; p.lnx_b = a.lnx_b;
-  p.state = a.state; p.elapsed = a.elapsed; p.y2 = a.y2;
+  p.state = a.state; p.elapsed = a.elapsed; p.y2 = a.y2; p.shift_src = a.shift_src; p.shift_dst = a.shift_dst;
   const int sum_r = a.R[0] + a.R[1] + a.R[2] + (a.layer0 ? 0 : a.R[3]);
   const size_t smem = static_cast<size_t>(kHead) * (sum_r * 2 + 64) + (a.wkv32 ? 0 : 8192);
   const dim3 grid(a.B * p.H), block(256);
