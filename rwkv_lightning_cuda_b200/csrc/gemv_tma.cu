@@ -15,7 +15,7 @@
 namespace rk {
 namespace {
 
-constexpr int kWarps = 8;
+constexpr int kMaxWarps = 16;
 constexpr int kMaxSlots = 6;
 constexpr int kPieceCap = 4096;  // bytes
 
@@ -32,11 +32,11 @@ __device__ __forceinline__ void fma_chunk(const uint4& q, const float* x, float&
   a0 = fmaf(xb.z, w3.x, a0); a1 = fmaf(xb.w, w3.y, a1);
 }
 
-template <int kM>
-__global__ void __launch_bounds__(kWarps * 32) gemv_tma_kernel(const GemvBatch p, int x_bytes, int n_slots, int slot_stride) {
+template <int kM, int kW>
+__global__ void __launch_bounds__(kW * 32) gemv_tma_kernel(const GemvBatch p, int x_bytes, int n_slots, int slot_stride) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
-  __shared__ __align__(8) uint64_t bars[kWarps][kMaxSlots];
-  __shared__ float red_scratch[kWarps];
+  __shared__ __align__(8) uint64_t bars[kW][kMaxSlots];
+  __shared__ float red_scratch[kW];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   int s = 0;
 #pragma unroll
@@ -45,7 +45,7 @@ __global__ void __launch_bounds__(kWarps * 32) gemv_tma_kernel(const GemvBatch p
   const GemvSeg& sg = p.seg[s];
   const int row0 = (blockIdx.x - sg.cta_begin) * sg.rows_per_cta;
   const int rows_end = min(sg.N, row0 + sg.rows_per_cta);
-  const int rpw = sg.rows_per_cta / kWarps;  // rows_per_cta is a multiple of the warp count
+  const int rpw = sg.rows_per_cta / kW;  // rows_per_cta is a multiple of the warp count
   const int r_begin = row0 + warp * rpw;
   const int r_end = min(rows_end, r_begin + rpw);
   const int parts = sg.parts, piece = sg.piece_bytes;
@@ -57,7 +57,7 @@ __global__ void __launch_bounds__(kWarps * 32) gemv_tma_kernel(const GemvBatch p
   unsigned char* ring = smem_raw + x_bytes + static_cast<size_t>(warp) * n_slots * slot_stride;
   // pieces of a row are visited in a per-warp rotated order so that the warps' streams do not march
   // through the same low address bits (and hence the same memory channels) in lock step
-  const int rot = (blockIdx.x * kWarps + warp) % parts;
+  const int rot = (blockIdx.x * kW + warp) % parts;
 
   if (lane == 0) {
 #pragma unroll
@@ -78,19 +78,33 @@ __global__ void __launch_bounds__(kWarps * 32) gemv_tma_kernel(const GemvBatch p
     if (++q_pp == parts) q_pp = 0;
     if (q_pp == rot) ++q_row;
   };
+  // Once this warp has requested its last piece it asks the L2 for its share of the next kernel's
+  // first reads (fire and forget).
+  auto prefetch_next = [&]() {
+    if (lane != 0) return;
+    const int gw = blockIdx.x * kW + warp, n_gw = gridDim.x * kW;
+    int e0 = 0;
+    for (int i = 0; i < p.n_pf; ++i) {
+      const GemvPrefetch& f = p.pf[i];
+      for (int e = ((gw - e0) % n_gw + n_gw) % n_gw; e < f.count; e += n_gw)
+          asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(f.base + static_cast<long long>(e) * f.stride), "r"(f.depth) : "memory");
+      e0 += f.count;
+    }
+  };
   // weights do not depend on the previous kernel: fill the ring before waiting for it
   for (int i = 0; i < n_slots && q_left > 0; ++i) issue();
+  if (q_left == 0) prefetch_next();
 
   LnPrefetch pf;
-  if (sg.ln_w) ln_prefetch<kWarps * 32>(sg, pf);
+  if (sg.ln_w) ln_prefetch<kW * 32>(sg, pf);
   pdl_wait();
   pdl_trigger();  // after the wait: at most this kernel and its successor are ever in flight together
   const bool first_cta = static_cast<int>(blockIdx.x) == sg.cta_begin;
   if (first_cta && sg.copy_src)
-    for (int i = threadIdx.x; i < (sg.copy_n >> 1); i += kWarps * 32)
+    for (int i = threadIdx.x; i < (sg.copy_n >> 1); i += kW * 32)
       reinterpret_cast<__half2*>(sg.copy_dst)[i] = reinterpret_cast<const __half2*>(sg.copy_src)[i];
-  if (sg.ln_w) stage_ln_mix<kM, kWarps * 32>(sg, xs, red_scratch, first_cta, pf);
-  else stage_activations<kM, kWarps * 32>(sg, nullptr, xs);
+  if (sg.ln_w) stage_ln_mix<kM, kW * 32>(sg, xs, red_scratch, first_cta, pf);
+  else stage_activations<kM, kW * 32>(sg, nullptr, xs);
   __syncthreads();
 
   const int chunks = piece >> 4;  // 16-byte chunks per piece
@@ -122,7 +136,10 @@ __global__ void __launch_bounds__(kWarps * 32) gemv_tma_kernel(const GemvBatch p
       }
     }
     __syncwarp();  // every lane has read the slot: it may be overwritten
-    if (q_left > 0) issue();
+    if (q_left > 0) {
+      issue();
+      if (q_left == 0) prefetch_next();
+    }
     if (++slot == n_slots) { slot = 0; phase ^= 1; }
     if (++pp == parts) pp = 0;
     if (++part == parts) {
@@ -142,7 +159,7 @@ __global__ void __launch_bounds__(kWarps * 32) gemv_tma_kernel(const GemvBatch p
 
 // Fills cta_begin / rows_per_cta / parts / piece_bytes for the bulk-copy kernel.  Returns false when
 // a problem does not fit it (non-fp16 weights, or a row that cannot be cut into 16-byte multiples).
-bool gemv_tma_plan(GemvBatch& b, int M, size_t* smem_bytes, int* grid, int* n_slots, int* slot_stride) {
+bool gemv_tma_plan(GemvBatch& b, int M, size_t* smem_bytes, int* grid, int* n_slots, int* slot_stride, int* n_warps) {
   size_t x_bytes = 0;
   double total_bytes = 0;
   for (int i = 0; i < b.n_seg; ++i) {
@@ -158,22 +175,22 @@ bool gemv_tma_plan(GemvBatch& b, int M, size_t* smem_bytes, int* grid, int* n_sl
     total_bytes += static_cast<double>(g.N) * row_bytes;
   }
   x_bytes = (x_bytes + 127) & ~static_cast<size_t>(127);
-  // Bytes in flight decide the achieved HBM rate (the loaded latency is several microseconds):
-  // two CTAs per SM with 3-slot rings when the activations are small (192 KiB in flight per SM),
-  // else one CTA per SM with rings as deep as the shared memory allows.
   int cap = kPieceCap;
-  int per_sm = 2, slots = 3;
+  // measured best on B200: one CTA of 16 warps per SM, two 4 KiB slots per warp (128 KiB in flight)
+  int per_sm = 1, slots = 2, kWarps = 16;
+  static const int env_warps = getenv("RWKV7_B200_GEMV_WARPS") ? atoi(getenv("RWKV7_B200_GEMV_WARPS")) : 0;
   static const int env_slots = getenv("RWKV7_B200_GEMV_SLOTS") ? atoi(getenv("RWKV7_B200_GEMV_SLOTS")) : 0;  // tuning aids
   static const int env_per_sm = getenv("RWKV7_B200_GEMV_PER_SM") ? atoi(getenv("RWKV7_B200_GEMV_PER_SM")) : 0;
   static const int env_cap = getenv("RWKV7_B200_GEMV_PIECE") ? atoi(getenv("RWKV7_B200_GEMV_PIECE")) : 0;
   if (env_cap >= 512 && env_cap <= kPieceCap) cap = env_cap;
-  if (x_bytes + static_cast<size_t>(kWarps) * 3 * cap > 112 * 1024) {
-    per_sm = 1;
+  if (x_bytes + static_cast<size_t>(kWarps) * slots * cap > 200 * 1024) {
+    kWarps = 8;  // very large activation rows: fewer warps, whatever ring depth still fits
     slots = static_cast<int>((200 * 1024 - x_bytes) / (static_cast<size_t>(kWarps) * cap));
     slots = std::min(slots, kMaxSlots);
     if (slots < 2) return false;
   }
   if (env_per_sm > 0) per_sm = env_per_sm;
+  if (env_warps == 8 || env_warps == 16) kWarps = env_warps;
   if (env_slots > 0) slots = std::min(env_slots, kMaxSlots);
   if (x_bytes + static_cast<size_t>(kWarps) * slots * cap > 200 * 1024) return false;
   for (int i = 0; i < b.n_seg; ++i) {
@@ -202,10 +219,26 @@ bool gemv_tma_plan(GemvBatch& b, int M, size_t* smem_bytes, int* grid, int* n_sl
   *grid = cta;
   *n_slots = slots;
   *slot_stride = cap;
+  *n_warps = kWarps;
   return true;
 }
 
-int gemv_tma_launch(cudaStream_t stream, const GemvBatch& b, int M, size_t smem_bytes, int grid, int n_slots, int slot_stride) {
+GemvPrefetch gemv_tma_prefetch_of(const void* w, int N, int K, int launch_rows) {
+  GemvPrefetch f;
+  const int rpw = std::max(1, (launch_rows + 148 * 16 - 1) / (148 * 16));
+  const long long row_bytes = static_cast<long long>(K) * 2;
+  f.base = static_cast<const char*>(w);
+  f.stride = rpw * row_bytes;
+  static const int env_depth = getenv("RWKV7_B200_PREFETCH_BYTES") ? atoi(getenv("RWKV7_B200_PREFETCH_BYTES")) : 0;  // off: measured no gain at 4-8 KiB, a loss at 32 KiB
+  f.depth = static_cast<int>(std::min<long long>(f.stride, env_depth)) & ~15;
+  f.count = f.depth > 0 ? (N + rpw - 1) / rpw : 0;
+  // the last block must not run past the matrix
+  if (static_cast<long long>(f.count - 1) * f.stride + f.depth > static_cast<long long>(N) * row_bytes) --f.count;
+  return f;
+}
+
+int gemv_tma_launch(cudaStream_t stream, const GemvBatch& b, int M, size_t smem_bytes, int grid, int n_slots, int slot_stride,
+                    int kWarps) {
   const int x_bytes = static_cast<int>(smem_bytes - static_cast<size_t>(kWarps) * n_slots * slot_stride);
   auto launch = [&](auto kernel) -> int {
     RK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
@@ -213,11 +246,20 @@ int gemv_tma_launch(cudaStream_t stream, const GemvBatch& b, int M, size_t smem_
     return kOk;
   };
   int s;
-  switch (M) {
-    case 1: s = launch(gemv_tma_kernel<1>); break;
-    case 2: s = launch(gemv_tma_kernel<2>); break;
-    case 3: s = launch(gemv_tma_kernel<3>); break;
-    default: s = launch(gemv_tma_kernel<4>); break;
+  if (kWarps == 16) {
+    switch (M) {
+      case 1: s = launch(gemv_tma_kernel<1, 16>); break;
+      case 2: s = launch(gemv_tma_kernel<2, 16>); break;
+      case 3: s = launch(gemv_tma_kernel<3, 16>); break;
+      default: s = launch(gemv_tma_kernel<4, 16>); break;
+    }
+  } else {
+    switch (M) {
+      case 1: s = launch(gemv_tma_kernel<1, 8>); break;
+      case 2: s = launch(gemv_tma_kernel<2, 8>); break;
+      case 3: s = launch(gemv_tma_kernel<3, 8>); break;
+      default: s = launch(gemv_tma_kernel<4, 8>); break;
+    }
   }
   if (s != kOk) return s;
   RK_LAUNCH_CHECK("gemv_tma launch");

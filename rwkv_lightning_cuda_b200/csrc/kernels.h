@@ -88,6 +88,11 @@ struct LinearArgs {
   const half* copy_src = nullptr;
   half* copy_dst = nullptr;
   int copy_n = 0;
+  // optional hint (first problem of a batch only): fp16 matrices the next GEMV launch in the stream will
+  // read, prefetched into L2 while this launch drains.  pf_launch_rows = total output rows of that launch.
+  const void* pf_w[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+  int pf_n[6] = {0, 0, 0, 0, 0, 0}, pf_k[6] = {0, 0, 0, 0, 0, 0};
+  int pf_launch_rows = 0;
 };
 int linear(cudaStream_t stream, const LinearArgs& args);
 // Up to 8 independent problems sharing M <= 4 in a single launch.

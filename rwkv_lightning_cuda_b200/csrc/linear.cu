@@ -282,12 +282,20 @@ int linear_batch(cudaStream_t stream, const LinearArgs* args, int n) {
     max_fmt = std::max(max_fmt, a.fmt);
   }
   for (int i = n; i < kMaxSeg; ++i) b.seg[i] = b.seg[0];
+  b.n_pf = 0;
+  for (int i = 0; i < kMaxPrefetch; ++i) {
+    b.pf[i] = GemvPrefetch{nullptr, 0, 0, 0};
+    if (args[0].pf_w[i] && args[0].pf_launch_rows > 0) {
+      const GemvPrefetch f = gemv_tma_prefetch_of(args[0].pf_w[i], args[0].pf_n[i], args[0].pf_k[i], args[0].pf_launch_rows);
+      if (f.count > 0) b.pf[b.n_pf++] = f;
+    }
+  }
 
   // fp16 weights: bulk-copy kernel (shared-memory rings fed by the copy engine)
   size_t tma_smem = 0;
-  int tma_grid = 0, tma_slots = 0, tma_stride = 0;
-  if (max_fmt == 0 && gemv_tma_plan(b, M, &tma_smem, &tma_grid, &tma_slots, &tma_stride))
-    return gemv_tma_launch(stream, b, M, tma_smem, tma_grid, tma_slots, tma_stride);
+  int tma_grid = 0, tma_slots = 0, tma_stride = 0, tma_warps = 0;
+  if (max_fmt == 0 && gemv_tma_plan(b, M, &tma_smem, &tma_grid, &tma_slots, &tma_stride, &tma_warps))
+    return gemv_tma_launch(stream, b, M, tma_smem, tma_grid, tma_slots, tma_stride, tma_warps);
 
   RK_REQUIRE(!fused, kShape, "linear_batch: the fused LayerNorm prologue needs fp16 weights and a row size the bulk-copy kernel accepts");
   RK_REQUIRE(smem <= 160 * 1024, kShape, "linear_batch: M*K too large for the activation staging buffer");

@@ -404,6 +404,14 @@ int Model::enqueue_decode(Workspace& ws, int B, half* shift, void* wkv, int* ela
       }
       seg[0].x_out = ws.xA; seg[0].n_out = ws.n1;
     }
+    {  // while this launch drains: the LoRA up matrices of the fused head kernel and the start of att.output
+      const DevBuf* ups[4] = {&W.w2t, &W.a2t, &W.g2t, &W.v2t};
+      const int rk[4] = {cfg_.rank_w, cfg_.rank_a, cfg_.rank_g, cfg_.rank_v};
+      int np = 0;
+      for (int i = 0; i < (li == 0 ? 3 : 4); ++i) { seg[0].pf_w[np] = ups[i]->p; seg[0].pf_n[np] = C; seg[0].pf_k[np] = rk[i]; ++np; }
+      seg[0].pf_w[np] = W.Wo.w.p; seg[0].pf_n[np] = C; seg[0].pf_k[np] = C;
+      seg[0].pf_launch_rows = C;
+    }
     RK_TRY(linear_batch(st, seg, li == 0 ? 6 : 7));
     TmixDecodeArgs ta;
     ta.B = B; ta.C = C; ta.layer0 = li == 0; ta.wkv32 = cfg_.wkv32 != 0;
@@ -420,14 +428,24 @@ int Model::enqueue_decode(Workspace& ws, int B, half* shift, void* wkv, int* ela
     if (li > 0) { ta.shift_src = ws.n1; ta.shift_dst = shift0; }
     RK_TRY(tmix_decode(st, ta));
     LinearArgs wo = mat(W.Wo, ws.y2, ws.att, kEpiNone);
+    wo.pf_w[0] = W.Wkey.w.p; wo.pf_n[0] = W.Wkey.N; wo.pf_k[0] = W.Wkey.K; wo.pf_launch_rows = W.Wkey.N;
     RK_TRY(linear_batch(st, &wo, 1));
     // channel mix: x <- xA + att, LN2, token shift, ffn.key with relu^2
     LinearArgs key = mat(W.Wkey, ws.xA, ws.hid, kEpiRelu2);
     key.res = ws.att; key.ln_w = W.ln2_w.as<half>(); key.ln_b = W.ln2_b.as<half>(); key.shift = shift1;
     key.mix = W.ffn_x_k.as<half>(); key.x_out = ws.xB; key.n_out = ws.n2;
+    key.pf_w[0] = W.Wval.w.p; key.pf_n[0] = W.Wval.N; key.pf_k[0] = W.Wval.K; key.pf_launch_rows = W.Wval.N;
     RK_TRY(linear_batch(st, &key, 1));
     LinearArgs val = mat(W.Wval, ws.hid, ws.ffn, kEpiNone);
     val.copy_src = ws.n2; val.copy_dst = shift1; val.copy_n = B * C;
+    if (li + 1 < L) {
+      const LayerWeights& Nx = layers_[static_cast<size_t>(li) + 1];
+      const Matrix* nm[3] = {&Nx.Wr, &Nx.Wk, &Nx.Wv};
+      for (int i = 0; i < 3; ++i) { val.pf_w[i] = nm[i]->w.p; val.pf_n[i] = C; val.pf_k[i] = C; }
+      val.pf_launch_rows = 3 * C + cfg_.rank_w + cfg_.rank_a + cfg_.rank_g + cfg_.rank_v;
+    } else {
+      val.pf_w[0] = head_.w.p; val.pf_n[0] = head_.N; val.pf_k[0] = head_.K; val.pf_launch_rows = head_.N;
+    }
     RK_TRY(linear_batch(st, &val, 1));
   }
   RK_TRY(advance_i32(st, elapsed, 1, B));
