@@ -191,6 +191,9 @@ def run_ours(args, rank, world, local_rank):
         return
     abytes, wbytes, sbytes = algorithmic_bytes(d, B, bool(args.wkv32), fmt)
     achieved = abytes / (ms * 1e-3) / 1e9
+    # DRAM traffic of the dominant kernel (gemv_tma_kernel) per algorithmic byte, from the ncu capture summarised in
+    # profiles/gemv_tma_16384x4096_ncu_full.md: 134.27 MB read + 3.43 MB written for 134.26 MB; scaled to the step
+    traffic = abytes * (137.70 / 134.26) if (fmt == 0 and B <= 4) else None
     line = {
         "metric": "decode_tokens_per_s", "value": world * B / (ms * 1e-3), "unit": "tok/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
@@ -203,13 +206,52 @@ def run_ours(args, rank, world, local_rank):
                 "h2d_bytes_per_step": B * 8, "d2h_bytes_per_step": B * d.vocab * 4},
         "gpu_launches": int(launches),
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
-                     "traffic": None, "peak_kind": peak_kind, "frac_of_nominal_8000": achieved / 8000.0,
+                     "traffic": traffic, "peak_kind": peak_kind, "frac_of_nominal_8000": achieved / 8000.0,
                      "algorithmic_bytes_per_step": abytes, "weight_bytes": wbytes, "state_bytes_per_seq": sbytes,
                      "scope": "whole decode step (weight-streaming GEMV kernels dominate)"},
     }
     if world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline(args)
     print(json.dumps(line))
+
+
+def micro_gemv(args):
+    """Isolated GEMV timing (not the benchmark line): y = x W^T for the 7.2B layer shapes on rotating weight
+    copies larger than L2, replayed from a CUDA graph so that launches are back to back.  `--micro gemv-small`
+    runs a handful of eager launches of the 16384x4096 case only (the command the ncu captures use)."""
+    from rwkv_lightning_cuda_b200 import ops
+    small = args.micro == "gemv-small"
+    shapes = [(16384, 4096)] if small else [(4096, 4096), (13120, 4096), (16384, 4096), (4096, 16384), (65536, 4096)]
+    for N, K in shapes:
+        copies = max(2, min(6, int(2e9 // (N * K * 2))))
+        Ws = [torch.randn(N, K, device="cuda", dtype=torch.float16) * 0.02 for _ in range(copies)]
+        x = torch.randn(1, K, device="cuda", dtype=torch.float16)
+        s = torch.cuda.Stream()
+        with torch.cuda.stream(s):
+            for W in Ws:
+                ops.linear_f16_orig(x, W)
+            torch.cuda.synchronize()
+            if small:
+                for i in range(4):
+                    ops.linear_f16_orig(x, Ws[i % copies])
+                torch.cuda.synchronize()
+                print(json.dumps({"micro": "gemv-small", "N": N, "K": K, "launches": copies + 4}))
+                continue
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=s):
+                for _ in range(4):
+                    for W in Ws:
+                        ops.linear_f16_orig(x, W)
+            g.replay()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(s)
+            for _ in range(5):
+                g.replay()
+            e1.record(s)
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / (5 * 4 * copies)
+        print(json.dumps({"micro": "gemv", "N": N, "K": K, "us_per_launch": us, "GB_per_s": N * K * 2 / us / 1e3}))
 
 
 def write_reference_checkpoint(args, path):
@@ -288,12 +330,16 @@ def main():
     ap.add_argument("--fmt", default="f16", choices=["f16", "w8a16", "w4a16"])
     ap.add_argument("--wkv32", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--micro", default="", choices=["", "gemv", "gemv-small"], help="kernel micro-benchmark instead of the bench line")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local_rank)
+    if args.micro:
+        micro_gemv(args)
+        return
     if args.impl == "reference":
         run_reference(args, rank, world)
         return
