@@ -92,6 +92,19 @@ def algorithmic_bytes(d, B, wkv32, fmt):
     return wbytes + B * (state + act), wbytes, state
 
 
+def max_over_ranks(values, world, device):
+    """Per-rank step times -> the slowest rank's (what a whole-job rate must be computed from)."""
+    t = torch.tensor(values, device=device, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return t.tolist()
+
+
+def whole_job_rate(world, batch_per_gpu, ms_per_step):
+    """Tokens per second of all replicas together: every rank decodes batch_per_gpu tokens per step."""
+    return world * batch_per_gpu / (ms_per_step * 1e-3)
+
+
 def build_model(args, dev_index, seed):
     from rwkv_lightning_cuda_b200 import backend as bk, synthetic, lib as L
     d = synthetic.CONFIGS[args.model]
@@ -183,10 +196,7 @@ def run_ours(args, rank, world, local_rank):
         e2e_ms = (time.perf_counter() - t0) * 1e3 / args.steps
         clocks = sampler.stop()
 
-    t = torch.tensor([ms, e2e_ms], device="cuda", dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms, e2e_ms = t.tolist()
+    ms, e2e_ms = max_over_ranks([ms, e2e_ms], world, "cuda")
     if rank != 0:
         return
     abytes, wbytes, sbytes = algorithmic_bytes(d, B, bool(args.wkv32), fmt)
@@ -195,14 +205,14 @@ def run_ours(args, rank, world, local_rank):
     # profiles/gemv_tma_16384x4096_ncu_full.md: 134.27 MB read + 3.43 MB written for 134.26 MB; scaled to the step
     traffic = abytes * (137.70 / 134.26) if (fmt == 0 and B <= 4) else None
     line = {
-        "metric": "decode_tokens_per_s", "value": world * B / (ms * 1e-3), "unit": "tok/s", "n_gpus": world,
+        "metric": "decode_tokens_per_s", "value": whole_job_rate(world, B, ms), "unit": "tok/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f16" if fmt == 0 else args.fmt, "data": "synthetic",
         "config": {"workload": f"RWKV-7 {args.model} random-init, decode, batch {B} per GPU, {'fp32' if args.wkv32 else 'fp16'} WKV state, weights {args.fmt}",
                    "batch_per_gpu": B, "parallelism": f"replicas x{world} (batch-sharded, no collective)",
                    "l2": "inputs larger than L2 (every step streams all weights)"},
         "clocks": clocks,
-        "e2e": {"value": world * B / (e2e_ms * 1e-3), "unit": "tok/s", "ms_per_step": e2e_ms,
+        "e2e": {"value": whole_job_rate(world, B, e2e_ms), "unit": "tok/s", "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": B * 8, "d2h_bytes_per_step": B * d.vocab * 4},
         "gpu_launches": int(launches),
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
