@@ -230,6 +230,8 @@ def micro_gemv(args):
     copies larger than L2, replayed from a CUDA graph so that launches are back to back.  `--micro gemv-small`
     runs a handful of eager launches of the 16384x4096 case only (the command the ncu captures use)."""
     from rwkv_lightning_cuda_b200 import ops
+    if args.micro.startswith("gemm"):
+        return micro_gemm(args)
     small = args.micro == "gemv-small"
     shapes = [(16384, 4096)] if small else [(4096, 4096), (13120, 4096), (16384, 4096), (4096, 16384), (65536, 4096)]
     for N, K in shapes:
@@ -262,6 +264,44 @@ def micro_gemv(args):
         torch.cuda.synchronize()
         us = e0.elapsed_time(e1) * 1e3 / (5 * 4 * copies)
         print(json.dumps({"micro": "gemv", "N": N, "K": K, "us_per_launch": us, "GB_per_s": N * K * 2 / us / 1e3}))
+
+
+def micro_gemm(args):
+    """Isolated tensor-core GEMM timing: y[M,N] = x[M,K] W[N,K]^T for batched-decode / prefill shapes of the 7.2B
+    model, graph-replayed on rotating weights.  `--micro gemm-small` runs a few eager launches of two shapes."""
+    from rwkv_lightning_cuda_b200 import ops
+    small = args.micro == "gemm-small"
+    shapes = [(256, 128, 4096), (256, 4096, 4096)] if small else \
+        [(256, 128, 4096), (256, 4096, 128), (256, 4096, 4096), (256, 4096, 16384), (256, 16384, 4096), (128, 4096, 4096), (2048, 4096, 4096)]
+    for M, K, N in shapes:
+        copies = max(2, min(6, int(1e9 // (N * K * 2))))
+        Ws = [torch.randn(N, K, device="cuda", dtype=torch.float16) * 0.02 for _ in range(copies)]
+        x = torch.randn(M, K, device="cuda", dtype=torch.float16)
+        s = torch.cuda.Stream()
+        with torch.cuda.stream(s):
+            for W in Ws:
+                ops.linear_f16_orig(x, W)
+            torch.cuda.synchronize()
+            if small:
+                continue
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=s):
+                for _ in range(4):
+                    for W in Ws:
+                        ops.linear_f16_orig(x, W)
+            g.replay()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(s)
+            for _ in range(5):
+                g.replay()
+            e1.record(s)
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / (5 * 4 * copies)
+        print(json.dumps({"micro": "gemm", "M": M, "K": K, "N": N, "us_per_launch": us, "TFLOP_per_s": 2.0 * M * N * K / us / 1e6,
+                          "weight_GB_per_s": N * K * 2 / us / 1e3}))
+    if small:
+        print(json.dumps({"micro": "gemm-small", "shapes": shapes}))
 
 
 def write_reference_checkpoint(args, path):
@@ -340,7 +380,7 @@ def main():
     ap.add_argument("--fmt", default="f16", choices=["f16", "w8a16", "w4a16"])
     ap.add_argument("--wkv32", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--micro", default="", choices=["", "gemv", "gemv-small"], help="kernel micro-benchmark instead of the bench line")
+    ap.add_argument("--micro", default="", choices=["", "gemv", "gemv-small", "gemm", "gemm-small"], help="kernel micro-benchmark instead of the bench line")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     rank = int(os.environ.get("RANK", "0"))

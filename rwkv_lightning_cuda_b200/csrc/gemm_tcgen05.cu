@@ -170,21 +170,64 @@ __global__ void __launch_bounds__(kThreads) gemm_tc_kernel(const __grid_constant
     const bool ok = mbar_wait(smem_u32(&acc_bar), 0);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     if (ok) {
+      // Phase A: TMEM -> registers -> an fp32 tile [Nt][128 (+4 pad)] in the (now idle) stage memory, so that
+      // phase B can write y with 8- or 16-byte stores along the channel dimension.
       const int q = warp & 3;
-      const int n = n0 + q * 32 + lane;
-      const float sc = (p.scale && n < p.N) ? __half2float(p.scale[n]) : 1.0f;
-      for (int c0 = 0; c0 < p.Nt; c0 += 16) {
-        if (m0 + c0 >= p.M) break;  // warp-uniform
+      float* tile = reinterpret_cast<float*>(smem_raw + (smem_base - smem_u32(smem_raw)));
+      constexpr int kLd = kBM + 4;
+      const int m_valid = min(p.Nt, p.M - m0);
+      for (int c0 = 0; c0 < m_valid; c0 += 16) {
         uint32_t r[16];
         tmem_ld16(tmem_acc + (static_cast<uint32_t>(q * 32) << 16) + c0, r);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        if (n < p.N) {
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const int m = m0 + c0 + j;
-            if (m >= p.M) break;
-            if (p.splits == 1) emit(p, m, n, __uint_as_float(r[j]) * sc);
-            else p.partial[(static_cast<size_t>(blockIdx.z) * p.M + m) * p.N + n] = __uint_as_float(r[j]);
+        for (int j = 0; j < 16; ++j) tile[(c0 + j) * kLd + q * 32 + lane] = __uint_as_float(r[j]);
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      // Phase B: thread t owns 4 consecutive channels of rows t/32, t/32 + 4, ...
+      const int t = threadIdx.x - 64;
+      const int c4 = (t & 31) * 4, n = n0 + c4;
+      if (n < p.N) {
+        float sc[4] = {1.f, 1.f, 1.f, 1.f};
+        if (p.scale) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) sc[i] = __half2float(p.scale[n + i]);
+        }
+        for (int ml = t >> 5; ml < m_valid; ml += 4) {
+          const float4 a4 = *reinterpret_cast<const float4*>(tile + ml * kLd + c4);
+          const float a[4] = {a4.x * sc[0], a4.y * sc[1], a4.z * sc[2], a4.w * sc[3]};
+          const size_t o = static_cast<size_t>(m0 + ml) * p.N + n;
+          if (p.splits > 1) {
+            *reinterpret_cast<float4*>(p.partial + static_cast<size_t>(blockIdx.z) * p.M * p.N + o) = a4;
+          } else if (p.epi == kEpiF32) {
+            float4 o4;
+            o4.x = __half2float(__float2half_rn(a[0])); o4.y = __half2float(__float2half_rn(a[1]));
+            o4.z = __half2float(__float2half_rn(a[2])); o4.w = __half2float(__float2half_rn(a[3]));
+            *reinterpret_cast<float4*>(static_cast<float*>(p.y) + o) = o4;
+          } else {
+            float e[4];
+            if (p.epi == kEpiRelu2) {
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const float u = fmaxf(__half2float(__float2half_rn(a[i])), 0.f);
+                e[i] = u * u;
+              }
+            } else if (p.epi == kEpiVres) {
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const float vv = __half2float(p.v[o + i]);
+                const float gate = 1.0f / (1.0f + expf(-(__half2float(p.v0[n + i]) + a[i])));
+                e[i] = vv + (__half2float(p.v_first[o + i]) - vv) * gate;
+              }
+            } else {
+#pragma unroll
+              for (int i = 0; i < 4; ++i) e[i] = a[i];
+            }
+            const __half2 lo = __floats2half2_rn(e[0], e[1]), hi = __floats2half2_rn(e[2], e[3]);
+            uint2 pk;
+            pk.x = *reinterpret_cast<const uint32_t*>(&lo);
+            pk.y = *reinterpret_cast<const uint32_t*>(&hi);
+            *reinterpret_cast<uint2*>(static_cast<half*>(p.y) + o) = pk;
           }
         }
       }
@@ -267,7 +310,7 @@ int pick_nt(int M) {
 
 bool gemm_tc_supported(const LinearArgs& a) {
   const int ldx = a.ldx ? a.ldx : a.K;
-  return a.fmt == 0 && a.in_act == kActNone && a.K % 8 == 0 && ldx % 8 == 0 && a.M > 4 &&
+  return a.fmt == 0 && a.in_act == kActNone && a.K % 8 == 0 && ldx % 8 == 0 && a.M > 4 && a.N % 4 == 0 &&
          (reinterpret_cast<uintptr_t>(a.x) & 15u) == 0 && (reinterpret_cast<uintptr_t>(a.w) & 15u) == 0;
 }
 
