@@ -91,6 +91,23 @@ int rwkv7_b200_model_set_tensor(rwkv7_b200_model* m, const char* name, const voi
 /* Builds device layouts (LoRA transposes, emb+LN0 table as cuda/rwkv7_v3a_ops.cu:153-187,
  * quantisation) and frees staging copies.  Synchronises the device. */
 int rwkv7_b200_model_finalize(rwkv7_b200_model* m);
+
+/* Head-sharded tensor parallelism (no counterpart in the reference, which drives one GPU:
+ * src/rwkv7_fast_v4.cu never selects a device).  One process or thread per GPU creates a model with
+ * tp_size = G and its own tp_rank, feeds every rank the FULL tensors through set_tensor (each rank keeps
+ * heads [rank*H/G, (rank+1)*H/G): rows of att.receptance/key/value, input columns of att.output, the
+ * per-channel att vectors and LoRA up-projections of those heads, ffn.key rows / ffn.value columns
+ * [rank*F/G, ...), head rows [rank*V/G, ...); LayerNorms, token-shift vectors, LoRA down-projections and
+ * the embedding table are replicated).  Every rank then runs the same forward calls with the same tokens;
+ * partial sums of att.output and ffn.value are added across ranks in fp32 (NCCL all-reduce, bound at run
+ * time from libnccl.so.2) and rounded to half once; the logits are all-gathered, so every rank returns
+ * the full [B, vocab].  The wkv state holds the rank's heads only (state_sizes reports the local size);
+ * shift and elapsed are replicated.  fp16 weights only.
+ *   rwkv7_b200_tp_unique_id: rank 0 fills 128 bytes and sends them to the other ranks (any host channel).
+ *   rwkv7_b200_model_tp_init: collective over all ranks, before the first forward. */
+int rwkv7_b200_tp_unique_id(void* out128);
+int rwkv7_b200_model_tp_init(rwkv7_b200_model* m, const void* unique_id128);
+
 int rwkv7_b200_model_destroy(rwkv7_b200_model* m);
 int rwkv7_b200_vocab_size(const rwkv7_b200_model* m);   /* ModelBackend::vocab_size, src/rwkv7_fast_v4.cu:1582 */
 

@@ -57,22 +57,39 @@ def _ptr(t: Optional[torch.Tensor]):
     return None if t is None else C.c_void_p(t.data_ptr())
 
 
+def tp_unique_id() -> bytes:
+    """128 bytes identifying a new tensor-parallel group; call on rank 0 and send to the other ranks."""
+    buf = C.create_string_buffer(128)
+    L.check(L.load_library().rwkv7_b200_tp_unique_id(buf))
+    return buf.raw
+
+
 class ModelBackend:
     """Drop-in counterpart of the reference ``ModelBackend`` (weights given as named tensors)."""
 
     def __init__(self, dims: ModelDims, tensors: Optional[Dict[str, torch.Tensor]] = None, use_wkv32: bool = False,
                  weight_format: int = L.FMT_F16, device: Optional[int] = None, model_path: str = "<synthetic>",
-                 finalize: bool = True):
+                 finalize: bool = True, tp_rank: int = 0, tp_size: int = 1, tp_unique_id: Optional[bytes] = None):
+        """``tp_size`` > 1: head-sharded tensor parallelism, one ModelBackend per GPU/process.  Every rank passes
+        the full ``tensors`` (its slice is kept), the 128-byte ``tp_unique_id`` made by :func:`tp_unique_id` on
+        rank 0 and shared over any host channel, and afterwards makes the same forward calls."""
         self._lib = L.load_library()
+        self.tp_rank, self.tp_size = (tp_rank, tp_size) if tp_size > 1 else (0, 1)
         self.dims = dims
         self.use_wkv32 = bool(use_wkv32)
         self._model_path = model_path
         self.device = torch.cuda.current_device() if device is None else device
         cfg = L.Config(dims.layers, dims.channels, dims.ffn, dims.vocab, dims.rank_w, dims.rank_a, dims.rank_v,
-                       dims.rank_g, weight_format, int(self.use_wkv32), self.device, 0, 1)
+                       dims.rank_g, weight_format, int(self.use_wkv32), self.device, self.tp_rank, self.tp_size)
         handle = C.c_void_p()
         L.check(self._lib.rwkv7_b200_model_create(C.byref(cfg), C.byref(handle)))
         self._h = handle
+        if self.tp_size > 1:
+            if tp_unique_id is None or len(tp_unique_id) != 128:
+                raise ValueError("tp_size > 1 needs the 128-byte tp_unique_id shared by rank 0")
+            buf = C.create_string_buffer(bytes(tp_unique_id), 128)
+            with torch.cuda.device(self.device):
+                L.check(self._lib.rwkv7_b200_model_tp_init(self._h, buf))
         for name, t in (tensors or {}).items():
             self.set_tensor(name, t)
         if finalize:
@@ -100,7 +117,7 @@ class ModelBackend:
         d = self.dims
         dev = torch.device("cuda", self.device)
         shift = torch.empty((d.layers, 2, batch_size, d.channels), dtype=torch.float16, device=dev)
-        wkv = torch.empty((d.layers, batch_size, d.heads, 64, 64), dtype=torch.float32 if self.use_wkv32 else torch.float16, device=dev)
+        wkv = torch.empty((d.layers, batch_size, d.heads // self.tp_size, 64, 64), dtype=torch.float32 if self.use_wkv32 else torch.float16, device=dev)
         elapsed = torch.empty((batch_size,), dtype=torch.int32, device=dev)
         assert shift.numel() == ns.value and wkv.numel() == nw.value and elapsed.numel() == ne.value
         stream = torch.cuda.current_stream(dev).cuda_stream

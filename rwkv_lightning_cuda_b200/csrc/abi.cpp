@@ -41,7 +41,15 @@ int rwkv7_b200_model_create(const rwkv7_b200_config* cfg, rwkv7_b200_model** out
   RK_REQUIRE(cfg->weight_format >= 0 && cfg->weight_format <= 2, kBadArg, "model_create: unknown weight format");
   RK_REQUIRE(cfg->weight_format != RWKV7_B200_FMT_W4A16 || (cfg->channels % 128 == 0 && cfg->ffn % 128 == 0), rk::kShape,
              "model_create: W4A16 needs channels and ffn to be multiples of 128");
-  RK_REQUIRE(cfg->tp_size <= 1, kBadArg, "model_create: tensor parallelism is not available in this build");
+  if (cfg->tp_size > 1) {
+    const int G = cfg->tp_size;
+    RK_REQUIRE(cfg->tp_rank >= 0 && cfg->tp_rank < G, kBadArg, "model_create: tp_rank %d outside [0, %d)", cfg->tp_rank, G);
+    RK_REQUIRE(cfg->weight_format == RWKV7_B200_FMT_F16, kBadArg, "model_create: tensor parallelism supports fp16 weights only");
+    RK_REQUIRE(cfg->channels % (64 * G) == 0, rk::kShape, "model_create: the head count %d does not divide over %d ranks",
+               cfg->channels / 64, G);
+    RK_REQUIRE(cfg->ffn % (32 * G) == 0 && cfg->vocab % (4 * G) == 0, rk::kShape,
+               "model_create: ffn must be a multiple of 32*tp_size and vocab of 4*tp_size");
+  }
   rwkv7_b200_model* m = new (std::nothrow) rwkv7_b200_model(*cfg);
   RK_REQUIRE(m, rk::kCuda, "model_create: out of host memory");
   *out = m;
@@ -52,6 +60,11 @@ int rwkv7_b200_model_set_tensor(rwkv7_b200_model* m, const char* name, const voi
                                 int on_device) {
   RK_REQUIRE(m, kBadArg, "null model");
   return m->impl.set_tensor(name, data, dtype, count, on_device);
+}
+int rwkv7_b200_tp_unique_id(void* out128) { return rk::TpComm::make_unique_id(out128); }
+int rwkv7_b200_model_tp_init(rwkv7_b200_model* m, const void* unique_id) {
+  RK_REQUIRE(m, kBadArg, "null model");
+  return m->impl.tp_init(unique_id);
 }
 int rwkv7_b200_model_finalize(rwkv7_b200_model* m) {
   RK_REQUIRE(m, kBadArg, "null model");

@@ -54,6 +54,7 @@ enum Epilogue : int {
   kEpiRelu2 = 1,   // h = half(acc); y = half(relu(h)^2)
   kEpiVres = 2,    // y = half(v + (v_first - v) * sigmoid(v0 + acc))
   kEpiF32 = 3,     // y32 = float(half(acc))   (logits)
+  kEpiRawF32 = 4,  // y32 = acc, not rounded: a partial sum another rank's partial is added to
 };
 
 struct EpiArgs {

@@ -79,7 +79,9 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
 // Applies the epilogue to one fp32 result: the layer's single rounding to half.
 __device__ __forceinline__ void emit(const GemmDev& p, int m, int n, float a) {
   const size_t o = static_cast<size_t>(m) * p.N + n;
-  if (p.epi == kEpiF32) {
+  if (p.epi == kEpiRawF32) {
+    static_cast<float*>(p.y)[o] = a;
+  } else if (p.epi == kEpiF32) {
     static_cast<float*>(p.y)[o] = __half2float(__float2half_rn(a));
   } else if (p.epi == kEpiRelu2) {
     const float t = fmaxf(__half2float(__float2half_rn(a)), 0.f);
@@ -199,6 +201,8 @@ __global__ void __launch_bounds__(kThreads) gemm_tc_kernel(const __grid_constant
           const size_t o = static_cast<size_t>(m0 + ml) * p.N + n;
           if (p.splits > 1) {
             *reinterpret_cast<float4*>(p.partial + static_cast<size_t>(blockIdx.z) * p.M * p.N + o) = a4;
+          } else if (p.epi == kEpiRawF32) {
+            *reinterpret_cast<float4*>(static_cast<float*>(p.y) + o) = make_float4(a[0], a[1], a[2], a[3]);
           } else if (p.epi == kEpiF32) {
             float4 o4;
             o4.x = __half2float(__float2half_rn(a[0])); o4.y = __half2float(__float2half_rn(a[1]));
@@ -318,7 +322,7 @@ int gemm_tc(cudaStream_t stream, const LinearArgs& a) {
   RK_REQUIRE(gemm_tc_supported(a), kShape, "gemm_tc: unsupported problem");
   const int ldx = a.ldx ? a.ldx : a.K;
   GemmDev p;
-  p.M = a.M; p.N = a.N; p.K = a.K; p.epi = a.epi; p.y = a.y; p.scale = nullptr;
+  p.M = a.M; p.N = a.N; p.K = a.K; p.epi = a.epi; p.y = a.y; p.scale = a.out_scale;
   p.v = a.ea.v; p.v_first = a.ea.v_first; p.v0 = a.ea.v0;
   p.Nt = pick_nt(a.M);
   const size_t stage_bytes = static_cast<size_t>(kBM) * 128 + static_cast<size_t>(p.Nt) * 128;

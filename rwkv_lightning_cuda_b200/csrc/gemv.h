@@ -61,7 +61,9 @@ struct GemvBatch {
 // Rounds and stores one fp32 accumulator: the single rounding point of a linear layer.
 __device__ __forceinline__ void store_result(const GemvSeg& sg, int m, int n, float a) {
   const size_t o = static_cast<size_t>(m) * sg.N + n;
-  if (sg.epi == kEpiF32) {
+  if (sg.epi == kEpiRawF32) {
+    static_cast<float*>(sg.y)[o] = a;
+  } else if (sg.epi == kEpiF32) {
     static_cast<float*>(sg.y)[o] = __half2float(__float2half_rn(a));
   } else if (sg.epi == kEpiRelu2) {
     const float t = fmaxf(__half2float(__float2half_rn(a)), 0.f);

@@ -28,6 +28,7 @@ struct RowOpArgs {
   int vocab = 0;
   const half* x = nullptr;          // [B*T,C]
   const half* residual = nullptr;   // optional, added to x in fp32
+  const float* residual_f32 = nullptr;  // instead of `residual`: fp32 values, rounded to half first (all-reduced partial sums)
   half* x_out = nullptr;            // optional: half(x + residual) or the gathered row
   // normalisation
   const half* ln_w = nullptr;
@@ -52,6 +53,8 @@ int tmix_lnx_rkvres_xg(cudaStream_t stream, int rows, int C, const half* y, cons
 int tmix_vres_gate(cudaStream_t stream, int rows, int C, const half* v, const half* v_first, const half* v0,
                    const half* v12, half* out);
 int advance_i32(cudaStream_t stream, int* x, int amount, int n);
+// src [G][B][Vl] (one block per rank, as an all-gather leaves it) -> dst [B][G*Vl]
+int interleave_gathered(cudaStream_t stream, const float* src, float* dst, int G, int B, int Vl);
 int relu_square(cudaStream_t stream, const half* x, half* out, long long n);
 int activate(cudaStream_t stream, const half* x, half* out, long long n, int act);  // half(tanh(x)) / half(sigmoid(x))
 int bf16_to_f16(cudaStream_t stream, const uint16_t* src, half* dst, long long n);
@@ -76,6 +79,11 @@ struct LinearArgs {
   // calls sharing it must not overlap on the GPU
   float* scratch = nullptr;
   size_t scratch_bytes = 0;
+  // optional: room for one dequantised fp16 copy of a W8A16/W4A16 matrix, used when rows > 4 (the weights are
+  // expanded once per call and fed to the tensor-core GEMM); and a per-output-channel factor for the accumulator
+  half* wq_scratch = nullptr;
+  size_t wq_scratch_bytes = 0;
+  const half* out_scale = nullptr;
   // optional fused prologue of the decode GEMV (M <= 4, fp16 weights, K == channels): see GemvSeg in gemv.h
   const half* res = nullptr;
   const half* ln_w = nullptr;
@@ -120,6 +128,7 @@ int tmix_decode(cudaStream_t stream, const TmixDecodeArgs& args);
 // ---- quant.cu
 int quant_pack_w8(cudaStream_t stream, int N, int K, const half* W, int8_t* q, half* scale);
 int quant_unpack_w8(cudaStream_t stream, int N, int K, const int8_t* q, const half* scale, half* W);
+int quant_unpack_w8_raw(cudaStream_t stream, int N, int K, const int8_t* q, half* W);  // half(q), scale not applied
 int quant_pack_w4(cudaStream_t stream, int N, int K, const half* W, uint8_t* q, half* scale, half* zero);
 int quant_unpack_w4(cudaStream_t stream, int N, int K, const uint8_t* q, const half* scale, const half* zero, half* W);
 

@@ -56,6 +56,8 @@ Workspace::~Workspace() {
 // ------------------------------------------------------------------ model
 Model::Model(const rwkv7_b200_config& cfg) : cfg_(cfg) {
   H_ = cfg.channels / kHead;
+  tp_size_ = cfg.tp_size > 1 ? cfg.tp_size : 1;
+  tp_rank_ = tp_size_ > 1 ? cfg.tp_rank : 0;
   layers_.resize(static_cast<size_t>(cfg.layers));
 }
 Model::~Model() {
@@ -96,6 +98,33 @@ int Model::upload_matrix(Matrix& m, int N, int K, const void* data, int dtype, l
   return upload(m.w, data, dtype, count, on_device, static_cast<long long>(N) * K);
 }
 
+// Copies the block [r0, r0+nr) x [c0, c0+nc) of a row-major [rows, cols] tensor (the caller always passes the whole
+// tensor; a tensor-parallel rank keeps only its share).
+int Model::upload_slice(DevBuf& dst, const void* data, int dtype, long long count, int on_device, int rows, int cols, int r0,
+                        int nr, int c0, int nc) {
+  if (nr == rows && nc == cols) return upload(dst, data, dtype, count, on_device, static_cast<long long>(rows) * cols);
+  RK_REQUIRE(count == static_cast<long long>(rows) * cols, kShape, "set_tensor: got %lld elements, expected %lld", count,
+             static_cast<long long>(rows) * cols);
+  RK_REQUIRE(dtype == RWKV7_B200_DT_F16 || dtype == RWKV7_B200_DT_BF16, kBadArg, "set_tensor: unknown dtype %d", dtype);
+  const size_t n = static_cast<size_t>(nr) * nc;
+  int s = dst.alloc(n * 2);
+  if (s != kOk) return s;
+  DevBuf tmp;
+  void* target = dst.p;
+  if (dtype == RWKV7_B200_DT_BF16) {
+    if ((s = tmp.alloc(n * 2)) != kOk) return s;
+    target = tmp.p;
+  }
+  const char* src = static_cast<const char*>(data) + (static_cast<size_t>(r0) * cols + c0) * 2;
+  RK_CUDA(cudaMemcpy2D(target, static_cast<size_t>(nc) * 2, src, static_cast<size_t>(cols) * 2, static_cast<size_t>(nc) * 2, nr,
+                       on_device ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice));
+  if (dtype == RWKV7_B200_DT_BF16) {
+    if ((s = bf16_to_f16(nullptr, tmp.as<uint16_t>(), dst.as<half>(), static_cast<long long>(n))) != kOk) return s;
+    RK_CUDA(cudaDeviceSynchronize());
+  }
+  return kOk;
+}
+
 int Model::set_tensor(const char* name, const void* data, int dtype, long long count, int on_device) {
   RK_REQUIRE(name && data, kBadArg, "set_tensor: null argument");
   RK_REQUIRE(!finalized_, kBadArg, "set_tensor: model already finalised");
@@ -115,7 +144,18 @@ int Model::set_tensor(const char* name, const void* data, int dtype, long long c
   }
   if (n == "ln_out.weight") return upload(ln_out_w_, data, dtype, count, on_device, C);
   if (n == "ln_out.bias") return upload(ln_out_b_, data, dtype, count, on_device, C);
-  if (n == "head.weight") return upload_matrix(head_, static_cast<int>(V), static_cast<int>(C), data, dtype, count, on_device);
+  // tensor parallel: this rank keeps heads [rank*H/G, (rank+1)*H/G), the matching slice of ffn and of the vocabulary
+  const int G = tp_size_, Cl = static_cast<int>(C) / G, Fl = static_cast<int>(F) / G, Vl = static_cast<int>(V) / G;
+  const int c_lo = tp_rank_ * Cl, f_lo = tp_rank_ * Fl, v_lo = tp_rank_ * Vl;
+  auto rows_of = [&](Matrix& m, int N, int K, int r0, int nr) {  // output-channel slice
+    m.N = nr; m.K = K; m.fmt = RWKV7_B200_FMT_F16;
+    return upload_slice(m.w, data, dtype, count, on_device, N, K, r0, nr, 0, K);
+  };
+  auto cols_of = [&](Matrix& m, int N, int K, int c0, int nc) {  // input-channel slice
+    m.N = N; m.K = nc; m.fmt = RWKV7_B200_FMT_F16;
+    return upload_slice(m.w, data, dtype, count, on_device, N, K, 0, N, c0, nc);
+  };
+  if (n == "head.weight") return rows_of(head_, static_cast<int>(V), static_cast<int>(C), v_lo, Vl);
 
   int layer = -1, off = 0;
   if (sscanf(name, "blocks.%d.%n", &layer, &off) < 1 || layer < 0 || layer >= cfg_.layers || off == 0) {
@@ -138,25 +178,34 @@ int Model::set_tensor(const char* name, const void* data, int dtype, long long c
   const VecSlot vecs[] = {
       {"ln1.weight", &L.ln1_w, C}, {"ln1.bias", &L.ln1_b, C}, {"ln2.weight", &L.ln2_w, C}, {"ln2.bias", &L.ln2_b, C},
       {"att.x_r", &L.mix[0], C}, {"att.x_w", &L.mix[1], C}, {"att.x_k", &L.mix[2], C}, {"att.x_v", &L.mix[3], C},
-      {"att.x_a", &L.mix[4], C}, {"att.x_g", &L.mix[5], C}, {"att.w0", &L.w0, C}, {"att.a0", &L.a0, C},
-      {"att.v0", &L.v0, C}, {"att.k_k", &L.k_k, C}, {"att.k_a", &L.k_a, C}, {"att.r_k", &L.r_k, C},
-      {"att.ln_x.weight", &L.lnx_w, C}, {"att.ln_x.bias", &L.lnx_b, C}, {"ffn.x_k", &L.ffn_x_k, C},
+      {"att.x_a", &L.mix[4], C}, {"att.x_g", &L.mix[5], C}, {"ffn.x_k", &L.ffn_x_k, C},
   };
   for (const VecSlot& v : vecs)
     if (key == v.key) return upload(*v.buf, data, dtype, count, on_device, v.n);
-  if (key == "att.receptance.weight") return upload_matrix(L.Wr, C, C, data, dtype, count, on_device);
-  if (key == "att.key.weight") return upload_matrix(L.Wk, C, C, data, dtype, count, on_device);
-  if (key == "att.value.weight") return upload_matrix(L.Wv, C, C, data, dtype, count, on_device);
-  if (key == "att.output.weight") return upload_matrix(L.Wo, C, C, data, dtype, count, on_device);
-  if (key == "ffn.key.weight") return upload_matrix(L.Wkey, F, C, data, dtype, count, on_device);
-  if (key == "ffn.value.weight") return upload_matrix(L.Wval, C, F, data, dtype, count, on_device);
-  struct LoraSlot { const char* key; long long n; };
-  const LoraSlot loras[] = {
-      {"att.w1", C * cfg_.rank_w}, {"att.w2", C * cfg_.rank_w}, {"att.a1", C * cfg_.rank_a}, {"att.a2", C * cfg_.rank_a},
-      {"att.g1", C * cfg_.rank_g}, {"att.g2", C * cfg_.rank_g}, {"att.v1", C * cfg_.rank_v}, {"att.v2", C * cfg_.rank_v},
+  const VecSlot per_head[] = {  // per-channel vectors applied after the projections: sliced with the heads
+      {"att.w0", &L.w0, C}, {"att.a0", &L.a0, C}, {"att.v0", &L.v0, C}, {"att.k_k", &L.k_k, C}, {"att.k_a", &L.k_a, C},
+      {"att.r_k", &L.r_k, C}, {"att.ln_x.weight", &L.lnx_w, C}, {"att.ln_x.bias", &L.lnx_b, C},
   };
-  for (const LoraSlot& l : loras)
-    if (key == l.key) return upload(lora_raw_[n], data, dtype, count, on_device, l.n);
+  for (const VecSlot& v : per_head)
+    if (key == v.key) return upload_slice(*v.buf, data, dtype, count, on_device, 1, static_cast<int>(C), 0, 1, c_lo, Cl);
+  const int Ci = static_cast<int>(C), Fi = static_cast<int>(F);
+  if (key == "att.receptance.weight") return rows_of(L.Wr, Ci, Ci, c_lo, Cl);
+  if (key == "att.key.weight") return rows_of(L.Wk, Ci, Ci, c_lo, Cl);
+  if (key == "att.value.weight") return rows_of(L.Wv, Ci, Ci, c_lo, Cl);
+  if (key == "att.output.weight") return cols_of(L.Wo, Ci, Ci, c_lo, Cl);
+  if (key == "ffn.key.weight") return rows_of(L.Wkey, Fi, Ci, f_lo, Fl);
+  if (key == "ffn.value.weight") return cols_of(L.Wval, Ci, Fi, f_lo, Fl);
+  struct LoraSlot { const char* key; int rank; bool up; };
+  const LoraSlot loras[] = {
+      {"att.w1", cfg_.rank_w, false}, {"att.w2", cfg_.rank_w, true}, {"att.a1", cfg_.rank_a, false}, {"att.a2", cfg_.rank_a, true},
+      {"att.g1", cfg_.rank_g, false}, {"att.g2", cfg_.rank_g, true}, {"att.v1", cfg_.rank_v, false}, {"att.v2", cfg_.rank_v, true},
+  };
+  for (const LoraSlot& l : loras) {
+    if (key != l.key) continue;
+    // down-projections [C, R] are replicated; up-projections [R, C] keep this rank's output channels
+    if (!l.up) return upload(lora_raw_[n], data, dtype, count, on_device, C * l.rank);
+    return upload_slice(lora_raw_[n], data, dtype, count, on_device, l.rank, Ci, 0, l.rank, c_lo, Cl);
+  }
   set_error("set_tensor: unknown tensor name '%s'", name);
   return kBadArg;
 }
@@ -195,7 +244,7 @@ int Model::finalize() {
   RK_REQUIRE(!finalized_, kBadArg, "finalize: called twice");
   int s = use_device();
   if (s != kOk) return s;
-  const int C = cfg_.channels, V = cfg_.vocab;
+  const int C = cfg_.channels, V = cfg_.vocab, Cl = C / tp_size_;
   if (!emb_ln0_.p) {
     RK_REQUIRE(emb_raw_.p && ln0_w_raw_.p && ln0_b_raw_.p, kNotReady, "finalize: need emb_ln0 or emb.weight + blocks.0.ln0.*");
     if ((s = emb_ln0_.alloc(static_cast<size_t>(V) * C * 2)) != kOk) return s;
@@ -212,9 +261,9 @@ int Model::finalize() {
     struct T { const char* key; DevBuf* dst; int rows, cols; };
     // checkpoint: x1 [C,R] (down), x2 [R,C] (up); device: down [R,C], up [C,R]
     const T ts[] = {
-        {"w1", &L.w1t, C, cfg_.rank_w}, {"w2", &L.w2t, cfg_.rank_w, C}, {"a1", &L.a1t, C, cfg_.rank_a},
-        {"a2", &L.a2t, cfg_.rank_a, C}, {"g1", &L.g1t, C, cfg_.rank_g}, {"g2", &L.g2t, cfg_.rank_g, C},
-        {"v1", &L.v1t, C, cfg_.rank_v}, {"v2", &L.v2t, cfg_.rank_v, C},
+        {"w1", &L.w1t, C, cfg_.rank_w}, {"w2", &L.w2t, cfg_.rank_w, Cl}, {"a1", &L.a1t, C, cfg_.rank_a},
+        {"a2", &L.a2t, cfg_.rank_a, Cl}, {"g1", &L.g1t, C, cfg_.rank_g}, {"g2", &L.g2t, cfg_.rank_g, Cl},
+        {"v1", &L.v1t, C, cfg_.rank_v}, {"v2", &L.v2t, cfg_.rank_v, Cl},
     };
     for (const T& t : ts) {
       if (li == 0 && t.key[0] == 'v') continue;  // layer 0 has no value residual
@@ -237,10 +286,17 @@ int Model::finalize() {
   return kOk;
 }
 
+int Model::tp_init(const void* unique_id) {
+  RK_REQUIRE(tp_size_ > 1, kBadArg, "tp_init: the model was created with tp_size <= 1");
+  int s = use_device();
+  if (s != kOk) return s;
+  return tp_.init(unique_id, tp_rank_, tp_size_);
+}
+
 int Model::state_sizes(int B, size_t* shift_elems, size_t* wkv_elems, size_t* elapsed_elems) const {
   RK_REQUIRE(B > 0, kBadArg, "batch_size must be positive");
   if (shift_elems) *shift_elems = static_cast<size_t>(cfg_.layers) * 2 * B * cfg_.channels;
-  if (wkv_elems) *wkv_elems = static_cast<size_t>(cfg_.layers) * B * H_ * kHead * kHead;
+  if (wkv_elems) *wkv_elems = static_cast<size_t>(cfg_.layers) * B * (H_ / tp_size_) * kHead * kHead;
   if (elapsed_elems) *elapsed_elems = static_cast<size_t>(B);
   return kOk;
 }
@@ -267,7 +323,7 @@ int Model::copy_state_slice(const void* src_shift, const void* src_wkv, const in
   int s = use_device();
   if (s != kOk) return s;
   const size_t C = static_cast<size_t>(cfg_.channels);
-  const size_t lane = static_cast<size_t>(H_) * kHead * kHead * (cfg_.wkv32 ? 4 : 2);
+  const size_t lane = static_cast<size_t>(H_ / tp_size_) * kHead * kHead * (cfg_.wkv32 ? 4 : 2);
   // one strided copy per buffer: [layers*2] rows of count*C halves, [layers] rows of count*lane bytes
   RK_CUDA(cudaMemcpy2DAsync(static_cast<char*>(dst_shift) + static_cast<size_t>(dst_off) * C * 2, static_cast<size_t>(dst_B) * C * 2,
                             static_cast<const char*>(src_shift) + static_cast<size_t>(src_off) * C * 2, static_cast<size_t>(src_B) * C * 2,
@@ -294,7 +350,7 @@ int Model::query_capacity(int chunk, rwkv7_b200_capacity* out) const {
   if (s != kOk) return s;
   RK_CUDA(cudaMemGetInfo(&out->free_vram_bytes, &out->total_vram_bytes));
   const size_t L = cfg_.layers, C = cfg_.channels;
-  const size_t state = L * 2 * C * 2 + L * H_ * kHead * kHead * (cfg_.wkv32 ? 4 : 2) + sizeof(int);
+  const size_t state = L * 2 * C * 2 + L * (H_ / tp_size_) * kHead * kHead * (cfg_.wkv32 ? 4 : 2) + sizeof(int);
   const size_t arena = workspace_halves(cfg_, static_cast<size_t>(chunk), 1) * 2 + static_cast<size_t>(chunk) * 8;
   out->bytes_per_batch = state + arena + static_cast<size_t>(cfg_.vocab) * 4;
   out->reserve_vram_bytes = std::max<size_t>(static_cast<size_t>(512) << 20, out->free_vram_bytes / 10);
@@ -326,9 +382,17 @@ Workspace* Model::workspace(int B, int T) {
   ws->xf = take(static_cast<size_t>(B) * C);
   ws->n1 = take(RC); ws->n2 = take(RC);
   ws->tokens = reinterpret_cast<int64_t*>(take(rows * 4 + 8));
+  if (tp_size_ > 1) {
+    const size_t n = std::max(rows * C, static_cast<size_t>(B) * cfg_.vocab * 2);
+    if (ws->part32.alloc(n * sizeof(float)) != kOk) return nullptr;
+  }
   if (rows > 4) {
     const size_t want = std::min<size_t>(static_cast<size_t>(256) << 20, rows * C * sizeof(float) * 8);
     if (ws->gemm_scratch.alloc(want) != kOk) return nullptr;
+    if (cfg_.weight_format != RWKV7_B200_FMT_F16) {
+      const size_t big = std::max(static_cast<size_t>(cfg_.vocab) * C, F * C) * sizeof(half);
+      if (ws->wq_scratch.alloc(big) != kOk) return nullptr;
+    }
   }
   for (int i = 0; i < Workspace::kSlots; ++i) {
     if (cudaMallocHost(&ws->tokens_pinned[i], rows * sizeof(int64_t)) != cudaSuccess) return nullptr;
@@ -343,7 +407,10 @@ int Model::lin(cudaStream_t s, int M, const Matrix& W, const half* x, void* y, i
   LinearArgs a;
   a.M = M; a.K = W.K; a.N = W.N; a.x = x; a.w = W.w.p; a.fmt = W.fmt;
   a.scale = W.scale.as<half>(); a.zero = W.zero.as<half>(); a.epi = epi; a.y = y;
-  if (cur_) { a.scratch = cur_->gemm_scratch.as<float>(); a.scratch_bytes = cur_->gemm_scratch.bytes; }
+  if (cur_) {
+    a.scratch = cur_->gemm_scratch.as<float>(); a.scratch_bytes = cur_->gemm_scratch.bytes;
+    a.wq_scratch = cur_->wq_scratch.as<half>(); a.wq_scratch_bytes = cur_->wq_scratch.bytes;
+  }
   return linear(s, a);
 }
 
@@ -457,14 +524,15 @@ int Model::enqueue_decode(Workspace& ws, int B, half* shift, void* wkv, int* ela
 
 int Model::enqueue(Workspace& ws, int B, int T, half* shift, void* wkv, int* elapsed, float* logits, cudaStream_t st) {
   const int C = cfg_.channels, L = cfg_.layers, rows = B * T;
+  const int G = tp_size_, Cl = C / G, Hl = H_ / G;  // this rank's share of channels / heads
   const EpiArgs none;
   cur_ = &ws;
   {
     TmixDecodeArgs probe;
     probe.B = B; probe.C = C; probe.wkv32 = cfg_.wkv32 != 0;
     probe.R[0] = cfg_.rank_w; probe.R[1] = cfg_.rank_a; probe.R[2] = cfg_.rank_g; probe.R[3] = cfg_.rank_v;
-    if (T == 1 && rows <= 4 && cfg_.weight_format == RWKV7_B200_FMT_F16 && tmix_decode_supported(probe) && C <= 4096 &&
-        C % 8 == 0)
+    if (G == 1 && T == 1 && rows <= 4 && cfg_.weight_format == RWKV7_B200_FMT_F16 && tmix_decode_supported(probe) &&
+        C <= 4096 && C % 8 == 0)
       return enqueue_decode(ws, B, shift, wkv, elapsed, logits, st);
   }
   {
@@ -481,11 +549,11 @@ int Model::enqueue(Workspace& ws, int B, int T, half* shift, void* wkv, int* ela
     half* shift1 = shift0 + static_cast<size_t>(B) * C;
     half *xr = ws.xm[0], *xw = ws.xm[1], *xk = ws.xm[2], *xv = ws.xm[3], *xa = ws.xm[4], *xg = ws.xm[5];
     half* v_lin = li == 0 ? ws.vfirst : ws.v;
-    const size_t wkv_off = static_cast<size_t>(li) * B * H_ * kHead * kHead;
+    const size_t wkv_off = static_cast<size_t>(li) * B * Hl * kHead * kHead;
     TmixDecodeArgs ta;
     ta.B = B; ta.C = C; ta.layer0 = li == 0; ta.wkv32 = cfg_.wkv32 != 0;
     ta.R[0] = cfg_.rank_w; ta.R[1] = cfg_.rank_a; ta.R[2] = cfg_.rank_g; ta.R[3] = cfg_.rank_v;
-    if (T == 1 && rows <= 4 && tmix_decode_supported(ta)) {
+    if (G == 1 && T == 1 && rows <= 4 && tmix_decode_supported(ta)) {
       // decode: r/k/v projections and the LoRA down-projections as one launch, then the fused head kernel
       auto mat = [&](const Matrix& Wm, const half* x, half* y) {
         LinearArgs a;
@@ -523,46 +591,62 @@ int Model::enqueue(Workspace& ws, int B, int T, half* shift, void* wkv, int* ela
         RK_TRY(activate(st, ws.l1[0], ws.l1[0], static_cast<long long>(rows) * cfg_.rank_w, kActTanh));
         RK_TRY(activate(st, ws.l1[2], ws.l1[2], static_cast<long long>(rows) * cfg_.rank_g, kActSigmoid));
       }
-      RK_TRY(lin16(st, rows, cfg_.rank_w, C, ws.l1[0], W.w2t.as<half>(), ws.w12, big ? kActNone : kActTanh, kEpiNone, none));
-      RK_TRY(lin16(st, rows, cfg_.rank_a, C, ws.l1[1], W.a2t.as<half>(), ws.a12, kActNone, kEpiNone, none));
-      RK_TRY(lin16(st, rows, cfg_.rank_g, C, ws.l1[2], W.g2t.as<half>(), ws.g, big ? kActNone : kActSigmoid, kEpiNone, none));
+      RK_TRY(lin16(st, rows, cfg_.rank_w, Cl, ws.l1[0], W.w2t.as<half>(), ws.w12, big ? kActNone : kActTanh, kEpiNone, none));
+      RK_TRY(lin16(st, rows, cfg_.rank_a, Cl, ws.l1[1], W.a2t.as<half>(), ws.a12, kActNone, kEpiNone, none));
+      RK_TRY(lin16(st, rows, cfg_.rank_g, Cl, ws.l1[2], W.g2t.as<half>(), ws.g, big ? kActNone : kActSigmoid, kEpiNone, none));
       const half* v_use = ws.vfirst;
       if (li > 0) {
         RK_TRY(lin16(st, rows, C, cfg_.rank_v, xv, W.v1t.as<half>(), ws.l1[3], kActNone, kEpiNone, none));
         if (big) {
-          RK_TRY(lin16(st, rows, cfg_.rank_v, C, ws.l1[3], W.v2t.as<half>(), ws.y, kActNone, kEpiNone, none));
-          RK_TRY(tmix_vres_gate(st, rows, C, ws.v, ws.vfirst, W.v0.as<half>(), ws.y, ws.vout));
+          RK_TRY(lin16(st, rows, cfg_.rank_v, Cl, ws.l1[3], W.v2t.as<half>(), ws.y, kActNone, kEpiNone, none));
+          RK_TRY(tmix_vres_gate(st, rows, Cl, ws.v, ws.vfirst, W.v0.as<half>(), ws.y, ws.vout));
         } else {
           EpiArgs ea;
           ea.v = ws.v; ea.v_first = ws.vfirst; ea.v0 = W.v0.as<half>();
-          RK_TRY(lin16(st, rows, cfg_.rank_v, C, ws.l1[3], W.v2t.as<half>(), ws.vout, kActNone, kEpiVres, ea));
+          RK_TRY(lin16(st, rows, cfg_.rank_v, Cl, ws.l1[3], W.v2t.as<half>(), ws.vout, kActNone, kEpiVres, ea));
         }
         v_use = ws.vout;
       }
-      RK_TRY(tmix_kk_a_gate(st, rows, C, ws.k, W.k_k.as<half>(), W.a0.as<half>(), ws.a12, W.k_a.as<half>(), ws.k2, ws.nkk, ws.kka));
+      RK_TRY(tmix_kk_a_gate(st, rows, Cl, ws.k, W.k_k.as<half>(), W.a0.as<half>(), ws.a12, W.k_a.as<half>(), ws.k2, ws.nkk, ws.kka));
       if (cfg_.wkv32) {
-        RK_TRY(wkv7_fp32(st, B, T, C, H_, static_cast<float*>(wkv) + wkv_off, ws.r, ws.w12, W.w0.as<half>(), ws.k2, v_use,
+        RK_TRY(wkv7_fp32(st, B, T, Cl, Hl, static_cast<float*>(wkv) + wkv_off, ws.r, ws.w12, W.w0.as<half>(), ws.k2, v_use,
                          ws.nkk, ws.kka, ws.y));
       } else {
         // the reference adds w0 in fp32 inside the kernel for T <= 16 and pre-rounds the sum otherwise
-        RK_TRY(wkv7_fp16(st, B, T, C, H_, static_cast<half*>(wkv) + wkv_off, ws.r, ws.w12, W.w0.as<half>(), T <= 16 ? 1 : 2,
+        RK_TRY(wkv7_fp16(st, B, T, Cl, Hl, static_cast<half*>(wkv) + wkv_off, ws.r, ws.w12, W.w0.as<half>(), T <= 16 ? 1 : 2,
                          ws.k2, v_use, ws.nkk, ws.kka, ws.y, elapsed));
       }
-      RK_TRY(tmix_lnx_rkvres_xg(st, rows, C, ws.y, ws.r, ws.k2, v_use, W.r_k.as<half>(), W.lnx_w.as<half>(), W.lnx_b.as<half>(),
+      RK_TRY(tmix_lnx_rkvres_xg(st, rows, Cl, ws.y, ws.r, ws.k2, v_use, W.r_k.as<half>(), W.lnx_w.as<half>(), W.lnx_b.as<half>(),
                                 ws.g, ws.y2));
     }
-    RK_TRY(lin(st, rows, W.Wo, ws.y2, ws.att, kEpiNone));
+    // Tensor parallel: att.output and ffn.value see only this rank's slice of their input, so they emit fp32
+    // partial sums that are added across ranks (NCCL) and rounded to half once, like the single-GPU layer.
+    if (G == 1) {
+      RK_TRY(lin(st, rows, W.Wo, ws.y2, ws.att, kEpiNone));
+    } else {
+      RK_TRY(lin(st, rows, W.Wo, ws.y2, ws.part32.p, kEpiRawF32));
+      RK_TRY(tp_.all_reduce_sum(ws.part32.as<float>(), static_cast<size_t>(rows) * C, st));
+    }
     {
       RowOpArgs a;
-      a.B = B; a.T = T; a.C = C; a.x = ws.xA; a.residual = ws.att; a.x_out = ws.xB;
+      a.B = B; a.T = T; a.C = C; a.x = ws.xA; a.x_out = ws.xB;
+      if (G == 1) a.residual = ws.att;
+      else a.residual_f32 = ws.part32.as<float>();
       a.ln_w = W.ln2_w.as<half>(); a.ln_b = W.ln2_b.as<half>(); a.shift = shift1; a.n_mix = 1;
       a.mix[0] = W.ffn_x_k.as<half>(); a.mix_out[0] = ws.mixed;
       RK_TRY(row_op(st, a));
     }
     RK_TRY(lin(st, rows, W.Wkey, ws.mixed, ws.hid, kEpiRelu2));
-    RK_TRY(lin(st, rows, W.Wval, ws.hid, ws.ffn, kEpiNone));
     RowOpArgs a;
-    a.B = B; a.T = T; a.C = C; a.x = ws.xB; a.residual = ws.ffn;
+    a.B = B; a.T = T; a.C = C; a.x = ws.xB;
+    if (G == 1) {
+      RK_TRY(lin(st, rows, W.Wval, ws.hid, ws.ffn, kEpiNone));
+      a.residual = ws.ffn;
+    } else {
+      RK_TRY(lin(st, rows, W.Wval, ws.hid, ws.part32.p, kEpiRawF32));
+      RK_TRY(tp_.all_reduce_sum(ws.part32.as<float>(), static_cast<size_t>(rows) * C, st));
+      a.residual_f32 = ws.part32.as<float>();
+    }
     if (li + 1 < L) {
       const LayerWeights& Nx = layers_[static_cast<size_t>(li) + 1];
       a.x_out = ws.xA; a.ln_w = Nx.ln1_w.as<half>(); a.ln_b = Nx.ln1_b.as<half>();
@@ -574,7 +658,17 @@ int Model::enqueue(Workspace& ws, int B, int T, half* shift, void* wkv, int* ela
     RK_TRY(row_op(st, a));
   }
   RK_TRY(advance_i32(st, elapsed, T, B));
-  RK_TRY(lin(st, B, head_, ws.xf, logits, kEpiF32));
+  if (G == 1) {
+    RK_TRY(lin(st, B, head_, ws.xf, logits, kEpiF32));
+  } else {
+    // every rank computes its slice of the vocabulary; gather [G][B][V/G] and interleave to [B][V]
+    const int Vl = cfg_.vocab / G;
+    float* loc = ws.part32.as<float>();
+    float* all = loc + static_cast<size_t>(B) * Vl;
+    RK_TRY(lin(st, B, head_, ws.xf, loc, kEpiF32));
+    RK_TRY(tp_.all_gather(loc, all, static_cast<size_t>(B) * Vl, st));
+    RK_TRY(interleave_gathered(st, all, logits, G, B, Vl));
+  }
   return kOk;
 }
 
@@ -600,7 +694,8 @@ int Model::forward(const int64_t* tokens_host, int B, int T, void* shift, void* 
   RK_CUDA(cudaMemcpyAsync(ws->tokens, ws->tokens_pinned[slot], static_cast<size_t>(rows) * sizeof(int64_t), cudaMemcpyHostToDevice, stream));
   RK_CUDA(cudaEventRecord(ws->tokens_copied[slot], stream));
 
-  if (T != 1 || stream == nullptr) {
+  // tensor-parallel steps are enqueued directly: their collectives are not recorded into graphs here
+  if (T != 1 || stream == nullptr || tp_size_ > 1) {
     const long long before = launch_counter();
     s = enqueue(*ws, B, T, static_cast<half*>(shift), wkv, elapsed, logits, stream);
     launches_ += launch_counter() - before;

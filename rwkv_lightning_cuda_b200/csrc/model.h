@@ -12,6 +12,7 @@
 
 #include "../../include/rwkv7_b200.h"
 #include "kernels.h"
+#include "tp_comm.h"
 
 namespace rk {
 
@@ -56,6 +57,8 @@ struct Workspace {
   half *hid, *l1[4], *xf, *n1, *n2;
   int64_t* tokens;
   DevBuf gemm_scratch;  // split-K partial sums of the tensor-core GEMM (rows > 4)
+  DevBuf wq_scratch;    // one dequantised fp16 matrix (quantised weights, rows > 4)
+  DevBuf part32;        // tensor parallel: fp32 partial sums [rows, C] / gathered logits
   // ring of pinned host staging slots for the token ids; a slot is reused only after the copy
   // that read it has completed, so callers may overwrite their token array as soon as forward returns
   static constexpr int kSlots = 4;
@@ -80,6 +83,7 @@ class Model {
                        void* dst_shift, void* dst_wkv, int* dst_elapsed, int dst_B, int dst_off, int count,
                        cudaStream_t stream) const;
   int query_capacity(int chunk, rwkv7_b200_capacity* out) const;
+  int tp_init(const void* unique_id);  // joins the tensor-parallel group (collective over all ranks)
 
   const rwkv7_b200_config& cfg() const { return cfg_; }
   long long launches() const { return launches_; }
@@ -101,6 +105,8 @@ class Model {
   int use_device() const;
   int upload(DevBuf& dst, const void* data, int dtype, long long count, int on_device, long long expect);
   int upload_matrix(Matrix& m, int N, int K, const void* data, int dtype, long long count, int on_device);
+  int upload_slice(DevBuf& dst, const void* data, int dtype, long long count, int on_device, int rows, int cols, int r0, int nr,
+                   int c0, int nc);
   int transpose_into(DevBuf& dst, const DevBuf& src, int rows, int cols);
   int quantize(Matrix& m);
   Workspace* workspace(int B, int T);
@@ -112,6 +118,8 @@ class Model {
 
   rwkv7_b200_config cfg_;
   int H_ = 0;
+  int tp_size_ = 1, tp_rank_ = 0;
+  TpComm tp_;
   bool finalized_ = false;
   std::vector<LayerWeights> layers_;
   DevBuf emb_ln0_, ln_out_w_, ln_out_b_;

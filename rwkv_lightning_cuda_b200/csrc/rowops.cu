@@ -13,6 +13,8 @@
 // Rounding points follow the reference: the sum x + residual and the LayerNorm output are each
 // rounded to half once, the interpolation reads the rounded LayerNorm output.
 #include "common.cuh"
+#include <algorithm>
+
 #include "kernels.h"
 
 namespace rk {
@@ -27,6 +29,7 @@ struct RowOpDev {
   const half* table;
   const half* x;
   const half* residual;
+  const float* residual_f32;  // alternative residual: fp32 sums, rounded to half before they are added
   half* x_out;
   const half* ln_w;
   const half* ln_b;
@@ -58,12 +61,17 @@ __device__ __forceinline__ void load_row(const RowOpDev& p, int b, int t, float2
   } else {
     const __half2* xs = reinterpret_cast<const __half2*>(p.x + row * p.C);
     const __half2* rs = p.residual ? reinterpret_cast<const __half2*>(p.residual + row * p.C) : nullptr;
+    const float2* rf = p.residual_f32 ? reinterpret_cast<const float2*>(p.residual_f32 + row * p.C) : nullptr;
     __half2 xv[kPairs], rv[kPairs];
 #pragma unroll
     for (int i = 0; i < kPairs; ++i) {
       const int q = threadIdx.x + kRowThreads * i;
       xv[i] = q < pairs ? xs[q] : __floats2half2_rn(0.f, 0.f);
       rv[i] = (rs && q < pairs) ? rs[q] : __floats2half2_rn(0.f, 0.f);
+      if (rf && q < pairs) {
+        const float2 t = rf[q];
+        rv[i] = __floats2half2_rn(t.x, t.y);
+      }
     }
 #pragma unroll
     for (int i = 0; i < kPairs; ++i) {
@@ -341,7 +349,7 @@ int row_op(cudaStream_t stream, const RowOpArgs& a) {
   RK_REQUIRE(!(a.ln_w && a.identity_norm), kBadArg, "row_op: identity_norm excludes LayerNorm weights");
   RowOpDev p;
   p.B = a.B; p.T = a.T; p.C = a.C; p.vocab = a.vocab; p.n_mix = a.n_mix; p.last_only = a.last_only ? 1 : 0; p.identity = a.identity_norm ? 1 : 0;
-  p.eps = a.eps; p.tokens = a.tokens; p.table = a.table; p.x = a.x; p.residual = a.residual; p.x_out = a.x_out;
+  p.eps = a.eps; p.tokens = a.tokens; p.table = a.table; p.x = a.x; p.residual = a.residual; p.residual_f32 = a.residual_f32; p.x_out = a.x_out;
   p.ln_w = a.ln_w; p.ln_b = a.ln_b; p.n_out = a.n_out; p.shift = a.shift; p.bad_token_flag = a.bad_token_flag;
   for (int m = 0; m < 6; ++m) {
     p.mix[m] = a.mix[m];
@@ -396,6 +404,26 @@ int tmix_vres_gate(cudaStream_t stream, int rows, int C, const half* v, const ha
   const long long total = static_cast<long long>(rows) * C;
   vres_gate_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, stream>>>(C, total, v, v_first, v0, v12, out);
   RK_LAUNCH_CHECK("vres_gate launch");
+  return kOk;
+}
+
+__global__ void interleave_gathered_kernel(const float4* __restrict__ src, float4* __restrict__ dst, int G, int B, int Vl4) {
+  const long long n = static_cast<long long>(G) * B * Vl4;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int v = static_cast<int>(i % Vl4);
+    const int b = static_cast<int>((i / Vl4) % B);
+    const int g = static_cast<int>(i / (static_cast<long long>(Vl4) * B));
+    dst[(static_cast<long long>(b) * G + g) * Vl4 + v] = src[i];
+  }
+}
+
+int interleave_gathered(cudaStream_t stream, const float* src, float* dst, int G, int B, int Vl) {
+  RK_REQUIRE(src && dst && G > 0 && B > 0 && Vl > 0 && Vl % 4 == 0, kBadArg, "interleave_gathered: bad argument");
+  const long long n = static_cast<long long>(G) * B * (Vl / 4);
+  const int blocks = static_cast<int>(std::min<long long>((n + 255) / 256, 148 * 8));
+  interleave_gathered_kernel<<<blocks, 256, 0, stream>>>(reinterpret_cast<const float4*>(src), reinterpret_cast<float4*>(dst), G, B, Vl / 4);
+  RK_LAUNCH_CHECK("interleave_gathered launch");
   return kOk;
 }
 

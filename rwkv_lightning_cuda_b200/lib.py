@@ -43,6 +43,8 @@ SIGNATURES = {
     "rwkv7_b200_model_create": [C.POINTER(Config), C.POINTER(_vp)],
     "rwkv7_b200_model_set_tensor": [_vp, C.c_char_p, _vp, _i, _ll, _i],
     "rwkv7_b200_model_finalize": [_vp],
+    "rwkv7_b200_tp_unique_id": [_vp],
+    "rwkv7_b200_model_tp_init": [_vp, _vp],
     "rwkv7_b200_model_destroy": [_vp],
     "rwkv7_b200_vocab_size": [_vp],
     "rwkv7_b200_state_sizes": [_vp, _i, C.POINTER(C.c_size_t), C.POINTER(C.c_size_t), C.POINTER(C.c_size_t)],

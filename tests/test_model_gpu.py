@@ -14,7 +14,7 @@ pytestmark = pytest.mark.gpu
 TINY = dict(layers=3, channels=128, ffn=512, vocab=320, rank_w=32, rank_a=32, rank_v=16, rank_g=64)
 
 
-def build_pair(fmt, wkv32, seed=0, dims=TINY):
+def build_pair(fmt, wkv32, seed=0, dims=TINY, **backend_kw):
     from rwkv_lightning_cuda_b200 import backend as bk, synthetic
     d = bk.ModelDims(**dims)
     ck = synthetic.make_checkpoint(d, seed=seed, device="cpu", dtype=torch.float16)
@@ -29,7 +29,7 @@ def build_pair(fmt, wkv32, seed=0, dims=TINY):
             continue
         om.set(name, t.numpy())
         dev_tensors[name] = t
-    gm = bk.ModelBackend(d, dev_tensors, use_wkv32=wkv32, weight_format=fmt)
+    gm = bk.ModelBackend(d, dev_tensors, use_wkv32=wkv32, weight_format=fmt, **backend_kw)
     return d, om, gm
 
 
@@ -74,10 +74,11 @@ def test_forward_matches_oracle_fp16_weights(wkv32, B, chunks, n_decode):
     assert np.abs(g_wkv - wkv.astype(np.float32)).max() <= 2e-2 * max(1.0, np.abs(wkv.astype(np.float32)).max())
 
 
+@pytest.mark.parametrize("B,chunks", [(2, (3,)), (3, (6, 2))])     # second case: more than four rows -> tensor-core path
 @pytest.mark.parametrize("fmt", [orc.FMT_W8A16, orc.FMT_W4A16])
-def test_forward_matches_oracle_quantised(fmt):
+def test_forward_matches_oracle_quantised(fmt, B, chunks):
     d, om, gm = build_pair(fmt, False)
-    worst, ids_ok, _, _ = run_both(d, om, gm, False, 2, (3,), 4)
+    worst, ids_ok, _, _ = run_both(d, om, gm, False, B, chunks, 4)
     print(f"[parity] model fmt={fmt}: worst logit err {worst:.3e}")
     assert worst < 2e-2
     assert ids_ok

@@ -31,3 +31,55 @@ def test_slowest_rank_sets_the_whole_job_rate():
         ms, e2e, rate = out[0]
         assert ms == 3.0 and e2e == 5.0            # max over ranks of each time
         assert rate == world * 4 / 3.0e-3          # both replicas' tokens over the slowest rank's step time
+
+
+def _tp_worker(rank, world, port, out):
+    """Each rank evaluates its share of a (projection -> per-head op -> output projection) chain and of the FFN on
+    its slice of the weights; the sum over ranks must equal the unsharded result."""
+    sys.path.insert(0, ROOT)
+    import numpy as np
+    from rwkv_lightning_cuda_b200 import tp
+    from rwkv_lightning_cuda_b200.backend import ModelDims
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    d = ModelDims(layers=1, channels=256, ffn=512, vocab=64, rank_w=8, rank_a=8, rank_v=8, rank_g=8)
+    rng = np.random.default_rng(7)           # same seed on every rank: the "checkpoint"
+    C, F = d.channels, d.ffn
+    full = {"blocks.0.att.receptance.weight": rng.standard_normal((C, C)), "blocks.0.att.output.weight": rng.standard_normal((C, C)),
+            "blocks.0.att.w2": rng.standard_normal((8, C)), "blocks.0.att.r_k": rng.standard_normal((d.heads, 64)),
+            "blocks.0.att.k_k": rng.standard_normal(C), "blocks.0.ffn.key.weight": rng.standard_normal((F, C)),
+            "blocks.0.ffn.value.weight": rng.standard_normal((C, F)), "head.weight": rng.standard_normal((d.vocab, C)),
+            "blocks.0.ln1.weight": rng.standard_normal(C)}
+    x = rng.standard_normal((3, C)); low = rng.standard_normal((3, 8))
+
+    def chain(w):
+        r = x @ w["blocks.0.att.receptance.weight"].T                     # [3, Cl]
+        r = r * w["blocks.0.att.k_k"] + low @ w["blocks.0.att.w2"]        # per-channel vector and LoRA up follow the heads
+        hl = w["blocks.0.att.r_k"].shape[0]
+        r = (r.reshape(3, hl, 64) * w["blocks.0.att.r_k"]).reshape(3, -1)  # per-head parameter
+        att = r @ w["blocks.0.att.output.weight"].T                       # partial sum over this rank's channels
+        hid = np.maximum(x @ w["blocks.0.ffn.key.weight"].T, 0) ** 2
+        return att, hid @ w["blocks.0.ffn.value.weight"].T, x @ w["head.weight"].T
+
+    mine = {k: tp.take_shard(k, v, d, rank, world) for k, v in full.items()}
+    assert mine["blocks.0.ln1.weight"] is full["blocks.0.ln1.weight"]     # replicated
+    att, ffn, logits = chain(mine)
+    att_t, ffn_t = torch.from_numpy(att.copy()), torch.from_numpy(ffn.copy())
+    dist.all_reduce(att_t); dist.all_reduce(ffn_t)
+    parts = [torch.zeros(3, d.vocab // world, dtype=torch.float64) for _ in range(world)]
+    dist.all_gather(parts, torch.from_numpy(logits.copy()))
+    want_att, want_ffn, want_logits = chain(full)
+    out[rank] = (float(np.abs(att_t.numpy() - want_att).max()), float(np.abs(ffn_t.numpy() - want_ffn).max()),
+                 float(np.abs(torch.cat(parts, 1).numpy() - want_logits).max()))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_head_sharded_partial_sums_add_up():
+    world = 2
+    with mp.Manager() as m:
+        out = m.dict()
+        mp.spawn(_tp_worker, args=(world, 29533, out), nprocs=world, join=True)
+        for rank in range(world):
+            assert max(out[rank]) < 1e-9, out[rank]
