@@ -105,11 +105,19 @@ def whole_job_rate(world, batch_per_gpu, ms_per_step):
     return world * batch_per_gpu / (ms_per_step * 1e-3)
 
 
-def build_model(args, dev_index, seed):
+def build_model(args, dev_index, seed, tp_rank=0, tp_size=1):
     from rwkv_lightning_cuda_b200 import backend as bk, synthetic, lib as L
     d = synthetic.CONFIGS[args.model]
+    if args.layers or args.vocab:          # reduced-depth timing aid for per-layer work; never a bench line
+        d = bk.ModelDims(args.layers or d.layers, d.channels, d.ffn, args.vocab or d.vocab, d.rank_w, d.rank_a, d.rank_v, d.rank_g)
     fmt = {"f16": L.FMT_F16, "w8a16": L.FMT_W8A16, "w4a16": L.FMT_W4A16}[args.fmt]
-    gm = bk.ModelBackend(d, None, use_wkv32=bool(args.wkv32), weight_format=fmt, device=dev_index, finalize=False)
+    ident = None
+    if tp_size > 1:                       # rank 0 makes the communicator id, the others receive it
+        box = [bk.tp_unique_id() if tp_rank == 0 else None]
+        dist.broadcast_object_list(box, src=0)
+        ident = box[0]
+    gm = bk.ModelBackend(d, None, use_wkv32=bool(args.wkv32), weight_format=fmt, device=dev_index, finalize=False,
+                         tp_rank=tp_rank, tp_size=tp_size, tp_unique_id=ident)
     gen = torch.Generator(device="cuda")
     gen.manual_seed(seed)
     for name, shape in synthetic.tensor_shapes(d).items():
@@ -208,7 +216,8 @@ def run_ours(args, rank, world, local_rank):
         "metric": "decode_tokens_per_s", "value": whole_job_rate(world, B, ms), "unit": "tok/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f16" if fmt == 0 else args.fmt, "data": "synthetic",
-        "config": {"workload": f"RWKV-7 {args.model} random-init, decode, batch {B} per GPU, {'fp32' if args.wkv32 else 'fp16'} WKV state, weights {args.fmt}",
+        "config": {"reduced": {"layers": args.layers, "vocab": args.vocab} if (args.layers or args.vocab) else None,
+                   "workload": f"RWKV-7 {args.model} random-init, decode, batch {B} per GPU, {'fp32' if args.wkv32 else 'fp16'} WKV state, weights {args.fmt}",
                    "batch_per_gpu": B, "parallelism": f"replicas x{world} (batch-sharded, no collective)",
                    "l2": "inputs larger than L2 (every step streams all weights)"},
         "clocks": clocks,
@@ -223,6 +232,70 @@ def run_ours(args, rank, world, local_rank):
     if world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline(args)
     print(json.dumps(line))
+
+
+def run_prefill(args, rank, world, local_rank):
+    """Secondary line (not the headline metric): chunked prefill of one long prompt.  With --tp the ranks form one
+    head-sharded tensor-parallel group working on the same prompt (strong scaling); without it every rank prefills
+    its own prompt (weak scaling)."""
+    from rwkv_lightning_cuda_b200 import backend as bk
+    tp = world if args.tp else 1
+    seed = 0 if tp > 1 else rank           # tensor-parallel ranks must draw the same checkpoint
+    d, gm, fmt = build_model(args, local_rank, seed, tp_rank=rank if tp > 1 else 0, tp_size=tp)
+    B, T, n_chunks = args.batch, args.chunk, args.prefill // args.chunk
+    st = gm.create_state(B)
+    lg = bk.DeviceLogits()
+    rng = np.random.default_rng(99 if tp > 1 else 99 + rank)
+    toks = torch.from_numpy(rng.integers(0, d.vocab, (n_chunks, B, T)))
+    stream = torch.cuda.Stream()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    with torch.cuda.stream(stream):
+        for i in range(min(args.warmup, n_chunks)):
+            gm._forward(toks[i], st, lg, sync=False)
+        barrier()
+        sampler = ClockSampler(local_rank)
+        launches0 = gm.kernel_launches()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for i in range(n_chunks):
+            gm._forward(toks[i], st, lg, sync=False)
+        e1.record(stream)
+        barrier()
+        ms = e0.elapsed_time(e1)
+        launches = gm.kernel_launches() - launches0
+        clocks = sampler.stop()
+    (ms,) = max_over_ranks([ms], world, "cuda")
+    if rank != 0:
+        return
+    prompts = B * (1 if tp > 1 else world)
+    tokens = prompts * n_chunks * T
+    C, F, L_ = d.channels, d.ffn, d.layers
+    p_layer = 4 * C * C + 2 * C * F + 2 * C * (d.rank_w + d.rank_a + d.rank_g + d.rank_v)
+    flops = 2.0 * (p_layer * L_ * tokens + d.vocab * C * prompts * n_chunks)      # the head runs on each chunk's last row
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as fh:
+            tf_peak, kind = float(json.load(fh)["bf16_tflops_sustained"]), "measured (sustained)"
+    except Exception:
+        tf_peak, kind = 1400.0, "fallback"
+    achieved = flops / (ms * 1e-3) / 1e12 / world
+    print(json.dumps({
+        "metric": "prefill_tokens_per_s", "value": tokens / (ms * 1e-3), "unit": "tok/s", "n_gpus": world, "steps": n_chunks,
+        "warmup": min(args.warmup, n_chunks), "ms_per_step": ms / n_chunks, "higher_is_better": True,
+        "scaling": "strong" if tp > 1 else "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"reduced": {"layers": args.layers, "vocab": args.vocab} if (args.layers or args.vocab) else None,
+                   "workload": f"RWKV-7 {args.model} random-init, prefill {n_chunks * T} tokens x {B} prompt(s) in chunks of {T}, "
+                               f"{'fp32' if args.wkv32 else 'fp16'} WKV state, weights {args.fmt}",
+                   "parallelism": f"tp{tp} (head-sharded, fp32 all-reduce after att.output and ffn.value)" if tp > 1 else f"replicas x{world}",
+                   "l2": "inputs larger than L2 (every chunk streams all weights)"},
+        "clocks": clocks, "gpu_launches": int(launches),
+        "roofline": {"bound": "tensor", "achieved": achieved, "peak": tf_peak, "unit": "TFLOP/s", "frac": achieved / tf_peak,
+                     "traffic": None, "peak_kind": kind, "scope": "whole prefill, per GPU"},
+    }))
 
 
 def micro_gemv(args):
@@ -380,6 +453,11 @@ def main():
     ap.add_argument("--fmt", default="f16", choices=["f16", "w8a16", "w4a16"])
     ap.add_argument("--wkv32", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--prefill", type=int, default=0, help="secondary line: prefill this many tokens in chunks instead of decoding")
+    ap.add_argument("--chunk", type=int, default=128)
+    ap.add_argument("--layers", type=int, default=0, help="timing aid: override the depth (the line then says so)")
+    ap.add_argument("--vocab", type=int, default=0, help="timing aid: override the vocabulary size")
+    ap.add_argument("--tp", action="store_true", help="with --prefill: the ranks form one head-sharded tensor-parallel group")
     ap.add_argument("--micro", default="", choices=["", "gemv", "gemv-small", "gemm", "gemm-small"], help="kernel micro-benchmark instead of the bench line")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
@@ -397,7 +475,10 @@ def main():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     try:
-        run_ours(args, rank, world, local_rank)
+        if args.prefill:
+            run_prefill(args, rank, world, local_rank)
+        else:
+            run_ours(args, rank, world, local_rank)
     finally:
         if world > 1:
             dist.destroy_process_group()

@@ -55,6 +55,9 @@ enum Epilogue : int {
   kEpiVres = 2,    // y = half(v + (v_first - v) * sigmoid(v0 + acc))
   kEpiF32 = 3,     // y32 = float(half(acc))   (logits)
   kEpiRawF32 = 4,  // y32 = acc, not rounded: a partial sum another rank's partial is added to
+  // internal to the library (tensor-core path only): LoRA activations of the many-row path
+  kEpiTanhH = 100,     // h = half(acc); y = half(tanh(h))
+  kEpiSigmoidH = 101,  // h = half(acc); y = half(sigmoid(h))
 };
 
 struct EpiArgs {

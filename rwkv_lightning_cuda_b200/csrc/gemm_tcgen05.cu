@@ -1,21 +1,33 @@
 // Tensor-core GEMM for row counts above the weight-streaming GEMV range (batched decode, prefill
-// chunks): y[M,N] = epi(x[M,K] W[N,K]^T), fp16 operands, fp32 accumulation in tensor memory.
+// chunks): y[M,N] = epi(x[M,K] W[N,K]^T), fp16 operands, fp32 accumulation in tensor memory.  Up to
+// eight such products that share M run as ONE persistent launch (a layer's r/k/v projections and
+// LoRA down-projections, or its four LoRA up-projections).
 //
-// sm_100a design: the weight matrix takes the MMA's M side ("swap AB"), so a CTA owns 128 output
-// channels (weight rows) and a tile of up to 256 activation rows; tiles of 128x64 (weights) and
-// Nt x 64 (activations) are brought into 128-byte-swizzled shared memory by TMA
-// (cp.async.bulk.tensor), one elected thread issues tcgen05.mma (cta_group::1, kind::f16,
-// M=128, N=Nt, K=16) into a TMEM accumulator, tcgen05.commit releases the stage, and four epilogue
-// warps read the accumulator back with tcgen05.ld, apply the epilogue and store y (one rounding to
-// half, the reference's rounding point for its cuBLAS calls, cuda/rwkv7_v3a_ops.cu:2235-2302).
+// sm_100a design: the weight matrix takes the MMA's M side ("swap AB"), so a work unit is 128 output
+// channels (weight rows) x a tile of Nt <= 256 activation rows x a range of K.  One CTA per SM walks
+// the unit list with a stride of the grid size.  Tiles of 128x64 (weights) and Nt x 64 (activations)
+// are brought into 128-byte-swizzled shared memory by TMA (cp.async.bulk.tensor) through one ring of
+// stages that keeps running across units; one elected thread issues tcgen05.mma (cta_group::1,
+// kind::f16, M=128, N=Nt, K=16) into one of two TMEM accumulators; tcgen05.commit releases the stage;
+// four epilogue warps read the finished accumulator back with tcgen05.ld, apply the epilogue and store
+// y (one rounding to half, the reference's rounding point for its cuBLAS calls,
+// cuda/rwkv7_v3a_ops.cu:2235-2302) while the next unit's MMAs fill the other accumulator.
 // Replaces rwkv7_v3a_linear_f16_orig_launch / _lt_cfg_launch / linear_orig_rows_* for rows > 4.
 //
-// Every mbarrier wait is bounded; on a time-out the kernel records it in a device flag, still
-// reaches its final barrier, frees its tensor memory and returns.
+// Narrow products are split along K so that every SM has work; the fp32 partial sums go to scratch and
+// a second small kernel adds them in split order (the result does not depend on timing).
+//
+// Every mbarrier wait is bounded; on a time-out the kernel records it in a device flag, every role
+// leaves its loop, the CTA reaches its final barrier, frees its tensor memory and returns.
 #include <cuda.h>
 
 #include <algorithm>
+#include <cstdlib>
+#include <cstring>
 #include <mutex>
+#include <string>
+#include <unordered_map>
+#include <vector>
 
 #include "common.cuh"
 #include "kernels.h"
@@ -23,21 +35,57 @@
 namespace rk {
 namespace {
 
-constexpr int kBM = 128;  // weight rows (output channels) per CTA = MMA M
+constexpr int kBM = 128;  // weight rows (output channels) per unit = MMA M
 constexpr int kBK = 64;   // halves per K block = one 128-byte swizzle row
-constexpr int kThreads = 192;
+constexpr int kEpiThreads = 256;  // eight epilogue warps: two per scheduler, each pair shares a TMEM lane quadrant
+constexpr int kCtrlThreads = 96;   // weight producer, MMA issuer, activation producer (one lane of a warp each)
+constexpr int kThreads = kCtrlThreads + kEpiThreads;
+constexpr int kMaxProb = 8;
+constexpr int kEpiRows = 32;             // activation rows transposed through shared memory at a time
+constexpr int kEpiLd = kBM + 4;          // padded row of the transposition tile (floats)
+constexpr int kEpiBytes = kEpiRows * kEpiLd * 4;
+constexpr int kMaxWStages = 10, kMaxXStages = 8;
 
 __device__ int g_gemm_timeout = 0;
 
-struct GemmDev {
-  int M, N, K, Nt, stages, epi;
-  int splits, kb_per_split;  // split-K: grid.z CTAs share an output tile, kb_per_split K blocks each
-  float* partial;            // [splits, M, N] fp32 partial sums (scratch), used when splits > 1
+// Optional timestamps of CTA 0 (a development build defines RK_GEMM_TRACE; the library does not).
+#ifdef RK_GEMM_TRACE
+__device__ unsigned long long g_gemm_trace[16];
+__device__ __forceinline__ void trace_point(int i) {
+  if (blockIdx.x == 0) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)::"memory");
+    g_gemm_trace[i] = t;
+  }
+}
+#define RK_TRACE(i) trace_point(i)
+#else
+#define RK_TRACE(i)
+#endif
+
+struct Prob {
+  int M, N, K, epi;
+  int tiles_n;               // ceil(N / 128)
+  int splits, kb_per_split;  // K blocks per unit
+  int unit_begin;            // index of this product's first work unit
+  int red_begin;             // first 256-thread block of the reduction kernel that belongs to this product
+  float* partial;            // [splits, M, N] fp32 partial sums, when splits > 1
   void* y;
-  const half* scale;    // optional per-output-channel factor applied to the accumulator
-  const half* v;        // kEpiVres
+  const half* scale;         // optional per-output-channel factor applied to the accumulator
+  const half* v;             // kEpiVres
   const half* v_first;
   const half* v0;
+};
+
+struct GroupDev {
+  int n_prob, total_units, Nt, w_stages, x_stages, tiles_m, red_blocks;
+  int w_dynamic;  // the weights may have been written by the previous kernel: wait for it before reading them
+  Prob prob[kMaxProb];
+};
+
+struct MapPack {
+  CUtensorMap w[kMaxProb];
+  CUtensorMap x[kMaxProb];
 };
 
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
@@ -45,6 +93,9 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
       ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
       : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
 // Shared-memory matrix descriptor: K-major tile, 128-byte swizzle, 8-row groups 1024 bytes apart.
@@ -76,185 +127,322 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
       : "r"(taddr));
 }
 
-// Applies the epilogue to one fp32 result: the layer's single rounding to half.
-__device__ __forceinline__ void emit(const GemmDev& p, int m, int n, float a) {
-  const size_t o = static_cast<size_t>(m) * p.N + n;
-  if (p.epi == kEpiRawF32) {
-    static_cast<float*>(p.y)[o] = a;
-  } else if (p.epi == kEpiF32) {
-    static_cast<float*>(p.y)[o] = __half2float(__float2half_rn(a));
-  } else if (p.epi == kEpiRelu2) {
-    const float t = fmaxf(__half2float(__float2half_rn(a)), 0.f);
-    static_cast<half*>(p.y)[o] = __float2half_rn(t * t);
-  } else if (p.epi == kEpiVres) {
+// What the epilogue needs of one product, copied into registers once per unit (reading the kernel parameter
+// block through a run-time index inside the store loop costs a dependent constant load per row).
+struct EpiCtx {
+  int M, N, epi, splits;
+  float* partial;
+  void* y;
+  const half *scale, *v, *v_first, *v0;
+};
+__device__ __forceinline__ EpiCtx make_ctx(const Prob& p) {
+  EpiCtx c;
+  c.M = p.M; c.N = p.N; c.epi = p.epi; c.splits = p.splits; c.partial = p.partial; c.y = p.y;
+  c.scale = p.scale; c.v = p.v; c.v_first = p.v_first; c.v0 = p.v0;
+  return c;
+}
+
+// The epilogue of one fp32 result (already scaled): the layer's single rounding to half follows in store4.
+__device__ __forceinline__ float epi_value(const EpiCtx& p, size_t o, int n, float a) {
+  if (p.epi == kEpiRelu2) {
+    const float u = fmaxf(__half2float(__float2half_rn(a)), 0.f);
+    return u * u;
+  }
+  if (p.epi == kEpiVres) {
     const float vv = __half2float(p.v[o]);
     const float gate = 1.0f / (1.0f + expf(-(__half2float(p.v0[n]) + a)));
-    static_cast<half*>(p.y)[o] = __float2half_rn(vv + (__half2float(p.v_first[o]) - vv) * gate);
+    return vv + (__half2float(p.v_first[o]) - vv) * gate;
+  }
+  if (p.epi == kEpiTanhH) return apply_in_act(__half2float(__float2half_rn(a)), kActTanh);
+  if (p.epi == kEpiSigmoidH) return apply_in_act(__half2float(__float2half_rn(a)), kActSigmoid);
+  return a;
+}
+
+__device__ __forceinline__ void store_half4(half* y, size_t o, float e0, float e1, float e2, float e3) {
+  const __half2 lo = __floats2half2_rn(e0, e1), hi = __floats2half2_rn(e2, e3);
+  uint2 pk;
+  pk.x = *reinterpret_cast<const uint32_t*>(&lo);
+  pk.y = *reinterpret_cast<const uint32_t*>(&hi);
+  *reinterpret_cast<uint2*>(y + o) = pk;
+}
+
+// Stores four consecutive output channels of one row.
+__device__ __forceinline__ void store4(const EpiCtx& p, int m, int n, const float (&a)[4]) {
+  const size_t o = static_cast<size_t>(m) * p.N + n;
+  if (p.epi == kEpiNone) {
+    store_half4(static_cast<half*>(p.y), o, a[0], a[1], a[2], a[3]);
+  } else if (p.epi == kEpiRawF32) {
+    *reinterpret_cast<float4*>(static_cast<float*>(p.y) + o) = make_float4(a[0], a[1], a[2], a[3]);
+  } else if (p.epi == kEpiF32) {
+    float4 o4;
+    o4.x = __half2float(__float2half_rn(a[0])); o4.y = __half2float(__float2half_rn(a[1]));
+    o4.z = __half2float(__float2half_rn(a[2])); o4.w = __half2float(__float2half_rn(a[3]));
+    *reinterpret_cast<float4*>(static_cast<float*>(p.y) + o) = o4;
   } else {
-    static_cast<half*>(p.y)[o] = __float2half_rn(a);
+    float e[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) e[i] = epi_value(p, o + i, n + i, a[i]);
+    store_half4(static_cast<half*>(p.y), o, e[0], e[1], e[2], e[3]);
   }
 }
 
-__global__ void __launch_bounds__(kThreads) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,
-                                                           const __grid_constant__ CUtensorMap map_x, const GemmDev p) {
-  extern __shared__ __align__(1024) unsigned char smem_raw[];
-  __shared__ __align__(8) uint64_t full_bar[8], empty_bar[8], acc_bar;
-  __shared__ uint32_t tmem_slot;
-  __shared__ int failed;
+// Barrier over the 256 epilogue threads that also ANDs a predicate.
+__device__ __forceinline__ bool epi_all(bool ok) {
+  uint32_t r;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\tsetp.ne.b32 q, %1, 0;\n\t"
+      "bar.red.and.pred p, 1, 256, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(r)
+      : "r"(static_cast<uint32_t>(ok))
+      : "memory");
+  return r != 0;
+}
 
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n0 = blockIdx.x * kBM, m0 = blockIdx.y * p.Nt;
+struct Unit {
+  int prob, n0, m0, kb_begin, kblocks, split;
+};
+
+__device__ __forceinline__ Unit decode_unit(const GroupDev& g, int u) {
+  int pi = 0;
+#pragma unroll
+  for (int i = 1; i < kMaxProb; ++i)
+    if (i < g.n_prob && u >= g.prob[i].unit_begin) pi = i;
+  const Prob& p = g.prob[pi];
+  int local = u - p.unit_begin;
+  // consecutive units are the row tiles of one weight tile: they run at the same time on neighbouring
+  // CTAs, so the weight tile comes from DRAM once and from L2 afterwards
+  const int mt = local % g.tiles_m;
+  local /= g.tiles_m;
+  const int nt = local % p.tiles_n, split = local / p.tiles_n;
+  Unit r;
+  r.prob = pi;
+  r.n0 = nt * kBM;
+  r.m0 = mt * g.Nt;
+  r.split = split;
+  r.kb_begin = split * p.kb_per_split;
   const int kb_total = (p.K + kBK - 1) / kBK;
-  const int kb_begin = blockIdx.z * p.kb_per_split;
-  const int kblocks = min(kb_total - kb_begin, p.kb_per_split);  // >= 1 by construction of the grid
-  const uint32_t stage_bytes = kBM * 128 + p.Nt * 128;
-  // the dynamic window is 1024-byte aligned by the launch (required by the 128-byte swizzle)
-  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  uint32_t tmem_cols = 32;
-  while (tmem_cols < static_cast<uint32_t>(p.Nt)) tmem_cols <<= 1;
+  r.kblocks = min(kb_total - r.kb_begin, p.kb_per_split);  // >= 1 by construction of the unit list
+  return r;
+}
+
+__global__ void __launch_bounds__(kThreads, 1) gemm_group_kernel(const __grid_constant__ MapPack maps, const GroupDev g) {
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  __shared__ __align__(8) uint64_t w_full[kMaxWStages], w_empty[kMaxWStages], x_full[kMaxXStages], x_empty[kMaxXStages];
+  __shared__ __align__(8) uint64_t acc_full[2], acc_empty[2];
+  __shared__ uint32_t tmem_slot;
+  __shared__ volatile int failed;
+
+  if (threadIdx.x == 0) RK_TRACE(0);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  constexpr uint32_t kWBytes = kBM * 128;
+  const uint32_t x_bytes = g.Nt * 128;
+  // the dynamic window is 1024-byte aligned here (required by the 128-byte swizzle): weight ring, activation ring,
+  // epilogue tile
+  const uint32_t w_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t x_base = w_base + g.w_stages * kWBytes;
+  float* const epi_tile = reinterpret_cast<float*>(smem_raw + (x_base - smem_u32(smem_raw)) + g.x_stages * x_bytes);
+  constexpr uint32_t kTmemCols = 512;  // two accumulators of up to 256 columns; one CTA per SM
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < p.stages; ++s) {
-      mbar_init(smem_u32(&full_bar[s]), 1);
-      mbar_init(smem_u32(&empty_bar[s]), 1);
+    for (int s = 0; s < g.w_stages; ++s) {
+      mbar_init(smem_u32(&w_full[s]), 1);
+      mbar_init(smem_u32(&w_empty[s]), 1);
     }
-    mbar_init(smem_u32(&acc_bar), 1);
+    for (int s = 0; s < g.x_stages; ++s) {
+      mbar_init(smem_u32(&x_full[s]), 1);
+      mbar_init(smem_u32(&x_empty[s]), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(smem_u32(&acc_full[a]), 1);
+      mbar_init(smem_u32(&acc_empty[a]), 1);
+    }
     failed = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"(tmem_cols) : "memory");
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"(kTmemCols) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-  const uint32_t tmem_acc = tmem_slot;
-
-  pdl_wait();
-  pdl_trigger();
+  const uint32_t tmem_base = tmem_slot;
+  if (threadIdx.x == 0) RK_TRACE(1);
 
   if (warp == 0) {
-    // ---- TMA producer
+    // ---- weight producer: a deep ring, because these tiles come from DRAM.  Weights that were written long before
+    // this launch do not depend on the previous kernel, so their requests start before the dependency wait.
     if (lane == 0) {
-      for (int kb = 0; kb < kblocks; ++kb) {
-        const int s = kb % p.stages;
-        if (kb >= p.stages && !mbar_wait(smem_u32(&empty_bar[s]), ((kb / p.stages) - 1) & 1)) { failed = 1; break; }
-        const uint32_t bar = smem_u32(&full_bar[s]);
-        const uint32_t a = smem_base + s * stage_bytes;
-        mbar_expect_tx(bar, stage_bytes);
-        tma_load_2d(a, &map_w, bar, (kb_begin + kb) * kBK, n0);
-        tma_load_2d(a + kBM * 128, &map_x, bar, (kb_begin + kb) * kBK, m0);
+      if (g.w_dynamic) pdl_wait();
+      bool ok = true;
+      int it = 0;
+      for (int ui = blockIdx.x; ui < g.total_units && ok && !failed; ui += gridDim.x) {
+        const Unit u = decode_unit(g, ui);
+        for (int kb = 0; kb < u.kblocks; ++kb, ++it) {
+          const int s = it % g.w_stages;
+          if (it >= g.w_stages && !mbar_wait(smem_u32(&w_empty[s]), ((it / g.w_stages) - 1) & 1)) { ok = false; break; }
+          const uint32_t bar = smem_u32(&w_full[s]);
+          mbar_expect_tx(bar, kWBytes);
+          tma_load_2d(w_base + s * kWBytes, &maps.w[u.prob], bar, (u.kb_begin + kb) * kBK, u.n0);
+        }
       }
+      if (!ok) failed = 1;
+    }
+  } else if (warp == 2) {
+    // ---- activation producer: a shallow ring, these tiles come from L2
+    if (lane == 0) {
+      pdl_wait();
+      pdl_trigger();
+      RK_TRACE(2);
+      bool ok = true;
+      int it = 0;
+      for (int ui = blockIdx.x; ui < g.total_units && ok && !failed; ui += gridDim.x) {
+        const Unit u = decode_unit(g, ui);
+        for (int kb = 0; kb < u.kblocks; ++kb, ++it) {
+          const int s = it % g.x_stages;
+          if (it >= g.x_stages && !mbar_wait(smem_u32(&x_empty[s]), ((it / g.x_stages) - 1) & 1)) { ok = false; break; }
+          const uint32_t bar = smem_u32(&x_full[s]);
+          mbar_expect_tx(bar, x_bytes);
+          tma_load_2d(x_base + s * x_bytes, &maps.x[u.prob], bar, (u.kb_begin + kb) * kBK, u.m0);
+        }
+      }
+      if (!ok) failed = 1;
     }
   } else if (warp == 1) {
     // ---- MMA issuer
     if (lane == 0) {
-      const uint32_t idesc = (1u << 4) | (static_cast<uint32_t>(p.Nt >> 3) << 17) | (static_cast<uint32_t>(kBM >> 4) << 24);
+      const uint32_t idesc = (1u << 4) | (static_cast<uint32_t>(g.Nt >> 3) << 17) | (static_cast<uint32_t>(kBM >> 4) << 24);
       bool ok = true;
-      for (int kb = 0; kb < kblocks && ok; ++kb) {
-        const int s = kb % p.stages;
-        ok = mbar_wait(smem_u32(&full_bar[s]), (kb / p.stages) & 1);
-        if (!ok) break;
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t a = smem_base + s * stage_bytes;
-        const uint64_t da = smem_desc(a), db = smem_desc(a + kBM * 128);
+      int it = 0, n_unit = 0;
+      for (int ui = blockIdx.x; ui < g.total_units && ok && !failed; ui += gridDim.x, ++n_unit) {
+        const Unit u = decode_unit(g, ui);
+        const int acc = n_unit & 1;
+        if (n_unit >= 2) {  // the epilogue of the unit that used this accumulator two units ago has drained it
+          ok = mbar_wait(smem_u32(&acc_empty[acc]), ((n_unit >> 1) - 1) & 1);
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        }
+        const uint32_t tmem_acc = tmem_base + static_cast<uint32_t>(acc * g.Nt);
+        for (int kb = 0; kb < u.kblocks; ++kb, ++it) {
+          const int ws = it % g.w_stages, xs = it % g.x_stages;
+          ok = mbar_wait(smem_u32(&x_full[xs]), (it / g.x_stages) & 1) && mbar_wait(smem_u32(&w_full[ws]), (it / g.w_stages) & 1);
+          if (!ok) break;
+          if (it == 0) RK_TRACE(3);
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint64_t da = smem_desc(w_base + ws * kWBytes), db = smem_desc(x_base + xs * x_bytes);
 #pragma unroll
-        for (int k4 = 0; k4 < kBK / 16; ++k4)  // 32 bytes further along the swizzled row per K=16 step
-          mma_f16(tmem_acc, da + 2 * k4, db + 2 * k4, idesc, (kb | k4) != 0);
-        mma_commit(smem_u32(&empty_bar[s]));
+          for (int k4 = 0; k4 < kBK / 16; ++k4)  // 32 bytes further along the swizzled row per K=16 step
+            mma_f16(tmem_acc, da + 2 * k4, db + 2 * k4, idesc, (kb | k4) != 0);
+          mma_commit(smem_u32(&w_empty[ws]));
+          mma_commit(smem_u32(&x_empty[xs]));
+        }
+        if (ok) mma_commit(smem_u32(&acc_full[acc]));
+        if (n_unit == 0) RK_TRACE(4);
       }
-      if (ok) mma_commit(smem_u32(&acc_bar));
-      else failed = 1;
+      if (!ok) failed = 1;
     }
   } else {
     // ---- epilogue: warp w reads TMEM lanes 32*(w%4) .. +31 = output channels n0 + that
-    const bool ok = mbar_wait(smem_u32(&acc_bar), 0);
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    if (ok) {
-      // Phase A: TMEM -> registers -> an fp32 tile [Nt][128 (+4 pad)] in the (now idle) stage memory, so that
-      // phase B can write y with 8- or 16-byte stores along the channel dimension.
-      const int q = warp & 3;
-      float* tile = reinterpret_cast<float*>(smem_raw + (smem_base - smem_u32(smem_raw)));
-      constexpr int kLd = kBM + 4;
-      const int m_valid = min(p.Nt, p.M - m0);
-      for (int c0 = 0; c0 < m_valid; c0 += 16) {
-        uint32_t r[16];
-        tmem_ld16(tmem_acc + (static_cast<uint32_t>(q * 32) << 16) + c0, r);
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-        for (int j = 0; j < 16; ++j) tile[(c0 + j) * kLd + q * 32 + lane] = __uint_as_float(r[j]);
+    pdl_wait();  // y and the partial sums may still be read by the previous kernel
+    const int q = warp & 3;
+    const int t = threadIdx.x - kCtrlThreads;
+    const int c4 = (t & 31) * 4;
+    int n_unit = 0;
+    for (int ui = blockIdx.x; ui < g.total_units; ui += gridDim.x, ++n_unit) {
+      const Unit u = decode_unit(g, ui);
+      const EpiCtx p = make_ctx(g.prob[u.prob]);
+      const int acc = n_unit & 1;
+      bool ok = !failed && mbar_wait(smem_u32(&acc_full[acc]), (n_unit >> 1) & 1);
+      // the four warps must agree, or the named barriers below would not match up
+      ok = epi_all(ok);
+      if (!ok) {
+        if (t == 0) failed = 1;
+        break;
       }
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      // Phase B: thread t owns 4 consecutive channels of rows t/32, t/32 + 4, ...
-      const int t = threadIdx.x - 64;
-      const int c4 = (t & 31) * 4, n = n0 + c4;
-      if (n < p.N) {
-        float sc[4] = {1.f, 1.f, 1.f, 1.f};
-        if (p.scale) {
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      if (t == 0 && n_unit == 0) RK_TRACE(5);
+      const uint32_t tmem_acc = tmem_base + static_cast<uint32_t>(acc * g.Nt) + (static_cast<uint32_t>(q * 32) << 16);
+      const int m_valid = min(g.Nt, p.M - u.m0);
+      const int n = u.n0 + c4;
+      float sc[4] = {1.f, 1.f, 1.f, 1.f};
+      if (p.scale && n < p.N) {
 #pragma unroll
-          for (int i = 0; i < 4; ++i) sc[i] = __half2float(p.scale[n + i]);
+        for (int i = 0; i < 4; ++i) sc[i] = __half2float(p.scale[n + i]);
+      }
+      for (int c0 = 0; c0 < m_valid; c0 += kEpiRows) {
+        // phase A: TMEM -> registers -> fp32 tile [32 rows][128 channels (+4 pad)]; the two warps of a lane
+        // quadrant take 16 rows each
+        const int half_rows = (warp - kCtrlThreads / 32) >> 2;
+        if (c0 + half_rows * 16 < g.Nt) {
+          uint32_t r0[16];
+          tmem_ld16(tmem_acc + c0 + half_rows * 16, r0);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+          for (int j = 0; j < 16; ++j) epi_tile[(half_rows * 16 + j) * kEpiLd + q * 32 + lane] = __uint_as_float(r0[j]);
         }
-        for (int ml = t >> 5; ml < m_valid; ml += 4) {
-          const float4 a4 = *reinterpret_cast<const float4*>(tile + ml * kLd + c4);
-          const float a[4] = {a4.x * sc[0], a4.y * sc[1], a4.z * sc[2], a4.w * sc[3]};
-          const size_t o = static_cast<size_t>(m0 + ml) * p.N + n;
-          if (p.splits > 1) {
-            *reinterpret_cast<float4*>(p.partial + static_cast<size_t>(blockIdx.z) * p.M * p.N + o) = a4;
-          } else if (p.epi == kEpiRawF32) {
-            *reinterpret_cast<float4*>(static_cast<float*>(p.y) + o) = make_float4(a[0], a[1], a[2], a[3]);
-          } else if (p.epi == kEpiF32) {
-            float4 o4;
-            o4.x = __half2float(__float2half_rn(a[0])); o4.y = __half2float(__float2half_rn(a[1]));
-            o4.z = __half2float(__float2half_rn(a[2])); o4.w = __half2float(__float2half_rn(a[3]));
-            *reinterpret_cast<float4*>(static_cast<float*>(p.y) + o) = o4;
-          } else {
-            float e[4];
-            if (p.epi == kEpiRelu2) {
+        if (t == 0 && n_unit == 0 && c0 == 0) RK_TRACE(8);
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        if (t == 0 && n_unit == 0 && c0 == 0) RK_TRACE(9);
+        // phase B: thread t owns 4 consecutive channels of rows t/32, t/32 + 8, ... of this slab
+        const int rows_here = min(kEpiRows, m_valid - c0);
+        if (n < p.N) {
+          constexpr int kIter = kEpiRows / (kEpiThreads / 32);
+          float4 a4[kIter];
 #pragma unroll
-              for (int i = 0; i < 4; ++i) {
-                const float u = fmaxf(__half2float(__float2half_rn(a[i])), 0.f);
-                e[i] = u * u;
-              }
-            } else if (p.epi == kEpiVres) {
+          for (int i = 0; i < kIter; ++i)  // all shared-memory reads first, then the stores
+            a4[i] = *reinterpret_cast<const float4*>(epi_tile + ((t >> 5) + (kEpiThreads / 32) * i) * kEpiLd + c4);
+          const int m_first = u.m0 + c0 + (t >> 5);
+          const size_t o_first = static_cast<size_t>(m_first) * p.N + n;
 #pragma unroll
-              for (int i = 0; i < 4; ++i) {
-                const float vv = __half2float(p.v[o + i]);
-                const float gate = 1.0f / (1.0f + expf(-(__half2float(p.v0[n + i]) + a[i])));
-                e[i] = vv + (__half2float(p.v_first[o + i]) - vv) * gate;
-              }
+          for (int i = 0; i < kIter; ++i) {
+            const int ml = (t >> 5) + (kEpiThreads / 32) * i;
+            if (ml >= rows_here) continue;
+            const size_t o = o_first + static_cast<size_t>((kEpiThreads / 32) * i) * p.N;
+            if (p.splits > 1) {
+              *reinterpret_cast<float4*>(p.partial + static_cast<size_t>(u.split) * p.M * p.N + o) = a4[i];
+            } else if (p.epi == kEpiNone && !p.scale) {
+              store_half4(static_cast<half*>(p.y), o, a4[i].x, a4[i].y, a4[i].z, a4[i].w);
             } else {
-#pragma unroll
-              for (int i = 0; i < 4; ++i) e[i] = a[i];
+              const float a[4] = {a4[i].x * sc[0], a4[i].y * sc[1], a4[i].z * sc[2], a4[i].w * sc[3]};
+              store4(p, m_first + (kEpiThreads / 32) * i, n, a);
             }
-            const __half2 lo = __floats2half2_rn(e[0], e[1]), hi = __floats2half2_rn(e[2], e[3]);
-            uint2 pk;
-            pk.x = *reinterpret_cast<const uint32_t*>(&lo);
-            pk.y = *reinterpret_cast<const uint32_t*>(&hi);
-            *reinterpret_cast<uint2*>(static_cast<half*>(p.y) + o) = pk;
           }
         }
+        if (t == 0 && n_unit == 0 && c0 == 0) RK_TRACE(10);
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        if (t == 0 && n_unit == 0 && c0 == 0) RK_TRACE(11);
       }
-    } else if (lane == 0) {
-      failed = 1;
+      // every warp's TMEM reads are complete (wait::ld + the barrier above): hand the accumulator back
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      if (t == 0) mbar_arrive(smem_u32(&acc_empty[acc]));
+      if (t == 0 && n_unit == 0) RK_TRACE(6);
     }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
+  if (threadIdx.x == 0) RK_TRACE(7);
   if (threadIdx.x == 0 && failed) atomicExch(&g_gemm_timeout, 1);
   if (warp == 1) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"(tmem_cols) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
   }
 }
 
-// Second pass of a split-K GEMM: adds the fp32 partial sums in split order (the result does not
-// depend on which CTA finished first) and applies the epilogue.  One thread per four output channels.
-__global__ void __launch_bounds__(256) splitk_reduce_kernel(const GemmDev p) {
+// Second pass of split-K products: adds the fp32 partial sums in split order (the result does not depend on which
+// CTA finished first) and applies the epilogue.  One thread per four output channels; blocks are laid out product
+// after product.
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(const GroupDev g) {
   pdl_wait();
   pdl_trigger();
+  int pi = 0;
+#pragma unroll
+  for (int i = 1; i < kMaxProb; ++i)
+    if (i < g.n_prob && g.prob[i].splits > 1 && static_cast<int>(blockIdx.x) >= g.prob[i].red_begin) pi = i;
+  const Prob& p = g.prob[pi];
+  if (p.splits <= 1) return;  // only when product 0 is unsplit and owns no blocks
   const int n4 = p.N >> 2;
-  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (i >= static_cast<long long>(p.M) * n4) return;
+  const long long i = static_cast<long long>(static_cast<int>(blockIdx.x) - p.red_begin) * blockDim.x + threadIdx.x;
+  if (i < 0 || i >= static_cast<long long>(p.M) * n4) return;
   const int m = static_cast<int>(i / n4), n = static_cast<int>(i - static_cast<long long>(m) * n4) * 4;
   const size_t plane = static_cast<size_t>(p.M) * p.N;
   const float* src = p.partial + static_cast<size_t>(m) * p.N + n;
@@ -263,9 +451,12 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const GemmDev p) {
     const float4 t = __ldcg(reinterpret_cast<const float4*>(src + z * plane));
     acc.x += t.x; acc.y += t.y; acc.z += t.z; acc.w += t.w;
   }
-  const float v[4] = {acc.x, acc.y, acc.z, acc.w};
+  float a[4] = {acc.x, acc.y, acc.z, acc.w};
+  if (p.scale) {
 #pragma unroll
-  for (int j = 0; j < 4; ++j) emit(p, m, n + j, v[j] * (p.scale ? __half2float(p.scale[n + j]) : 1.0f));
+    for (int j = 0; j < 4; ++j) a[j] *= __half2float(p.scale[n + j]);
+  }
+  store4(make_ctx(p), m, n, a);
 }
 
 }  // namespace
@@ -290,8 +481,35 @@ EncodeFn encode_fn() {
 }
 
 // 2-D fp16 tensor [rows, cols] with row stride ld (elements), boxes of 64 columns x box_rows rows,
-// 128-byte swizzle, zero fill outside the tensor.
+// 128-byte swizzle, zero fill outside the tensor.  Encoded maps are kept: a model asks for the same few
+// hundred (pointer, shape) combinations on every call.
+struct MapKey {
+  const void* base;
+  int rows, cols, ld, box_rows;
+  bool operator==(const MapKey& o) const {
+    return base == o.base && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows;
+  }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    size_t h = reinterpret_cast<size_t>(k.base);
+    for (int v : {k.rows, k.cols, k.ld, k.box_rows}) h = h * 1000003u ^ static_cast<size_t>(v);
+    return h;
+  }
+};
+
 int make_map(CUtensorMap* map, const void* base, int rows, int cols, int ld, int box_rows) {
+  static std::mutex mu;
+  static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+  const MapKey key{base, rows, cols, ld, box_rows};
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) {
+      *map = it->second;
+      return kOk;
+    }
+  }
   EncodeFn fn = encode_fn();
   RK_REQUIRE(fn, kCuda, "gemm_tc: cuTensorMapEncodeTiled is not available from this driver");
   const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
@@ -302,63 +520,205 @@ int make_map(CUtensorMap* map, const void* base, int rows, int cols, int ld, int
                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   RK_REQUIRE(r == CUDA_SUCCESS, kCuda, "gemm_tc: cuTensorMapEncodeTiled failed with %d (rows=%d cols=%d ld=%d)", static_cast<int>(r), rows, cols, ld);
+  std::lock_guard<std::mutex> lock(mu);
+  if (cache.size() > 8192) cache.clear();
+  cache.emplace(key, *map);
   return kOk;
 }
 
-int pick_nt(int M) {
-  if (M >= 256) return 256;
-  return ((M + 15) / 16) * 16;
+int sm_count() {
+  static int n[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (!n[dev]) {
+    int v = 0;
+    if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) v = 148;
+    n[dev] = v;
+  }
+  return n[dev];
 }
 
-}  // namespace
+int round16(int m) { return ((m + 15) / 16) * 16; }
 
-bool gemm_tc_supported(const LinearArgs& a) {
+// Chooses the row-tile width and the K split of every product: the candidate with the smallest estimated
+// makespan over the SMs (in units of one K block streamed by one CTA) wins.  Smaller row tiles and K splits
+// both make more units; splitting K costs partial-sum traffic and the second kernel, narrower row tiles cost
+// re-reads of the weight tile from L2.
+struct Plan {
+  int Nt = 0, tiles_m = 0, total_units = 0;
+  int splits[kMaxProb] = {0}, kbps[kMaxProb] = {0};
+  double cost = 1e30;
+  bool any_split = false;
+};
+
+Plan make_plan_uncached(const LinearArgs* a, int n, size_t scratch_bytes, int sms);
+
+// Plans depend only on the shapes; a model asks for the same few again and again.
+Plan make_plan(const LinearArgs* a, int n, size_t scratch_bytes, int sms) {
+  static std::mutex mu;
+  static std::unordered_map<std::string, Plan> cache;
+  std::string key;
+  key.reserve(16 + 8 * static_cast<size_t>(n));
+  auto put = [&key](long long v) { key.append(reinterpret_cast<const char*>(&v), sizeof(v)); };
+  put(a[0].M); put(n); put(static_cast<long long>(scratch_bytes)); put(sms);
+  for (int i = 0; i < n; ++i) { put(a[i].N); put(a[i].K); }
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) return it->second;
+  }
+  const Plan p = make_plan_uncached(a, n, scratch_bytes, sms);
+  std::lock_guard<std::mutex> lock(mu);
+  if (cache.size() > 4096) cache.clear();
+  cache.emplace(std::move(key), p);
+  return p;
+}
+
+Plan make_plan_uncached(const LinearArgs* a, int n, size_t scratch_bytes, int sms) {
+  const int M = a[0].M;
+  int nts[3], n_nt = 0;
+  nts[n_nt++] = std::min(256, round16(M));
+  if (M > 128) nts[n_nt++] = 128;
+  if (M > 64) nts[n_nt++] = 64;
+  static const int targets[] = {1 << 30, 128, 96, 64, 48, 32, 24, 16, 12, 8, 6, 4};
+  // tuning aids: force the row-tile width / the K blocks per unit
+  static const int force_nt = [] { const char* e = getenv("RWKV7_B200_GEMM_NT"); return e ? atoi(e) : 0; }();
+  static const int force_target = [] { const char* e = getenv("RWKV7_B200_GEMM_TARGET"); return e ? atoi(e) : 0; }();
+  Plan best;
+  std::vector<double> load(static_cast<size_t>(sms));
+  for (int ni = 0; ni < n_nt; ++ni) {
+    const int Nt = nts[ni], tiles_m = (M + Nt - 1) / Nt;
+    if (force_nt && Nt != force_nt && !(ni == 0 && force_nt > Nt)) continue;
+    for (int target : targets) {
+      if (force_target && target != force_target) continue;
+      Plan p;
+      p.Nt = Nt;
+      p.tiles_m = tiles_m;
+      size_t need = 0;
+      for (int i = 0; i < n; ++i) {
+        const int kb = (a[i].K + kBK - 1) / kBK;
+        int s = std::max(1, std::min((kb + target - 1) / target, 32));
+        if (a[i].N % 4 != 0) s = 1;
+        p.kbps[i] = (kb + s - 1) / s;
+        p.splits[i] = (kb + p.kbps[i] - 1) / p.kbps[i];  // no empty split
+        if (p.splits[i] > 1) {
+          p.any_split = true;
+          need += static_cast<size_t>(p.splits[i]) * M * a[i].N * sizeof(float);
+        }
+      }
+      if (need > scratch_bytes) continue;
+      std::fill(load.begin(), load.end(), 0.0);
+      int u = 0;
+      for (int i = 0; i < n; ++i) {
+        const int tiles_n = (a[i].N + kBM - 1) / kBM;
+        const int units = tiles_n * tiles_m * p.splits[i];
+        // weight tile from DRAM for the first row tile, from L2 for the others; epilogue cost grows with Nt
+        const double epi = (p.splits[i] > 1 ? 2.0 : 1.0) * Nt / 128.0 + 1.5;
+        for (int k = 0; k < units; ++k, ++u) {
+          const bool first_row_tile = (k % tiles_m) == 0;
+          load[static_cast<size_t>(u % sms)] += p.kbps[i] * (first_row_tile ? 1.0 : 0.6) + epi;
+        }
+      }
+      p.total_units = u;
+      p.cost = *std::max_element(load.begin(), load.end()) + (p.any_split ? 10.0 : 0.0);
+      if (p.cost < best.cost) best = p;
+    }
+  }
+  return best;
+}
+
+bool problem_ok(const LinearArgs& a) {
   const int ldx = a.ldx ? a.ldx : a.K;
   return a.fmt == 0 && a.in_act == kActNone && a.K % 8 == 0 && ldx % 8 == 0 && a.M > 4 && a.N % 4 == 0 &&
          (reinterpret_cast<uintptr_t>(a.x) & 15u) == 0 && (reinterpret_cast<uintptr_t>(a.w) & 15u) == 0;
 }
 
-int gemm_tc(cudaStream_t stream, const LinearArgs& a) {
-  RK_REQUIRE(gemm_tc_supported(a), kShape, "gemm_tc: unsupported problem");
-  const int ldx = a.ldx ? a.ldx : a.K;
-  GemmDev p;
-  p.M = a.M; p.N = a.N; p.K = a.K; p.epi = a.epi; p.y = a.y; p.scale = a.out_scale;
-  p.v = a.ea.v; p.v_first = a.ea.v_first; p.v0 = a.ea.v0;
-  p.Nt = pick_nt(a.M);
-  const size_t stage_bytes = static_cast<size_t>(kBM) * 128 + static_cast<size_t>(p.Nt) * 128;
-  p.stages = static_cast<int>(std::min<size_t>(8, (200 * 1024) / stage_bytes));
-  const size_t smem = stage_bytes * p.stages + 1024;
-  CUtensorMap map_w, map_x;
-  int s = make_map(&map_w, a.w, a.N, a.K, a.K, kBM);
-  if (s != kOk) return s;
-  s = make_map(&map_x, a.x, a.M, a.K, ldx, p.Nt);
-  if (s != kOk) return s;
-  RK_CUDA(cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 201 * 1024 + 1024));
-  // Split K over grid.z until the grid covers the SMs: a tile of 128 output channels per CTA alone
-  // leaves most of them idle for the narrow layers (C x C projections, LoRA).  Needs scratch for the
-  // fp32 partial sums (a second small kernel adds them in split order); without it the kernel runs unsplit.
-  const int tiles = ((a.N + kBM - 1) / kBM) * ((a.M + p.Nt - 1) / p.Nt);
-  const int kb_total = (a.K + kBK - 1) / kBK;
-  int splits = 1;
-  if (a.scratch && tiles < 120 && a.N % 4 == 0) {
-    splits = std::min({(148 + tiles - 1) / tiles, std::max(1, kb_total / 2), 32});
-    const size_t per_split = static_cast<size_t>(a.M) * a.N * sizeof(float);
-    splits = static_cast<int>(std::min<size_t>(splits, a.scratch_bytes / per_split));
-    splits = std::max(splits, 1);
+}  // namespace
+
+bool gemm_tc_supported(const LinearArgs& a) { return problem_ok(a); }
+
+// Up to eight products with the same row count in one launch (plus one reduction launch if any K is split).
+// Split-K needs scratch (taken from the first product's args); without it every product runs unsplit.
+int gemm_group(cudaStream_t stream, const LinearArgs* a, int n) {
+  RK_REQUIRE(a && n >= 1 && n <= kMaxProb, kBadArg, "gemm_group: 1..%d products", kMaxProb);
+  for (int i = 0; i < n; ++i) {
+    RK_REQUIRE(problem_ok(a[i]), kShape, "gemm_group: unsupported product %d", i);
+    RK_REQUIRE(a[i].M == a[0].M, kShape, "gemm_group: all products must share M");
+    RK_REQUIRE(a[i].y, kBadArg, "gemm_group: null output");
   }
-  p.kb_per_split = (kb_total + splits - 1) / splits;
-  p.splits = (kb_total + p.kb_per_split - 1) / p.kb_per_split;  // no empty split
-  p.partial = a.scratch;
-  const dim3 grid((a.N + kBM - 1) / kBM, (a.M + p.Nt - 1) / p.Nt, p.splits), block(kThreads);
-  RK_CUDA(launch_pdl(gemm_tc_kernel, grid, block, smem, stream, map_w, map_x, p));
-  RK_LAUNCH_CHECK("gemm_tc launch");
-  if (p.splits > 1) {
-    const long long work = static_cast<long long>(a.M) * (a.N / 4);
-    RK_CUDA(launch_pdl(splitk_reduce_kernel, dim3(static_cast<unsigned>((work + 255) / 256)), dim3(256), 0, stream, p));
+  const int sms = sm_count();
+  const Plan plan = make_plan(a, n, a[0].scratch ? a[0].scratch_bytes : 0, sms);
+  RK_REQUIRE(plan.Nt > 0 && plan.total_units > 0, kShape, "gemm_group: no launch plan");
+
+  static MapPack maps;  // filled and consumed under the lock: kernel parameters are copied at launch
+  static std::mutex mu;
+  GroupDev g = {};
+  g.n_prob = n;
+  g.Nt = plan.Nt;
+  g.tiles_m = plan.tiles_m;
+  g.total_units = plan.total_units;
+  // shared memory: a shallow activation ring (tiles from L2) and as deep a weight ring (tiles from DRAM) as fits
+  const size_t x_bytes = static_cast<size_t>(g.Nt) * 128, w_bytes = static_cast<size_t>(kBM) * 128;
+  // (every byte an SM takes in, from DRAM or L2, shares one path of roughly 80 GB/s, so with wide row tiles the
+  // activation tiles are the larger part of the traffic; measured best: equal depth up to 128 rows, 3 + 6 above)
+  const size_t budget = 224 * 1024 - kEpiBytes;
+  if (g.Nt > 128) {
+    g.x_stages = 3;
+    g.w_stages = static_cast<int>(std::min<size_t>(kMaxWStages, (budget - g.x_stages * x_bytes) / w_bytes));
+  } else {
+    g.x_stages = g.w_stages = static_cast<int>(std::min<size_t>(kMaxXStages, budget / (x_bytes + w_bytes)));
+  }
+  const size_t smem = w_bytes * g.w_stages + x_bytes * g.x_stages + kEpiBytes + 1024;
+  g.w_dynamic = 0;
+  for (int i = 0; i < n; ++i) g.w_dynamic |= a[i].w_dynamic ? 1 : 0;
+
+  std::lock_guard<std::mutex> lock(mu);
+  float* scratch = a[0].scratch;
+  int unit = 0, red = 0;
+  for (int i = 0; i < n; ++i) {
+    Prob& p = g.prob[i];
+    p.M = a[i].M; p.N = a[i].N; p.K = a[i].K; p.epi = a[i].epi; p.y = a[i].y; p.scale = a[i].out_scale;
+    p.v = a[i].ea.v; p.v_first = a[i].ea.v_first; p.v0 = a[i].ea.v0;
+    p.tiles_n = (a[i].N + kBM - 1) / kBM;
+    p.splits = plan.splits[i];
+    p.kb_per_split = plan.kbps[i];
+    p.unit_begin = unit;
+    unit += p.tiles_n * g.tiles_m * p.splits;
+    p.red_begin = red;
+    p.partial = nullptr;
+    if (p.splits > 1) {
+      p.partial = scratch;
+      scratch += static_cast<size_t>(p.splits) * p.M * p.N;
+      red += static_cast<int>((static_cast<long long>(p.M) * (p.N / 4) + 255) / 256);
+    }
+    int s = make_map(&maps.w[i], a[i].w, a[i].N, a[i].K, a[i].K, kBM);
+    if (s != kOk) return s;
+    s = make_map(&maps.x[i], a[i].x, a[i].M, a[i].K, a[i].ldx ? a[i].ldx : a[i].K, g.Nt);
+    if (s != kOk) return s;
+  }
+  for (int i = n; i < kMaxProb; ++i) {
+    maps.w[i] = maps.w[0];
+    maps.x[i] = maps.x[0];
+  }
+  g.red_blocks = red;
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  RK_CUDA(cudaGetDevice(&dev));
+  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    RK_CUDA(cudaFuncSetAttribute(gemm_group_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 225 * 1024));
+    attr_set[dev] = true;
+  }
+  const dim3 grid(static_cast<unsigned>(std::min(sms, g.total_units))), block(kThreads);
+  RK_CUDA(launch_pdl(gemm_group_kernel, grid, block, smem, stream, maps, g));
+  RK_LAUNCH_CHECK("gemm_group launch");
+  if (red > 0) {
+    RK_CUDA(launch_pdl(splitk_reduce_kernel, dim3(static_cast<unsigned>(red)), dim3(256), 0, stream, g));
     RK_LAUNCH_CHECK("splitk_reduce launch");
   }
   return kOk;
 }
+
+int gemm_tc(cudaStream_t stream, const LinearArgs& a) { return gemm_group(stream, &a, 1); }
 
 // ---------------------------------------------------------------------------------------------
 // Split-K GEMM for callers that must not allocate: the fp32 partial sums go to a fixed device array

@@ -84,6 +84,9 @@ struct LinearArgs {
   half* wq_scratch = nullptr;
   size_t wq_scratch_bytes = 0;
   const half* out_scale = nullptr;
+  // tensor-core path: true when w may have been written by the kernel launched just before this call on the same
+  // stream (then its tiles are not requested until that kernel has completed); a model's resident weights set false
+  bool w_dynamic = true;
   // optional fused prologue of the decode GEMV (M <= 4, fp16 weights, K == channels): see GemvSeg in gemv.h
   const half* res = nullptr;
   const half* ln_w = nullptr;
@@ -105,6 +108,9 @@ struct LinearArgs {
 int linear(cudaStream_t stream, const LinearArgs& args);
 // Up to 8 independent problems sharing M <= 4 in a single launch.
 int linear_batch(cudaStream_t stream, const LinearArgs* args, int n);
+// Up to eight products with the same M > 4: one tensor-core launch when every product has fp16 weights and no
+// input activation (split-K scratch is taken from args[0]); otherwise one linear() call per product.
+int linear_group(cudaStream_t stream, const LinearArgs* args, int n);
 
 // ---- tmix_decode.cu : fused one-token time-mix core (LoRA up + gates + WKV + GroupNorm/gate)
 struct TmixDecodeArgs {

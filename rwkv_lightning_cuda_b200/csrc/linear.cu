@@ -22,6 +22,7 @@
 namespace rk {
 
 int gemm_tc(cudaStream_t stream, const LinearArgs& a);  // gemm_tcgen05.cu
+int gemm_group(cudaStream_t stream, const LinearArgs* a, int n);
 bool gemm_tc_supported(const LinearArgs& a);
 
 namespace {
@@ -342,6 +343,7 @@ int linear(cudaStream_t stream, const LinearArgs& a) {
     LinearArgs b = a;
     b.fmt = 0;
     b.w = a.wq_scratch;
+    b.w_dynamic = true;  // written by the unpack kernel launched just below
     b.scale = nullptr;
     b.zero = nullptr;
     if (a.fmt == 1) {
@@ -365,6 +367,29 @@ int linear(cudaStream_t stream, const LinearArgs& a) {
     if (a.ea.v_first) c.ea.v_first = a.ea.v_first + static_cast<size_t>(m0) * a.N;
     s = linear_batch(stream, &c, 1);
     if (s != kOk) return s;
+  }
+  return kOk;
+}
+
+int linear_group(cudaStream_t stream, const LinearArgs* args, int n) {
+  RK_REQUIRE(args && n >= 1 && n <= 8, kBadArg, "linear_group: 1..8 products");
+  bool together = true;
+  for (int i = 0; i < n; ++i) together = together && args[i].M > 4 && args[i].M == args[0].M && gemm_tc_supported(args[i]);
+  if (together) return gemm_group(stream, args, n);
+  for (int i = 0; i < n; ++i) {
+    LinearArgs b = args[i];
+    int act = kActNone;
+    if (b.epi == kEpiTanhH) act = kActTanh;
+    if (b.epi == kEpiSigmoidH) act = kActSigmoid;
+    if (act != kActNone) b.epi = kEpiNone;
+    if (!b.scratch) { b.scratch = args[0].scratch; b.scratch_bytes = args[0].scratch_bytes; }
+    int s = linear(stream, b);
+    if (s != kOk) return s;
+    if (act != kActNone) {
+      half* y = static_cast<half*>(b.y);
+      s = activate(stream, y, y, static_cast<long long>(b.M) * b.N, act);
+      if (s != kOk) return s;
+    }
   }
   return kOk;
 }

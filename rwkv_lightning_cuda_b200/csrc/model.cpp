@@ -387,7 +387,7 @@ Workspace* Model::workspace(int B, int T) {
     if (ws->part32.alloc(n * sizeof(float)) != kOk) return nullptr;
   }
   if (rows > 4) {
-    const size_t want = std::min<size_t>(static_cast<size_t>(256) << 20, rows * C * sizeof(float) * 8);
+    const size_t want = std::min<size_t>(static_cast<size_t>(512) << 20, rows * C * sizeof(float) * 24);
     if (ws->gemm_scratch.alloc(want) != kOk) return nullptr;
     if (cfg_.weight_format != RWKV7_B200_FMT_F16) {
       const size_t big = std::max(static_cast<size_t>(cfg_.vocab) * C, F * C) * sizeof(half);
@@ -407,6 +407,7 @@ int Model::lin(cudaStream_t s, int M, const Matrix& W, const half* x, void* y, i
   LinearArgs a;
   a.M = M; a.K = W.K; a.N = W.N; a.x = x; a.w = W.w.p; a.fmt = W.fmt;
   a.scale = W.scale.as<half>(); a.zero = W.zero.as<half>(); a.epi = epi; a.y = y;
+  a.w_dynamic = false;  // resident weights
   if (cur_) {
     a.scratch = cur_->gemm_scratch.as<float>(); a.scratch_bytes = cur_->gemm_scratch.bytes;
     a.wq_scratch = cur_->wq_scratch.as<half>(); a.wq_scratch_bytes = cur_->wq_scratch.bytes;
@@ -418,6 +419,7 @@ int Model::lin16(cudaStream_t s, int M, int K, int N, const half* x, const half*
                  const EpiArgs& ea) {
   LinearArgs a;
   a.M = M; a.K = K; a.N = N; a.x = x; a.w = w; a.fmt = RWKV7_B200_FMT_F16; a.in_act = in_act; a.epi = epi; a.ea = ea; a.y = y;
+  a.w_dynamic = false;
   if (cur_) { a.scratch = cur_->gemm_scratch.as<float>(); a.scratch_bytes = cur_->gemm_scratch.bytes; }
   return linear(s, a);
 }
@@ -580,32 +582,64 @@ int Model::enqueue(Workspace& ws, int B, int T, half* shift, void* wkv, int* ela
       ta.elapsed = elapsed; ta.y2 = ws.y2;
       RK_TRY(tmix_decode(st, ta));
     } else {
-      RK_TRY(lin(st, rows, W.Wr, xr, ws.r, kEpiNone));
-      RK_TRY(lin(st, rows, W.Wk, xk, ws.k, kEpiNone));
-      RK_TRY(lin(st, rows, W.Wv, xv, v_lin, kEpiNone));
-      RK_TRY(lin16(st, rows, C, cfg_.rank_w, xw, W.w1t.as<half>(), ws.l1[0], kActNone, kEpiNone, none));
-      RK_TRY(lin16(st, rows, C, cfg_.rank_a, xa, W.a1t.as<half>(), ws.l1[1], kActNone, kEpiNone, none));
-      RK_TRY(lin16(st, rows, C, cfg_.rank_g, xg, W.g1t.as<half>(), ws.l1[2], kActNone, kEpiNone, none));
       const bool big = rows > 4;  // the reference rounds tanh/sigmoid and the v LoRA output to half for larger row counts
-      if (big) {
-        RK_TRY(activate(st, ws.l1[0], ws.l1[0], static_cast<long long>(rows) * cfg_.rank_w, kActTanh));
-        RK_TRY(activate(st, ws.l1[2], ws.l1[2], static_cast<long long>(rows) * cfg_.rank_g, kActSigmoid));
-      }
-      RK_TRY(lin16(st, rows, cfg_.rank_w, Cl, ws.l1[0], W.w2t.as<half>(), ws.w12, big ? kActNone : kActTanh, kEpiNone, none));
-      RK_TRY(lin16(st, rows, cfg_.rank_a, Cl, ws.l1[1], W.a2t.as<half>(), ws.a12, kActNone, kEpiNone, none));
-      RK_TRY(lin16(st, rows, cfg_.rank_g, Cl, ws.l1[2], W.g2t.as<half>(), ws.g, big ? kActNone : kActSigmoid, kEpiNone, none));
       const half* v_use = ws.vfirst;
-      if (li > 0) {
-        RK_TRY(lin16(st, rows, C, cfg_.rank_v, xv, W.v1t.as<half>(), ws.l1[3], kActNone, kEpiNone, none));
-        if (big) {
-          RK_TRY(lin16(st, rows, cfg_.rank_v, Cl, ws.l1[3], W.v2t.as<half>(), ws.y, kActNone, kEpiNone, none));
+      if (big) {
+        // many rows: two tensor-core launches -- r/k/v with the four LoRA down-projections (tanh / sigmoid as
+        // their epilogues), then the four LoRA up-projections
+        auto dense = [&](const Matrix& Wm, const half* x, void* y) {
+          LinearArgs a;
+          a.M = rows; a.K = Wm.K; a.N = Wm.N; a.x = x; a.w = Wm.w.p; a.fmt = Wm.fmt; a.y = y; a.w_dynamic = false;
+          a.scratch = ws.gemm_scratch.as<float>(); a.scratch_bytes = ws.gemm_scratch.bytes;
+          return a;
+        };
+        auto low = [&](const DevBuf& w, int K, int N, const half* x, half* y, int epi) {
+          LinearArgs a;
+          a.M = rows; a.K = K; a.N = N; a.x = x; a.w = w.p; a.fmt = RWKV7_B200_FMT_F16; a.epi = epi; a.y = y; a.w_dynamic = false;
+          a.scratch = ws.gemm_scratch.as<float>(); a.scratch_bytes = ws.gemm_scratch.bytes;
+          return a;
+        };
+        LinearArgs grp[7];
+        int ng = 0;
+        if (cfg_.weight_format == RWKV7_B200_FMT_F16) {
+          grp[ng++] = dense(W.Wr, xr, ws.r); grp[ng++] = dense(W.Wk, xk, ws.k); grp[ng++] = dense(W.Wv, xv, v_lin);
+        } else {  // quantised matrices are expanded one at a time through a shared scratch buffer
+          RK_TRY(lin(st, rows, W.Wr, xr, ws.r, kEpiNone));
+          RK_TRY(lin(st, rows, W.Wk, xk, ws.k, kEpiNone));
+          RK_TRY(lin(st, rows, W.Wv, xv, v_lin, kEpiNone));
+        }
+        grp[ng++] = low(W.w1t, C, cfg_.rank_w, xw, ws.l1[0], kEpiTanhH);
+        grp[ng++] = low(W.a1t, C, cfg_.rank_a, xa, ws.l1[1], kEpiNone);
+        grp[ng++] = low(W.g1t, C, cfg_.rank_g, xg, ws.l1[2], kEpiSigmoidH);
+        if (li > 0) grp[ng++] = low(W.v1t, C, cfg_.rank_v, xv, ws.l1[3], kEpiNone);
+        RK_TRY(linear_group(st, grp, ng));
+        ng = 0;
+        grp[ng++] = low(W.w2t, cfg_.rank_w, Cl, ws.l1[0], ws.w12, kEpiNone);
+        grp[ng++] = low(W.a2t, cfg_.rank_a, Cl, ws.l1[1], ws.a12, kEpiNone);
+        grp[ng++] = low(W.g2t, cfg_.rank_g, Cl, ws.l1[2], ws.g, kEpiNone);
+        if (li > 0) grp[ng++] = low(W.v2t, cfg_.rank_v, Cl, ws.l1[3], ws.y, kEpiNone);
+        RK_TRY(linear_group(st, grp, ng));
+        if (li > 0) {
           RK_TRY(tmix_vres_gate(st, rows, Cl, ws.v, ws.vfirst, W.v0.as<half>(), ws.y, ws.vout));
-        } else {
+          v_use = ws.vout;
+        }
+      } else {
+        RK_TRY(lin(st, rows, W.Wr, xr, ws.r, kEpiNone));
+        RK_TRY(lin(st, rows, W.Wk, xk, ws.k, kEpiNone));
+        RK_TRY(lin(st, rows, W.Wv, xv, v_lin, kEpiNone));
+        RK_TRY(lin16(st, rows, C, cfg_.rank_w, xw, W.w1t.as<half>(), ws.l1[0], kActNone, kEpiNone, none));
+        RK_TRY(lin16(st, rows, C, cfg_.rank_a, xa, W.a1t.as<half>(), ws.l1[1], kActNone, kEpiNone, none));
+        RK_TRY(lin16(st, rows, C, cfg_.rank_g, xg, W.g1t.as<half>(), ws.l1[2], kActNone, kEpiNone, none));
+        RK_TRY(lin16(st, rows, cfg_.rank_w, Cl, ws.l1[0], W.w2t.as<half>(), ws.w12, kActTanh, kEpiNone, none));
+        RK_TRY(lin16(st, rows, cfg_.rank_a, Cl, ws.l1[1], W.a2t.as<half>(), ws.a12, kActNone, kEpiNone, none));
+        RK_TRY(lin16(st, rows, cfg_.rank_g, Cl, ws.l1[2], W.g2t.as<half>(), ws.g, kActSigmoid, kEpiNone, none));
+        if (li > 0) {
+          RK_TRY(lin16(st, rows, C, cfg_.rank_v, xv, W.v1t.as<half>(), ws.l1[3], kActNone, kEpiNone, none));
           EpiArgs ea;
           ea.v = ws.v; ea.v_first = ws.vfirst; ea.v0 = W.v0.as<half>();
           RK_TRY(lin16(st, rows, cfg_.rank_v, Cl, ws.l1[3], W.v2t.as<half>(), ws.vout, kActNone, kEpiVres, ea));
+          v_use = ws.vout;
         }
-        v_use = ws.vout;
       }
       RK_TRY(tmix_kk_a_gate(st, rows, Cl, ws.k, W.k_k.as<half>(), W.a0.as<half>(), ws.a12, W.k_a.as<half>(), ws.k2, ws.nkk, ws.kka));
       if (cfg_.wkv32) {
