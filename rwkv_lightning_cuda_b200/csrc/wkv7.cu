@@ -203,81 +203,140 @@ __global__ void __launch_bounds__(256) wkv7_fp32_decode_kernel(
 }
 
 // ---------------------------------------------------------------------------------------
-// fp32 state, T tokens (prefill chunks).  Sequential in t; 4 lanes share a row (16 columns
-// each) so a head keeps 256 threads busy and each reduction is a 2-step shuffle.  The state
-// lives in registers for the whole chunk; token vectors are double-buffered in shared memory
-// (segments padded by 4 floats so the four lanes' float4 reads hit distinct banks).
-template <bool kAddW0>
-__global__ void __launch_bounds__(256) wkv7_fp32_scan_kernel(
+// fp32 state, T tokens (prefill chunks).  Sequential in t.  A thread owns two rows x 16 columns of the state in
+// registers for the whole chunk; four lanes share a row pair, so each reduction is a 2-step shuffle.  (Every
+// thread reads the 16 columns' worth of five token vectors from shared memory per step; with one row per thread
+// that traffic, not the arithmetic, sets the step time -- two rows per thread halve it.)  A CTA covers kRows rows
+// of one head: 64, or 32 when there are few heads, so that a head's two halves run on two SMs.
+// Token vectors are staged eight tokens at a time: every thread fetches its share of the NEXT block into
+// registers before it computes the current block (the global-memory latency hides behind eight recurrence
+// steps), then converts it into a double-buffered fp32 block in shared memory (segments padded by 4 floats so
+// the four lanes' float4 reads hit distinct banks).  One barrier per block; the steps inside a block only
+// exchange data through shuffles.
+template <bool kAddW0, int kRows>
+__global__ void __launch_bounds__(kRows * 2) wkv7_fp32_scan_kernel(
     int T, int C, int H, float* __restrict__ state, const half* __restrict__ r,
     const half* __restrict__ w, const half* __restrict__ w0, const half* __restrict__ k,
     const half* __restrict__ v, const half* __restrict__ a, const half* __restrict__ b,
     half* __restrict__ y) {
-  constexpr int kSeg = 20;  // 16 floats + 4 pad
-  __shared__ __align__(16) float vecs[2][5][4 * kSeg];  // r, decay, k, a, b
-  __shared__ float vsm[2][kHead];
+  constexpr int kSeg = 20;   // 16 floats + 4 pad
+  constexpr int kBlk = 8;    // tokens per staged block
+  constexpr int kThreads = kRows * 2;
+  constexpr int kSlots = kBlk * (kHead / 2) / kThreads;  // half2 slots of a block each thread stages (per vector)
+  constexpr int kParts = kHead / kRows;                  // CTAs per head
+  __shared__ __align__(16) float vecs[2][5][kBlk][4 * kSeg];  // r, decay, k, a, b
+  __shared__ __align__(8) float vsm[2][kBlk][kHead];
 
-  const int bh = blockIdx.x;
+  const int bh = blockIdx.x / kParts;
+  const int part = blockIdx.x - bh * kParts;
   const int b_id = bh / H;
   const int h = bh - b_id * H;
   const int tid = threadIdx.x;
-  const int row = tid >> 2, q = tid & 3;
+  const int row = part * kRows + (tid >> 2) * 2, q = tid & 3;   // rows row, row + 1
   float* srow = state + static_cast<size_t>(bh) * (kHead * kHead) + row * kHead + q * 16;
   const size_t tok0 = (static_cast<size_t>(b_id) * T) * C + static_cast<size_t>(h) * kHead;
 
-  float S[16];
+  __half2 pre[kSlots][6];
+  float2 w0f[kSlots];
 #pragma unroll
-  for (int c = 0; c < 4; ++c) {
-    const float4 t4 = reinterpret_cast<const float4*>(srow)[c];
-    S[4 * c] = t4.x; S[4 * c + 1] = t4.y; S[4 * c + 2] = t4.z; S[4 * c + 3] = t4.w;
+  for (int i = 0; i < kSlots; ++i) {
+    const int ch = ((tid + i * kThreads) & 31) * 2;
+    w0f[i] = kAddW0 ? __half22float2(*reinterpret_cast<const __half2*>(w0 + h * kHead + ch)) : make_float2(0.f, 0.f);
   }
-  float w0f = 0.f;
-  if (kAddW0 && tid < kHead) w0f = __half2float(w0[h * kHead + tid]);
-
-  auto stage = [&](int t, int buf) {
-    if (tid < kHead) {
-      const size_t idx = tok0 + static_cast<size_t>(t) * C + tid;
-      const int slot = (tid >> 4) * kSeg + (tid & 15);
-      float wf = __half2float(w[idx]);
-      if (kAddW0) wf = __half2float(__float2half_rn(wf + w0f));
-      vecs[buf][0][slot] = __half2float(r[idx]);
-      vecs[buf][1][slot] = decay_f32(wf);
-      vecs[buf][2][slot] = __half2float(k[idx]);
-      vecs[buf][3][slot] = __half2float(a[idx]);
-      vecs[buf][4][slot] = __half2float(b[idx]);
-      vsm[buf][tid] = __half2float(v[idx]);
+  auto fetch = [&](int t_first) {
+#pragma unroll
+    for (int i = 0; i < kSlots; ++i) {
+      const int slot = tid + i * kThreads;  // token slot / 32 of the block, channels 2 * (slot % 32) and + 1
+      const int t = t_first + (slot >> 5);
+      if (t < T) {
+        const size_t idx = tok0 + static_cast<size_t>(t) * C + (slot & 31) * 2;
+        pre[i][0] = *reinterpret_cast<const __half2*>(r + idx);
+        pre[i][1] = *reinterpret_cast<const __half2*>(w + idx);
+        pre[i][2] = *reinterpret_cast<const __half2*>(k + idx);
+        pre[i][3] = *reinterpret_cast<const __half2*>(a + idx);
+        pre[i][4] = *reinterpret_cast<const __half2*>(b + idx);
+        pre[i][5] = *reinterpret_cast<const __half2*>(v + idx);
+      }
     }
   };
-  stage(0, 0);
-  for (int t = 0; t < T; ++t) {
-    const int cur = t & 1;
-    __syncthreads();
-    if (t + 1 < T) stage(t + 1, cur ^ 1);
-    const float* rv = &vecs[cur][0][q * kSeg];
-    const float* wv = &vecs[cur][1][q * kSeg];
-    const float* kv = &vecs[cur][2][q * kSeg];
-    const float* av = &vecs[cur][3][q * kSeg];
-    const float* bv = &vecs[cur][4][q * kSeg];
-    float sa = 0.f;
+  auto put = [&](int buf) {
 #pragma unroll
-    for (int j = 0; j < 16; ++j) sa = fmaf(S[j], av[j], sa);
-    sa += __shfl_xor_sync(0xffffffffu, sa, 1);
-    sa += __shfl_xor_sync(0xffffffffu, sa, 2);
-    const float vi = vsm[cur][row];
-    float yy = 0.f;
-#pragma unroll
-    for (int j = 0; j < 16; ++j) {
-      const float s = S[j] * wv[j] + sa * bv[j] + kv[j] * vi;
-      S[j] = s;
-      yy = fmaf(s, rv[j], yy);
+    for (int i = 0; i < kSlots; ++i) {
+      const int slot = tid + i * kThreads;
+      const int tok = slot >> 5, ch = (slot & 31) * 2;
+      const int pos = (ch >> 4) * kSeg + (ch & 15);
+      float2 wf = __half22float2(pre[i][1]);
+      if (kAddW0) {
+        wf.x = __half2float(__float2half_rn(wf.x + w0f[i].x));
+        wf.y = __half2float(__float2half_rn(wf.y + w0f[i].y));
+      }
+      *reinterpret_cast<float2*>(&vecs[buf][0][tok][pos]) = __half22float2(pre[i][0]);
+      *reinterpret_cast<float2*>(&vecs[buf][1][tok][pos]) = make_float2(decay_f32(wf.x), decay_f32(wf.y));
+      *reinterpret_cast<float2*>(&vecs[buf][2][tok][pos]) = __half22float2(pre[i][2]);
+      *reinterpret_cast<float2*>(&vecs[buf][3][tok][pos]) = __half22float2(pre[i][3]);
+      *reinterpret_cast<float2*>(&vecs[buf][4][tok][pos]) = __half22float2(pre[i][4]);
+      *reinterpret_cast<float2*>(&vsm[buf][tok][ch]) = __half22float2(pre[i][5]);
     }
-    yy += __shfl_xor_sync(0xffffffffu, yy, 1);
-    yy += __shfl_xor_sync(0xffffffffu, yy, 2);
-    if (q == 0) y[tok0 + static_cast<size_t>(t) * C + row] = __float2half_rn(yy);
+  };
+
+  fetch(0);
+  float S0[16], S1[16];
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    const float4 t0 = reinterpret_cast<const float4*>(srow)[c];
+    const float4 t1 = reinterpret_cast<const float4*>(srow + kHead)[c];
+    S0[4 * c] = t0.x; S0[4 * c + 1] = t0.y; S0[4 * c + 2] = t0.z; S0[4 * c + 3] = t0.w;
+    S1[4 * c] = t1.x; S1[4 * c + 1] = t1.y; S1[4 * c + 2] = t1.z; S1[4 * c + 3] = t1.w;
+  }
+
+  int buf = 0;
+  for (int t0 = 0; t0 < T; t0 += kBlk, buf ^= 1) {
+    put(buf);          // tokens t0 .. t0+7 (slots of tokens >= T hold stale values and are not used)
+    __syncthreads();   // also: every warp has finished the block before last, which used this buffer
+    if (t0 + kBlk < T) fetch(t0 + kBlk);
+    const int n_here = min(kBlk, T - t0);
+    for (int tl = 0; tl < n_here; ++tl) {  // (fully unrolling the block and splitting the sums measured slower)
+      const float* rv = &vecs[buf][0][tl][q * kSeg];
+      const float* wv = &vecs[buf][1][tl][q * kSeg];
+      const float* kv = &vecs[buf][2][tl][q * kSeg];
+      const float* av = &vecs[buf][3][tl][q * kSeg];
+      const float* bv = &vecs[buf][4][tl][q * kSeg];
+      float sa0 = 0.f, sa1 = 0.f;
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        const float aj = av[j];
+        sa0 = fmaf(S0[j], aj, sa0);
+        sa1 = fmaf(S1[j], aj, sa1);
+      }
+      sa0 += __shfl_xor_sync(0xffffffffu, sa0, 1);
+      sa1 += __shfl_xor_sync(0xffffffffu, sa1, 1);
+      sa0 += __shfl_xor_sync(0xffffffffu, sa0, 2);
+      sa1 += __shfl_xor_sync(0xffffffffu, sa1, 2);
+      const float2 vi = *reinterpret_cast<const float2*>(&vsm[buf][tl][row]);
+      float y0 = 0.f, y1 = 0.f;
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        const float wj = wv[j], bj = bv[j], kj = kv[j], rj = rv[j];
+        const float s0 = S0[j] * wj + sa0 * bj + kj * vi.x;
+        const float s1 = S1[j] * wj + sa1 * bj + kj * vi.y;
+        S0[j] = s0;
+        S1[j] = s1;
+        y0 = fmaf(s0, rj, y0);
+        y1 = fmaf(s1, rj, y1);
+      }
+      y0 += __shfl_xor_sync(0xffffffffu, y0, 1);
+      y1 += __shfl_xor_sync(0xffffffffu, y1, 1);
+      y0 += __shfl_xor_sync(0xffffffffu, y0, 2);
+      y1 += __shfl_xor_sync(0xffffffffu, y1, 2);
+      if (q == 0)
+        *reinterpret_cast<__half2*>(y + tok0 + static_cast<size_t>(t0 + tl) * C + row) = __floats2half2_rn(y0, y1);
+    }
   }
 #pragma unroll
-  for (int c = 0; c < 4; ++c)
-    reinterpret_cast<float4*>(srow)[c] = make_float4(S[4 * c], S[4 * c + 1], S[4 * c + 2], S[4 * c + 3]);
+  for (int c = 0; c < 4; ++c) {
+    reinterpret_cast<float4*>(srow)[c] = make_float4(S0[4 * c], S0[4 * c + 1], S0[4 * c + 2], S0[4 * c + 3]);
+    reinterpret_cast<float4*>(srow + kHead)[c] = make_float4(S1[4 * c], S1[4 * c + 1], S1[4 * c + 2], S1[4 * c + 3]);
+  }
 }
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -312,8 +371,16 @@ int wkv7_fp32(cudaStream_t stream, int B, int T, int C, int H, float* state, con
     if (w0) wkv7_fp32_decode_kernel<true><<<grid, block, 0, stream>>>(C, H, state, r, w, w0, k, v, a, b, y);
     else wkv7_fp32_decode_kernel<false><<<grid, block, 0, stream>>>(C, H, state, r, w, w0, k, v, a, b, y);
   } else {
-    if (w0) wkv7_fp32_scan_kernel<true><<<grid, block, 0, stream>>>(T, C, H, state, r, w, w0, k, v, a, b, y);
-    else wkv7_fp32_scan_kernel<false><<<grid, block, 0, stream>>>(T, C, H, state, r, w, w0, k, v, a, b, y);
+    // few heads: two CTAs per head, so that the sequential scan spreads over twice as many SMs
+    if (B * H <= 160) {
+      const dim3 g2(B * H * 2), b2(64);
+      if (w0) wkv7_fp32_scan_kernel<true, 32><<<g2, b2, 0, stream>>>(T, C, H, state, r, w, w0, k, v, a, b, y);
+      else wkv7_fp32_scan_kernel<false, 32><<<g2, b2, 0, stream>>>(T, C, H, state, r, w, w0, k, v, a, b, y);
+    } else {
+      const dim3 b1(128);
+      if (w0) wkv7_fp32_scan_kernel<true, 64><<<grid, b1, 0, stream>>>(T, C, H, state, r, w, w0, k, v, a, b, y);
+      else wkv7_fp32_scan_kernel<false, 64><<<grid, b1, 0, stream>>>(T, C, H, state, r, w, w0, k, v, a, b, y);
+    }
   }
   RK_LAUNCH_CHECK("wkv7_fp32 launch");
   return kOk;
