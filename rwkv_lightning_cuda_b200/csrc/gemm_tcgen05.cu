@@ -79,6 +79,7 @@ struct Prob {
 
 struct GroupDev {
   int n_prob, total_units, Nt, w_stages, x_stages, tiles_m, red_blocks;
+  int bm;         // output channels per work unit: 128, or 256 for the CTA-pair kernel
   int w_dynamic;  // the weights may have been written by the previous kernel: wait for it before reading them
   Prob prob[kMaxProb];
 };
@@ -96,6 +97,48 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
 }
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+// ---- CTA-pair (cta_group::2) forms: two CTAs of a cluster work on one 256-channel tile.  Each loads its own 128
+// weight rows and HALF of the activation tile; the leader (cluster rank 0) issues the MMAs for both.
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// Address of the same shared-memory location in the CTA of the given cluster rank.
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// The destination is this CTA's shared memory; the barrier (a shared::cluster address) is the leader's.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t cluster_bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(cluster_bar), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void mma_f16_pair(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrives on the barrier at this shared-memory offset in both CTAs of the pair once the MMAs issued so far are done.
+__device__ __forceinline__ void mma_commit_pair(uint32_t bar) {
+  const uint16_t both = 3;
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(bar), "h"(both)
+               : "memory");
 }
 
 // Shared-memory matrix descriptor: K-major tile, 128-byte swizzle, 8-row groups 1024 bytes apart.
@@ -216,7 +259,7 @@ __device__ __forceinline__ Unit decode_unit(const GroupDev& g, int u) {
   const int nt = local % p.tiles_n, split = local / p.tiles_n;
   Unit r;
   r.prob = pi;
-  r.n0 = nt * kBM;
+  r.n0 = nt * g.bm;
   r.m0 = mt * g.Nt;
   r.split = split;
   r.kb_begin = split * p.kb_per_split;
@@ -225,6 +268,7 @@ __device__ __forceinline__ Unit decode_unit(const GroupDev& g, int u) {
   return r;
 }
 
+template <bool kPair>
 __global__ void __launch_bounds__(kThreads, 1) gemm_group_kernel(const __grid_constant__ MapPack maps, const GroupDev g) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   __shared__ __align__(8) uint64_t w_full[kMaxWStages], w_empty[kMaxWStages], x_full[kMaxXStages], x_empty[kMaxXStages];
@@ -235,7 +279,12 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_group_kernel(const __grid_co
   if (threadIdx.x == 0) RK_TRACE(0);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   constexpr uint32_t kWBytes = kBM * 128;
-  const uint32_t x_bytes = g.Nt * 128;
+  // CTA pair: cluster rank 0 leads; every CTA stages its own 128 weight rows and half of the activation rows
+  const uint32_t rank = kPair ? cluster_rank() : 0u;
+  const int first_unit = kPair ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
+  const int unit_stride = kPair ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
+  const int x_rows = kPair ? g.Nt / 2 : g.Nt;
+  const uint32_t x_bytes = x_rows * 128;
   // the dynamic window is 1024-byte aligned here (required by the 128-byte swizzle): weight ring, activation ring,
   // epilogue tile
   const uint32_t w_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -254,17 +303,24 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_group_kernel(const __grid_co
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(smem_u32(&acc_full[a]), 1);
-      mbar_init(smem_u32(&acc_empty[a]), 1);
+      mbar_init(smem_u32(&acc_empty[a]), kPair ? 2 : 1);  // one arrival per CTA whose epilogue drains the accumulator
     }
     failed = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"(kTmemCols) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    if (kPair) {
+      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"(kTmemCols) : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    } else {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"(kTmemCols) : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
+  __syncwarp();
+  if (kPair) cluster_sync_all();  // the peer's barriers are initialised before anything signals them
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = tmem_slot;
   if (threadIdx.x == 0) RK_TRACE(1);
@@ -276,14 +332,20 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_group_kernel(const __grid_co
       if (g.w_dynamic) pdl_wait();
       bool ok = true;
       int it = 0;
-      for (int ui = blockIdx.x; ui < g.total_units && ok && !failed; ui += gridDim.x) {
+      for (int ui = first_unit; ui < g.total_units && ok && !failed; ui += unit_stride) {
         const Unit u = decode_unit(g, ui);
         for (int kb = 0; kb < u.kblocks; ++kb, ++it) {
           const int s = it % g.w_stages;
           if (it >= g.w_stages && !mbar_wait(smem_u32(&w_empty[s]), ((it / g.w_stages) - 1) & 1)) { ok = false; break; }
           const uint32_t bar = smem_u32(&w_full[s]);
-          mbar_expect_tx(bar, kWBytes);
-          tma_load_2d(w_base + s * kWBytes, &maps.w[u.prob], bar, (u.kb_begin + kb) * kBK, u.n0);
+          if (kPair) {  // both CTAs' tiles complete the leader's barrier
+            if (rank == 0) mbar_expect_tx(bar, 2 * kWBytes);
+            tma_load_2d_pair(w_base + s * kWBytes, &maps.w[u.prob], map_to_rank(bar, 0), (u.kb_begin + kb) * kBK,
+                             u.n0 + static_cast<int>(rank) * kBM);
+          } else {
+            mbar_expect_tx(bar, kWBytes);
+            tma_load_2d(w_base + s * kWBytes, &maps.w[u.prob], bar, (u.kb_begin + kb) * kBK, u.n0);
+          }
         }
       }
       if (!ok) failed = 1;
@@ -296,25 +358,33 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_group_kernel(const __grid_co
       RK_TRACE(2);
       bool ok = true;
       int it = 0;
-      for (int ui = blockIdx.x; ui < g.total_units && ok && !failed; ui += gridDim.x) {
+      for (int ui = first_unit; ui < g.total_units && ok && !failed; ui += unit_stride) {
         const Unit u = decode_unit(g, ui);
         for (int kb = 0; kb < u.kblocks; ++kb, ++it) {
           const int s = it % g.x_stages;
           if (it >= g.x_stages && !mbar_wait(smem_u32(&x_empty[s]), ((it / g.x_stages) - 1) & 1)) { ok = false; break; }
           const uint32_t bar = smem_u32(&x_full[s]);
-          mbar_expect_tx(bar, x_bytes);
-          tma_load_2d(x_base + s * x_bytes, &maps.x[u.prob], bar, (u.kb_begin + kb) * kBK, u.m0);
+          if (kPair) {
+            if (rank == 0) mbar_expect_tx(bar, 2 * x_bytes);
+            tma_load_2d_pair(x_base + s * x_bytes, &maps.x[u.prob], map_to_rank(bar, 0), (u.kb_begin + kb) * kBK,
+                             u.m0 + static_cast<int>(rank) * x_rows);
+          } else {
+            mbar_expect_tx(bar, x_bytes);
+            tma_load_2d(x_base + s * x_bytes, &maps.x[u.prob], bar, (u.kb_begin + kb) * kBK, u.m0);
+          }
         }
       }
       if (!ok) failed = 1;
     }
   } else if (warp == 1) {
     // ---- MMA issuer
-    if (lane == 0) {
-      const uint32_t idesc = (1u << 4) | (static_cast<uint32_t>(g.Nt >> 3) << 17) | (static_cast<uint32_t>(kBM >> 4) << 24);
+    if (lane == 0 && rank == 0) {
+      // fp32 accumulate, fp16 operands, both K-major; N = row-tile width, M = 128 per CTA
+      const uint32_t idesc = (1u << 4) | (static_cast<uint32_t>(g.Nt >> 3) << 17) |
+                             (static_cast<uint32_t>((kPair ? 2 * kBM : kBM) >> 4) << 24);
       bool ok = true;
       int it = 0, n_unit = 0;
-      for (int ui = blockIdx.x; ui < g.total_units && ok && !failed; ui += gridDim.x, ++n_unit) {
+      for (int ui = first_unit; ui < g.total_units && ok && !failed; ui += unit_stride, ++n_unit) {
         const Unit u = decode_unit(g, ui);
         const int acc = n_unit & 1;
         if (n_unit >= 2) {  // the epilogue of the unit that used this accumulator two units ago has drained it
@@ -331,12 +401,22 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_group_kernel(const __grid_co
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const uint64_t da = smem_desc(w_base + ws * kWBytes), db = smem_desc(x_base + xs * x_bytes);
 #pragma unroll
-          for (int k4 = 0; k4 < kBK / 16; ++k4)  // 32 bytes further along the swizzled row per K=16 step
-            mma_f16(tmem_acc, da + 2 * k4, db + 2 * k4, idesc, (kb | k4) != 0);
-          mma_commit(smem_u32(&w_empty[ws]));
-          mma_commit(smem_u32(&x_empty[xs]));
+          for (int k4 = 0; k4 < kBK / 16; ++k4) {  // 32 bytes further along the swizzled row per K=16 step
+            if (kPair) mma_f16_pair(tmem_acc, da + 2 * k4, db + 2 * k4, idesc, (kb | k4) != 0);
+            else mma_f16(tmem_acc, da + 2 * k4, db + 2 * k4, idesc, (kb | k4) != 0);
+          }
+          if (kPair) {
+            mma_commit_pair(smem_u32(&w_empty[ws]));
+            mma_commit_pair(smem_u32(&x_empty[xs]));
+          } else {
+            mma_commit(smem_u32(&w_empty[ws]));
+            mma_commit(smem_u32(&x_empty[xs]));
+          }
         }
-        if (ok) mma_commit(smem_u32(&acc_full[acc]));
+        if (ok) {
+          if (kPair) mma_commit_pair(smem_u32(&acc_full[acc]));
+          else mma_commit(smem_u32(&acc_full[acc]));
+        }
         if (n_unit == 0) RK_TRACE(4);
       }
       if (!ok) failed = 1;
@@ -348,8 +428,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_group_kernel(const __grid_co
     const int t = threadIdx.x - kCtrlThreads;
     const int c4 = (t & 31) * 4;
     int n_unit = 0;
-    for (int ui = blockIdx.x; ui < g.total_units; ui += gridDim.x, ++n_unit) {
-      const Unit u = decode_unit(g, ui);
+    for (int ui = first_unit; ui < g.total_units; ui += unit_stride, ++n_unit) {
+      Unit u = decode_unit(g, ui);
+      u.n0 += static_cast<int>(rank) * kBM;  // this CTA's 128 channels of the tile
       const EpiCtx p = make_ctx(g.prob[u.prob]);
       const int acc = n_unit & 1;
       bool ok = !failed && mbar_wait(smem_u32(&acc_full[acc]), (n_unit >> 1) & 1);
@@ -415,7 +496,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_group_kernel(const __grid_co
       // every warp's TMEM reads are complete (wait::ld + the barrier above): hand the accumulator back
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       asm volatile("bar.sync 1, 256;" ::: "memory");
-      if (t == 0) mbar_arrive(smem_u32(&acc_empty[acc]));
+      if (t == 0) {
+        if (kPair) mbar_arrive_cluster(map_to_rank(smem_u32(&acc_empty[acc]), 0));
+        else mbar_arrive(smem_u32(&acc_empty[acc]));
+      }
       if (t == 0 && n_unit == 0) RK_TRACE(6);
     }
   }
@@ -423,8 +507,11 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_group_kernel(const __grid_co
   __syncthreads();
   if (threadIdx.x == 0) RK_TRACE(7);
   if (threadIdx.x == 0 && failed) atomicExch(&g_gemm_timeout, 1);
+  __syncwarp();
+  if (kPair) cluster_sync_all();  // neither CTA leaves while its partner may still signal its barriers or read its tiles
   if (warp == 1) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+    if (kPair) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+    else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
   }
 }
 
@@ -551,35 +638,40 @@ struct Plan {
   bool any_split = false;
 };
 
-Plan make_plan_uncached(const LinearArgs* a, int n, size_t scratch_bytes, int sms);
+Plan make_plan_uncached(const LinearArgs* a, int n, size_t scratch_bytes, int sms, int bm);
 
 // Plans depend only on the shapes; a model asks for the same few again and again.
-Plan make_plan(const LinearArgs* a, int n, size_t scratch_bytes, int sms) {
+// sms: CTAs (bm == 128) or CTA pairs (bm == 256) that walk the unit list.
+Plan make_plan(const LinearArgs* a, int n, size_t scratch_bytes, int sms, int bm) {
   static std::mutex mu;
   static std::unordered_map<std::string, Plan> cache;
   std::string key;
   key.reserve(16 + 8 * static_cast<size_t>(n));
   auto put = [&key](long long v) { key.append(reinterpret_cast<const char*>(&v), sizeof(v)); };
-  put(a[0].M); put(n); put(static_cast<long long>(scratch_bytes)); put(sms);
+  put(a[0].M); put(n); put(static_cast<long long>(scratch_bytes)); put(sms); put(bm);
   for (int i = 0; i < n; ++i) { put(a[i].N); put(a[i].K); }
   {
     std::lock_guard<std::mutex> lock(mu);
     auto it = cache.find(key);
     if (it != cache.end()) return it->second;
   }
-  const Plan p = make_plan_uncached(a, n, scratch_bytes, sms);
+  const Plan p = make_plan_uncached(a, n, scratch_bytes, sms, bm);
   std::lock_guard<std::mutex> lock(mu);
   if (cache.size() > 4096) cache.clear();
   cache.emplace(std::move(key), p);
   return p;
 }
 
-Plan make_plan_uncached(const LinearArgs* a, int n, size_t scratch_bytes, int sms) {
+Plan make_plan_uncached(const LinearArgs* a, int n, size_t scratch_bytes, int sms, int bm) {
   const int M = a[0].M;
   int nts[3], n_nt = 0;
-  nts[n_nt++] = std::min(256, round16(M));
-  if (M > 128) nts[n_nt++] = 128;
-  if (M > 64) nts[n_nt++] = 64;
+  if (bm == 2 * kBM) {
+    nts[n_nt++] = std::min(256, ((M + 31) / 32) * 32);  // each CTA of a pair stages half of the row tile
+  } else {
+    nts[n_nt++] = std::min(256, round16(M));
+    if (M > 128) nts[n_nt++] = 128;
+    if (M > 64) nts[n_nt++] = 64;
+  }
   static const int targets[] = {1 << 30, 128, 96, 64, 48, 32, 24, 16, 12, 8, 6, 4};
   // tuning aids: force the row-tile width / the K blocks per unit
   static const int force_nt = [] { const char* e = getenv("RWKV7_B200_GEMM_NT"); return e ? atoi(e) : 0; }();
@@ -610,7 +702,7 @@ Plan make_plan_uncached(const LinearArgs* a, int n, size_t scratch_bytes, int sm
       std::fill(load.begin(), load.end(), 0.0);
       int u = 0;
       for (int i = 0; i < n; ++i) {
-        const int tiles_n = (a[i].N + kBM - 1) / kBM;
+        const int tiles_n = (a[i].N + bm - 1) / bm;
         const int units = tiles_n * tiles_m * p.splits[i];
         // weight tile from DRAM for the first row tile, from L2 for the others; epilogue cost grows with Nt
         const double epi = (p.splits[i] > 1 ? 2.0 : 1.0) * Nt / 128.0 + 1.5;
@@ -647,22 +739,55 @@ int gemm_group(cudaStream_t stream, const LinearArgs* a, int n) {
     RK_REQUIRE(a[i].y, kBadArg, "gemm_group: null output");
   }
   const int sms = sm_count();
-  const Plan plan = make_plan(a, n, a[0].scratch ? a[0].scratch_bytes : 0, sms);
+  // CTA pairs (cta_group::2: each CTA stages half of the activation tile) are opt-in: on the shapes of this model
+  // they measured equal to single CTAs (M = 256 .. 2048), so the simpler kernel is the default.
+  static const int pair_mode = [] { const char* e = getenv("RWKV7_B200_GEMM_PAIR"); return e ? atoi(e) : 0; }();
+  static std::mutex mu;
+  static int pairs_dev[64] = {0};  // co-resident CTA pairs per device; -1 = cluster launch not available
+  int dev = 0;
+  RK_CUDA(cudaGetDevice(&dev));
+  RK_REQUIRE(dev >= 0 && dev < 64, kBadArg, "gemm_group: device ordinal out of range");
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (!pairs_dev[dev]) {
+      RK_CUDA(cudaFuncSetAttribute(gemm_group_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 225 * 1024));
+      RK_CUDA(cudaFuncSetAttribute(gemm_group_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 225 * 1024));
+      cudaLaunchConfig_t probe = {};
+      probe.gridDim = dim3(static_cast<unsigned>(sms & ~1));
+      probe.blockDim = dim3(kThreads);
+      probe.dynamicSmemBytes = 200 * 1024;
+      cudaLaunchAttribute at[1];
+      at[0].id = cudaLaunchAttributeClusterDimension;
+      at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+      probe.attrs = at;
+      probe.numAttrs = 1;
+      int clusters = 0;
+      if (cudaOccupancyMaxActiveClusters(&clusters, gemm_group_kernel<true>, &probe) != cudaSuccess || clusters < 1) {
+        cudaGetLastError();
+        clusters = -1;
+      }
+      pairs_dev[dev] = clusters;
+    }
+  }
+  const bool pair = pair_mode == 1 && pairs_dev[dev] > 0;
+  const int walkers = pair ? std::min(pairs_dev[dev], sms / 2) : sms;
+  const int bm = pair ? 2 * kBM : kBM;
+  const Plan plan = make_plan(a, n, a[0].scratch ? a[0].scratch_bytes : 0, walkers, bm);
   RK_REQUIRE(plan.Nt > 0 && plan.total_units > 0, kShape, "gemm_group: no launch plan");
 
   static MapPack maps;  // filled and consumed under the lock: kernel parameters are copied at launch
-  static std::mutex mu;
   GroupDev g = {};
   g.n_prob = n;
+  g.bm = bm;
   g.Nt = plan.Nt;
   g.tiles_m = plan.tiles_m;
   g.total_units = plan.total_units;
-  // shared memory: a shallow activation ring (tiles from L2) and as deep a weight ring (tiles from DRAM) as fits
-  const size_t x_bytes = static_cast<size_t>(g.Nt) * 128, w_bytes = static_cast<size_t>(kBM) * 128;
-  // (every byte an SM takes in, from DRAM or L2, shares one path of roughly 80 GB/s, so with wide row tiles the
-  // activation tiles are the larger part of the traffic; measured best: equal depth up to 128 rows, 3 + 6 above)
+  // shared memory: an activation ring and a weight ring.  Measured best: equal depth, except 3 + 6 for a single
+  // wide row tile (the memory-bound batched-decode shape).
+  const int x_rows = pair ? g.Nt / 2 : g.Nt;
+  const size_t x_bytes = static_cast<size_t>(x_rows) * 128, w_bytes = static_cast<size_t>(kBM) * 128;
   const size_t budget = 224 * 1024 - kEpiBytes;
-  if (g.Nt > 128) {
+  if (x_rows > 128 && g.tiles_m == 1) {
     g.x_stages = 3;
     g.w_stages = static_cast<int>(std::min<size_t>(kMaxWStages, (budget - g.x_stages * x_bytes) / w_bytes));
   } else {
@@ -679,7 +804,7 @@ int gemm_group(cudaStream_t stream, const LinearArgs* a, int n) {
     Prob& p = g.prob[i];
     p.M = a[i].M; p.N = a[i].N; p.K = a[i].K; p.epi = a[i].epi; p.y = a[i].y; p.scale = a[i].out_scale;
     p.v = a[i].ea.v; p.v_first = a[i].ea.v_first; p.v0 = a[i].ea.v0;
-    p.tiles_n = (a[i].N + kBM - 1) / kBM;
+    p.tiles_n = (a[i].N + bm - 1) / bm;
     p.splits = plan.splits[i];
     p.kb_per_split = plan.kbps[i];
     p.unit_begin = unit;
@@ -693,7 +818,7 @@ int gemm_group(cudaStream_t stream, const LinearArgs* a, int n) {
     }
     int s = make_map(&maps.w[i], a[i].w, a[i].N, a[i].K, a[i].K, kBM);
     if (s != kOk) return s;
-    s = make_map(&maps.x[i], a[i].x, a[i].M, a[i].K, a[i].ldx ? a[i].ldx : a[i].K, g.Nt);
+    s = make_map(&maps.x[i], a[i].x, a[i].M, a[i].K, a[i].ldx ? a[i].ldx : a[i].K, x_rows);
     if (s != kOk) return s;
   }
   for (int i = n; i < kMaxProb; ++i) {
@@ -701,15 +826,24 @@ int gemm_group(cudaStream_t stream, const LinearArgs* a, int n) {
     maps.x[i] = maps.x[0];
   }
   g.red_blocks = red;
-  static bool attr_set[64] = {false};
-  int dev = 0;
-  RK_CUDA(cudaGetDevice(&dev));
-  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-    RK_CUDA(cudaFuncSetAttribute(gemm_group_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 225 * 1024));
-    attr_set[dev] = true;
+  if (pair) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(2 * std::min(walkers, g.total_units)));
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute at[2];
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+    at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = 2;
+    RK_CUDA(cudaLaunchKernelEx(&cfg, gemm_group_kernel<true>, maps, g));
+  } else {
+    const dim3 grid(static_cast<unsigned>(std::min(walkers, g.total_units))), block(kThreads);
+    RK_CUDA(launch_pdl(gemm_group_kernel<false>, grid, block, smem, stream, maps, g));
   }
-  const dim3 grid(static_cast<unsigned>(std::min(sms, g.total_units))), block(kThreads);
-  RK_CUDA(launch_pdl(gemm_group_kernel, grid, block, smem, stream, maps, g));
   RK_LAUNCH_CHECK("gemm_group launch");
   if (red > 0) {
     RK_CUDA(launch_pdl(splitk_reduce_kernel, dim3(static_cast<unsigned>(red)), dim3(256), 0, stream, g));
