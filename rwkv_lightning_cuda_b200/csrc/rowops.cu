@@ -200,6 +200,142 @@ __global__ void __launch_bounds__(kRowThreads) row_op_kernel(const RowOpDev p) {
   }
 }
 
+// ---- Chunks (T > 1) with many rows.  512 threads per row, so that a thread holds half as many pairs, and the
+// second row a CTA needs -- the previous token (t > 0), or the chunk's last token, which the CTAs of t == 0 store as
+// the new shift state -- is loaded together with its own row and normalised in the same chain of reductions.
+constexpr int kChunkThreads = 512;
+
+template <int kPairs>
+__device__ __forceinline__ void load_row_chunk(const RowOpDev& p, int b, int t, float2 (&v)[kPairs]) {
+  const size_t row = static_cast<size_t>(b) * p.T + t;
+  const int pairs = p.C >> 1;
+  const __half2* xs = reinterpret_cast<const __half2*>(p.x + row * p.C);
+  const __half2* rs = p.residual ? reinterpret_cast<const __half2*>(p.residual + row * p.C) : nullptr;
+  const float2* rf = p.residual_f32 ? reinterpret_cast<const float2*>(p.residual_f32 + row * p.C) : nullptr;
+#pragma unroll
+  for (int i = 0; i < kPairs; ++i) {
+    const int q = threadIdx.x + kChunkThreads * i;
+    float2 a = make_float2(0.f, 0.f), r = make_float2(0.f, 0.f);
+    if (q < pairs) {
+      a = __half22float2(xs[q]);
+      if (rs) r = __half22float2(rs[q]);
+      if (rf) {
+        const float2 t2 = rf[q];
+        r = __half22float2(__floats2half2_rn(t2.x, t2.y));
+      }
+    }
+    v[i] = make_float2(a.x + r.x, a.y + r.y);
+  }
+}
+
+// Sums two values over the CTA with one pair of barriers; every thread receives both totals.
+__device__ __forceinline__ float2 block_sum2_chunk(float a, float b, float* scratch /* 2 * kChunkThreads/32 floats */) {
+  a = warp_sum(a);
+  b = warp_sum(b);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  __syncthreads();  // scratch may still be read from a previous call
+  if (lane == 0) {
+    scratch[warp] = a;
+    scratch[kChunkThreads / 32 + warp] = b;
+  }
+  __syncthreads();
+  float ta = 0.f, tb = 0.f;
+#pragma unroll
+  for (int w = 0; w < kChunkThreads / 32; ++w) {
+    ta += scratch[w];
+    tb += scratch[kChunkThreads / 32 + w];
+  }
+  return make_float2(ta, tb);
+}
+
+// grid = rows.  Needs x (not the embedding table), LayerNorm weights or identity, n_mix > 0, not last_only.
+template <int kPairs>
+__global__ void __launch_bounds__(kChunkThreads) row_op_chunk_kernel(const RowOpDev p) {
+  __shared__ float scratch[2 * kChunkThreads / 32];
+  const int b = blockIdx.x / p.T, t = blockIdx.x - b * p.T;
+  const size_t row = static_cast<size_t>(b) * p.T + t;
+  const int pairs = p.C >> 1;
+  __half2 lw[kPairs], lb[kPairs], mixv[kPairs][6];
+  float2 prev[kPairs];
+  __half2* shift2 = reinterpret_cast<__half2*>(p.shift + static_cast<size_t>(b) * p.C);
+#pragma unroll
+  for (int i = 0; i < kPairs; ++i) {
+    const int q = threadIdx.x + kChunkThreads * i;
+    prev[i] = make_float2(0.f, 0.f);
+    if (q >= pairs) continue;
+    if (p.ln_w) {
+      lw[i] = reinterpret_cast<const __half2*>(p.ln_w)[q];
+      lb[i] = reinterpret_cast<const __half2*>(p.ln_b)[q];
+    }
+#pragma unroll
+    for (int m = 0; m < 6; ++m)
+      if (m < p.n_mix) mixv[i][m] = reinterpret_cast<const __half2*>(p.mix[m])[q];
+    if (t == 0) prev[i] = __half22float2(shift2[q]);  // last written one launch ago at the latest
+  }
+  pdl_wait();
+  pdl_trigger();
+  float2 cur[kPairs], oth[kPairs];
+  load_row_chunk<kPairs>(p, b, t, cur);
+  load_row_chunk<kPairs>(p, b, t != 0 ? t - 1 : p.T - 1, oth);
+  if (p.x_out) {
+#pragma unroll
+    for (int i = 0; i < kPairs; ++i) {
+      const int q = threadIdx.x + kChunkThreads * i;
+      if (q < pairs) reinterpret_cast<__half2*>(p.x_out + row * p.C)[q] = __floats2half2_rn(cur[i].x, cur[i].y);
+    }
+  }
+  if (!p.identity) {
+    float s = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int i = 0; i < kPairs; ++i) {  // absent pairs hold zeros
+      s += cur[i].x + cur[i].y;
+      s2 += oth[i].x + oth[i].y;
+    }
+    const float inv_c = 1.0f / static_cast<float>(p.C);
+    float2 mean = block_sum2_chunk(s, s2, scratch);
+    mean.x *= inv_c;
+    mean.y *= inv_c;
+    float sv = 0.f, sv2 = 0.f;
+#pragma unroll
+    for (int i = 0; i < kPairs; ++i) {
+      if (threadIdx.x + kChunkThreads * i < pairs) {
+        const float d0 = cur[i].x - mean.x, d1 = cur[i].y - mean.x;
+        sv += d0 * d0 + d1 * d1;
+        const float e0 = oth[i].x - mean.y, e1 = oth[i].y - mean.y;
+        sv2 += e0 * e0 + e1 * e1;
+      }
+    }
+    const float2 var = block_sum2_chunk(sv, sv2, scratch);
+    const float rstd = rsqrtf(var.x * inv_c + p.eps), rstd2 = rsqrtf(var.y * inv_c + p.eps);
+#pragma unroll
+    for (int i = 0; i < kPairs; ++i) {
+      if (threadIdx.x + kChunkThreads * i < pairs) {
+        const float2 w = __half22float2(lw[i]);
+        const float2 bb = __half22float2(lb[i]);
+        cur[i] = __half22float2(__floats2half2_rn((cur[i].x - mean.x) * rstd * w.x + bb.x, (cur[i].y - mean.x) * rstd * w.y + bb.y));
+        oth[i] = __half22float2(__floats2half2_rn((oth[i].x - mean.y) * rstd2 * w.x + bb.x, (oth[i].y - mean.y) * rstd2 * w.y + bb.y));
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < kPairs; ++i) {
+    const int q = threadIdx.x + kChunkThreads * i;
+    if (q >= pairs) continue;
+    if (p.n_out) reinterpret_cast<__half2*>(p.n_out + row * p.C)[q] = __floats2half2_rn(cur[i].x, cur[i].y);
+    const float2 pv = t != 0 ? oth[i] : prev[i];
+    const float dx0 = pv.x - cur[i].x, dx1 = pv.y - cur[i].y;
+#pragma unroll
+    for (int m = 0; m < 6; ++m) {
+      if (m < p.n_mix) {
+        const float2 c = __half22float2(mixv[i][m]);
+        reinterpret_cast<__half2*>(p.mix_out[m] + row * p.C)[q] = __floats2half2_rn(cur[i].x + dx0 * c.x, cur[i].y + dx1 * c.y);
+      }
+    }
+    // only the CTAs of t == 0 touch shift[b]; each has consumed its old pairs above
+    if (t == 0) shift2[q] = __floats2half2_rn(oth[i].x, oth[i].y);
+  }
+}
+
 // kk = normalize(k * k_k) per head, a = sigmoid(a0 + a12), k' = k (1 + (a - 1) k_a);
 // emits k', -kk and kk*a (the WKV "a" and "b" operands).  One warp per (row, head).
 // Reference: tmix_kk_a_gate_kernel, cuda/rwkv7_fast_ops_fp16.cu:129-172.
@@ -357,6 +493,17 @@ int row_op(cudaStream_t stream, const RowOpArgs& a) {
     RK_REQUIRE(m >= a.n_mix || (a.mix[m] && a.mix_out[m]), kBadArg, "row_op: mix tensor %d missing", m);
   }
   const int rows = a.last_only ? a.B : a.B * a.T;
+  if (a.T > 1 && rows > 32 && !a.last_only && a.n_mix > 0 && !a.table && a.C >= 1024 && a.C <= 8192) {
+    const int need512 = (a.C / 2 + kChunkThreads - 1) / kChunkThreads;
+    const dim3 grid(rows), block(kChunkThreads);
+    cudaError_t e;
+    if (need512 <= 2) e = launch_pdl(row_op_chunk_kernel<2>, grid, block, 0, stream, p);
+    else if (need512 <= 4) e = launch_pdl(row_op_chunk_kernel<4>, grid, block, 0, stream, p);
+    else e = launch_pdl(row_op_chunk_kernel<8>, grid, block, 0, stream, p);
+    RK_CUDA(e);
+    RK_LAUNCH_CHECK("row_op (chunk) launch");
+    return kOk;
+  }
   const int need = (a.C / 2 + kRowThreads - 1) / kRowThreads;  // pairs per thread
   RK_REQUIRE(need <= 16, kShape, "row_op: C=%d too large (max 8192)", a.C);
   const int kp = need <= 1 ? 1 : need <= 2 ? 2 : need <= 4 ? 4 : need <= 8 ? 8 : 16;
