@@ -344,7 +344,7 @@ def micro_gemm(args):
     model, graph-replayed on rotating weights.  `--micro gemm-small` runs a few eager launches of two shapes."""
     from rwkv_lightning_cuda_b200 import ops
     small = args.micro == "gemm-small"
-    shapes = [(256, 128, 4096), (256, 4096, 4096)] if small else \
+    shapes = [(256, 4096, 16384), (128, 4096, 16384)] if small else \
         [(256, 128, 4096), (256, 4096, 128), (256, 4096, 4096), (256, 4096, 16384), (256, 16384, 4096), (128, 4096, 4096), (2048, 4096, 4096)]
     for M, K, N in shapes:
         copies = max(2, min(6, int(1e9 // (N * K * 2))))
