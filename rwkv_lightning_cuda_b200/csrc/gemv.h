@@ -50,6 +50,8 @@ struct GemvPrefetch {
   int depth, count;
 };
 
+bool gemv_tma_fits(int M, int K);  // gemv_tma.cu
+
 struct GemvBatch {
   int n_seg;
   GemvSeg seg[kMaxSeg];
@@ -74,6 +76,61 @@ __device__ __forceinline__ void store_result(const GemvSeg& sg, int m, int n, fl
     static_cast<half*>(sg.y)[o] = __float2half_rn(vv + (__half2float(sg.v_first[o]) - vv) * gate);
   } else {
     static_cast<half*>(sg.y)[o] = __float2half_rn(a);
+  }
+}
+
+// Expands one 16-byte weight chunk to fp32.
+template <int kFmt>
+__device__ __forceinline__ void dequant_chunk(const uint4& q, float* out, float s, float z);
+
+template <>
+__device__ __forceinline__ void dequant_chunk<0>(const uint4& q, float* out, float, float) {
+  const uint32_t u[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = h2f2(u[i]);
+    out[2 * i] = f.x;
+    out[2 * i + 1] = f.y;
+  }
+}
+
+// int8 -> exact integer-valued float via the fp16 "1024 + n" encoding.
+template <>
+__device__ __forceinline__ void dequant_chunk<1>(const uint4& q, float* out, float, float) {
+  const uint32_t u[4] = {q.x, q.y, q.z, q.w};
+  const __half2 bias = __floats2half2_rn(1152.f, 1152.f);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const uint32_t t = u[i] ^ 0x80808080u;
+    uint32_t h01 = __byte_perm(t, 0x64646464u, 0x4140);
+    uint32_t h23 = __byte_perm(t, 0x64646464u, 0x4342);
+    const float2 a = __half22float2(__hsub2(*reinterpret_cast<__half2*>(&h01), bias));
+    const float2 b = __half22float2(__hsub2(*reinterpret_cast<__half2*>(&h23), bias));
+    out[4 * i] = a.x;
+    out[4 * i + 1] = a.y;
+    out[4 * i + 2] = b.x;
+    out[4 * i + 3] = b.y;
+  }
+}
+
+// int4 -> half((q - zero) * scale), the written definition of the W4A16 weight value.
+template <>
+__device__ __forceinline__ void dequant_chunk<2>(const uint4& q, float* out, float s, float z) {
+  const uint32_t u[4] = {q.x, q.y, q.z, q.w};
+  const __half2 zb = __float2half2_rn(1024.f + z);
+  const __half2 s2 = __float2half2_rn(s);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    // byte j of the word holds elements 2j (low nibble) and 2j+1 (high nibble)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const uint32_t byte = (u[i] >> (8 * j)) & 0xffu;
+      uint32_t pair = (byte & 0xfu) | ((byte >> 4) << 16) | 0x64006400u;
+      const __half2 w2 = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&pair), zb), s2);
+      const float2 f = __half22float2(w2);
+      out[8 * i + 2 * j] = f.x;
+      out[8 * i + 2 * j + 1] = f.y;
+    }
   }
 }
 

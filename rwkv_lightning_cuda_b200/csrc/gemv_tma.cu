@@ -1,5 +1,5 @@
-// fp16 weight-streaming GEMV (M <= 4) with the weights staged through shared memory by the
-// bulk-copy engine: every warp owns a ring of kSlots buffers, one lane requests the next piece of
+// Weight-streaming GEMV (M <= 4; fp16, W8A16 or W4A16 weights, dequantised in registers) with the
+// weights staged through shared memory by the bulk-copy engine: every warp owns a ring of kSlots buffers, one lane requests the next piece of
 // the warp's contiguous weight stream with cp.async.bulk (completion on an mbarrier), the warp
 // consumes pieces in order with 128-bit shared-memory loads and re-arms the slot it has just read.
 // About kSlots * 4 KiB per warp (96 KiB per CTA) are in flight without holding registers, which is
@@ -32,7 +32,8 @@ __device__ __forceinline__ void fma_chunk(const uint4& q, const float* x, float&
   a0 = fmaf(xb.z, w3.x, a0); a1 = fmaf(xb.w, w3.y, a1);
 }
 
-template <int kM, int kW>
+// kQuant: some problem of the launch has int8 / int4 weights (the fp16-only instantiation carries no dequant code).
+template <int kM, int kW, bool kQuant>
 __global__ void __launch_bounds__(kW * 32) gemv_tma_kernel(const GemvBatch p, int x_bytes, int n_slots, int slot_stride) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   __shared__ __align__(8) uint64_t bars[kW][kMaxSlots];
@@ -51,7 +52,9 @@ __global__ void __launch_bounds__(kW * 32) gemv_tma_kernel(const GemvBatch p, in
   const int parts = sg.parts, piece = sg.piece_bytes;
   const int total = r_end > r_begin ? (r_end - r_begin) * parts : 0;
   const int K = sg.K;
-  const char* stream = static_cast<const char*>(sg.w) + static_cast<size_t>(r_begin) * K * 2;
+  const int fmt = kQuant ? sg.fmt : 0;
+  const int elems = fmt == 0 ? 8 : fmt == 1 ? 16 : 32;  // weights per 16-byte chunk
+  const char* stream = static_cast<const char*>(sg.w) + static_cast<size_t>(r_begin) * parts * piece;
 
   float* xs = reinterpret_cast<float*>(smem_raw);  // activations, fp32, input activation applied
   unsigned char* ring = smem_raw + x_bytes + static_cast<size_t>(warp) * n_slots * slot_stride;
@@ -119,20 +122,76 @@ __global__ void __launch_bounds__(kW * 32) gemv_tma_kernel(const GemvBatch p, in
       return;
     }
     const uint4* wsm = reinterpret_cast<const uint4*>(ring + slot * slot_stride) + lane;
-    const float* xk = xs + pp * (piece >> 1) + lane * 8;
-    if (piece == kPieceCap) {
-      uint4 q[8];
+    if (!kQuant || fmt == 0) {
+      const float* xk = xs + pp * (piece >> 1) + lane * 8;
+      if (piece == kPieceCap) {
+        uint4 q[8];
 #pragma unroll
-      for (int it = 0; it < 8; ++it) q[it] = wsm[it * 32];
+        for (int it = 0; it < 8; ++it) q[it] = wsm[it * 32];
 #pragma unroll
-      for (int it = 0; it < 8; ++it)
+        for (int it = 0; it < 8; ++it)
 #pragma unroll
-        for (int m = 0; m < kM; ++m) fma_chunk(q[it], xk + m * K + it * 256, acc0[m], acc1[m]);
+          for (int m = 0; m < kM; ++m) fma_chunk(q[it], xk + m * K + it * 256, acc0[m], acc1[m]);
+      } else {
+        for (int c = lane; c < chunks; c += 32) {
+          const uint4 q = wsm[c - lane];
+#pragma unroll
+          for (int m = 0; m < kM; ++m) fma_chunk(q, xk + m * K + (c - lane) * 8, acc0[m], acc1[m]);
+        }
+      }
     } else {
-      for (int c = lane; c < chunks; c += 32) {
-        const uint4 q = wsm[c - lane];
+      // int8 / int4, dequantised in registers (exact integer-valued floats for W8A16, half((q - zero) * scale) for
+      // W4A16) and multiplied with fp32 activations from shared memory.  A lane takes 4-byte words of the piece
+      // (word = lane + 32 j), so that consecutive lanes read consecutive 16 / 32 bytes of activations: no bank
+      // conflicts, which 16-byte weight chunks per lane would cause on the activation side.
+      const uint32_t* wsm32 = reinterpret_cast<const uint32_t*>(ring + slot * slot_stride);
+      const int words = piece >> 2;
+      if (fmt == 1) {
+        const int k_piece = pp * piece;  // one byte per weight
+        const __half2 bias = __floats2half2_rn(1152.f, 1152.f);
+#pragma unroll 4
+        for (int wd = lane; wd < words; wd += 32) {
+          const uint32_t t = wsm32[wd] ^ 0x80808080u;
+          uint32_t h01 = __byte_perm(t, 0x64646464u, 0x4140);
+          uint32_t h23 = __byte_perm(t, 0x64646464u, 0x4342);
+          const float2 w01 = __half22float2(__hsub2(*reinterpret_cast<__half2*>(&h01), bias));
+          const float2 w23 = __half22float2(__hsub2(*reinterpret_cast<__half2*>(&h23), bias));
 #pragma unroll
-        for (int m = 0; m < kM; ++m) fma_chunk(q, xk + m * K + (c - lane) * 8, acc0[m], acc1[m]);
+          for (int m = 0; m < kM; ++m) {
+            const float4 xv = *reinterpret_cast<const float4*>(xs + m * K + k_piece + wd * 4);
+            acc0[m] = fmaf(xv.x, w01.x, acc0[m]); acc1[m] = fmaf(xv.y, w01.y, acc1[m]);
+            acc0[m] = fmaf(xv.z, w23.x, acc0[m]); acc1[m] = fmaf(xv.w, w23.y, acc1[m]);
+          }
+        }
+      } else {
+        const int k_piece = pp * piece * 2;  // two weights per byte
+        const half* srow = sg.scale + static_cast<size_t>(row) * (K >> 7);
+        const half* zrow = sg.zero + static_cast<size_t>(row) * (K >> 7);
+#pragma unroll 2
+        for (int wd = lane; wd < words; wd += 32) {
+          const uint32_t u = wsm32[wd];
+          const int k = k_piece + wd * 8;
+          const __half2 zb = __float2half2_rn(1024.f + __half2float(zrow[k >> 7]));
+          const __half2 s2 = __half2half2(srow[k >> 7]);
+          float wf[8];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {  // byte j holds elements 2j (low nibble) and 2j+1 (high nibble)
+            const uint32_t byte = (u >> (8 * j)) & 0xffu;
+            uint32_t pair = (byte & 0xfu) | ((byte >> 4) << 16) | 0x64006400u;
+            const float2 f = __half22float2(__hmul2(__hsub2(*reinterpret_cast<__half2*>(&pair), zb), s2));
+            wf[2 * j] = f.x;
+            wf[2 * j + 1] = f.y;
+          }
+#pragma unroll
+          for (int m = 0; m < kM; ++m) {
+            const float4 xa = *reinterpret_cast<const float4*>(xs + m * K + k);
+            const float4 xb = *reinterpret_cast<const float4*>(xs + m * K + k + 4);
+            acc0[m] = fmaf(xa.x, wf[0], acc0[m]); acc1[m] = fmaf(xa.y, wf[1], acc1[m]);
+            acc0[m] = fmaf(xa.z, wf[2], acc0[m]); acc1[m] = fmaf(xa.w, wf[3], acc1[m]);
+            acc0[m] = fmaf(xb.x, wf[4], acc0[m]); acc1[m] = fmaf(xb.y, wf[5], acc1[m]);
+            acc0[m] = fmaf(xb.z, wf[6], acc0[m]); acc1[m] = fmaf(xb.w, wf[7], acc1[m]);
+          }
+        }
       }
     }
     __syncwarp();  // every lane has read the slot: it may be overwritten
@@ -146,7 +205,8 @@ __global__ void __launch_bounds__(kW * 32) gemv_tma_kernel(const GemvBatch p, in
       part = 0;
 #pragma unroll
       for (int m = 0; m < kM; ++m) {
-        const float a = warp_sum(acc0[m] + acc1[m]);
+        float a = warp_sum(acc0[m] + acc1[m]);
+        if (kQuant && fmt == 1) a *= __half2float(sg.scale[row]);  // W8A16: one scale per output channel
         if (lane == 0) store_result(sg, m, row, a);
         acc0[m] = acc1[m] = 0.f;
       }
@@ -164,8 +224,9 @@ bool gemv_tma_plan(GemvBatch& b, int M, size_t* smem_bytes, int* grid, int* n_sl
   double total_bytes = 0;
   for (int i = 0; i < b.n_seg; ++i) {
     GemvSeg& g = b.seg[i];
-    if (g.fmt != 0) return false;
-    const int row_bytes = g.K * 2;
+    if (g.fmt == 2 && g.K % 128 != 0) return false;
+    const int row_bytes = g.fmt == 0 ? g.K * 2 : g.fmt == 1 ? g.K : g.K / 2;
+    if (row_bytes % 16 != 0) return false;
     int parts = (row_bytes + kPieceCap - 1) / kPieceCap;
     while (parts <= 64 && (row_bytes % (parts * 16) != 0)) ++parts;
     if (parts > 64) return false;
@@ -195,7 +256,7 @@ bool gemv_tma_plan(GemvBatch& b, int M, size_t* smem_bytes, int* grid, int* n_sl
   if (x_bytes + static_cast<size_t>(kWarps) * slots * cap > 200 * 1024) return false;
   for (int i = 0; i < b.n_seg; ++i) {
     GemvSeg& g = b.seg[i];
-    const int row_bytes = g.K * 2;
+    const int row_bytes = g.fmt == 0 ? g.K * 2 : g.fmt == 1 ? g.K : g.K / 2;
     int parts = (row_bytes + cap - 1) / cap;
     while (parts <= 256 && (row_bytes % (parts * 16) != 0)) ++parts;
     if (parts > 256) return false;
@@ -208,7 +269,7 @@ bool gemv_tma_plan(GemvBatch& b, int M, size_t* smem_bytes, int* grid, int* n_sl
   int cta = 0;
   for (int i = 0; i < b.n_seg; ++i) {
     GemvSeg& g = b.seg[i];
-    const double share = static_cast<double>(g.N) * g.K * 2 / total_bytes;
+    const double share = static_cast<double>(g.N) * g.parts * g.piece_bytes / total_bytes;
     const int n = std::max(1, static_cast<int>(share * budget + 0.5));
     const int rpw = std::max(1, (g.N + n * kWarps - 1) / (n * kWarps));
     g.rows_per_cta = rpw * kWarps;
@@ -221,6 +282,12 @@ bool gemv_tma_plan(GemvBatch& b, int M, size_t* smem_bytes, int* grid, int* n_sl
   *slot_stride = cap;
   *n_warps = kWarps;
   return true;
+}
+
+// Whether M rows of K fp32 activations fit beside the smallest ring (8 warps, two 4 KiB slots) the planner accepts.
+bool gemv_tma_fits(int M, int K) {
+  const size_t x_bytes = (static_cast<size_t>(M) * K * 4 + 127) & ~static_cast<size_t>(127);
+  return x_bytes + static_cast<size_t>(8) * 2 * kPieceCap <= 200 * 1024;
 }
 
 GemvPrefetch gemv_tma_prefetch_of(const void* w, int N, int K, int launch_rows) {
@@ -245,20 +312,38 @@ int gemv_tma_launch(cudaStream_t stream, const GemvBatch& b, int M, size_t smem_
     RK_CUDA(launch_pdl(kernel, dim3(grid), dim3(kWarps * 32), smem_bytes, stream, b, x_bytes, n_slots, slot_stride));
     return kOk;
   };
+  bool quant = false;
+  for (int i = 0; i < b.n_seg; ++i) quant = quant || b.seg[i].fmt != 0;
   int s;
-  if (kWarps == 16) {
+  if (!quant) {
+    if (kWarps == 16) {
+      switch (M) {
+        case 1: s = launch(gemv_tma_kernel<1, 16, false>); break;
+        case 2: s = launch(gemv_tma_kernel<2, 16, false>); break;
+        case 3: s = launch(gemv_tma_kernel<3, 16, false>); break;
+        default: s = launch(gemv_tma_kernel<4, 16, false>); break;
+      }
+    } else {
+      switch (M) {
+        case 1: s = launch(gemv_tma_kernel<1, 8, false>); break;
+        case 2: s = launch(gemv_tma_kernel<2, 8, false>); break;
+        case 3: s = launch(gemv_tma_kernel<3, 8, false>); break;
+        default: s = launch(gemv_tma_kernel<4, 8, false>); break;
+      }
+    }
+  } else if (kWarps == 16) {
     switch (M) {
-      case 1: s = launch(gemv_tma_kernel<1, 16>); break;
-      case 2: s = launch(gemv_tma_kernel<2, 16>); break;
-      case 3: s = launch(gemv_tma_kernel<3, 16>); break;
-      default: s = launch(gemv_tma_kernel<4, 16>); break;
+      case 1: s = launch(gemv_tma_kernel<1, 16, true>); break;
+      case 2: s = launch(gemv_tma_kernel<2, 16, true>); break;
+      case 3: s = launch(gemv_tma_kernel<3, 16, true>); break;
+      default: s = launch(gemv_tma_kernel<4, 16, true>); break;
     }
   } else {
     switch (M) {
-      case 1: s = launch(gemv_tma_kernel<1, 8>); break;
-      case 2: s = launch(gemv_tma_kernel<2, 8>); break;
-      case 3: s = launch(gemv_tma_kernel<3, 8>); break;
-      default: s = launch(gemv_tma_kernel<4, 8>); break;
+      case 1: s = launch(gemv_tma_kernel<1, 8, true>); break;
+      case 2: s = launch(gemv_tma_kernel<2, 8, true>); break;
+      case 3: s = launch(gemv_tma_kernel<3, 8, true>); break;
+      default: s = launch(gemv_tma_kernel<4, 8, true>); break;
     }
   }
   if (s != kOk) return s;

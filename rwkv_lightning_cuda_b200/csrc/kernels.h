@@ -108,6 +108,8 @@ struct LinearArgs {
 int linear(cudaStream_t stream, const LinearArgs& args);
 // Up to 8 independent problems sharing M <= 4 in a single launch.
 int linear_batch(cudaStream_t stream, const LinearArgs* args, int n);
+// Whether linear_batch can run M rows of K inputs with the fused prologue (bulk-copy kernel: activations in shared memory).
+bool linear_batch_fused_fits(int M, int K);
 // Up to eight products with the same M > 4: one tensor-core launch when every product has fp16 weights and no
 // input activation (split-K scratch is taken from args[0]); otherwise one linear() call per product.
 int linear_group(cudaStream_t stream, const LinearArgs* args, int n);

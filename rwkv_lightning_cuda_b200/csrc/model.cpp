@@ -430,7 +430,7 @@ int Model::lin16(cudaStream_t s, int M, int K, int N, const half* x, const half*
     if (_s != kOk) return _s;   \
   } while (0)
 
-// Decode step for up to four sequences with fp16 weights: five launches per layer.  The residual
+// Decode step for up to four sequences (fp16, W8A16 or W4A16 weights): five launches per layer.  The residual
 // add + LayerNorm + token shift in front of the r/k/v (+LoRA down) projections, of ffn.key and of
 // the lm-head run as the prologue of those GEMV kernels; the shift states are updated by the kernel
 // that follows (the fused head kernel, the ffn.value GEMV).
@@ -439,6 +439,7 @@ int Model::enqueue_decode(Workspace& ws, int B, half* shift, void* wkv, int* ela
   auto mat = [&](const Matrix& Wm, const half* x, void* y, int epi) {
     LinearArgs a;
     a.M = rows; a.K = Wm.K; a.N = Wm.N; a.x = x; a.w = Wm.w.p; a.fmt = Wm.fmt; a.epi = epi; a.y = y;
+    a.scale = Wm.scale.as<half>(); a.zero = Wm.zero.as<half>();
     return a;
   };
   auto low = [&](const DevBuf& w, int R, const half* x, half* y) {
@@ -533,8 +534,10 @@ int Model::enqueue(Workspace& ws, int B, int T, half* shift, void* wkv, int* ela
     TmixDecodeArgs probe;
     probe.B = B; probe.C = C; probe.wkv32 = cfg_.wkv32 != 0;
     probe.R[0] = cfg_.rank_w; probe.R[1] = cfg_.rank_a; probe.R[2] = cfg_.rank_g; probe.R[3] = cfg_.rank_v;
-    if (G == 1 && T == 1 && rows <= 4 && cfg_.weight_format == RWKV7_B200_FMT_F16 && tmix_decode_supported(probe) &&
-        C <= 4096 && C % 8 == 0)
+    const bool rows_ok = cfg_.weight_format == RWKV7_B200_FMT_F16 ? C % 8 == 0 : (C % 128 == 0 && cfg_.ffn % 128 == 0);
+    // the fused path stages a step's activations in shared memory: B rows of ffn inputs must fit
+    if (G == 1 && T == 1 && rows <= 4 && tmix_decode_supported(probe) && C <= 4096 && rows_ok &&
+        linear_batch_fused_fits(rows, cfg_.ffn) && linear_batch_fused_fits(rows, C))
       return enqueue_decode(ws, B, shift, wkv, elapsed, logits, st);
   }
   {

@@ -320,10 +320,11 @@ int tmix_decode(cudaStream_t stream, const TmixDecodeArgs& a) {
   const size_t smem = static_cast<size_t>(kHead) * (sum_r * 2 + 64) + (a.wkv32 ? 0 : 8192);
   const dim3 grid(a.B * p.H), block(256);
   if (a.wkv32) {
-    if (smem > 48 * 1024) RK_CUDA(cudaFuncSetAttribute(tmix_decode_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    // always raised: the kernel's static shared memory counts against the default 48 KiB limit as well
+    RK_CUDA(cudaFuncSetAttribute(tmix_decode_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
     RK_CUDA(launch_pdl(tmix_decode_kernel<true>, grid, block, smem, stream, p));
   } else {
-    if (smem > 48 * 1024) RK_CUDA(cudaFuncSetAttribute(tmix_decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    RK_CUDA(cudaFuncSetAttribute(tmix_decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
     RK_CUDA(launch_pdl(tmix_decode_kernel<false>, grid, block, smem, stream, p));
   }
   RK_LAUNCH_CHECK("tmix_decode launch");

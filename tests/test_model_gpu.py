@@ -134,3 +134,16 @@ def test_decode_graph_replay_is_deterministic_and_matches_eager():
         torch.cuda.synchronize()
         outs.append(torch.stack(seq))
     assert torch.equal(outs[0], outs[1])
+
+
+@pytest.mark.parametrize("dims,B", [
+    (dict(TINY, layers=2, ffn=16384), 4),      # four rows of ffn inputs do not fit the fused decode kernels' shared memory
+    (dict(TINY, layers=2, ffn=16384), 2),      # two rows do
+    (dict(TINY, layers=2, rank_w=64, rank_a=64, rank_v=32, rank_g=128), 1),   # 0.1B ranks: exactly 48 KiB of dynamic shared memory
+])
+def test_decode_shapes_at_the_edges_of_the_fused_path(dims, B):
+    d, om, gm = build_pair(orc.FMT_F16, False, dims=dims)
+    worst, ids_ok, _, _ = run_both(d, om, gm, False, B, (2,), 3)
+    print(f"[parity] edge shapes {dims} B={B}: worst logit err {worst:.3e}")
+    assert worst < 2e-2
+    assert ids_ok
