@@ -712,7 +712,7 @@ Plan make_plan_uncached(const LinearArgs* a, int n, size_t scratch_bytes, int sm
 
 bool problem_ok(const LinearArgs& a) {
   const int ldx = a.ldx ? a.ldx : a.K;
-  return a.fmt == 0 && a.in_act == kActNone && a.K % 8 == 0 && ldx % 8 == 0 && a.M > 4 && a.N % 4 == 0 &&
+  return a.fmt == 0 && a.in_act == kActNone && a.K % 8 == 0 && ldx % 8 == 0 && a.M >= 2 && a.N % 4 == 0 &&
          (reinterpret_cast<uintptr_t>(a.x) & 15u) == 0 && (reinterpret_cast<uintptr_t>(a.w) & 15u) == 0;
 }
 
@@ -848,7 +848,7 @@ constexpr size_t kStaticScratchFloats = static_cast<size_t>(4) << 20;  // 16 MiB
 static __device__ __align__(256) float g_static_scratch[kStaticScratchFloats];
 
 int gemm_tc_static_scratch(cudaStream_t stream, const LinearArgs& a) {
-  RK_REQUIRE(gemm_tc_supported(a), kShape, "linear (static scratch): needs more than 4 rows, fp16 weights, K %% 8 == 0");
+  RK_REQUIRE(a.M > 4 && gemm_tc_supported(a), kShape, "linear (static scratch): needs more than 4 rows, fp16 weights, K %% 8 == 0");
   RK_REQUIRE(a.N % 4 == 0, kShape, "linear (static scratch): N must be a multiple of 4");
   // at least two K splits must fit: 2 * M * N floats
   RK_REQUIRE(static_cast<size_t>(a.M) * a.N * 2 <= kStaticScratchFloats, kShape,

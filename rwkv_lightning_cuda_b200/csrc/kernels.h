@@ -87,6 +87,9 @@ struct LinearArgs {
   // tensor-core path: true when w may have been written by the kernel launched just before this call on the same
   // stream (then its tiles are not requested until that kernel has completed); a model's resident weights set false
   bool w_dynamic = true;
+  // 2..4 rows normally take the GEMV kernels (whose time grows with the row count); set this to send a large fp16
+  // product of 2..4 rows to the tensor-core kernel instead, which streams the weights once whatever the row count
+  bool prefer_tc = false;
   // optional fused prologue of the decode GEMV (M <= 4, fp16 weights, K == channels): see GemvSeg in gemv.h
   const half* res = nullptr;
   const half* ln_w = nullptr;

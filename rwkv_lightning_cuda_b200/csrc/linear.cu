@@ -282,7 +282,7 @@ int linear_batch(cudaStream_t stream, const LinearArgs* args, int n) {
 int linear(cudaStream_t stream, const LinearArgs& a) {
   int s = check_args(a);
   if (s != kOk) return s;
-  if (a.M > 4 && gemm_tc_supported(a)) return gemm_tc(stream, a);
+  if ((a.M > 4 || (a.prefer_tc && a.M >= 2)) && gemm_tc_supported(a)) return gemm_tc(stream, a);
   if (a.M > 4 && a.fmt != 0 && a.in_act == kActNone && a.wq_scratch &&
       a.wq_scratch_bytes >= static_cast<size_t>(a.N) * a.K * sizeof(half)) {
     // quantised weights, many rows: expand to fp16 once, then the tensor-core GEMM
@@ -322,7 +322,8 @@ bool linear_batch_fused_fits(int M, int K) { return M >= 1 && M <= 4 && gemv_tma
 int linear_group(cudaStream_t stream, const LinearArgs* args, int n) {
   RK_REQUIRE(args && n >= 1 && n <= 8, kBadArg, "linear_group: 1..8 products");
   bool together = true;
-  for (int i = 0; i < n; ++i) together = together && args[i].M > 4 && args[i].M == args[0].M && gemm_tc_supported(args[i]);
+  for (int i = 0; i < n; ++i)
+    together = together && (args[i].M > 4 || (args[i].prefer_tc && args[i].M >= 2)) && args[i].M == args[0].M && gemm_tc_supported(args[i]);
   if (together) return gemm_group(stream, args, n);
   for (int i = 0; i < n; ++i) {
     LinearArgs b = args[i];

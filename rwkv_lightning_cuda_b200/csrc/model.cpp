@@ -386,7 +386,7 @@ Workspace* Model::workspace(int B, int T) {
     const size_t n = std::max(rows * C, static_cast<size_t>(B) * cfg_.vocab * 2);
     if (ws->part32.alloc(n * sizeof(float)) != kOk) return nullptr;
   }
-  if (rows > 4) {
+  if (rows >= 2) {
     const size_t want = std::min<size_t>(static_cast<size_t>(512) << 20, rows * C * sizeof(float) * 24);
     if (ws->gemm_scratch.alloc(want) != kOk) return nullptr;
     if (cfg_.weight_format != RWKV7_B200_FMT_F16) {
@@ -408,6 +408,7 @@ int Model::lin(cudaStream_t s, int M, const Matrix& W, const half* x, void* y, i
   a.M = M; a.K = W.K; a.N = W.N; a.x = x; a.w = W.w.p; a.fmt = W.fmt;
   a.scale = W.scale.as<half>(); a.zero = W.zero.as<half>(); a.epi = epi; a.y = y;
   a.w_dynamic = false;  // resident weights
+  a.prefer_tc = true;   // 2..4 rows of a large matrix: tensor cores (the GEMV's time grows with the row count)
   if (cur_) {
     a.scratch = cur_->gemm_scratch.as<float>(); a.scratch_bytes = cur_->gemm_scratch.bytes;
     a.wq_scratch = cur_->wq_scratch.as<half>(); a.wq_scratch_bytes = cur_->wq_scratch.bytes;
@@ -536,7 +537,9 @@ int Model::enqueue(Workspace& ws, int B, int T, half* shift, void* wkv, int* ela
     probe.R[0] = cfg_.rank_w; probe.R[1] = cfg_.rank_a; probe.R[2] = cfg_.rank_g; probe.R[3] = cfg_.rank_v;
     const bool rows_ok = cfg_.weight_format == RWKV7_B200_FMT_F16 ? C % 8 == 0 : (C % 128 == 0 && cfg_.ffn % 128 == 0);
     // the fused path stages a step's activations in shared memory: B rows of ffn inputs must fit
-    if (G == 1 && T == 1 && rows <= 4 && tmix_decode_supported(probe) && C <= 4096 && rows_ok &&
+    // fp16 weights with 2..4 rows go through the general path below: tensor cores for the large matrices
+    const bool gemv_rows = rows == 1 || cfg_.weight_format != RWKV7_B200_FMT_F16;
+    if (G == 1 && T == 1 && rows <= 4 && gemv_rows && tmix_decode_supported(probe) && C <= 4096 && rows_ok &&
         linear_batch_fused_fits(rows, cfg_.ffn) && linear_batch_fused_fits(rows, C))
       return enqueue_decode(ws, B, shift, wkv, elapsed, logits, st);
   }
@@ -574,7 +577,17 @@ int Model::enqueue(Workspace& ws, int B, int T, half* shift, void* wkv, int* ela
       LinearArgs seg[7] = {mat(W.Wr, xr, ws.r), mat(W.Wk, xk, ws.k), mat(W.Wv, xv, v_lin),
                            low(W.w1t, cfg_.rank_w, xw, ws.l1[0]), low(W.a1t, cfg_.rank_a, xa, ws.l1[1]),
                            low(W.g1t, cfg_.rank_g, xg, ws.l1[2]), low(W.v1t, cfg_.rank_v, xv, ws.l1[3])};
-      RK_TRY(linear_batch(st, seg, li == 0 ? 6 : 7));
+      if (rows >= 2 && cfg_.weight_format == RWKV7_B200_FMT_F16) {
+        // 2..4 rows: the three C x C projections as one tensor-core launch, the small LoRA down-projections as one GEMV
+        for (int i = 0; i < 3; ++i) {
+          seg[i].prefer_tc = true; seg[i].w_dynamic = false;
+          seg[i].scratch = ws.gemm_scratch.as<float>(); seg[i].scratch_bytes = ws.gemm_scratch.bytes;
+        }
+        RK_TRY(linear_group(st, seg, 3));
+        RK_TRY(linear_batch(st, seg + 3, li == 0 ? 3 : 4));
+      } else {
+        RK_TRY(linear_batch(st, seg, li == 0 ? 6 : 7));
+      }
       for (int i = 0; i < 4; ++i) ta.l1[i] = ws.l1[i];
       ta.up[0] = W.w2t.as<half>(); ta.up[1] = W.a2t.as<half>(); ta.up[2] = W.g2t.as<half>(); ta.up[3] = W.v2t.as<half>();
       ta.r = ws.r; ta.k = ws.k; ta.v = v_lin; ta.v_first = ws.vfirst;
