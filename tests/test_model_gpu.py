@@ -147,3 +147,15 @@ def test_decode_shapes_at_the_edges_of_the_fused_path(dims, B):
     print(f"[parity] edge shapes {dims} B={B}: worst logit err {worst:.3e}")
     assert worst < 2e-2
     assert ids_ok
+
+
+def test_full_size_0p1B_prefill_and_greedy_decode_match_the_oracle():
+    """The smallest benchmark configuration at its real size (12 layers, d=768, FFN 3072, vocabulary 65536, LoRA ranks
+    64/64/32/128): a 32-token prefill chunk on the tensor cores, then greedy decode steps on the GEMV path."""
+    dims = dict(layers=12, channels=768, ffn=3072, vocab=65536, rank_w=64, rank_a=64, rank_v=32, rank_g=128)
+    d, om, gm = build_pair(orc.FMT_F16, False, dims=dims)
+    worst, ids_ok, (shift, wkv, elapsed), st = run_both(d, om, gm, False, 1, (32,), 4)
+    print(f"[parity] 0.1B full size: worst logit err {worst:.3e}")
+    assert worst < 2e-2
+    assert ids_ok
+    assert (st.elapsed.cpu().numpy() == elapsed).all()
