@@ -286,6 +286,36 @@ int Model::finalize() {
   return kOk;
 }
 
+int Model::ensure_expanded() {
+  if (expanded_state_ != 0 || cfg_.weight_format == RWKV7_B200_FMT_F16) return kOk;
+  expanded_state_ = -1;
+  const char* env = getenv("RWKV7_B200_EXPANDED_WEIGHTS");
+  if (env && atoi(env) == 0) return kOk;
+  std::vector<Matrix*> all;
+  for (LayerWeights& L : layers_)
+    for (Matrix* m : {&L.Wr, &L.Wk, &L.Wv, &L.Wo, &L.Wkey, &L.Wval}) all.push_back(m);
+  all.push_back(&head_);
+  size_t need = 0;
+  for (const Matrix* m : all) need += static_cast<size_t>(m->N) * m->K * sizeof(half);
+  size_t free_b = 0, total_b = 0;
+  RK_CUDA(cudaMemGetInfo(&free_b, &total_b));
+  if (need + total_b / 5 > free_b) return kOk;  // keep a fifth of the device free: fall back to expanding per call
+  for (Matrix* m : all) {
+    if (m->w16.alloc(static_cast<size_t>(m->N) * m->K * sizeof(half)) != kOk) {
+      for (Matrix* u : all) u->w16.release();
+      cudaGetLastError();
+      return kOk;
+    }
+    int s;
+    if (m->fmt == RWKV7_B200_FMT_W8A16) s = quant_unpack_w8_raw(nullptr, m->N, m->K, m->w.as<int8_t>(), m->w16.as<half>());
+    else s = quant_unpack_w4(nullptr, m->N, m->K, m->w.as<uint8_t>(), m->scale.as<half>(), m->zero.as<half>(), m->w16.as<half>());
+    if (s != kOk) return s;
+  }
+  RK_CUDA(cudaDeviceSynchronize());
+  expanded_state_ = 1;
+  return kOk;
+}
+
 int Model::tp_init(const void* unique_id) {
   RK_REQUIRE(tp_size_ > 1, kBadArg, "tp_init: the model was created with tp_size <= 1");
   int s = use_device();
@@ -389,7 +419,7 @@ Workspace* Model::workspace(int B, int T) {
   if (rows >= 2) {
     const size_t want = std::min<size_t>(static_cast<size_t>(512) << 20, rows * C * sizeof(float) * 24);
     if (ws->gemm_scratch.alloc(want) != kOk) return nullptr;
-    if (cfg_.weight_format != RWKV7_B200_FMT_F16) {
+    if (cfg_.weight_format != RWKV7_B200_FMT_F16 && expanded_state_ != 1) {
       const size_t big = std::max(static_cast<size_t>(cfg_.vocab) * C, F * C) * sizeof(half);
       if (ws->wq_scratch.alloc(big) != kOk) return nullptr;
     }
@@ -407,6 +437,10 @@ int Model::lin(cudaStream_t s, int M, const Matrix& W, const half* x, void* y, i
   LinearArgs a;
   a.M = M; a.K = W.K; a.N = W.N; a.x = x; a.w = W.w.p; a.fmt = W.fmt;
   a.scale = W.scale.as<half>(); a.zero = W.zero.as<half>(); a.epi = epi; a.y = y;
+  if (W.w16.p && M > 4) {  // expanded copy: straight to the tensor cores
+    a.w = W.w16.p; a.fmt = RWKV7_B200_FMT_F16; a.scale = nullptr; a.zero = nullptr;
+    a.out_scale = W.fmt == RWKV7_B200_FMT_W8A16 ? W.scale.as<half>() : nullptr;
+  }
   a.w_dynamic = false;  // resident weights
   a.prefer_tc = true;   // 2..4 rows of a large matrix: tensor cores (the GEMV's time grows with the row count)
   if (cur_) {
@@ -606,6 +640,10 @@ int Model::enqueue(Workspace& ws, int B, int T, half* shift, void* wkv, int* ela
         auto dense = [&](const Matrix& Wm, const half* x, void* y) {
           LinearArgs a;
           a.M = rows; a.K = Wm.K; a.N = Wm.N; a.x = x; a.w = Wm.w.p; a.fmt = Wm.fmt; a.y = y; a.w_dynamic = false;
+          if (Wm.w16.p) {
+            a.w = Wm.w16.p; a.fmt = RWKV7_B200_FMT_F16;
+            a.out_scale = Wm.fmt == RWKV7_B200_FMT_W8A16 ? Wm.scale.as<half>() : nullptr;
+          }
           a.scratch = ws.gemm_scratch.as<float>(); a.scratch_bytes = ws.gemm_scratch.bytes;
           return a;
         };
@@ -617,9 +655,9 @@ int Model::enqueue(Workspace& ws, int B, int T, half* shift, void* wkv, int* ela
         };
         LinearArgs grp[7];
         int ng = 0;
-        if (cfg_.weight_format == RWKV7_B200_FMT_F16) {
+        if (cfg_.weight_format == RWKV7_B200_FMT_F16 || W.Wr.w16.p) {
           grp[ng++] = dense(W.Wr, xr, ws.r); grp[ng++] = dense(W.Wk, xk, ws.k); grp[ng++] = dense(W.Wv, xv, v_lin);
-        } else {  // quantised matrices are expanded one at a time through a shared scratch buffer
+        } else {  // quantised matrices without an expanded copy: expanded one at a time through a shared scratch buffer
           RK_TRY(lin(st, rows, W.Wr, xr, ws.r, kEpiNone));
           RK_TRY(lin(st, rows, W.Wk, xk, ws.k, kEpiNone));
           RK_TRY(lin(st, rows, W.Wv, xv, v_lin, kEpiNone));
@@ -735,6 +773,10 @@ int Model::forward(const int64_t* tokens_host, int B, int T, void* shift, void* 
   if (s != kOk) return s;
 
   std::lock_guard<std::mutex> lock(mu_);
+  if (rows > 4 && cfg_.weight_format != RWKV7_B200_FMT_F16 && expanded_state_ == 0) {
+    s = ensure_expanded();  // before any stream capture: it allocates
+    if (s != kOk) return s;
+  }
   Workspace* ws = workspace(B, T);
   RK_REQUIRE(ws, kCuda, "forward: workspace allocation failed for B=%d T=%d", B, T);
   const int slot = ws->slot;

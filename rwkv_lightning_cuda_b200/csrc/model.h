@@ -37,6 +37,10 @@ struct DevBuf {
 struct Matrix {
   int N = 0, K = 0, fmt = RWKV7_B200_FMT_F16;
   DevBuf w, scale, zero;
+  // Quantised formats only, optional: the matrix expanded to fp16 once (W8A16: the integer codes, the channel scale is
+  // applied to the accumulator; W4A16: the dequantised values) for calls with more than four rows, which run on the
+  // tensor cores.  Built at the first such call while memory allows; the packed copy keeps serving the GEMV path.
+  DevBuf w16;
 };
 
 struct LayerWeights {
@@ -83,7 +87,8 @@ class Model {
                        void* dst_shift, void* dst_wkv, int* dst_elapsed, int dst_B, int dst_off, int count,
                        cudaStream_t stream) const;
   int query_capacity(int chunk, rwkv7_b200_capacity* out) const;
-  int tp_init(const void* unique_id);  // joins the tensor-parallel group (collective over all ranks)
+  int tp_init(const void* unique_id);
+  int ensure_expanded();  // see Matrix::w16  // joins the tensor-parallel group (collective over all ranks)
 
   const rwkv7_b200_config& cfg() const { return cfg_; }
   long long launches() const { return launches_; }
@@ -119,6 +124,7 @@ class Model {
   rwkv7_b200_config cfg_;
   int H_ = 0;
   int tp_size_ = 1, tp_rank_ = 0;
+  int expanded_state_ = 0;  // 0 not tried, 1 built, -1 unavailable (switched off or not enough memory)
   TpComm tp_;
   bool finalized_ = false;
   std::vector<LayerWeights> layers_;
