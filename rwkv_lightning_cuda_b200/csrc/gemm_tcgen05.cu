@@ -48,20 +48,6 @@ constexpr int kMaxStages = 8;
 
 __device__ int g_gemm_timeout = 0;
 
-// Optional timestamps of CTA 0 (a development build defines RK_GEMM_TRACE; the library does not).
-#ifdef RK_GEMM_TRACE
-__device__ unsigned long long g_gemm_trace[16];
-__device__ __forceinline__ void trace_point(int i) {
-  if (blockIdx.x == 0) {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)::"memory");
-    g_gemm_trace[i] = t;
-  }
-}
-#define RK_TRACE(i) trace_point(i)
-#else
-#define RK_TRACE(i)
-#endif
 
 struct Prob {
   int M, N, K, epi;
@@ -276,7 +262,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_group_kernel(const __grid_co
   __shared__ uint32_t tmem_slot;
   __shared__ volatile int failed;
 
-  if (threadIdx.x == 0) RK_TRACE(0);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   constexpr uint32_t kWBytes = kBM * 128;
   // CTA pair: cluster rank 0 leads; every CTA stages its own 128 weight rows and half of the activation rows
@@ -319,7 +304,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_group_kernel(const __grid_co
   if (kPair) cluster_sync_all();  // the peer's barriers are initialised before anything signals them
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = tmem_slot;
-  if (threadIdx.x == 0) RK_TRACE(1);
 
   if (warp == 0) {
     // ---- TMA producer: one ring of stages, each a weight tile followed by an activation tile.  Weights that were
@@ -353,7 +337,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_group_kernel(const __grid_co
       }
       pdl_wait();
       pdl_trigger();
-      RK_TRACE(2);
       bool ok = true;
       int it = 0;
       for (int ui = first_unit; ui < g.total_units && ok && !failed; ui += unit_stride) {
@@ -390,7 +373,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_group_kernel(const __grid_co
           const int s = it % g.stages;
           ok = mbar_wait(smem_u32(&full_bar[s]), (it / g.stages) & 1);
           if (!ok) break;
-          if (it == 0) RK_TRACE(3);
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const uint64_t da = smem_desc(ring + s * stage_bytes), db = smem_desc(ring + s * stage_bytes + kWBytes);
 #pragma unroll
@@ -408,7 +390,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_group_kernel(const __grid_co
           if (kPair) mma_commit_pair(smem_u32(&acc_full[acc]));
           else mma_commit(smem_u32(&acc_full[acc]));
         }
-        if (n_unit == 0) RK_TRACE(4);
       }
       if (!ok) failed = 1;
     }
@@ -432,7 +413,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_group_kernel(const __grid_co
         break;
       }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      if (t == 0 && n_unit == 0) RK_TRACE(5);
       const uint32_t tmem_acc = tmem_base + static_cast<uint32_t>(acc * g.Nt) + (static_cast<uint32_t>(q * 32) << 16);
       const int m_valid = min(g.Nt, p.M - u.m0);
       const int n = u.n0 + c4;
@@ -452,9 +432,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_group_kernel(const __grid_co
 #pragma unroll
           for (int j = 0; j < 16; ++j) epi_tile[(half_rows * 16 + j) * kEpiLd + q * 32 + lane] = __uint_as_float(r0[j]);
         }
-        if (t == 0 && n_unit == 0 && c0 == 0) RK_TRACE(8);
         asm volatile("bar.sync 1, 256;" ::: "memory");
-        if (t == 0 && n_unit == 0 && c0 == 0) RK_TRACE(9);
         // phase B: thread t owns 4 consecutive channels of rows t/32, t/32 + 8, ... of this slab
         const int rows_here = min(kEpiRows, m_valid - c0);
         if (n < p.N) {
@@ -480,9 +458,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_group_kernel(const __grid_co
             }
           }
         }
-        if (t == 0 && n_unit == 0 && c0 == 0) RK_TRACE(10);
         asm volatile("bar.sync 1, 256;" ::: "memory");
-        if (t == 0 && n_unit == 0 && c0 == 0) RK_TRACE(11);
       }
       // every warp's TMEM reads are complete (wait::ld + the barrier above): hand the accumulator back
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -491,12 +467,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_group_kernel(const __grid_co
         if (kPair) mbar_arrive_cluster(map_to_rank(smem_u32(&acc_empty[acc]), 0));
         else mbar_arrive(smem_u32(&acc_empty[acc]));
       }
-      if (t == 0 && n_unit == 0) RK_TRACE(6);
     }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
-  if (threadIdx.x == 0) RK_TRACE(7);
   if (threadIdx.x == 0 && failed) atomicExch(&g_gemm_timeout, 1);
   __syncwarp();
   if (kPair) cluster_sync_all();  // neither CTA leaves while its partner may still signal its barriers or read its tiles
