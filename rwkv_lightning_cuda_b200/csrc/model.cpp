@@ -787,7 +787,8 @@ int Model::forward(const int64_t* tokens_host, int B, int T, void* shift, void* 
   RK_CUDA(cudaEventRecord(ws->tokens_copied[slot], stream));
 
   // tensor-parallel steps are enqueued directly: their collectives are not recorded into graphs here
-  if (T != 1 || stream == nullptr || tp_size_ > 1) {
+  static const bool no_graph = [] { const char* e = getenv("RWKV7_B200_NO_GRAPH"); return e && atoi(e) != 0; }();  // tuning aid
+  if (T != 1 || stream == nullptr || tp_size_ > 1 || no_graph) {
     const long long before = launch_counter();
     s = enqueue(*ws, B, T, static_cast<half*>(shift), wkv, elapsed, logits, stream);
     launches_ += launch_counter() - before;
