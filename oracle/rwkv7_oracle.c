@@ -20,7 +20,12 @@
  *   orc_wkv_fp16 .............. cuda/rwkv7_wkv_fp16_v2.cu:41-52,110-208
  *   orc_forward ............... src/rwkv7_fast_v4.cu:1046-1345
  * The W8A16 / W4A16 functions have no counterpart in the reference (it has no
- * quantisation); they are the written definition of those formats for this project.
+ * quantisation); they are the written definition of those formats for this project
+ * (parity unpinned for them).
+ *
+ * Pinned: every function above is checked on the CPU against outputs recorded from the
+ * reference's own kernels and from its whole ModelBackend (tests/golden/*.npz, made by
+ * tests/golden/make_golden.py; checked by tests/test_golden_cpu.py).
  *
  * Where the reference sums in an unspecified parallel order in fp32 (dot products,
  * LayerNorm statistics) the oracle sums in double: the result is the correctly rounded

@@ -159,3 +159,31 @@ def test_full_size_0p1B_prefill_and_greedy_decode_match_the_oracle():
     assert worst < 2e-2
     assert ids_ok
     assert (st.elapsed.cpu().numpy() == elapsed).all()
+
+
+@pytest.mark.parametrize("wkv32", [False, True])
+def test_library_matches_the_reference_backend_golden(wkv32):
+    """The library against what the reference's own ModelBackend produced on a B200 for the same checkpoint and tokens
+    (tests/golden/ref_model_tiny.npz): prefill chunks of 5 and 3 tokens, four greedy decode steps, final state."""
+    from rwkv_lightning_cuda_b200 import backend as bk
+    from tests.test_golden_cpu import GOLDEN_DIMS, golden_model_calls
+    tag = "s32" if wkv32 else "s16"
+    m, calls = golden_model_calls(tag)
+    d, om, gm = build_pair(orc.FMT_F16, wkv32, dims=GOLDEN_DIMS)
+    B = int(m["B"])
+    st = gm.create_state(B); lg = bk.DeviceLogits()
+    worst = 0.0
+    for toks, want in calls:
+        if toks.shape[1] == 1:
+            gm.forward_decode(toks[:, 0].tolist(), st, lg)
+        else:
+            gm.forward_prefill(toks.tolist(), st, lg)
+        got = lg.values.cpu().numpy()
+        worst = max(worst, float(np.abs(got - want).max() / (np.abs(want).max() if wkv32 else 1.0)))
+        assert (got.argmax(-1) == want.argmax(-1)).all()
+    print(f"[parity] library vs reference backend ({tag}): worst logit err {worst:.3e}")
+    assert worst < (1e-4 * 50 if wkv32 else 2e-2)
+    assert (st.elapsed.cpu().numpy() == m[tag + "_elapsed"]).all()
+    assert np.abs(st.shift.cpu().numpy().astype(np.float32) - m[tag + "_shift"].astype(np.float32)).max() < 2e-2
+    ref_wkv = m[tag + "_wkv"].astype(np.float32)
+    assert np.abs(st.wkv_state.cpu().numpy().astype(np.float32) - ref_wkv).max() <= 2e-2 * max(1.0, float(np.abs(ref_wkv).max()))

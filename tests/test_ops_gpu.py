@@ -272,3 +272,38 @@ def test_linear_fp16_cta_pair_kernel():
     env = dict(os.environ, RWKV7_B200_GEMM_PAIR="1", PYTHONPATH=root)
     res = subprocess.run([sys.executable, "-c", code], cwd=root, env=env, capture_output=True, text=True, timeout=600)
     assert res.returncode == 0 and "pair ok" in res.stdout, res.stdout[-2000:] + res.stderr[-4000:]
+
+
+def test_ops_match_the_reference_kernels_golden(ops):
+    """The library's kernels against outputs of the reference's own kernels recorded on a B200 (tests/golden/ref_ops.npz)."""
+    import os
+    from tests.helpers import GOLDEN
+    g = np.load(os.path.join(GOLDEN, "ref_ops.npz"))
+    B, T, H = int(g["wkv_B"]), int(g["wkv_T"]), int(g["wkv_H"])
+    ins = [dev(g["wkv_" + n]) for n in "rwkvab"]
+    for tag, w0 in (("wkv16", None), ("wkv16w0", g["wkv_w0"])):
+        st = dev(g["wkv_s0"].copy())
+        y = ops.wkv_fp16_seq(B, T, H, st, *ins, dev(g["wkv_elapsed"]), w0=None if w0 is None else dev(w0))
+        assert (host(y).view(np.uint16) == g[tag + "_y"].reshape(host(y).shape).view(np.uint16)).all(), tag      # same instruction sequence
+        assert (host(st).view(np.uint16) == g[tag + "_state"].view(np.uint16)).all(), tag
+    st = dev(g["wkv32_s0"].copy())
+    y = ops.wkv_fp32io16(B, T, H, st, *ins)
+    assert np.abs(host(st) - g["wkv32_state"]).max() / np.abs(g["wkv32_state"]).max() < 1e-4
+    assert_close16(host(y).reshape(g["wkv32_y"].shape), g["wkv32_y"], max_ulp=2, min_exact=0.9, what="wkv_fp32 vs reference")
+    rows = g["gate_k"].shape[0]; Hg = g["gate_k"].shape[1] // 64
+    got = ops.tmix_kk_a_gate(rows, 1, Hg, dev(g["gate_k"]), dev(g["gate_k_k"]), dev(g["gate_a0"]), dev(g["gate_a12"]), dev(g["gate_k_a"]))
+    for i, n in enumerate(("new_k", "neg_kk", "kka")):
+        assert_close16(host(got[i]), g["gate_out"][i], what="kk_a_gate vs reference " + n)
+    got = ops.tmix_lnx_rkvres_xg(rows, 1, Hg, dev(g["lnx_y"]), dev(g["lnx_r"]), dev(g["gate_k"]), dev(g["lnx_v"]), dev(g["lnx_r_k"]),
+                                 dev(g["lnx_w"]), dev(g["lnx_b"]), dev(g["lnx_g"]))
+    assert_close16(host(got), g["lnx_out"], what="lnx_rkvres_xg vs reference")
+    assert_close16(host(ops.tmix_vres_gate(rows, 1, dev(g["lnx_v"]), dev(g["vres_vf"]), dev(g["vres_v0"]), dev(g["vres_v12"]))),
+                   g["vres_out"], what="vres_gate vs reference")
+    x, res, w, b = g["ln_x"], g["ln_res"], g["ln_w"], g["ln_b"]
+    sh = dev(g["mix_shift0"].copy())
+    xo, outs = ops.add_layer_norm_tmix_mix6_f16(x.shape[0], 1, dev(x), dev(res), sh, dev(w), dev(b), [dev(m) for m in g["mix_coef"]])
+    assert (host(xo).view(np.uint16) == g["lnmix6_xo"].view(np.uint16)).all()
+    for i in range(6):
+        assert_close16(host(outs[i]), g["lnmix6_out"][i], max_ulp=3, min_exact=0.9, what=f"add_ln_tmix_mix6[{i}] vs reference")
+    assert_close16(host(sh), g["lnmix6_shift"], what="shift vs reference")
+    assert_close16(host(ops.linear_f16_orig(dev(g["lin_x"]), dev(g["lin_W"]))), g["lin_y"], max_ulp=1, what="linear vs reference GEMV")
