@@ -24,8 +24,9 @@
  * (parity unpinned for them).
  *
  * Pinned: every function above is checked on the CPU against outputs recorded from the
- * reference's own kernels and from its whole ModelBackend (tests/golden/*.npz, made by
- * tests/golden/make_golden.py; checked by tests/test_golden_cpu.py).
+ * reference's own kernels and from its whole ModelBackend (ref_ops.npz and
+ * ref_model_tiny.npz under tests/golden, made by make_golden.py there; checked by
+ * tests/test_golden_cpu.py).
  *
  * Where the reference sums in an unspecified parallel order in fp32 (dot products,
  * LayerNorm statistics) the oracle sums in double: the result is the correctly rounded
