@@ -46,9 +46,11 @@ __global__ void __launch_bounds__(kW * 32) gemv_tma_kernel(const GemvBatch p, in
   const GemvSeg& sg = p.seg[s];
   const int row0 = (blockIdx.x - sg.cta_begin) * sg.rows_per_cta;
   const int rows_end = min(sg.N, row0 + sg.rows_per_cta);
-  const int rpw = sg.rows_per_cta / kW;  // rows_per_cta is a multiple of the warp count
-  const int r_begin = row0 + warp * rpw;
-  const int r_end = min(rows_end, r_begin + rpw);
+  // the CTA's rows are shared out over its warps as evenly as they go (the first `rem` warps take one more)
+  const int rows_here = max(rows_end - row0, 0);
+  const int base = rows_here / kW, rem = rows_here - base * kW;
+  const int r_begin = row0 + warp * base + min(warp, rem);
+  const int r_end = r_begin + base + (warp < rem ? 1 : 0);
   const int parts = sg.parts, piece = sg.piece_bytes;
   const int total = r_end > r_begin ? (r_end - r_begin) * parts : 0;
   const int K = sg.K;
@@ -264,15 +266,44 @@ bool gemv_tma_plan(GemvBatch& b, int M, size_t* smem_bytes, int* grid, int* n_sl
     g.piece_bytes = row_bytes / parts;
   }
   const size_t smem = x_bytes + static_cast<size_t>(kWarps) * slots * cap;
-  // CTAs are shared out by weight bytes; every warp of a problem gets the same number of rows
+  // CTAs are shared out by weight bytes: every problem starts with its rounded-down share (at least one CTA), the
+  // rest go one at a time to whichever problem has the most bytes per CTA, so that all SMs finish together.  (Rows
+  // per CTA need not be a multiple of the warp count: 4096 rows on 148 SMs are 28 rows each, not 32 on 128 SMs.)
   const int budget = 148 * per_sm;
+  int n_cta[kMaxSeg];
+  int used = 0;
+  for (int i = 0; i < b.n_seg; ++i) {
+    const GemvSeg& g = b.seg[i];
+    const double share = static_cast<double>(g.N) * g.parts * g.piece_bytes / total_bytes;
+    n_cta[i] = std::max(1, std::min(g.N, static_cast<int>(share * budget)));
+    used += n_cta[i];
+  }
+  while (used < budget) {
+    int best = -1;
+    double worst = 0;
+    for (int i = 0; i < b.n_seg; ++i) {
+      const GemvSeg& g = b.seg[i];
+      if (n_cta[i] >= g.N) continue;
+      const double per = static_cast<double>((g.N + n_cta[i] - 1) / n_cta[i]) * g.parts * g.piece_bytes;
+      if (per > worst) { worst = per; best = i; }
+    }
+    if (best < 0) break;
+    ++n_cta[best];
+    ++used;
+  }
+  // Small launches (a few MB: narrow models) are latency-bound, not bandwidth-bound: there fewer, fatter CTAs measured
+  // faster, so every warp of a problem gets the same whole number of rows as if all CTAs were used.
+  const bool small = total_bytes < 8.0 * 1024 * 1024;
   int cta = 0;
   for (int i = 0; i < b.n_seg; ++i) {
     GemvSeg& g = b.seg[i];
-    const double share = static_cast<double>(g.N) * g.parts * g.piece_bytes / total_bytes;
-    const int n = std::max(1, static_cast<int>(share * budget + 0.5));
-    const int rpw = std::max(1, (g.N + n * kWarps - 1) / (n * kWarps));
-    g.rows_per_cta = rpw * kWarps;
+    if (small) {
+      const double share = static_cast<double>(g.N) * g.parts * g.piece_bytes / total_bytes;
+      const int n = std::max(1, static_cast<int>(share * budget + 0.5));
+      g.rows_per_cta = std::max(1, (g.N + n * kWarps - 1) / (n * kWarps)) * kWarps;
+    } else {
+      g.rows_per_cta = (g.N + n_cta[i] - 1) / n_cta[i];
+    }
     g.cta_begin = cta;
     cta += (g.N + g.rows_per_cta - 1) / g.rows_per_cta;
   }
