@@ -211,7 +211,7 @@ def run_ours(args, rank, world, local_rank):
     achieved = abytes / (ms * 1e-3) / 1e9
     # DRAM traffic of the dominant kernel (gemv_tma_kernel) per algorithmic byte, from the ncu capture summarised in
     # profiles/gemv_tma_16384x4096_ncu_full.md: 134.28 MB read + 3.58 MB written for 134.26 MB; scaled to the step
-    traffic = abytes * (137.86 / 134.26) if (fmt == 0 and B <= 4) else None
+    traffic = abytes * (137.86 / 134.26) if (fmt == 0 and B == 1) else None
     line = {
         "metric": "decode_tokens_per_s", "value": whole_job_rate(world, B, ms), "unit": "tok/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
