@@ -48,6 +48,10 @@ int row_op(cudaStream_t stream, const RowOpArgs& args);
 
 int tmix_kk_a_gate(cudaStream_t stream, int rows, int C, const half* k, const half* k_k, const half* a0,
                    const half* a12, const half* k_a, half* new_k, half* neg_kk, half* kka);
+// tmix_kk_a_gate and tmix_vres_gate in one launch (the same warp handles a head's 64 channels for both)
+int tmix_kk_a_vres_gate(cudaStream_t stream, int rows, int C, const half* k, const half* k_k, const half* a0, const half* a12,
+                        const half* k_a, half* new_k, half* neg_kk, half* kka, const half* v, const half* v_first,
+                        const half* v0, const half* v12, half* v_out);
 int tmix_lnx_rkvres_xg(cudaStream_t stream, int rows, int C, const half* y, const half* r, const half* k,
                        const half* v, const half* r_k, const half* w, const half* b, const half* g, half* out);
 int tmix_vres_gate(cudaStream_t stream, int rows, int C, const half* v, const half* v_first, const half* v0,

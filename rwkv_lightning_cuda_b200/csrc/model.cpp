@@ -634,6 +634,7 @@ int Model::enqueue(Workspace& ws, int B, int T, half* shift, void* wkv, int* ela
     } else {
       const bool big = rows > 4;  // the reference rounds tanh/sigmoid and the v LoRA output to half for larger row counts
       const half* v_use = ws.vfirst;
+      bool gates_fused = false;
       if (big) {
         // many rows: two tensor-core launches -- r/k/v with the four LoRA down-projections (tanh / sigmoid as
         // their epilogues), then the four LoRA up-projections
@@ -673,8 +674,8 @@ int Model::enqueue(Workspace& ws, int B, int T, half* shift, void* wkv, int* ela
         grp[ng++] = low(W.g2t, cfg_.rank_g, Cl, ws.l1[2], ws.g, kEpiNone);
         if (li > 0) grp[ng++] = low(W.v2t, cfg_.rank_v, Cl, ws.l1[3], ws.y, kEpiNone);
         RK_TRY(linear_group(st, grp, ng));
-        if (li > 0) {
-          RK_TRY(tmix_vres_gate(st, rows, Cl, ws.v, ws.vfirst, W.v0.as<half>(), ws.y, ws.vout));
+        if (li > 0) {  // the value-residual gate runs in the kk / a gate launch below
+          gates_fused = true;
           v_use = ws.vout;
         }
       } else {
@@ -695,7 +696,12 @@ int Model::enqueue(Workspace& ws, int B, int T, half* shift, void* wkv, int* ela
           v_use = ws.vout;
         }
       }
-      RK_TRY(tmix_kk_a_gate(st, rows, Cl, ws.k, W.k_k.as<half>(), W.a0.as<half>(), ws.a12, W.k_a.as<half>(), ws.k2, ws.nkk, ws.kka));
+      if (gates_fused) {
+        RK_TRY(tmix_kk_a_vres_gate(st, rows, Cl, ws.k, W.k_k.as<half>(), W.a0.as<half>(), ws.a12, W.k_a.as<half>(), ws.k2, ws.nkk, ws.kka,
+                                   ws.v, ws.vfirst, W.v0.as<half>(), ws.y, ws.vout));
+      } else {
+        RK_TRY(tmix_kk_a_gate(st, rows, Cl, ws.k, W.k_k.as<half>(), W.a0.as<half>(), ws.a12, W.k_a.as<half>(), ws.k2, ws.nkk, ws.kka));
+      }
       if (cfg_.wkv32) {
         RK_TRY(wkv7_fp32(st, B, T, Cl, Hl, static_cast<float*>(wkv) + wkv_off, ws.r, ws.w12, W.w0.as<half>(), ws.k2, v_use,
                          ws.nkk, ws.kka, ws.y));

@@ -14,6 +14,7 @@
 // rounded to half once, the interpolation reads the rounded LayerNorm output.
 #include "common.cuh"
 #include <algorithm>
+#include <cstdlib>
 
 #include "kernels.h"
 
@@ -118,7 +119,7 @@ __device__ __forceinline__ void ln_row(const RowOpDev& p, float2 (&v)[kPairs], f
 // outputs of pairs i in [s*kPairs/n_slices, (s+1)*kPairs/n_slices) so that a single decode row is
 // spread over several SMs.
 template <int kPairs>
-__global__ void __launch_bounds__(kRowThreads) row_op_kernel(const RowOpDev p) {
+__device__ __forceinline__ void row_op_body(const RowOpDev& p) {
   __shared__ float scratch[kRowThreads / 32];
   int b, t;
   if (p.last_only) {
@@ -198,6 +199,18 @@ __global__ void __launch_bounds__(kRowThreads) row_op_kernel(const RowOpDev p) {
     for (int i = 0; i < kPairs; ++i)
       if (owned(i)) shift2[threadIdx.x + kRowThreads * i] = __floats2half2_rn(cur[i].x, cur[i].y);
   }
+}
+
+template <int kPairs>
+__global__ void __launch_bounds__(kRowThreads) row_op_kernel(const RowOpDev p) {
+  row_op_body<kPairs>(p);
+}
+
+// The same kernel compiled for at most 128 registers, so that two CTAs share an SM: for launches with more rows than
+// SMs (batched decode), where one CTA per SM means a second wave.
+template <int kPairs>
+__global__ void __launch_bounds__(kRowThreads, 2) row_op_two_per_sm_kernel(const RowOpDev p) {
+  row_op_body<kPairs>(p);
 }
 
 // ---- Chunks (T > 1) with many rows.  512 threads per row, so that a thread holds half as many pairs, and the
@@ -342,13 +355,24 @@ __global__ void __launch_bounds__(kChunkThreads) row_op_chunk_kernel(const RowOp
 __global__ void __launch_bounds__(128) kk_a_gate_kernel(
     int H, long long n_heads_total, const half* __restrict__ k, const half* __restrict__ k_k,
     const half* __restrict__ a0, const half* __restrict__ a12, const half* __restrict__ k_a,
-    half* __restrict__ new_k, half* __restrict__ neg_kk, half* __restrict__ kka) {
+    half* __restrict__ new_k, half* __restrict__ neg_kk, half* __restrict__ kka,
+    // optional second job for the same channels: the value-residual gate (vres_gate_kernel's formula)
+    const half* __restrict__ v, const half* __restrict__ v_first, const half* __restrict__ v0,
+    const half* __restrict__ v12, half* __restrict__ v_out) {
   const long long bth = static_cast<long long>(blockIdx.x) * 4 + (threadIdx.x >> 5);
   if (bth >= n_heads_total) return;
   const int lane = threadIdx.x & 31;
   const int h = static_cast<int>(bth % H);
   const long long idx = bth * kHead + lane * 2;
   const int c = h * kHead + lane * 2;
+  if (v_out) {
+    const float2 vv = __half22float2(*reinterpret_cast<const __half2*>(v + idx));
+    const float2 vf = __half22float2(*reinterpret_cast<const __half2*>(v_first + idx));
+    const float2 b0 = __half22float2(*reinterpret_cast<const __half2*>(v0 + c));
+    const float2 lo = __half22float2(*reinterpret_cast<const __half2*>(v12 + idx));
+    const float g0 = sigmoid_fast(b0.x + lo.x), g1 = sigmoid_fast(b0.y + lo.y);
+    *reinterpret_cast<__half2*>(v_out + idx) = __floats2half2_rn(fmaf(vf.x - vv.x, g0, vv.x), fmaf(vf.y - vv.y, g1, vv.y));
+  }
   const float2 kv = __half22float2(*reinterpret_cast<const __half2*>(k + idx));
   const float2 ks = __half22float2(*reinterpret_cast<const __half2*>(k_k + c));
   const float u0 = kv.x * ks.x, u1 = kv.y * ks.y;
@@ -510,6 +534,12 @@ int row_op(cudaStream_t stream, const RowOpArgs& a) {
   p.n_slices = rows <= 32 ? kp : 1;  // spread few rows over more SMs
   const dim3 grid(p.n_slices, rows), block(kRowThreads);
   cudaError_t e;
+  if (rows > 148 && kp == 8) {
+    e = launch_pdl(row_op_two_per_sm_kernel<8>, grid, block, 0, stream, p);
+    RK_CUDA(e);
+    RK_LAUNCH_CHECK("row_op launch");
+    return kOk;
+  }
   switch (kp) {
     case 1: e = launch_pdl(row_op_kernel<1>, grid, block, 0, stream, p); break;
     case 2: e = launch_pdl(row_op_kernel<2>, grid, block, 0, stream, p); break;
@@ -528,8 +558,23 @@ int tmix_kk_a_gate(cudaStream_t stream, int rows, int C, const half* k, const ha
   RK_REQUIRE(k && k_k && a0 && a12 && k_a && new_k && neg_kk && kka, kBadArg, "kk_a_gate: null pointer");
   const int H = C / kHead;
   const long long total = static_cast<long long>(rows) * H;
-  kk_a_gate_kernel<<<static_cast<unsigned>((total + 3) / 4), 128, 0, stream>>>(H, total, k, k_k, a0, a12, k_a, new_k, neg_kk, kka);
+  kk_a_gate_kernel<<<static_cast<unsigned>((total + 3) / 4), 128, 0, stream>>>(H, total, k, k_k, a0, a12, k_a, new_k, neg_kk, kka,
+                                                                            nullptr, nullptr, nullptr, nullptr, nullptr);
   RK_LAUNCH_CHECK("kk_a_gate launch");
+  return kOk;
+}
+
+int tmix_kk_a_vres_gate(cudaStream_t stream, int rows, int C, const half* k, const half* k_k, const half* a0, const half* a12,
+                        const half* k_a, half* new_k, half* neg_kk, half* kka, const half* v, const half* v_first,
+                        const half* v0, const half* v12, half* v_out) {
+  RK_REQUIRE(rows > 0 && C > 0 && C % kHead == 0, kShape, "kk_a_vres_gate: C must be a multiple of 64");
+  RK_REQUIRE(k && k_k && a0 && a12 && k_a && new_k && neg_kk && kka && v && v_first && v0 && v12 && v_out, kBadArg,
+             "kk_a_vres_gate: null pointer");
+  const int H = C / kHead;
+  const long long total = static_cast<long long>(rows) * H;
+  kk_a_gate_kernel<<<static_cast<unsigned>((total + 3) / 4), 128, 0, stream>>>(H, total, k, k_k, a0, a12, k_a, new_k, neg_kk, kka, v,
+                                                                            v_first, v0, v12, v_out);
+  RK_LAUNCH_CHECK("kk_a_vres_gate launch");
   return kOk;
 }
 
