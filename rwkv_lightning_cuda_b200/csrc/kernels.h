@@ -125,6 +125,9 @@ int linear_group(cudaStream_t stream, const LinearArgs* args, int n);
 struct TmixDecodeArgs {
   int B = 0, C = 0;
   bool layer0 = false, wkv32 = false;
+  // the many-row numerics of the reference (more than four rows): tanh / sigmoid of the LoRA inputs and the v LoRA
+  // output are rounded to half, and the value-residual gate uses the stand-alone gate kernel's formula
+  bool round_act = false;
   int R[4] = {0, 0, 0, 0};                                   // ranks of w, a, g, v
   const half* l1[4] = {nullptr, nullptr, nullptr, nullptr};  // [B,R] LoRA down outputs
   const half* up[4] = {nullptr, nullptr, nullptr, nullptr};  // [C,R] LoRA up matrices

@@ -634,7 +634,7 @@ int Model::enqueue(Workspace& ws, int B, int T, half* shift, void* wkv, int* ela
     } else {
       const bool big = rows > 4;  // the reference rounds tanh/sigmoid and the v LoRA output to half for larger row counts
       const half* v_use = ws.vfirst;
-      bool gates_fused = false;
+      bool gates_fused = false, core_done = false;
       if (big) {
         // many rows: two tensor-core launches -- r/k/v with the four LoRA down-projections (tanh / sigmoid as
         // their epilogues), then the four LoRA up-projections
@@ -663,11 +663,32 @@ int Model::enqueue(Workspace& ws, int B, int T, half* shift, void* wkv, int* ela
           RK_TRY(lin(st, rows, W.Wk, xk, ws.k, kEpiNone));
           RK_TRY(lin(st, rows, W.Wv, xv, v_lin, kEpiNone));
         }
-        grp[ng++] = low(W.w1t, C, cfg_.rank_w, xw, ws.l1[0], kEpiTanhH);
+        // A few sequences, one token each: the fused time-mix kernel (LoRA up + gates + WKV + GroupNorm, one CTA per
+        // sequence and head) replaces five launches; it applies tanh / sigmoid itself, with the many-row rounding.
+        TmixDecodeArgs tf;
+        tf.B = B; tf.C = C; tf.layer0 = li == 0; tf.wkv32 = cfg_.wkv32 != 0; tf.round_act = true;
+        tf.R[0] = cfg_.rank_w; tf.R[1] = cfg_.rank_a; tf.R[2] = cfg_.rank_g; tf.R[3] = cfg_.rank_v;
+        // (every CTA re-reads its head's LoRA-up rows: worth it while those re-reads stay small -- measured faster at
+        // 3.5 and 17 MB per layer, slower at 54 MB)
+        const size_t up_reads = static_cast<size_t>(rows) * C * (cfg_.rank_w + cfg_.rank_a + cfg_.rank_g + cfg_.rank_v) * sizeof(half);
+        const bool few = G == 1 && T == 1 && rows <= 16 && up_reads <= (static_cast<size_t>(20) << 20) && tmix_decode_supported(tf);
+        grp[ng++] = low(W.w1t, C, cfg_.rank_w, xw, ws.l1[0], few ? kEpiNone : kEpiTanhH);
         grp[ng++] = low(W.a1t, C, cfg_.rank_a, xa, ws.l1[1], kEpiNone);
-        grp[ng++] = low(W.g1t, C, cfg_.rank_g, xg, ws.l1[2], kEpiSigmoidH);
+        grp[ng++] = low(W.g1t, C, cfg_.rank_g, xg, ws.l1[2], few ? kEpiNone : kEpiSigmoidH);
         if (li > 0) grp[ng++] = low(W.v1t, C, cfg_.rank_v, xv, ws.l1[3], kEpiNone);
         RK_TRY(linear_group(st, grp, ng));
+        if (few) {
+          for (int i = 0; i < 4; ++i) tf.l1[i] = ws.l1[i];
+          tf.up[0] = W.w2t.as<half>(); tf.up[1] = W.a2t.as<half>(); tf.up[2] = W.g2t.as<half>(); tf.up[3] = W.v2t.as<half>();
+          tf.r = ws.r; tf.k = ws.k; tf.v = v_lin; tf.v_first = ws.vfirst;
+          tf.w0 = W.w0.as<half>(); tf.a0 = W.a0.as<half>(); tf.v0 = W.v0.as<half>(); tf.k_k = W.k_k.as<half>();
+          tf.k_a = W.k_a.as<half>(); tf.r_k = W.r_k.as<half>(); tf.lnx_w = W.lnx_w.as<half>(); tf.lnx_b = W.lnx_b.as<half>();
+          tf.state = cfg_.wkv32 ? static_cast<void*>(static_cast<float*>(wkv) + wkv_off)
+                                : static_cast<void*>(static_cast<half*>(wkv) + wkv_off);
+          tf.elapsed = elapsed; tf.y2 = ws.y2;
+          RK_TRY(tmix_decode(st, tf));
+          core_done = true;
+        } else {
         ng = 0;
         grp[ng++] = low(W.w2t, cfg_.rank_w, Cl, ws.l1[0], ws.w12, kEpiNone);
         grp[ng++] = low(W.a2t, cfg_.rank_a, Cl, ws.l1[1], ws.a12, kEpiNone);
@@ -678,6 +699,7 @@ int Model::enqueue(Workspace& ws, int B, int T, half* shift, void* wkv, int* ela
           gates_fused = true;
           v_use = ws.vout;
         }
+        }  // !few
       } else {
         RK_TRY(lin(st, rows, W.Wr, xr, ws.r, kEpiNone));
         RK_TRY(lin(st, rows, W.Wk, xk, ws.k, kEpiNone));
@@ -696,22 +718,24 @@ int Model::enqueue(Workspace& ws, int B, int T, half* shift, void* wkv, int* ela
           v_use = ws.vout;
         }
       }
-      if (gates_fused) {
-        RK_TRY(tmix_kk_a_vres_gate(st, rows, Cl, ws.k, W.k_k.as<half>(), W.a0.as<half>(), ws.a12, W.k_a.as<half>(), ws.k2, ws.nkk, ws.kka,
-                                   ws.v, ws.vfirst, W.v0.as<half>(), ws.y, ws.vout));
-      } else {
-        RK_TRY(tmix_kk_a_gate(st, rows, Cl, ws.k, W.k_k.as<half>(), W.a0.as<half>(), ws.a12, W.k_a.as<half>(), ws.k2, ws.nkk, ws.kka));
+      if (!core_done) {  // (otherwise everything up to y2 was done by the fused time-mix kernel)
+        if (gates_fused) {
+          RK_TRY(tmix_kk_a_vres_gate(st, rows, Cl, ws.k, W.k_k.as<half>(), W.a0.as<half>(), ws.a12, W.k_a.as<half>(), ws.k2, ws.nkk, ws.kka,
+                                     ws.v, ws.vfirst, W.v0.as<half>(), ws.y, ws.vout));
+        } else {
+          RK_TRY(tmix_kk_a_gate(st, rows, Cl, ws.k, W.k_k.as<half>(), W.a0.as<half>(), ws.a12, W.k_a.as<half>(), ws.k2, ws.nkk, ws.kka));
+        }
+        if (cfg_.wkv32) {
+          RK_TRY(wkv7_fp32(st, B, T, Cl, Hl, static_cast<float*>(wkv) + wkv_off, ws.r, ws.w12, W.w0.as<half>(), ws.k2, v_use,
+                           ws.nkk, ws.kka, ws.y));
+        } else {
+          // the reference adds w0 in fp32 inside the kernel for T <= 16 and pre-rounds the sum otherwise
+          RK_TRY(wkv7_fp16(st, B, T, Cl, Hl, static_cast<half*>(wkv) + wkv_off, ws.r, ws.w12, W.w0.as<half>(), T <= 16 ? 1 : 2,
+                           ws.k2, v_use, ws.nkk, ws.kka, ws.y, elapsed));
+        }
+        RK_TRY(tmix_lnx_rkvres_xg(st, rows, Cl, ws.y, ws.r, ws.k2, v_use, W.r_k.as<half>(), W.lnx_w.as<half>(), W.lnx_b.as<half>(),
+                                  ws.g, ws.y2));
       }
-      if (cfg_.wkv32) {
-        RK_TRY(wkv7_fp32(st, B, T, Cl, Hl, static_cast<float*>(wkv) + wkv_off, ws.r, ws.w12, W.w0.as<half>(), ws.k2, v_use,
-                         ws.nkk, ws.kka, ws.y));
-      } else {
-        // the reference adds w0 in fp32 inside the kernel for T <= 16 and pre-rounds the sum otherwise
-        RK_TRY(wkv7_fp16(st, B, T, Cl, Hl, static_cast<half*>(wkv) + wkv_off, ws.r, ws.w12, W.w0.as<half>(), T <= 16 ? 1 : 2,
-                         ws.k2, v_use, ws.nkk, ws.kka, ws.y, elapsed));
-      }
-      RK_TRY(tmix_lnx_rkvres_xg(st, rows, Cl, ws.y, ws.r, ws.k2, v_use, W.r_k.as<half>(), W.lnx_w.as<half>(), W.lnx_b.as<half>(),
-                                ws.g, ws.y2));
     }
     // Tensor parallel: att.output and ffn.value see only this rank's slice of their input, so they emit fp32
     // partial sums that are added across ranks (NCCL) and rounded to half once, like the single-GPU layer.

@@ -23,7 +23,7 @@ constexpr float kNegLog2e = -1.4426950408889634f;
 __device__ int g_tmix_timeout = 0;  // set when the bounded wait for the weight rows gives up
 
 struct TmixDev {
-  int C, H, layer0;
+  int C, H, layer0, round_act;
   int R[4];               // ranks of w, a, g, v
   const half* l1[4];      // [B, R] LoRA down outputs
   const half* up[4];      // [C, R] LoRA up matrices (row = output channel)
@@ -102,8 +102,13 @@ __global__ void __launch_bounds__(256) tmix_decode_kernel(const TmixDev p) {
     if (p.layer0 && s == 3) continue;
     for (int i = tid; i < p.R[s]; i += 256) {
       float x = __half2float(p.l1[s][static_cast<size_t>(b_id) * p.R[s] + i]);
-      if (s == 0) x = tanhf(x);
-      if (s == 2) x = 1.0f / (1.0f + expf(-x));
+      if (p.round_act) {  // what the separate activation kernels of the many-row path produce
+        if (s == 0) x = __half2float(__float2half_rn(apply_in_act(x, kActTanh)));
+        if (s == 2) x = __half2float(__float2half_rn(apply_in_act(x, kActSigmoid)));
+      } else {
+        if (s == 0) x = tanhf(x);
+        if (s == 2) x = 1.0f / (1.0f + expf(-x));
+      }
       acts[s * 512 + i] = x;
     }
   }
@@ -149,8 +154,13 @@ __global__ void __launch_bounds__(256) tmix_decode_kernel(const TmixDev p) {
     if (p.layer0) {
       v_use = vf;
     } else {
-      const float gate = 1.0f / (1.0f + expf(-(__half2float(p.v0[c]) + res[3][tid])));
-      v_use = __half2float(__float2half_rn(vf + (vfirstf - vf) * gate));
+      if (p.round_act) {
+        const float gate = sigmoid_fast(__half2float(p.v0[c]) + __half2float(__float2half_rn(res[3][tid])));
+        v_use = __half2float(__float2half_rn(fmaf(vfirstf - vf, gate, vf)));
+      } else {
+        const float gate = 1.0f / (1.0f + expf(-(__half2float(p.v0[c]) + res[3][tid])));
+        v_use = __half2float(__float2half_rn(vf + (vfirstf - vf) * gate));
+      }
     }
     hv[5][tid] = __float2half_rn(v_use);
     const float u = kf * __half2float(p.k_k[c]);
@@ -311,7 +321,7 @@ int tmix_decode(cudaStream_t stream, const TmixDecodeArgs& a) {
   RK_REQUIRE(tmix_decode_supported(a), kShape, "tmix_decode: LoRA ranks too large for the shared-memory staging");
   RK_REQUIRE(a.state && a.elapsed && a.r && a.k && a.v && a.v_first && a.y2, kBadArg, "tmix_decode: null pointer");
   TmixDev p;
-  p.C = a.C; p.H = a.C / kHead; p.layer0 = a.layer0 ? 1 : 0;
+  p.C = a.C; p.H = a.C / kHead; p.layer0 = a.layer0 ? 1 : 0; p.round_act = a.round_act ? 1 : 0;
   for (int s = 0; s < 4; ++s) { p.R[s] = a.R[s]; p.l1[s] = a.l1[s]; p.up[s] = a.up[s]; }
   p.r = a.r; p.k = a.k; p.v = a.v; p.v_first = a.v_first;
   p.w0 = a.w0; p.a0 = a.a0; p.v0 = a.v0; p.k_k = a.k_k; p.k_a = a.k_a; p.r_k = a.r_k; p.lnx_w = a.lnx_w; p.lnx_b = a.lnx_b;
