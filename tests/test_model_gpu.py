@@ -60,7 +60,7 @@ def run_both(d, om, gm, wkv32, B, chunks, n_decode, seed=1):
 
 
 @pytest.mark.parametrize("wkv32", [False, True])
-@pytest.mark.parametrize("B,chunks,n_decode", [(1, (5, 3), 6), (2, (4,), 4), (1, (20,), 2)])
+@pytest.mark.parametrize("B,chunks,n_decode", [(1, (5, 3), 6), (2, (4,), 4), (1, (20,), 2), (6, (2,), 3)])   # last: 5..16 one-token rows
 def test_forward_matches_oracle_fp16_weights(wkv32, B, chunks, n_decode):
     d, om, gm = build_pair(orc.FMT_F16, wkv32)
     worst, ids_ok, (shift, wkv, elapsed), st = run_both(d, om, gm, wkv32, B, chunks, n_decode)
