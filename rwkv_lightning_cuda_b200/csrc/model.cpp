@@ -433,11 +433,20 @@ Workspace* Model::workspace(int B, int T) {
   return raw;
 }
 
+// Row count from which quantised weights take the tensor-core route through their fp16 copies (below it: the GEMV
+// kernels on the packed weights, whose time grows with the row count).  Measured cross-over: 3 rows for W8A16
+// (1.5B: 1.61 vs 1.73 ms per step), 2 rows for W4A16 (2.9B: 2.45 vs 2.97 ms), whose dequantisation costs more per row.
+static int quant_tc_rows(int fmt) {
+  static const int env = [] { const char* e = getenv("RWKV7_B200_QUANT_TC_ROWS"); return e ? atoi(e) : 0; }();
+  if (env >= 2) return env;
+  return fmt == RWKV7_B200_FMT_W4A16 ? 2 : 3;
+}
+
 int Model::lin(cudaStream_t s, int M, const Matrix& W, const half* x, void* y, int epi) {
   LinearArgs a;
   a.M = M; a.K = W.K; a.N = W.N; a.x = x; a.w = W.w.p; a.fmt = W.fmt;
   a.scale = W.scale.as<half>(); a.zero = W.zero.as<half>(); a.epi = epi; a.y = y;
-  if (W.w16.p && M > 4) {  // expanded copy: straight to the tensor cores
+  if (W.w16.p && M >= quant_tc_rows(W.fmt)) {  // expanded copy: straight to the tensor cores
     a.w = W.w16.p; a.fmt = RWKV7_B200_FMT_F16; a.scale = nullptr; a.zero = nullptr;
     a.out_scale = W.fmt == RWKV7_B200_FMT_W8A16 ? W.scale.as<half>() : nullptr;
   }
@@ -572,7 +581,8 @@ int Model::enqueue(Workspace& ws, int B, int T, half* shift, void* wkv, int* ela
     const bool rows_ok = cfg_.weight_format == RWKV7_B200_FMT_F16 ? C % 8 == 0 : (C % 128 == 0 && cfg_.ffn % 128 == 0);
     // the fused path stages a step's activations in shared memory: B rows of ffn inputs must fit
     // fp16 weights with 2..4 rows go through the general path below: tensor cores for the large matrices
-    const bool gemv_rows = rows == 1 || cfg_.weight_format != RWKV7_B200_FMT_F16;
+    const bool quant_tc = cfg_.weight_format != RWKV7_B200_FMT_F16 && expanded_state_ == 1 && rows >= quant_tc_rows(cfg_.weight_format);
+    const bool gemv_rows = rows == 1 || (cfg_.weight_format != RWKV7_B200_FMT_F16 && !quant_tc);
     if (G == 1 && T == 1 && rows <= 4 && gemv_rows && tmix_decode_supported(probe) && C <= 4096 && rows_ok &&
         linear_batch_fused_fits(rows, cfg_.ffn) && linear_batch_fused_fits(rows, C))
       return enqueue_decode(ws, B, shift, wkv, elapsed, logits, st);
@@ -611,7 +621,14 @@ int Model::enqueue(Workspace& ws, int B, int T, half* shift, void* wkv, int* ela
       LinearArgs seg[7] = {mat(W.Wr, xr, ws.r), mat(W.Wk, xk, ws.k), mat(W.Wv, xv, v_lin),
                            low(W.w1t, cfg_.rank_w, xw, ws.l1[0]), low(W.a1t, cfg_.rank_a, xa, ws.l1[1]),
                            low(W.g1t, cfg_.rank_g, xg, ws.l1[2]), low(W.v1t, cfg_.rank_v, xv, ws.l1[3])};
-      if (rows >= 2 && cfg_.weight_format == RWKV7_B200_FMT_F16) {
+      if (rows >= 2 && (cfg_.weight_format == RWKV7_B200_FMT_F16 || (W.Wr.w16.p && rows >= quant_tc_rows(cfg_.weight_format)))) {
+        for (int i = 0; i < 3; ++i) {  // quantised: the fp16 copies
+          const Matrix* m3[3] = {&W.Wr, &W.Wk, &W.Wv};
+          if (m3[i]->w16.p) {
+            seg[i].w = m3[i]->w16.p; seg[i].fmt = RWKV7_B200_FMT_F16; seg[i].scale = nullptr; seg[i].zero = nullptr;
+            seg[i].out_scale = m3[i]->fmt == RWKV7_B200_FMT_W8A16 ? m3[i]->scale.as<half>() : nullptr;
+          }
+        }
         // 2..4 rows: the three C x C projections as one tensor-core launch, the small LoRA down-projections as one GEMV
         for (int i = 0; i < 3; ++i) {
           seg[i].prefer_tc = true; seg[i].w_dynamic = false;
@@ -803,7 +820,7 @@ int Model::forward(const int64_t* tokens_host, int B, int T, void* shift, void* 
   if (s != kOk) return s;
 
   std::lock_guard<std::mutex> lock(mu_);
-  if (rows > 4 && cfg_.weight_format != RWKV7_B200_FMT_F16 && expanded_state_ == 0) {
+  if (cfg_.weight_format != RWKV7_B200_FMT_F16 && rows >= quant_tc_rows(cfg_.weight_format) && expanded_state_ == 0) {
     s = ensure_expanded();  // before any stream capture: it allocates
     if (s != kOk) return s;
   }
