@@ -582,7 +582,12 @@ int Model::enqueue(Workspace& ws, int B, int T, half* shift, void* wkv, int* ela
     // the fused path stages a step's activations in shared memory: B rows of ffn inputs must fit
     // fp16 weights with 2..4 rows go through the general path below: tensor cores for the large matrices
     const bool quant_tc = cfg_.weight_format != RWKV7_B200_FMT_F16 && expanded_state_ == 1 && rows >= quant_tc_rows(cfg_.weight_format);
-    const bool gemv_rows = rows == 1 || (cfg_.weight_format != RWKV7_B200_FMT_F16 && !quant_tc);
+    // measured cross-over for fp16 weights: 2 rows from the 1.5B layer width up (1.5B: 1.51 vs 1.53 ms at 2 rows, 1.58 vs
+    // 2.18 at 3), 4 rows for narrow models, whose steps are launch-bound (0.1B: 0.42 ms on the GEMV route vs 0.54 at 2 rows)
+    static const int fp16_tc_env = [] { const char* e = getenv("RWKV7_B200_FP16_TC_ROWS"); return e ? atoi(e) : 0; }();
+    const int fp16_tc_rows = fp16_tc_env >= 2 ? fp16_tc_env : (C < 1536 ? 4 : 2);
+    const bool gemv_rows = rows == 1 || (cfg_.weight_format != RWKV7_B200_FMT_F16 && !quant_tc) ||
+                           (cfg_.weight_format == RWKV7_B200_FMT_F16 && rows < fp16_tc_rows);
     if (G == 1 && T == 1 && rows <= 4 && gemv_rows && tmix_decode_supported(probe) && C <= 4096 && rows_ok &&
         linear_batch_fused_fits(rows, cfg_.ffn) && linear_batch_fused_fits(rows, C))
       return enqueue_decode(ws, B, shift, wkv, elapsed, logits, st);
