@@ -579,8 +579,8 @@ int Model::enqueue(Workspace& ws, int B, int T, half* shift, void* wkv, int* ela
     probe.B = B; probe.C = C; probe.wkv32 = cfg_.wkv32 != 0;
     probe.R[0] = cfg_.rank_w; probe.R[1] = cfg_.rank_a; probe.R[2] = cfg_.rank_g; probe.R[3] = cfg_.rank_v;
     const bool rows_ok = cfg_.weight_format == RWKV7_B200_FMT_F16 ? C % 8 == 0 : (C % 128 == 0 && cfg_.ffn % 128 == 0);
-    // the fused path stages a step's activations in shared memory: B rows of ffn inputs must fit
-    // fp16 weights with 2..4 rows go through the general path below: tensor cores for the large matrices
+    // Which one-token steps of up to four rows take the five-launch GEMV path (enqueue_decode); the others go through
+    // the general path below, with the large matrices on the tensor cores.
     const bool quant_tc = cfg_.weight_format != RWKV7_B200_FMT_F16 && expanded_state_ == 1 && rows >= quant_tc_rows(cfg_.weight_format);
     // measured cross-over for fp16 weights: 2 rows from the 1.5B layer width up (1.5B: 1.51 vs 1.53 ms at 2 rows, 1.58 vs
     // 2.18 at 3), 4 rows for narrow models, whose steps are launch-bound (0.1B: 0.42 ms on the GEMV route vs 0.54 at 2 rows)
@@ -588,6 +588,7 @@ int Model::enqueue(Workspace& ws, int B, int T, half* shift, void* wkv, int* ela
     const int fp16_tc_rows = fp16_tc_env >= 2 ? fp16_tc_env : (C < 1536 ? 4 : 2);
     const bool gemv_rows = rows == 1 || (cfg_.weight_format != RWKV7_B200_FMT_F16 && !quant_tc) ||
                            (cfg_.weight_format == RWKV7_B200_FMT_F16 && rows < fp16_tc_rows);
+    // (the fused path stages a step's activations in shared memory: B rows of ffn inputs must fit)
     if (G == 1 && T == 1 && rows <= 4 && gemv_rows && tmix_decode_supported(probe) && C <= 4096 && rows_ok &&
         linear_batch_fused_fits(rows, cfg_.ffn) && linear_batch_fused_fits(rows, C))
       return enqueue_decode(ws, B, shift, wkv, elapsed, logits, st);
@@ -711,17 +712,17 @@ int Model::enqueue(Workspace& ws, int B, int T, half* shift, void* wkv, int* ela
           RK_TRY(tmix_decode(st, tf));
           core_done = true;
         } else {
-        ng = 0;
-        grp[ng++] = low(W.w2t, cfg_.rank_w, Cl, ws.l1[0], ws.w12, kEpiNone);
-        grp[ng++] = low(W.a2t, cfg_.rank_a, Cl, ws.l1[1], ws.a12, kEpiNone);
-        grp[ng++] = low(W.g2t, cfg_.rank_g, Cl, ws.l1[2], ws.g, kEpiNone);
-        if (li > 0) grp[ng++] = low(W.v2t, cfg_.rank_v, Cl, ws.l1[3], ws.y, kEpiNone);
-        RK_TRY(linear_group(st, grp, ng));
-        if (li > 0) {  // the value-residual gate runs in the kk / a gate launch below
-          gates_fused = true;
-          v_use = ws.vout;
+          ng = 0;
+          grp[ng++] = low(W.w2t, cfg_.rank_w, Cl, ws.l1[0], ws.w12, kEpiNone);
+          grp[ng++] = low(W.a2t, cfg_.rank_a, Cl, ws.l1[1], ws.a12, kEpiNone);
+          grp[ng++] = low(W.g2t, cfg_.rank_g, Cl, ws.l1[2], ws.g, kEpiNone);
+          if (li > 0) grp[ng++] = low(W.v2t, cfg_.rank_v, Cl, ws.l1[3], ws.y, kEpiNone);
+          RK_TRY(linear_group(st, grp, ng));
+          if (li > 0) {  // the value-residual gate runs in the kk / a gate launch below
+            gates_fused = true;
+            v_use = ws.vout;
+          }
         }
-        }  // !few
       } else {
         RK_TRY(lin(st, rows, W.Wr, xr, ws.r, kEpiNone));
         RK_TRY(lin(st, rows, W.Wk, xk, ws.k, kEpiNone));
