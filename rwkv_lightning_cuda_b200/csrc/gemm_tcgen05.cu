@@ -9,7 +9,7 @@
 // are brought into 128-byte-swizzled shared memory by TMA (cp.async.bulk.tensor) through one ring of
 // stages that keeps running across units; one elected thread issues tcgen05.mma (cta_group::1,
 // kind::f16, M=128, N=Nt, K=16) into one of two TMEM accumulators; tcgen05.commit releases the stage;
-// four epilogue warps read the finished accumulator back with tcgen05.ld, apply the epilogue and store
+// eight epilogue warps read the finished accumulator back with tcgen05.ld, apply the epilogue and store
 // y (one rounding to half, the reference's rounding point for its cuBLAS calls,
 // cuda/rwkv7_v3a_ops.cu:2235-2302) while the next unit's MMAs fill the other accumulator.
 // Replaces rwkv7_v3a_linear_f16_orig_launch / _lt_cfg_launch / linear_orig_rows_* for rows > 4.
@@ -47,7 +47,6 @@ constexpr int kEpiBytes = kEpiRows * kEpiLd * 4;
 constexpr int kMaxStages = 8;
 
 __device__ int g_gemm_timeout = 0;
-
 
 struct Prob {
   int M, N, K, epi;
