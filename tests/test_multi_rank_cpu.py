@@ -83,3 +83,32 @@ def test_head_sharded_partial_sums_add_up():
         mp.spawn(_tp_worker, args=(world, 29533, out), nprocs=world, join=True)
         for rank in range(world):
             assert max(out[rank]) < 1e-9, out[rank]
+
+
+def test_shard_rule_partitions_every_split_tensor():
+    """For every checkpoint tensor the ranks' slices are disjoint, in rank order, and together cover the split axis; tensors
+    the rule does not split come back whole.  Bad rank / indivisible sizes are refused."""
+    import numpy as np
+    import pytest
+    from rwkv_lightning_cuda_b200 import synthetic, tp
+    from rwkv_lightning_cuda_b200.backend import ModelDims
+    d = ModelDims(layers=2, channels=256, ffn=1024, vocab=512, rank_w=32, rank_a=32, rank_v=16, rank_g=64)
+    split_names = 0
+    for name, shape in synthetic.tensor_shapes(d).items():
+        full = np.arange(int(np.prod(shape)), dtype=np.int64).reshape(shape)
+        for world in (2, 4):
+            parts = [tp.take_shard(name, full, d, r, world) for r in range(world)]
+            plan = tp.shard_of(name, d, 0, world)
+            if plan is None:
+                assert all(p is full for p in parts), name
+                continue
+            split_names += world == 2
+            axis = plan[0]
+            assert np.array_equal(np.concatenate(parts, axis=axis), full), name
+            assert all(p.shape[axis] * world == full.shape[axis] for p in parts), name
+        assert tp.shard_of(name, d, 0, 1) is None
+    assert split_names == 2 * 18 - 2 + 1          # 18 split tensors per layer (layer 0 has no v0 and no v2) + the head
+    with pytest.raises(ValueError):
+        tp.shard_of("head.weight", d, 2, 2)
+    with pytest.raises(ValueError):
+        tp.shard_of("head.weight", ModelDims(layers=1, channels=192, ffn=512, vocab=512), 0, 2)   # 3 heads over 2 ranks
