@@ -14,7 +14,8 @@ namespace rk {
 // ---- wkv7.cu
 int wkv7_fp16(cudaStream_t stream, int B, int T, int C, int H, half* state, const half* r, const half* w,
               const half* w0, int w_mode, const half* k, const half* v, const half* a, const half* b,
-              half* y, const int* elapsed);
+              half* y, const int* elapsed, int channel0 = 0);  // channel0: index of channel 0 in the whole model (a
+                                                               // tensor-parallel rank's slice starts later): phase of the decay dither
 int wkv7_fp32(cudaStream_t stream, int B, int T, int C, int H, float* state, const half* r, const half* w,
               const half* w0, const half* k, const half* v, const half* a, const half* b, half* y);
 

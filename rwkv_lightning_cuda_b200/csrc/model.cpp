@@ -754,7 +754,7 @@ int Model::enqueue(Workspace& ws, int B, int T, half* shift, void* wkv, int* ela
         } else {
           // the reference adds w0 in fp32 inside the kernel for T <= 16 and pre-rounds the sum otherwise
           RK_TRY(wkv7_fp16(st, B, T, Cl, Hl, static_cast<half*>(wkv) + wkv_off, ws.r, ws.w12, W.w0.as<half>(), T <= 16 ? 1 : 2,
-                           ws.k2, v_use, ws.nkk, ws.kka, ws.y, elapsed));
+                           ws.k2, v_use, ws.nkk, ws.kka, ws.y, elapsed, tp_rank_ * Cl));
         }
         RK_TRY(tmix_lnx_rkvres_xg(st, rows, Cl, ws.y, ws.r, ws.k2, v_use, W.r_k.as<half>(), W.lnx_w.as<half>(), W.lnx_b.as<half>(),
                                   ws.g, ws.y2));

@@ -37,7 +37,7 @@ __global__ void __launch_bounds__(64) wkv7_fp16_kernel(
     int T, int C, int H, half* __restrict__ state, const half* __restrict__ r,
     const half* __restrict__ w, const half* __restrict__ w0, const half* __restrict__ k,
     const half* __restrict__ v, const half* __restrict__ a, const half* __restrict__ b,
-    half* __restrict__ y, const int* __restrict__ elapsed) {
+    half* __restrict__ y, const int* __restrict__ elapsed, int channel0) {
   __shared__ __align__(128) uint4 tile[512];
   __shared__ __align__(16) half vec[2][6][kHead];  // r, w, k, a, b, v
   __shared__ __align__(16) half dvec[kHead];
@@ -65,7 +65,7 @@ __global__ void __launch_bounds__(64) wkv7_fp16_kernel(
   if (i < 48) cp_async16(&vec[0][vi][chunk * 8], my_src + tok0 + chunk * 8);
   cp_async_commit();
 
-  const int phase0 = elapsed[b_id] + h * kHead + i;
+  const int phase0 = elapsed[b_id] + channel0 + h * kHead + i;  // the dither counts channels of the whole model
   float w0f = 0.f;
   if (kWMode != 0) w0f = __half2float(w0[h * kHead + i]);
 
@@ -345,16 +345,16 @@ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) ==
 
 int wkv7_fp16(cudaStream_t stream, int B, int T, int C, int H, half* state, const half* r, const half* w,
               const half* w0, int w_mode, const half* k, const half* v, const half* a, const half* b,
-              half* y, const int* elapsed) {
+              half* y, const int* elapsed, int channel0) {
   RK_REQUIRE(B > 0 && T > 0 && H > 0 && C == H * kHead, kShape, "wkv7_fp16: need B,T,H > 0 and C == 64*H");
   RK_REQUIRE(state && r && w && k && v && a && b && y && elapsed, kBadArg, "wkv7_fp16: null pointer");
   RK_REQUIRE(w_mode == 0 || w0, kBadArg, "wkv7_fp16: w0 required for w_mode %d", w_mode);
   RK_REQUIRE(aligned16(state) && aligned16(r) && aligned16(w) && aligned16(k) && aligned16(v) && aligned16(a) &&
                  aligned16(b), kBadArg, "wkv7_fp16: tensors must be 16-byte aligned");
   const dim3 grid(B * H), block(64);
-  if (w_mode == 0) wkv7_fp16_kernel<0><<<grid, block, 0, stream>>>(T, C, H, state, r, w, w0, k, v, a, b, y, elapsed);
-  else if (w_mode == 1) wkv7_fp16_kernel<1><<<grid, block, 0, stream>>>(T, C, H, state, r, w, w0, k, v, a, b, y, elapsed);
-  else if (w_mode == 2) wkv7_fp16_kernel<2><<<grid, block, 0, stream>>>(T, C, H, state, r, w, w0, k, v, a, b, y, elapsed);
+  if (w_mode == 0) wkv7_fp16_kernel<0><<<grid, block, 0, stream>>>(T, C, H, state, r, w, w0, k, v, a, b, y, elapsed, channel0);
+  else if (w_mode == 1) wkv7_fp16_kernel<1><<<grid, block, 0, stream>>>(T, C, H, state, r, w, w0, k, v, a, b, y, elapsed, channel0);
+  else if (w_mode == 2) wkv7_fp16_kernel<2><<<grid, block, 0, stream>>>(T, C, H, state, r, w, w0, k, v, a, b, y, elapsed, channel0);
   else RK_REQUIRE(false, kBadArg, "wkv7_fp16: w_mode must be 0, 1 or 2");
   RK_LAUNCH_CHECK("wkv7_fp16 launch");
   return kOk;
