@@ -202,9 +202,18 @@ def run_ours(args, rank, world, local_rank):
             gm.forward_to_host(toks[1 + total + 3 + i], st, lg, out_host)
         torch.cuda.synchronize()
         e2e_ms = (time.perf_counter() - t0) * 1e3 / args.steps
+        # the same steps with the greedy choice of the next token on the device: first ids in, chosen ids out, one call
+        ids_host = torch.empty((args.steps, B), dtype=torch.int32).pin_memory()
+        gm.decode_greedy(toks[0].reshape(-1), min(args.warmup, 3), st, lg)
+        barrier()
+        launches_g0 = gm.kernel_launches()
+        t0 = time.perf_counter()
+        gm.decode_greedy(toks[0].reshape(-1), args.steps, st, lg, out_host=ids_host)
+        greedy_ms = (time.perf_counter() - t0) * 1e3 / args.steps
+        launches_g = gm.kernel_launches() - launches_g0
         clocks = sampler.stop()
 
-    ms, e2e_ms = max_over_ranks([ms, e2e_ms], world, "cuda")
+    ms, e2e_ms, greedy_ms = max_over_ranks([ms, e2e_ms, greedy_ms], world, "cuda")
     if rank != 0:
         return
     abytes, wbytes, sbytes = algorithmic_bytes(d, B, bool(args.wkv32), fmt)
@@ -223,6 +232,9 @@ def run_ours(args, rank, world, local_rank):
         "clocks": clocks,
         "e2e": {"value": whole_job_rate(world, B, e2e_ms), "unit": "tok/s", "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": B * 8, "d2h_bytes_per_step": B * d.vocab * 4},
+        "e2e_greedy": {"value": whole_job_rate(world, B, greedy_ms), "unit": "tok/s", "ms_per_step": greedy_ms,
+                       "what": "decode steps + greedy token choice on the device, one host call for all steps",
+                       "h2d_bytes_per_call": B * 8, "d2h_bytes_per_call": args.steps * B * 4, "gpu_launches": int(launches_g)},
         "gpu_launches": int(launches),
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
                      "traffic": traffic, "peak_kind": peak_kind, "frac_of_nominal_8000": achieved / 8000.0,

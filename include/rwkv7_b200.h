@@ -134,6 +134,26 @@ int rwkv7_b200_forward(rwkv7_b200_model* m, const int64_t* tokens_host, int B, i
 int rwkv7_b200_forward_to_host(rwkv7_b200_model* m, const int64_t* tokens_host, int B, int T, void* shift,
                                void* wkv, int* elapsed, float* logits, float* logits_host, void* stream);
 
+/* The step after the path, kept on the device: `steps` decode steps in a row, each followed by a greedy choice of
+ * every sequence's next token, with no host round trip between them.  Replaces, for top_p == 0 (the sampler's greedy
+ * case, src/utils/sampling.cu:507-512), the engine's loop forward_decode -> sampler -> copy to the host -> next
+ * forward_decode (src/rwkv_sampler.cpp:47-111; kernel src/utils/sampling.cu:205-471).
+ * first_tokens_host [B] feeds step 0.  penalties is NULL or a device array fp32 [B][vocab] that is subtracted from
+ * the logits and updated after every choice as the reference's sampler does (:253, :460-469:
+ * p = p * penalty_decay + (chosen ? (p == 0 ? presence_penalty : repetition_penalty) : 0)); +inf masks a token.
+ * Among equal values the lowest token id wins (the reference draws among them at random).
+ * out_tokens is a device array int32 [steps][B]; logits (fp32 [B][vocab], device) holds the last step's logits
+ * afterwards.  out_tokens_host NULL: asynchronous like rwkv7_b200_forward; otherwise the tokens are also copied
+ * there and `stream` is synchronised.  Not available for tensor-parallel models (BAD_ARG). */
+int rwkv7_b200_decode_greedy(rwkv7_b200_model* m, const int64_t* first_tokens_host, int B, int steps, void* shift,
+                             void* wkv, int* elapsed, float* logits, float* penalties, float presence_penalty,
+                             float repetition_penalty, float penalty_decay, int* out_tokens, int* out_tokens_host,
+                             void* stream);
+/* The choice alone, for a caller that runs its own loop: out[b] = argmax_i (logits[b][i] - penalties[b][i]) with the
+ * penalty update above; next_tokens (int64 [B], may be NULL) receives the same ids. */
+int rwkv7_b200_greedy_pick(void* stream, int B, int V, const float* logits, float* penalties, float presence_penalty,
+                           float repetition_penalty, float penalty_decay, int* out, int64_t* next_tokens);
+
 /* Replaces ModelBackend::copy_state_slice (src/rwkv7_fast_v4.cu:1421-1504): copies `count`
  * sequences from a state of batch size src_B (starting at src_offset) into a state of batch size
  * dst_B (starting at dst_offset).  Enqueued on `stream`. */

@@ -209,6 +209,35 @@ def wkv_fp16(B, T, H, state, r, w, w0, k, v, a, b, elapsed):
     return y
 
 
+def greedy_pick(logits, penalties=None, presence=0.0, repetition=0.0, decay=1.0):
+    """The reference sampler's greedy case (top_p == 0 => top_k = 1, src/utils/sampling.cu:507-512) restated in numpy.
+
+    Per row: value = finite(logit) - penalty (:253 with :139-142: NaN -> 0, +-inf -> +-FLT_MAX; the temperature is a
+    positive factor and drops out of an argmax), token = the largest value's index (the lowest index among equal
+    values -- the reference draws among them at random), then penalty = fma(penalty, decay, chosen ? (penalty == 0 ?
+    presence : repetition) : 0) (:460-469).  ``penalties`` (fp32 [B, V]) is updated in place.  Returns int32 [B].
+    """
+    lg = np.asarray(logits, dtype=np.float32)
+    fmax = np.finfo(np.float32).max
+    val = np.where(np.isnan(lg), np.float32(0), np.clip(lg, -fmax, fmax)).astype(np.float32)
+    if penalties is not None:
+        with np.errstate(invalid="ignore", over="ignore"):
+            val = (val - penalties).astype(np.float32)
+    out = np.zeros(lg.shape[0], dtype=np.int32)
+    for b in range(lg.shape[0]):
+        row = val[b]
+        ok = ~np.isnan(row)
+        if ok.any():
+            out[b] = int(np.flatnonzero(ok & (row == row[ok].max()))[0])
+        if penalties is not None:
+            p = penalties[b].astype(np.float64)
+            add = np.zeros_like(p)
+            add[out[b]] = presence if penalties[b, out[b]] == 0 else repetition
+            with np.errstate(invalid="ignore", over="ignore"):
+                penalties[b] = (p * float(np.float32(decay)) + add.astype(np.float32)).astype(np.float32)
+    return out
+
+
 class Model:
     """Whole-model oracle; tensors are set by checkpoint name as float16 arrays."""
 

@@ -102,6 +102,25 @@ int rwkv7_b200_forward_to_host(rwkv7_b200_model* m, const int64_t* tokens_host, 
   return kOk;
 }
 
+int rwkv7_b200_decode_greedy(rwkv7_b200_model* m, const int64_t* first_tokens_host, int B, int steps, void* shift, void* wkv,
+                             int* elapsed, float* logits, float* penalties, float presence_penalty, float repetition_penalty,
+                             float penalty_decay, int* out_tokens, int* out_tokens_host, void* stream) {
+  RK_REQUIRE(m, kBadArg, "null model");
+  int s = m->impl.decode_greedy(first_tokens_host, B, steps, shift, wkv, elapsed, logits, penalties, presence_penalty,
+                                repetition_penalty, penalty_decay, out_tokens, st(stream));
+  if (s != kOk || !out_tokens_host) return s;
+  RK_CUDA(cudaMemcpyAsync(out_tokens_host, out_tokens, static_cast<size_t>(B) * steps * sizeof(int), cudaMemcpyDeviceToHost,
+                          st(stream)));
+  RK_CUDA(cudaStreamSynchronize(st(stream)));
+  return kOk;
+}
+
+int rwkv7_b200_greedy_pick(void* stream, int B, int V, const float* logits, float* penalties, float presence_penalty,
+                           float repetition_penalty, float penalty_decay, int* out, int64_t* next_tokens) {
+  return rk::greedy_pick(st(stream), B, V, logits, penalties, presence_penalty, repetition_penalty, penalty_decay, out,
+                         next_tokens);
+}
+
 int rwkv7_b200_copy_state_slice(const rwkv7_b200_model* m, const void* src_shift, const void* src_wkv, const int* src_elapsed,
                                 int src_B, int src_offset, void* dst_shift, void* dst_wkv, int* dst_elapsed, int dst_B,
                                 int dst_offset, int count, void* stream) {

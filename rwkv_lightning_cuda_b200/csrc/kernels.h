@@ -58,6 +58,11 @@ int tmix_lnx_rkvres_xg(cudaStream_t stream, int rows, int C, const half* y, cons
 int tmix_vres_gate(cudaStream_t stream, int rows, int C, const half* v, const half* v_first, const half* v0,
                    const half* v12, half* out);
 int advance_i32(cudaStream_t stream, int* x, int amount, int n);
+
+// Greedy token choice per sequence over fp32 logits [B, V] with optional penalties [B, V] (updated in place); the token
+// goes to out[b] and, when next_tokens is given, to next_tokens[b] (the next decode step's input).  See greedy.cu.
+int greedy_pick(cudaStream_t stream, int B, int V, const float* logits, float* penalties, float presence, float repetition,
+                float decay, int* out, int64_t* next_tokens);
 // src [G][B][Vl] (one block per rank, as an all-gather leaves it) -> dst [B][G*Vl]
 int interleave_gathered(cudaStream_t stream, const float* src, float* dst, int G, int B, int Vl);
 int relu_square(cudaStream_t stream, const half* x, half* out, long long n);

@@ -824,20 +824,31 @@ int Model::forward(const int64_t* tokens_host, int B, int T, void* shift, void* 
     RK_REQUIRE(tokens_host[i] >= 0 && tokens_host[i] < cfg_.vocab, kBadArg, "token id out of range");
   int s = use_device();
   if (s != kOk) return s;
-
   std::lock_guard<std::mutex> lock(mu_);
+  return step(tokens_host, B, T, shift, wkv, elapsed, logits, stream, nullptr);
+}
+
+// One forward with mu_ held.  tokens_host == nullptr: the ids are in the workspace's device buffer already (written
+// by the greedy pick of the previous step).
+int Model::step(const int64_t* tokens_host, int B, int T, void* shift, void* wkv, int* elapsed, float* logits,
+                cudaStream_t stream, Workspace** ws_out) {
+  const long long rows = static_cast<long long>(B) * T;
+  int s = kOk;
   if (cfg_.weight_format != RWKV7_B200_FMT_F16 && rows >= quant_tc_rows(cfg_.weight_format) && expanded_state_ == 0) {
     s = ensure_expanded();  // before any stream capture: it allocates
     if (s != kOk) return s;
   }
   Workspace* ws = workspace(B, T);
   RK_REQUIRE(ws, kCuda, "forward: workspace allocation failed for B=%d T=%d", B, T);
-  const int slot = ws->slot;
-  ws->slot = (slot + 1) % Workspace::kSlots;
-  RK_CUDA(cudaEventSynchronize(ws->tokens_copied[slot]));  // the copy that last read this slot is done
-  std::memcpy(ws->tokens_pinned[slot], tokens_host, static_cast<size_t>(rows) * sizeof(int64_t));
-  RK_CUDA(cudaMemcpyAsync(ws->tokens, ws->tokens_pinned[slot], static_cast<size_t>(rows) * sizeof(int64_t), cudaMemcpyHostToDevice, stream));
-  RK_CUDA(cudaEventRecord(ws->tokens_copied[slot], stream));
+  if (ws_out) *ws_out = ws;
+  if (tokens_host) {
+    const int slot = ws->slot;
+    ws->slot = (slot + 1) % Workspace::kSlots;
+    RK_CUDA(cudaEventSynchronize(ws->tokens_copied[slot]));  // the copy that last read this slot is done
+    std::memcpy(ws->tokens_pinned[slot], tokens_host, static_cast<size_t>(rows) * sizeof(int64_t));
+    RK_CUDA(cudaMemcpyAsync(ws->tokens, ws->tokens_pinned[slot], static_cast<size_t>(rows) * sizeof(int64_t), cudaMemcpyHostToDevice, stream));
+    RK_CUDA(cudaEventRecord(ws->tokens_copied[slot], stream));
+  }
 
   // tensor-parallel steps are enqueued directly: their collectives are not recorded into graphs here
   static const bool no_graph = [] { const char* e = getenv("RWKV7_B200_NO_GRAPH"); return e && atoi(e) != 0; }();  // tuning aid
@@ -878,6 +889,36 @@ int Model::forward(const int64_t* tokens_host, int B, int T, void* shift, void* 
   it->second.last_use = ++tick_;
   RK_CUDA(cudaGraphLaunch(it->second.exec, stream));
   launches_ += it->second.launches;
+  return kOk;
+}
+
+// A run of greedy decode steps without a host round trip: after every step one kernel picks each sequence's token
+// and writes it where the next step's embedding gather reads it.  Replaces, for top_p == 0, the loop
+// forward_decode -> sampler -> copy to the host -> next forward_decode of the reference's engine
+// (src/rwkv_sampler.cpp:47-111, src/utils/sampling.cu:205-471,507-512).
+int Model::decode_greedy(const int64_t* first_tokens_host, int B, int steps, void* shift, void* wkv, int* elapsed,
+                         float* logits, float* penalties, float presence, float repetition, float decay, int* out_tokens,
+                         cudaStream_t stream) {
+  RK_REQUIRE(finalized_, kNotReady, "decode_greedy: model not finalised");
+  RK_REQUIRE(B > 0, kBadArg, "token_batches must not be empty");
+  RK_REQUIRE(steps > 0, kBadArg, "decode_greedy: steps must be positive");
+  RK_REQUIRE(first_tokens_host && shift && wkv && elapsed && logits && out_tokens, kBadArg, "decode_greedy: null pointer");
+  RK_REQUIRE(tp_size_ == 1, kBadArg, "decode_greedy: not available for a tensor-parallel model");
+  for (int i = 0; i < B; ++i)
+    RK_REQUIRE(first_tokens_host[i] >= 0 && first_tokens_host[i] < cfg_.vocab, kBadArg, "token id out of range");
+  int s = use_device();
+  if (s != kOk) return s;
+  std::lock_guard<std::mutex> lock(mu_);
+  for (int i = 0; i < steps; ++i) {
+    Workspace* ws = nullptr;
+    s = step(i == 0 ? first_tokens_host : nullptr, B, 1, shift, wkv, elapsed, logits, stream, &ws);
+    if (s != kOk) return s;
+    const long long before = launch_counter();
+    s = greedy_pick(stream, B, cfg_.vocab, logits, penalties, presence, repetition, decay, out_tokens + static_cast<size_t>(i) * B,
+                    ws->tokens);
+    launches_ += launch_counter() - before;
+    if (s != kOk) return s;
+  }
   return kOk;
 }
 

@@ -81,6 +81,8 @@ class Model {
   int finalize();
   int forward(const int64_t* tokens_host, int B, int T, void* shift, void* wkv, int* elapsed, float* logits,
               cudaStream_t stream);
+  int decode_greedy(const int64_t* first_tokens_host, int B, int steps, void* shift, void* wkv, int* elapsed, float* logits,
+                    float* penalties, float presence, float repetition, float decay, int* out_tokens, cudaStream_t stream);
   int state_sizes(int B, size_t* shift_elems, size_t* wkv_elems, size_t* elapsed_elems) const;
   int state_init(int B, void* shift, void* wkv, int* elapsed, cudaStream_t stream) const;
   int copy_state_slice(const void* src_shift, const void* src_wkv, const int* src_elapsed, int src_B, int src_off,
@@ -115,6 +117,8 @@ class Model {
   int transpose_into(DevBuf& dst, const DevBuf& src, int rows, int cols);
   int quantize(Matrix& m);
   Workspace* workspace(int B, int T);
+  int step(const int64_t* tokens_host, int B, int T, void* shift, void* wkv, int* elapsed, float* logits, cudaStream_t stream,
+           Workspace** ws_out);
   int enqueue(Workspace& ws, int B, int T, half* shift, void* wkv, int* elapsed, float* logits, cudaStream_t s);
   int enqueue_decode(Workspace& ws, int B, half* shift, void* wkv, int* elapsed, float* logits, cudaStream_t s);
   int lin(cudaStream_t s, int M, const Matrix& W, const half* x, void* y, int epi);

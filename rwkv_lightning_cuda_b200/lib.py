@@ -51,6 +51,8 @@ SIGNATURES = {
     "rwkv7_b200_state_init": [_vp, _i, _vp, _vp, _vp, _vp],
     "rwkv7_b200_forward": [_vp, _vp, _i, _i, _vp, _vp, _vp, _vp, _vp],
     "rwkv7_b200_forward_to_host": [_vp, _vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp],
+    "rwkv7_b200_decode_greedy": [_vp, _vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _f, _f, _f, _vp, _vp, _vp],
+    "rwkv7_b200_greedy_pick": [_vp, _i, _i, _vp, _vp, _f, _f, _f, _vp, _vp],
     "rwkv7_b200_copy_state_slice": [_vp, _vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _i, _vp],
     "rwkv7_b200_query_capacity": [_vp, _i, C.POINTER(Capacity)],
     "rwkv7_b200_kernel_launches": [_vp],

@@ -124,6 +124,15 @@ def advance_i32(x, amount):
     L.check(L.load_library().rwkv7_b200_advance_i32(_s(), _p(x), amount, x.numel()))
 
 
+def greedy_pick(logits, penalties=None, presence_penalty=0.0, repetition_penalty=0.0, penalty_decay=1.0, next_tokens=None):
+    """Token ids int32 [B] = argmax(logits - penalties) per row; ``penalties`` is updated in place."""
+    B, V = logits.shape
+    out = torch.empty((B,), dtype=torch.int32, device=logits.device)
+    L.check(L.load_library().rwkv7_b200_greedy_pick(_s(), B, V, _p(logits), _p(penalties), presence_penalty, repetition_penalty,
+                                                    penalty_decay, _p(out), _p(next_tokens)))
+    return out
+
+
 def _out(x, N, epi):
     return torch.empty((x.shape[0], N), dtype=torch.float32 if epi == L.EPI_F32 else torch.float16, device=x.device)
 

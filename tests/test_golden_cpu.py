@@ -132,3 +132,32 @@ def test_whole_model_matches_the_reference_backend(wkv32):
     assert np.abs(shift.astype(np.float32) - m[tag + "_shift"].astype(np.float32)).max() < 2e-2
     ref_wkv = m[tag + "_wkv"].astype(np.float32)
     assert np.abs(wkv.astype(np.float32) - ref_wkv).max() <= 2e-2 * max(1.0, float(np.abs(ref_wkv).max()))
+
+
+def test_greedy_pick_reproduces_the_reference_sampler_tests_known_answers():
+    """The known answers of the reference's own sampler test for its greedy case (test/sampler_test.cpp:30-75):
+    top_p = 0 picks the largest logit, and with presence 2 / frequency 5 / decay 0.5 the chosen token's penalty
+    goes 0 -> 2 -> 6 while the others stay 0."""
+    logits = np.array([[0.25, 3.0, 1.0, -1.0]], dtype=np.float32)
+    assert orc.greedy_pick(logits).tolist() == [1]
+    pen = np.zeros((1, 4), dtype=np.float32)
+    assert orc.greedy_pick(logits, pen, 0.0, 0.0, 0.996).tolist() == [1]
+    assert np.all(pen == 0)
+    logits = np.array([[100.0, 0.0, 0.0, 0.0]], dtype=np.float32)
+    pen = np.zeros((1, 4), dtype=np.float32)
+    assert orc.greedy_pick(logits, pen, 2.0, 5.0, 0.5).tolist() == [0]
+    np.testing.assert_allclose(pen[0], [2.0, 0.0, 0.0, 0.0], atol=1e-6)
+    assert orc.greedy_pick(logits, pen, 2.0, 5.0, 0.5).tolist() == [0]
+    np.testing.assert_allclose(pen[0], [6.0, 0.0, 0.0, 0.0], atol=1e-6)
+
+
+def test_greedy_pick_edge_values():
+    """NaN logits count as 0, infinities are clamped, +inf penalties mask a token, the lowest id wins a tie."""
+    inf, nan = np.inf, np.nan
+    logits = np.array([[nan, -1.0, -inf, -0.5], [1.0, inf, inf, 0.0], [2.0, 5.0, 5.0, 1.0], [3.0, 9.0, 1.0, 0.0]], dtype=np.float32)
+    assert orc.greedy_pick(logits).tolist() == [0, 1, 1, 1]
+    pen = np.zeros((4, 4), dtype=np.float32)
+    pen[3, 1] = inf
+    pen[2, 1] = 0.5
+    assert orc.greedy_pick(logits, pen, 1.0, 2.0, 0.5).tolist() == [0, 1, 2, 0]
+    assert pen[2].tolist() == [0.0, 0.25, 1.0, 0.0] and pen[3, 0] == 1.0 and pen[3, 1] == inf

@@ -187,3 +187,62 @@ def test_library_matches_the_reference_backend_golden(wkv32):
     assert np.abs(st.shift.cpu().numpy().astype(np.float32) - m[tag + "_shift"].astype(np.float32)).max() < 2e-2
     ref_wkv = m[tag + "_wkv"].astype(np.float32)
     assert np.abs(st.wkv_state.cpu().numpy().astype(np.float32) - ref_wkv).max() <= 2e-2 * max(1.0, float(np.abs(ref_wkv).max()))
+
+
+@pytest.mark.parametrize("use_stream", [False, True])     # default stream: eager launches; side stream: graph replay
+def test_decode_greedy_equals_the_step_by_step_loop_and_the_oracle(use_stream):
+    """The on-device greedy loop against (1) the same library driven step by step from the host with the oracle's
+    greedy pick on the copied-back logits: identical ids, penalties, logits and state; (2) the CPU oracle's own
+    model + pick chain: identical ids."""
+    from rwkv_lightning_cuda_b200 import backend as bk
+    d, om, gm = build_pair(orc.FMT_F16, False)
+    B, steps = 3, 6
+    first = [7, 11, 200]
+    prompt = [[5, 6, 7], [8, 9, 10], [3, 2, 1]]
+    pres, rep, decay = 0.4, 0.3, 0.9
+    s = torch.cuda.Stream() if use_stream else torch.cuda.default_stream()
+    with torch.cuda.stream(s):
+        # (a) on the device
+        st_a = gm.create_state(B); lg_a = bk.DeviceLogits()
+        gm.forward_prefill(prompt, st_a, lg_a)
+        pen_a = torch.zeros((B, d.vocab), dtype=torch.float32, device="cuda")
+        host = torch.empty((steps, B), dtype=torch.int32).pin_memory()
+        ids_a = gm.decode_greedy(first, steps, st_a, lg_a, pen_a, pres, rep, decay, out_host=host)
+        assert torch.equal(ids_a.cpu(), host)
+        # (b) step by step from the host
+        st_b = gm.create_state(B); lg_b = bk.DeviceLogits()
+        gm.forward_prefill(prompt, st_b, lg_b)
+        pen_b = np.zeros((B, d.vocab), dtype=np.float32)
+        cur, ids_b = list(first), []
+        for _ in range(steps):
+            gm.forward_decode(cur, st_b, lg_b)
+            cur = orc.greedy_pick(lg_b.values.cpu().numpy(), pen_b, pres, rep, decay).tolist()
+            ids_b.append(cur)
+    torch.cuda.synchronize()
+    assert host.tolist() == ids_b
+    assert np.array_equal(pen_a.cpu().numpy(), pen_b)
+    assert torch.equal(lg_a.values, lg_b.values)
+    assert torch.equal(st_a.wkv_state, st_b.wkv_state) and torch.equal(st_a.shift, st_b.shift)
+    assert torch.equal(st_a.elapsed, st_b.elapsed)
+    # (c) the oracle's own chain
+    shift, wkv, elapsed = om.new_state(B, False)
+    om.forward(np.array(prompt), shift, wkv, elapsed, lora_round_act=1)
+    pen_c = np.zeros((B, d.vocab), dtype=np.float32)
+    cur, ids_c = np.array(first), []
+    for _ in range(steps):
+        cur = orc.greedy_pick(om.forward(cur[:, None], shift, wkv, elapsed, lora_round_act=0), pen_c, pres, rep, decay)
+        ids_c.append(cur.tolist())
+    assert ids_c == ids_b
+
+
+def test_decode_greedy_argument_errors():
+    from rwkv_lightning_cuda_b200 import backend as bk, lib as L
+    d, om, gm = build_pair(orc.FMT_F16, False)
+    st = gm.create_state(2); lg = bk.DeviceLogits()
+    with pytest.raises(L.Rwkv7B200Error, match="steps must be positive"):
+        gm.decode_greedy([1, 2], 0, st, lg)
+    with pytest.raises(L.Rwkv7B200Error, match="token id out of range"):
+        gm.decode_greedy([1, d.vocab], 2, st, lg)
+    with pytest.raises(L.Rwkv7B200Error, match="state batch size mismatch"):
+        gm.decode_greedy([1, 2, 3], 2, st, lg)
+    assert int(st.elapsed.sum()) == 0          # nothing ran

@@ -307,3 +307,26 @@ def test_ops_match_the_reference_kernels_golden(ops):
         assert_close16(host(outs[i]), g["lnmix6_out"][i], max_ulp=3, min_exact=0.9, what=f"add_ln_tmix_mix6[{i}] vs reference")
     assert_close16(host(sh), g["lnmix6_shift"], what="shift vs reference")
     assert_close16(host(ops.linear_f16_orig(dev(g["lin_x"]), dev(g["lin_W"]))), g["lin_y"], max_ulp=1, what="linear vs reference GEMV")
+
+
+@pytest.mark.parametrize("V", [65536, 1030, 8])     # 1030: rows not 16-byte aligned (scalar loads)
+def test_greedy_pick_matches_the_oracle(V):
+    """Bit-exact ids and penalties against the numpy restatement of the reference sampler's greedy case, with NaN and
+    infinite logits, masked tokens, repeated maxima and two consecutive picks (penalty == 0 versus != 0 branches)."""
+    from rwkv_lightning_cuda_b200 import ops
+    rng = np.random.default_rng(V)
+    B = 5
+    logits = rng.standard_normal((B, V)).astype(np.float32) * 4
+    logits[0, V // 2] = np.nan; logits[1, 1] = np.inf; logits[1, V - 1] = np.inf; logits[2, 0] = -np.inf
+    logits[3, [2, V - 2]] = logits[3].max() + 1          # a tie: the lower id wins
+    pen = (rng.random((B, V)) < 0.3).astype(np.float32) * rng.random((B, V)).astype(np.float32)
+    pen[4, int(logits[4].argmax())] = np.inf             # the best token of row 4 is masked
+    pen_g = torch.from_numpy(pen.copy()).cuda()
+    lg = torch.from_numpy(logits).cuda()
+    nxt = torch.zeros(B, dtype=torch.int64, device="cuda")
+    for _ in range(2):
+        want = orc.greedy_pick(logits, pen, 0.7, 0.45, 0.996)
+        got = ops.greedy_pick(lg, pen_g, 0.7, 0.45, 0.996, next_tokens=nxt)
+        assert got.cpu().tolist() == want.tolist() and nxt.cpu().tolist() == want.tolist()
+        assert np.array_equal(pen_g.cpu().numpy(), pen, equal_nan=True)
+    assert ops.greedy_pick(lg).cpu().tolist() == orc.greedy_pick(logits).tolist()
