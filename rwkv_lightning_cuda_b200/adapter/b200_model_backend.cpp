@@ -111,6 +111,28 @@ void B200ModelBackend::forward_decode(const std::vector<int64_t>& token_batch, G
   run(token_batch.data(), static_cast<int>(token_batch.size()), 1, state, logits);
 }
 
+std::vector<int> B200ModelBackend::decode_greedy(const std::vector<int64_t>& token_batch, int steps, GenerationState& state,
+                                                 DeviceLogits& logits, float* penalties, double alpha_presence,
+                                                 double alpha_frequency, double alpha_decay) const {
+  if (token_batch.empty()) throw std::runtime_error("token_batches must not be empty");
+  const int B = static_cast<int>(token_batch.size());
+  if (state.batch_size != B) throw std::runtime_error("state batch size mismatch");
+  if (state.wkv32 != use_wkv32_) throw std::runtime_error("state wkv precision mismatch");
+  if (steps <= 0) throw std::runtime_error("decode_greedy: steps must be positive");
+  logits.rows = B;
+  logits.vocab_size = vocab_size();
+  logits.values.resize(static_cast<size_t>(B) * logits.vocab_size, "alloc backend logits f32");
+  rwkv7_fast_v4::DeviceBuffer<int> ids_dev;
+  ids_dev.resize(static_cast<size_t>(B) * steps, "alloc greedy token ids");
+  std::vector<int> ids(static_cast<size_t>(B) * steps);
+  void* wkv = use_wkv32_ ? static_cast<void*>(state.wkv_state32.p) : static_cast<void*>(state.wkv_state.p);
+  // the host pointer makes the call copy the ids back and synchronise the stream
+  check(rwkv7_b200_decode_greedy(model_, token_batch.data(), B, steps, state.shift.p, wkv, state.elapsed.p, logits.values.p,
+                                 penalties, static_cast<float>(alpha_presence), static_cast<float>(alpha_frequency),
+                                 static_cast<float>(alpha_decay), ids_dev.p, ids.data(), stream_));
+  return ids;
+}
+
 void B200ModelBackend::copy_state_slice(const GenerationState& src, int src_offset, GenerationState& dst, int dst_offset,
                                         int count) const {
   if (src.wkv32 != dst.wkv32 || src.wkv32 != use_wkv32_) throw std::runtime_error("state slice wkv precision mismatch");

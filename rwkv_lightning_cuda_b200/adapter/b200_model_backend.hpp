@@ -8,6 +8,7 @@
 #pragma once
 
 #include <string>
+#include <vector>
 
 #include "rwkv_server_backend.hpp"  // from the reference tree
 
@@ -28,6 +29,12 @@ class B200ModelBackend final : public IModelBackend {
   void forward_prefill(const std::vector<std::vector<int64_t>>& token_batches, GenerationState& state,
                        DeviceLogits& logits) const override;
   void forward_decode(const std::vector<int64_t>& token_batch, GenerationState& state, DeviceLogits& logits) const override;
+  // Not part of IModelBackend: `steps` decode steps with the sampler's greedy case (top_p == 0,
+  // src/utils/sampling.cu:507-512) applied on the device after each one; returns the ids [steps][B].  `penalties` is the
+  // sampler state's device array fp32 [B][vocab] (src/rwkv_sampler.cpp:47-111 passes the same one to its kernel) or null.
+  std::vector<int> decode_greedy(const std::vector<int64_t>& token_batch, int steps, GenerationState& state,
+                                 DeviceLogits& logits, float* penalties, double alpha_presence, double alpha_frequency,
+                                 double alpha_decay) const;
   void copy_state_slice(const GenerationState& src, int src_offset, GenerationState& dst, int dst_offset,
                         int count) const override;
   void copy_logits_slice(const DeviceLogits& src, int src_offset, DeviceLogits& dst, int dst_offset,
