@@ -33,6 +33,37 @@ class ModelDims:
         return self.channels // 64
 
 
+def infer_model_dims(shapes: Dict[str, Sequence[int]]) -> ModelDims:
+    """Model dimensions from a checkpoint's tensor names and shapes, by the reference's rule
+    (infer_model_dims, include/rwkv7_fast_v4_common.hpp:262-288; LoRA ranks from the shapes as in
+    src/rwkv7_fast_v4.cu:1168-1171).  Raises ValueError with the reference's messages."""
+    vocab = channels = heads = head_size = ffn = layers = 0
+    for name, shape in shapes.items():
+        shape = tuple(shape)
+        if name == "emb.weight" and len(shape) == 2:
+            vocab, channels = shape
+        elif name == "blocks.0.att.r_k" and len(shape) == 2:
+            heads, head_size = shape
+        elif name == "blocks.0.ffn.key.weight" and len(shape) == 2:
+            ffn = shape[0]
+        if name.startswith("blocks."):
+            idx = name[7:].split(".", 1)
+            if len(idx) == 2 and idx[0].isdigit():
+                layers = max(layers, int(idx[0]) + 1)
+    if not (layers > 0 and channels > 0 and heads > 0 and head_size > 0 and vocab > 0 and ffn > 0):
+        raise ValueError("could not infer model dimensions")
+    if channels != heads * head_size:
+        raise ValueError("C must equal H*N")
+    if head_size != 64:
+        raise ValueError("current kernels require head size 64")
+
+    def rank(name, default):
+        shape = tuple(shapes.get(name, ()))
+        return int(shape[1]) if len(shape) == 2 else default
+    return ModelDims(layers, channels, ffn, vocab, rank("blocks.0.att.w1", 0), rank("blocks.0.att.a1", 0),
+                     rank("blocks.1.att.v1", 8), rank("blocks.0.att.g1", 0))    # one layer: the value residual is unused
+
+
 class GenerationState:
     """Mirror of rwkv7_server::GenerationState: the four device buffers and their layouts."""
 
@@ -94,6 +125,22 @@ class ModelBackend:
             self.set_tensor(name, t)
         if finalize:
             self.finalize()
+
+    @classmethod
+    def from_pth(cls, model_path: str, use_wkv32: bool = False, weight_format: int = L.FMT_F16, **kw) -> "ModelBackend":
+        """The reference's constructor (ModelBackend(model_path, use_wkv32, ...), include/rwkv_server_backend.hpp:106-109):
+        reads a torch ``.pth`` checkpoint with the reference's tensor names (bf16 or fp16), infers the dimensions as
+        the reference does and uploads tensor by tensor; layer 0's unused v0/v1/v2 are skipped
+        (include/rwkv7_fast_v4_common.hpp:323-328)."""
+        ck = torch.load(model_path, map_location="cpu", mmap=True, weights_only=True)
+        dims = infer_model_dims({k: tuple(v.shape) for k, v in ck.items()})
+        self = cls(dims, None, use_wkv32=use_wkv32, weight_format=weight_format, model_path=model_path, finalize=False, **kw)
+        for name, t in ck.items():
+            if name in ("blocks.0.att.v0", "blocks.0.att.v1", "blocks.0.att.v2"):
+                continue
+            self.set_tensor(name, t)
+        self.finalize()
+        return self
 
     def finalize(self) -> None:
         """Builds the device layouts once every tensor has been set (streaming loaders call

@@ -75,3 +75,20 @@ def test_adapter_compiles_against_the_unmodified_reference_headers():
            os.path.join(ROOT, "rwkv_lightning_cuda_b200", "adapter", "b200_model_backend.cpp")]
     res = subprocess.run(cmd, capture_output=True, text=True)
     assert res.returncode == 0, res.stderr
+
+
+def test_infer_model_dims_follows_the_reference_rule():
+    """Dimensions and LoRA ranks come from the checkpoint's tensor shapes as in the reference
+    (include/rwkv7_fast_v4_common.hpp:262-288); its three failure messages are kept."""
+    from rwkv_lightning_cuda_b200 import backend as bk, synthetic
+    d = bk.ModelDims(3, 128, 512, 320, 32, 24, 16, 64)
+    shapes = synthetic.tensor_shapes(d)
+    assert bk.infer_model_dims(shapes) == d
+    one = {k: v for k, v in shapes.items() if not k.startswith(("blocks.1.", "blocks.2."))}
+    assert bk.infer_model_dims(one) == bk.ModelDims(1, 128, 512, 320, 32, 24, 8, 64)
+    with pytest.raises(ValueError, match="could not infer model dimensions"):
+        bk.infer_model_dims({k: v for k, v in shapes.items() if k != "emb.weight"})
+    with pytest.raises(ValueError, match="C must equal H\\*N"):
+        bk.infer_model_dims({**shapes, "blocks.0.att.r_k": (3, 64)})
+    with pytest.raises(ValueError, match="head size 64"):
+        bk.infer_model_dims({**shapes, "blocks.0.att.r_k": (4, 32)})

@@ -246,3 +246,28 @@ def test_decode_greedy_argument_errors():
     with pytest.raises(L.Rwkv7B200Error, match="state batch size mismatch"):
         gm.decode_greedy([1, 2, 3], 2, st, lg)
     assert int(st.elapsed.sum()) == 0          # nothing ran
+
+
+def test_from_pth_loads_a_bf16_checkpoint_like_the_reference_constructor(tmp_path):
+    """A torch .pth file with the reference's tensor names in bf16 (the format its loader accepts): dimensions are
+    inferred from the shapes, layer 0's unused value-residual tensors are skipped, and the logits equal those of a
+    model given the same tensors directly."""
+    from rwkv_lightning_cuda_b200 import backend as bk, synthetic
+    d = bk.ModelDims(**TINY)
+    ck = {k: v.to(torch.bfloat16) for k, v in synthetic.make_checkpoint(d, seed=3, device="cpu", dtype=torch.float16).items()}
+    ck["blocks.0.att.v0"] = torch.zeros(d.channels, dtype=torch.bfloat16)          # present in real files, never used
+    ck["blocks.0.att.v1"] = torch.zeros((d.channels, d.rank_v), dtype=torch.bfloat16)
+    ck["blocks.0.att.v2"] = torch.zeros((d.rank_v, d.channels), dtype=torch.bfloat16)
+    path = str(tmp_path / "tiny.pth")
+    torch.save(ck, path)
+    a = bk.ModelBackend.from_pth(path)
+    assert a.dims == d and a.model_path() == path
+    b = bk.ModelBackend(d, {k: v for k, v in ck.items() if k not in ("blocks.0.att.v0", "blocks.0.att.v1", "blocks.0.att.v2")})
+    toks = [[1, 2, 3, 4, 5], [9, 8, 7, 6, 5]]
+    outs = []
+    for m in (a, b):
+        st = m.create_state(2); lg = bk.DeviceLogits()
+        m.forward_prefill(toks, st, lg)
+        m.forward_decode([11, 12], st, lg)
+        outs.append(lg.values.clone())
+    assert torch.isfinite(outs[0]).all() and torch.equal(outs[0], outs[1])
