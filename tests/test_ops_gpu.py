@@ -126,7 +126,9 @@ def test_head_gates(ops, rows, H):
 
 
 @pytest.mark.parametrize("M,K,N", [(1, 768, 768), (2, 2560, 96), (4, 64, 768), (3, 4096, 130), (1, 3072, 768), (6, 256, 64),
-                                   (128, 768, 768), (300, 1024, 640), (17, 96, 96), (256, 4096, 256)])
+                                   (128, 768, 768), (300, 1024, 640), (17, 96, 96), (256, 4096, 256),
+                                   # 65 .. 128 rows, ragged N, K long enough for split-K
+                                   (65, 256, 260), (100, 4096, 520), (128, 2048, 132), (96, 64, 1024)])
 def test_linear_fp16(ops, M, K, N):
     from rwkv_lightning_cuda_b200 import lib as L
     rng = np.random.default_rng(M * 7 + N)
