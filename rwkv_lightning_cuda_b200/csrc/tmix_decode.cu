@@ -91,6 +91,15 @@ __global__ void __launch_bounds__(256) tmix_decode_kernel(const TmixDev p) {
     }
   }
   cp_async_commit();
+  // This head's per-channel parameters are static too: requested here, used far down the dependent chain (read where
+  // they are used, each cost a DRAM round trip in the middle of it -- between two steps the 14 GB of weights pass
+  // through L2, so none of them is still cached).
+  half c_v0 = __float2half_rn(0.f), c_kk = c_v0, c_w0 = c_v0, c_a0 = c_v0, c_ka = c_v0, c_rk = c_v0, c_lw = c_v0, c_lb = c_v0;
+  if (tid < kHead) {
+    const int c = h * kHead + tid;
+    if (!p.layer0) c_v0 = p.v0[c];
+    c_kk = p.k_k[c]; c_w0 = p.w0[c]; c_a0 = p.a0[c]; c_ka = p.k_a[c]; c_rk = p.r_k[c]; c_lw = p.lnx_w[c]; c_lb = p.lnx_b[c];
+  }
 
   pdl_wait();
   pdl_trigger();
@@ -113,7 +122,9 @@ __global__ void __launch_bounds__(256) tmix_decode_kernel(const TmixDev p) {
     }
   }
   float kf = 0.f, vf = 0.f, vfirstf = 0.f;
+  int elapsed_b = 0;
   if (tid < kHead) {
+    elapsed_b = p.elapsed[b_id];
     hv[0][tid] = p.r[tok + tid];
     kf = __half2float(p.k[tok + tid]);
     vf = __half2float(p.v[tok + tid]);
@@ -155,20 +166,20 @@ __global__ void __launch_bounds__(256) tmix_decode_kernel(const TmixDev p) {
       v_use = vf;
     } else {
       if (p.round_act) {
-        const float gate = sigmoid_fast(__half2float(p.v0[c]) + __half2float(__float2half_rn(res[3][tid])));
+        const float gate = sigmoid_fast(__half2float(c_v0) + __half2float(__float2half_rn(res[3][tid])));
         v_use = __half2float(__float2half_rn(fmaf(vfirstf - vf, gate, vf)));
       } else {
-        const float gate = 1.0f / (1.0f + expf(-(__half2float(p.v0[c]) + res[3][tid])));
+        const float gate = 1.0f / (1.0f + expf(-(__half2float(c_v0) + res[3][tid])));
         v_use = __half2float(__float2half_rn(vf + (vfirstf - vf) * gate));
       }
     }
     hv[5][tid] = __float2half_rn(v_use);
-    const float u = kf * __half2float(p.k_k[c]);
+    const float u = kf * __half2float(c_kk);
     const float ss = warp_sum(u * u);
     if (lane == 0) red[warp] = ss;
     // decay pre-activation
     float wf = __half2float(w12);
-    const float w0f = __half2float(p.w0[c]);
+    const float w0f = __half2float(c_w0);
     float d;
     if (kWkv32) {
       wf = __half2float(__float2half_rn(wf + w0f));  // the reference pre-adds w0 and rounds for the fp32 state
@@ -176,13 +187,13 @@ __global__ void __launch_bounds__(256) tmix_decode_kernel(const TmixDev p) {
       acts[tid] = d;                                  // fp32 decay, reuses the activation buffer
     } else {
       wf += w0f;
-      const int rot = static_cast<int>(2654435769u * static_cast<unsigned>(p.elapsed[b_id] + c));
+      const int rot = static_cast<int>(2654435769u * static_cast<unsigned>(elapsed_b + c));
       d = exp2f(kNegExpHalfLog2e / (1.0f + exp2f(kNegLog2e * wf))) - 1.0f + kTwoNeg41 * static_cast<float>(rot);
       hv[1][tid] = __float2half_rn(d);
     }
     // kk / a / k' need the head-wide norm: finish after the barrier below
     acts[512 + tid] = u;
-    acts[1024 + tid] = sigmoid_fast(__half2float(p.a0[c]) + __half2float(a12));
+    acts[1024 + tid] = sigmoid_fast(__half2float(c_a0) + __half2float(a12));
   }
   __syncthreads();
   if (tid < kHead) {
@@ -190,7 +201,7 @@ __global__ void __launch_bounds__(256) tmix_decode_kernel(const TmixDev p) {
     const float inv_d = 1.0f / fmaxf(sqrtf(red[0] + red[1]), 1.0e-12f);
     const float kk = acts[512 + tid] * inv_d;
     const float av = acts[1024 + tid];
-    const float ka = __half2float(p.k_a[c]);
+    const float ka = __half2float(c_ka);
     hv[2][tid] = __float2half_rn(kf * fmaf(av, ka, 1.0f - ka));
     hv[3][tid] = __float2half_rn(-kk);
     hv[4][tid] = __float2half_rn(kk * av);
@@ -290,7 +301,7 @@ __global__ void __launch_bounds__(256) tmix_decode_kernel(const TmixDev p) {
     const float mean = (red[0] + red[1]) * (1.0f / 64.0f);
     dmean = yv - mean;
     const float ss = warp_sum(dmean * dmean);
-    const float dot = warp_sum(__half2float(hv[0][tid]) * __half2float(hv[2][tid]) * __half2float(p.r_k[h * kHead + tid]));
+    const float dot = warp_sum(__half2float(hv[0][tid]) * __half2float(hv[2][tid]) * __half2float(c_rk));
     if (lane == 0) {
       red[2 + warp] = ss;
       acts[1536 + warp] = dot;
@@ -301,7 +312,7 @@ __global__ void __launch_bounds__(256) tmix_decode_kernel(const TmixDev p) {
     const int c = h * kHead + tid;
     const float rstd = rsqrtf((red[2] + red[3]) * (1.0f / 64.0f) + 64.0e-5f);
     const float rkv = acts[1536] + acts[1537];
-    const float out = (dmean * rstd * __half2float(p.lnx_w[c]) + __half2float(p.lnx_b[c]) + rkv * v_use) * __half2float(hv[6][tid]);
+    const float out = (dmean * rstd * __half2float(c_lw) + __half2float(c_lb) + rkv * v_use) * __half2float(hv[6][tid]);
     p.y2[tok + tid] = __float2half_rn(out);
   }
 }
