@@ -117,7 +117,32 @@ __global__ void __launch_bounds__(kW * 32) gemv_tma_kernel(const GemvBatch p, in
 #pragma unroll
   for (int m = 0; m < kM; ++m) acc0[m] = acc1[m] = 0.f;
   int slot = 0, phase = 0, pp = rot, part = 0, row = r_begin;
+  // Quantisation parameters are requested ahead of their use (read where they are used they cost a cache-miss round
+  // trip per piece): W8A16 -- the row's scale when the row begins; W4A16 -- lane g holds (scale, zero) of group g
+  // (and g + 32) of a piece, loaded one piece ahead, and hands them out by shuffle.
+  float row_scale = 1.f;
+  uint32_t sz_cur[2] = {0u, 0u}, sz_next[2] = {0u, 0u};
+  const int groups = kQuant && fmt == 2 ? piece >> 6 : 0;  // 128 weights = 64 bytes per group
+  auto load_sz = [&](int r, int part_idx, uint32_t (&dst)[2]) {
+    const size_t g0 = static_cast<size_t>(r) * (K >> 7) + static_cast<size_t>(part_idx) * groups;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int g = lane + 32 * i;
+      if (g < groups) {
+        const __half2 pk = __halves2half2(sg.scale[g0 + g], sg.zero[g0 + g]);
+        dst[i] = *reinterpret_cast<const uint32_t*>(&pk);
+      }
+    }
+  };
+  if (kQuant && total > 0) {
+    if (fmt == 1) row_scale = __half2float(sg.scale[row]);
+    if (fmt == 2) load_sz(row, pp, sz_cur);
+  }
   for (int pc = 0; pc < total; ++pc) {
+    if (kQuant && fmt == 2 && pc + 1 < total) {  // the piece after this one: next part of the row, or the next row
+      int npp = pp + 1 == parts ? 0 : pp + 1;
+      load_sz(part + 1 == parts ? row + 1 : row, npp, sz_next);
+    }
     const uint32_t bar = smem_u32(&bars[warp][slot]);
     if (!mbar_try_wait(bar, phase) && !mbar_wait(bar, phase)) {
       if (lane == 0) atomicExch(&g_gemv_timeout, 1);
@@ -167,22 +192,24 @@ __global__ void __launch_bounds__(kW * 32) gemv_tma_kernel(const GemvBatch p, in
         }
       } else {
         const int k_piece = pp * piece * 2;  // two weights per byte
-        const half* srow = sg.scale + static_cast<size_t>(row) * (K >> 7);
-        const half* zrow = sg.zero + static_cast<size_t>(row) * (K >> 7);
 #pragma unroll 2
-        for (int wd = lane; wd < words; wd += 32) {
+        for (int w0 = 0; w0 < words; w0 += 32) {  // uniform trip count: every lane takes part in the shuffle
+          const int wd = w0 + lane;
+          const int gi = wd >> 4;                  // 16 words = 128 weights = one group
+          const uint32_t pk = __shfl_sync(0xffffffffu, (w0 >> 9) ? sz_cur[1] : sz_cur[0], gi & 31);
+          if (wd >= words) continue;
+          const __half2 sz = *reinterpret_cast<const __half2*>(&pk);
           const uint32_t u = wsm32[wd];
           const int k = k_piece + wd * 8;
-          const __half2 zb = __float2half2_rn(1024.f + __half2float(zrow[k >> 7]));
-          const __half2 s2 = __half2half2(srow[k >> 7]);
+          const __half2 zb = __float2half2_rn(1024.f + __high2float(sz));
+          const __half2 s2 = __half2half2(__low2half(sz));
           float wf[8];
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {  // byte j holds elements 2j (low nibble) and 2j+1 (high nibble)
-            const uint32_t byte = (u >> (8 * j)) & 0xffu;
-            uint32_t pair = (byte & 0xfu) | ((byte >> 4) << 16) | 0x64006400u;
+          for (int j = 0; j < 4; ++j) {  // nibble n of the word is element n: a shift and one mask give elements (j, j + 4)
+            uint32_t pair = ((u >> (4 * j)) & 0x000f000fu) | 0x64006400u;  // 1024 + q in both halves
             const float2 f = __half22float2(__hmul2(__hsub2(*reinterpret_cast<__half2*>(&pair), zb), s2));
-            wf[2 * j] = f.x;
-            wf[2 * j + 1] = f.y;
+            wf[j] = f.x;
+            wf[j + 4] = f.y;
           }
 #pragma unroll
           for (int m = 0; m < kM; ++m) {
@@ -201,6 +228,7 @@ __global__ void __launch_bounds__(kW * 32) gemv_tma_kernel(const GemvBatch p, in
       issue();
       if (q_left == 0) prefetch_next();
     }
+    if (kQuant && fmt == 2) { sz_cur[0] = sz_next[0]; sz_cur[1] = sz_next[1]; }
     if (++slot == n_slots) { slot = 0; phase ^= 1; }
     if (++pp == parts) pp = 0;
     if (++part == parts) {
@@ -208,11 +236,12 @@ __global__ void __launch_bounds__(kW * 32) gemv_tma_kernel(const GemvBatch p, in
 #pragma unroll
       for (int m = 0; m < kM; ++m) {
         float a = warp_sum(acc0[m] + acc1[m]);
-        if (kQuant && fmt == 1) a *= __half2float(sg.scale[row]);  // W8A16: one scale per output channel
+        if (kQuant && fmt == 1) a *= row_scale;  // W8A16: one scale per output channel
         if (lane == 0) store_result(sg, m, row, a);
         acc0[m] = acc1[m] = 0.f;
       }
       ++row;
+      if (kQuant && fmt == 1 && pc + 1 < total) row_scale = __half2float(sg.scale[row]);
     }
   }
 }
@@ -230,7 +259,8 @@ bool gemv_tma_plan(GemvBatch& b, int M, size_t* smem_bytes, int* grid, int* n_sl
     const int row_bytes = g.fmt == 0 ? g.K * 2 : g.fmt == 1 ? g.K : g.K / 2;
     if (row_bytes % 16 != 0) return false;
     int parts = (row_bytes + kPieceCap - 1) / kPieceCap;
-    while (parts <= 64 && (row_bytes % (parts * 16) != 0)) ++parts;
+    const int unit = g.fmt == 2 ? 64 : 16;  // W4A16: a piece holds whole quantisation groups (64 bytes each)
+    while (parts <= 64 && (row_bytes % (parts * unit) != 0)) ++parts;
     if (parts > 64) return false;
     g.parts = parts;
     g.piece_bytes = row_bytes / parts;
@@ -260,7 +290,8 @@ bool gemv_tma_plan(GemvBatch& b, int M, size_t* smem_bytes, int* grid, int* n_sl
     GemvSeg& g = b.seg[i];
     const int row_bytes = g.fmt == 0 ? g.K * 2 : g.fmt == 1 ? g.K : g.K / 2;
     int parts = (row_bytes + cap - 1) / cap;
-    while (parts <= 256 && (row_bytes % (parts * 16) != 0)) ++parts;
+    const int unit = g.fmt == 2 ? 64 : 16;
+    while (parts <= 256 && (row_bytes % (parts * unit) != 0)) ++parts;
     if (parts > 256) return false;
     g.parts = parts;
     g.piece_bytes = row_bytes / parts;
