@@ -105,12 +105,37 @@ __global__ void __launch_bounds__(256) tmix_decode_kernel(const TmixDev p) {
   pdl_trigger();
   if (p.shift_src && tid < kHead / 2)
     reinterpret_cast<__half2*>(p.shift_dst + tok)[tid] = reinterpret_cast<const __half2*>(p.shift_src + tok)[tid];
+  // ---- everything the previous kernel wrote is requested at once (ranks are at most 512: two values per thread and
+  // matrix); taken one matrix after the other, each load would wait for the previous one's shared-memory store
+  half raw[4][2];
+#pragma unroll
+  for (int s = 0; s < 4; ++s) {
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const int i = tid + 256 * j;
+      raw[s][j] = __float2half_rn(0.f);
+      if (!(p.layer0 && s == 3) && i < p.R[s]) raw[s][j] = p.l1[s][static_cast<size_t>(b_id) * p.R[s] + i];
+    }
+  }
+  float kf = 0.f, vf = 0.f, vfirstf = 0.f;
+  int elapsed_b = 0;
+  half r_in = __float2half_rn(0.f);
+  if (tid < kHead) {
+    elapsed_b = p.elapsed[b_id];
+    r_in = p.r[tok + tid];
+    kf = __half2float(p.k[tok + tid]);
+    vf = __half2float(p.v[tok + tid]);
+    vfirstf = __half2float(p.v_first[tok + tid]);
+  }
   // ---- LoRA inputs with their activations, kept in fp32
 #pragma unroll
   for (int s = 0; s < 4; ++s) {
     if (p.layer0 && s == 3) continue;
-    for (int i = tid; i < p.R[s]; i += 256) {
-      float x = __half2float(p.l1[s][static_cast<size_t>(b_id) * p.R[s] + i]);
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const int i = tid + 256 * j;
+      if (i >= p.R[s]) continue;
+      float x = __half2float(raw[s][j]);
       if (p.round_act) {  // what the separate activation kernels of the many-row path produce
         if (s == 0) x = __half2float(__float2half_rn(apply_in_act(x, kActTanh)));
         if (s == 2) x = __half2float(__float2half_rn(apply_in_act(x, kActSigmoid)));
@@ -121,15 +146,7 @@ __global__ void __launch_bounds__(256) tmix_decode_kernel(const TmixDev p) {
       acts[s * 512 + i] = x;
     }
   }
-  float kf = 0.f, vf = 0.f, vfirstf = 0.f;
-  int elapsed_b = 0;
-  if (tid < kHead) {
-    elapsed_b = p.elapsed[b_id];
-    hv[0][tid] = p.r[tok + tid];
-    kf = __half2float(p.k[tok + tid]);
-    vf = __half2float(p.v[tok + tid]);
-    vfirstf = __half2float(p.v_first[tok + tid]);
-  }
+  if (tid < kHead) hv[0][tid] = r_in;
   cp_async_wait<0>();
   __syncthreads();
   if (!mbar_wait(smem_u32(&wbar), 0)) {  // uniform: every thread waits on the same barrier
