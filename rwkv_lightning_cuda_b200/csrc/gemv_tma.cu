@@ -33,8 +33,10 @@ __device__ __forceinline__ void fma_chunk(const uint4& q, const float* x, float&
 }
 
 // kQuant: some problem of the launch has int8 / int4 weights (the fp16-only instantiation carries no dequant code).
+// One CTA per SM by design (the rings take most of the shared memory): saying so in the launch bounds lets the compiler
+// spend registers on keeping more weight chunks in flight per lane (2.94 -> 2.86 ms per 7.2B decode step).
 template <int kM, int kW, bool kQuant>
-__global__ void __launch_bounds__(kW * 32) gemv_tma_kernel(const GemvBatch p, int x_bytes, int n_slots, int slot_stride) {
+__global__ void __launch_bounds__(kW * 32, 1) gemv_tma_kernel(const GemvBatch p, int x_bytes, int n_slots, int slot_stride) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   __shared__ __align__(8) uint64_t bars[kW][kMaxSlots];
   __shared__ float red_scratch[kW];
