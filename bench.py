@@ -1,20 +1,26 @@
 """Benchmark of the RWKV-7 forward hot path: decode tokens/s on the 7.2B configuration.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--model 7.2B] [--batch 1]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
 One step = one decode forward of `batch` sequences (one new token each) through the whole model.
 Weights are random-init N(0, 0.02) of the named architecture, generated on the device; token ids
 are uniform random.  With N > 1 (torchrun, one rank per GPU) every rank runs an independent
 replica on its own sequences: the path shards by batch with no data-path collective, so the
 figure is weak scaling (batch per GPU fixed).  Prints ONE JSON line on rank 0.
+
+The headline (`value`, `e2e`, `roofline`) is the 7.2B fp16 model at B=1.  The same line carries, timed in the
+same run, the other workloads of the benchmark definition under their own keys: `b256` (7.2B, 256 sequences),
+`w8a16_1p5B` (B = 1, 8, 32, 64), `w4a16_2p9B_b256`, `prefill_16k` (7.2B, 16384 tokens in chunks of 128, fp32
+state) and, with N > 1, `tp_prefill` (the ranks as one head-sharded group, with a parity check of that path against
+the CPU oracle on a small model first).  `--only headline` skips them.  `check` compares a fixed short run's logits
+with what the reference arm (`--impl reference`, run before on the same machine) left for it.
 """
 import argparse
 import json
 import os
-import statistics
-import subprocess
 import sys
 import tempfile
+import threading
 import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
@@ -24,50 +30,68 @@ import numpy as np
 import torch
 import torch.distributed as dist
 
+HANDOFF = os.path.join(ROOT, ".bench_handoff")     # the reference arm leaves its check logits here for the other arm
+CHECK_PROMPT = [11, 4099, 65000, 7]                # fixed ids of the correctness run: a 4-token chunk ...
+CHECK_NEXT = 123                                   # ... and one decode step
+
 
 def measured_peaks():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
         d = json.load(open(p))
-        return float(d["hbm_gbs"]), "measured"
-    return 6650.0, "fallback"
+        return float(d["hbm_gbs"]), float(d.get("bf16_tflops_sustained", 1400.0)), "measured"
+    return 6650.0, 1400.0, "fallback"
 
 
 class ClockSampler:
-    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
-         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    """SM clock and throttle reasons of one GPU, read through NVML every 20 ms on a host thread while a timed region
+    runs (reading only; nothing is set)."""
 
     def __init__(self, index):
-        self.f = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        self.rows = []
+        self.stop_flag = threading.Event()
+        self.max_mhz = None
+        self.thread = None
         try:
-            self.p = subprocess.Popen(["nvidia-smi", f"--id={index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100"],
-                                      stdout=self.f, stderr=subprocess.DEVNULL)
+            import pynvml
+            self.nv = pynvml
+            pynvml.nvmlInit()
+            vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+            phys = int(vis.split(",")[index]) if vis and all(v.strip().isdigit() for v in vis.split(",")) else index
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(phys)
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM))
+            self.thread = threading.Thread(target=self._run, daemon=True)
+            self.thread.start()
         except Exception:
-            self.p = None
+            self.thread = None
+
+    def _run(self):
+        nv = self.nv
+        while not self.stop_flag.is_set():
+            try:
+                self.rows.append((nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM),
+                                  nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                                  if hasattr(nv, "nvmlDeviceGetCurrentClocksEventReasons")
+                                  else nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)))
+            except Exception:
+                pass
+            time.sleep(0.02)
 
     def stop(self):
-        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
-        if self.p is None:
+        out = {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "samples": 0}
+        if self.thread is None:
             return out
-        self.p.terminate()
-        try:
-            self.p.wait(timeout=5)
-        except Exception:
-            self.p.kill()
-        self.f.flush()
-        rows = [l.strip().split(", ") for l in open(self.f.name) if l.strip()]
-        os.unlink(self.f.name)
-        rows = [r for r in rows if len(r) >= 9]
-        if not rows:
+        self.stop_flag.set()
+        self.thread.join(timeout=2)
+        if not self.rows:
             return out
-        sm = [float(r[1]) for r in rows if r[1].replace(".", "").isdigit()]
-        out["sm_mhz"] = statistics.median(sm) if sm else None
-        out["sm_max_mhz"] = float(rows[0][2]) if rows[0][2].replace(".", "").isdigit() else None
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for i, n in enumerate(names):
-            if any(r[5 + i].strip() == "Active" for r in rows):
-                out["reasons"].append(n)
-        out["samples"] = len(rows)
+        clocks = sorted(r[0] for r in self.rows)
+        out["sm_mhz"] = float(clocks[len(clocks) // 2])
+        out["samples"] = len(clocks)
+        bits = {"hw_slowdown": 0x8, "sw_power_cap": 0x4, "sw_thermal_slowdown": 0x20, "hw_thermal_slowdown": 0x40}
+        for name, bit in bits.items():
+            if any(r[1] & bit for r in self.rows):
+                out["reasons"].append(name)
         return out
 
 
@@ -92,8 +116,15 @@ def algorithmic_bytes(d, B, wkv32, fmt):
     return wbytes + B * (state + act), wbytes, state
 
 
-def max_over_ranks(values, world, device):
-    """Per-rank step times -> the slowest rank's (what a whole-job rate must be computed from)."""
+def step_flops(d, rows, heads_rows):
+    """Multiply-adds x 2 of the dense products of one forward: `rows` rows through the layers, `heads_rows` through the head."""
+    C, F = d.channels, d.ffn
+    p_layer = 4 * C * C + 2 * C * F + 2 * C * (d.rank_w + d.rank_a + d.rank_g + d.rank_v)
+    return 2.0 * (p_layer * d.layers * rows + d.vocab * C * heads_rows)
+
+
+def max_over_ranks(values, world, device="cuda"):
+    """Per-rank times -> the slowest rank's (what a whole-job rate must be computed from)."""
     t = torch.tensor(values, device=device, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -105,18 +136,24 @@ def whole_job_rate(world, batch_per_gpu, ms_per_step):
     return world * batch_per_gpu / (ms_per_step * 1e-3)
 
 
-def build_model(args, dev_index, seed, tp_rank=0, tp_size=1):
+def barrier(world):
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+
+
+def build_model(model, fmt_name, wkv32, dev_index, seed, tp_rank=0, tp_size=1, layers=0, vocab=0):
     from rwkv_lightning_cuda_b200 import backend as bk, synthetic, lib as L
-    d = synthetic.CONFIGS[args.model]
-    if args.layers or args.vocab:          # reduced-depth timing aid for per-layer work; never a bench line
-        d = bk.ModelDims(args.layers or d.layers, d.channels, d.ffn, args.vocab or d.vocab, d.rank_w, d.rank_a, d.rank_v, d.rank_g)
-    fmt = {"f16": L.FMT_F16, "w8a16": L.FMT_W8A16, "w4a16": L.FMT_W4A16}[args.fmt]
+    d = synthetic.CONFIGS[model]
+    if layers or vocab:          # reduced-depth timing aid for per-layer work; never a bench line
+        d = bk.ModelDims(layers or d.layers, d.channels, d.ffn, vocab or d.vocab, d.rank_w, d.rank_a, d.rank_v, d.rank_g)
+    fmt = {"f16": L.FMT_F16, "w8a16": L.FMT_W8A16, "w4a16": L.FMT_W4A16}[fmt_name]
     ident = None
     if tp_size > 1:                       # rank 0 makes the communicator id, the others receive it
         box = [bk.tp_unique_id() if tp_rank == 0 else None]
         dist.broadcast_object_list(box, src=0)
         ident = box[0]
-    gm = bk.ModelBackend(d, None, use_wkv32=bool(args.wkv32), weight_format=fmt, device=dev_index, finalize=False,
+    gm = bk.ModelBackend(d, None, use_wkv32=bool(wkv32), weight_format=fmt, device=dev_index, finalize=False,
                          tp_rank=tp_rank, tp_size=tp_size, tp_unique_id=ident)
     gen = torch.Generator(device="cuda")
     gen.manual_seed(seed)
@@ -129,12 +166,12 @@ def build_model(args, dev_index, seed, tp_rank=0, tp_size=1):
     return d, gm, fmt
 
 
-def cpu_baseline(args):
+def cpu_baseline(model, wkv32):
     """The CPU oracle timed on this host's cores: 2 layers + lm-head of one B=1 decode token of the
     same architecture, layer time extrapolated to the full depth."""
     from oracle import oracle as orc
     from rwkv_lightning_cuda_b200 import backend as bk, synthetic
-    full = synthetic.CONFIGS[args.model]
+    full = synthetic.CONFIGS[model]
     vocab = min(full.vocab, 8192)      # the table is only gathered from; the head is timed on its own
     d = bk.ModelDims(2, full.channels, full.ffn, vocab, full.rank_w, full.rank_a, full.rank_v, full.rank_g)
     ck = synthetic.make_checkpoint(d, seed=0, device="cpu")
@@ -144,7 +181,7 @@ def cpu_baseline(args):
         if name in ("emb.weight", "blocks.0.ln0.weight", "blocks.0.ln0.bias"):
             continue
         om.set(name, t.numpy())
-    shift, wkv, elapsed = om.new_state(1, bool(args.wkv32))
+    shift, wkv, elapsed = om.new_state(1, bool(wkv32))
     om.forward(np.array([[1]]), shift, wkv, elapsed)
     t0 = time.perf_counter(); reps = 2
     for i in range(reps):
@@ -158,68 +195,171 @@ def cpu_baseline(args):
     t_token = per_layer * full.layers + t_head_small * (full.vocab / vocab)
     cores = os.cpu_count() or 1
     return {"value": 1.0 / t_token, "unit": "tok/s", "cores": cores, "kind": "port",
-            "sample": f"2 of {full.layers} layers + lm-head rows of one B=1 decode token of {args.model}, extrapolated to full depth and vocab"}
+            "sample": f"2 of {full.layers} layers + lm-head rows of one B=1 decode token of {model}, extrapolated to full depth and vocab"}
 
 
-def run_ours(args, rank, world, local_rank):
+def check_logits_ours(gm, d):
+    """The fixed short run both arms make from a zero state: a 4-token chunk, then one decode step."""
     from rwkv_lightning_cuda_b200 import backend as bk
-    hbm_peak, peak_kind = measured_peaks()
-    d, gm, fmt = build_model(args, local_rank, seed=rank)
-    B = args.batch
+    st = gm.create_state(1)
+    lg = bk.DeviceLogits()
+    gm.forward_prefill([[t % d.vocab for t in CHECK_PROMPT]], st, lg)
+    gm.forward_decode([CHECK_NEXT % d.vocab], st, lg)
+    return lg.values[0].cpu().numpy()
+
+
+def correctness_check(gm, d, model, wkv32):
+    path = os.path.join(HANDOFF, f"ref_logits_{model}_{int(bool(wkv32))}.npy")
+    mine = check_logits_ours(gm, d)
+    if not os.path.exists(path):
+        return {"against": None, "note": "no logits from the reference arm on this machine (run bench.py --impl reference first)",
+                "finite": bool(np.isfinite(mine).all())}
+    ref = np.load(path)
+    if ref.shape != mine.shape:
+        return {"against": None, "note": "the reference arm ran another configuration"}
+    top2 = np.sort(ref)[-2:]
+    return {"against": "reference arm on this machine: same seeded checkpoint, 4-token chunk + 1 decode step from a zero state",
+            "max_abs_diff": float(np.abs(mine - ref).max()), "argmax_equal": bool(mine.argmax() == ref.argmax()),
+            "ref_top2_margin": float(top2[1] - top2[0]), "max_abs_logit": float(np.abs(ref).max()), "tolerance": 2e-2}
+
+
+def time_decode(gm, d, B, steps, warmup, world, rank, e2e=True, greedy=True):
+    """Device-timed decode steps (graph replays, CUDA events on the launching stream), then the same steps through
+    the host-buffer call and through the on-device greedy loop (wall clock, synchronised)."""
+    from rwkv_lightning_cuda_b200 import backend as bk
     st = gm.create_state(B)
     lg = bk.DeviceLogits()
     rng = np.random.default_rng(1234 + rank)
-    total = args.warmup + args.steps
+    total = warmup + steps
     toks = torch.from_numpy(rng.integers(0, d.vocab, (2 * total + 8, B, 1)))
     stream = torch.cuda.Stream()
-    out_host = torch.empty((B, d.vocab), dtype=torch.float32).pin_memory()
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
+    out = {}
     with torch.cuda.stream(stream):
-        for i in range(args.warmup):                                            # also makes the state non-zero
+        for i in range(warmup):                                            # also makes the state non-zero
             gm._forward(toks[1 + i], st, lg, sync=False)
-        barrier()
-        sampler = ClockSampler(local_rank)
+        barrier(world)
         launches0 = gm.kernel_launches()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record(stream)
-        for i in range(args.steps):
-            gm._forward(toks[1 + args.warmup + i], st, lg, sync=False)
+        for i in range(steps):
+            gm._forward(toks[1 + warmup + i], st, lg, sync=False)
         e1.record(stream)
-        barrier()
-        ms = e0.elapsed_time(e1) / args.steps
-        launches = gm.kernel_launches() - launches0
-        # end to end through the host-buffer call: token ids in host memory in, logits in host memory out
-        for i in range(min(args.warmup, 3)):
-            gm.forward_to_host(toks[1 + total + i], st, lg, out_host)
-        barrier()
-        t0 = time.perf_counter()
-        for i in range(args.steps):
-            gm.forward_to_host(toks[1 + total + 3 + i], st, lg, out_host)
-        torch.cuda.synchronize()
-        e2e_ms = (time.perf_counter() - t0) * 1e3 / args.steps
-        # the same steps with the greedy choice of the next token on the device: first ids in, chosen ids out, one call
-        ids_host = torch.empty((args.steps, B), dtype=torch.int32).pin_memory()
-        gm.decode_greedy(toks[0].reshape(-1), min(args.warmup, 3), st, lg)
-        barrier()
-        launches_g0 = gm.kernel_launches()
-        t0 = time.perf_counter()
-        gm.decode_greedy(toks[0].reshape(-1), args.steps, st, lg, out_host=ids_host)
-        greedy_ms = (time.perf_counter() - t0) * 1e3 / args.steps
-        launches_g = gm.kernel_launches() - launches_g0
-        clocks = sampler.stop()
+        barrier(world)
+        out["ms"] = e0.elapsed_time(e1) / steps
+        out["launches"] = gm.kernel_launches() - launches0
+        if e2e:   # token ids in host memory in, logits in (pinned) host memory out, synchronised every step
+            out_host = torch.empty((B, d.vocab), dtype=torch.float32).pin_memory()
+            for i in range(min(warmup, 3)):
+                gm.forward_to_host(toks[1 + total + i], st, lg, out_host)
+            barrier(world)
+            t0 = time.perf_counter()
+            for i in range(steps):
+                gm.forward_to_host(toks[1 + total + 3 + i], st, lg, out_host)
+            torch.cuda.synchronize()
+            out["e2e_ms"] = (time.perf_counter() - t0) * 1e3 / steps
+            del out_host
+        if greedy:  # the greedy choice of the next token on the device: first ids in, chosen ids out, one call
+            ids_host = torch.empty((steps, B), dtype=torch.int32).pin_memory()
+            gm.decode_greedy(toks[0].reshape(-1), min(warmup, 3), st, lg)
+            barrier(world)
+            l0 = gm.kernel_launches()
+            t0 = time.perf_counter()
+            gm.decode_greedy(toks[0].reshape(-1), steps, st, lg, out_host=ids_host)
+            out["greedy_ms"] = (time.perf_counter() - t0) * 1e3 / steps
+            out["greedy_launches"] = gm.kernel_launches() - l0
+    del st, lg
+    return out
 
-    ms, e2e_ms, greedy_ms = max_over_ranks([ms, e2e_ms, greedy_ms], world, "cuda")
-    if rank != 0:
-        return
+
+def decode_entry(d, fmt, B, wkv32, t, world, hbm_peak, tf_peak):
+    """One secondary workload's figures."""
+    ms = t["ms"]
+    abytes, wbytes, sbytes = algorithmic_bytes(d, B, bool(wkv32), fmt)
+    gbs = abytes / (ms * 1e-3) / 1e9
+    tfs = step_flops(d, B, B) / (ms * 1e-3) / 1e12
+    e = {"value": whole_job_rate(world, B, ms), "unit": "tok/s", "ms_per_step": ms, "batch_per_gpu": B, "gpu_launches": int(t["launches"]),
+         "algorithmic_bytes_per_step": abytes, "hbm_gbs": gbs, "hbm_frac": gbs / hbm_peak, "tensor_tflops": tfs, "tensor_frac": tfs / tf_peak}
+    if "e2e_ms" in t:
+        e["e2e"] = {"value": whole_job_rate(world, B, t["e2e_ms"]), "unit": "tok/s", "ms_per_step": t["e2e_ms"],
+                    "h2d_bytes_per_step": B * 8, "d2h_bytes_per_step": B * d.vocab * 4}
+    if "greedy_ms" in t:
+        e["e2e_greedy"] = {"value": whole_job_rate(world, B, t["greedy_ms"]), "unit": "tok/s", "ms_per_step": t["greedy_ms"],
+                           "h2d_bytes_per_call": B * 8, "d2h_bytes_per_step": B * 4}
+    return e
+
+
+def time_prefill(gm, d, B, T, n_chunks, warmup, world, rank, same_tokens):
+    from rwkv_lightning_cuda_b200 import backend as bk
+    st = gm.create_state(B)
+    lg = bk.DeviceLogits()
+    rng = np.random.default_rng(99 if same_tokens else 99 + rank)
+    toks = torch.from_numpy(rng.integers(0, d.vocab, (n_chunks, B, T)))
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        for i in range(min(warmup, n_chunks)):
+            gm._forward(toks[i], st, lg, sync=False)
+        barrier(world)
+        launches0 = gm.kernel_launches()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for i in range(n_chunks):
+            gm._forward(toks[i], st, lg, sync=False)
+        e1.record(stream)
+        barrier(world)
+        ms = e0.elapsed_time(e1)
+        launches = gm.kernel_launches() - launches0
+    del st, lg
+    return ms, launches
+
+
+def prefill_entry(d, B, T, n_chunks, ms, launches, prompts, gpus_sharing, tf_peak):
+    tokens = prompts * n_chunks * T
+    flops = step_flops(d, tokens, prompts * n_chunks)      # the head runs on each chunk's last row
+    tfs = flops / (ms * 1e-3) / 1e12 / gpus_sharing
+    return {"value": tokens / (ms * 1e-3), "unit": "tok/s", "tokens": tokens, "chunk": T, "ms_per_chunk": ms / n_chunks,
+            "gpu_launches": int(launches), "tensor_tflops_per_gpu": tfs, "tensor_frac": tfs / tf_peak}
+
+
+def tp_parity(rank, world):
+    """The head-sharded path against the CPU oracle on a small model (both state precisions, tensor-core and GEMV row
+    counts), run by all ranks before the tensor-parallel timing.  Returns (ok, worst fp16-state error, worst fp32-state error)."""
+    from oracle import oracle as orc
+    from rwkv_lightning_cuda_b200 import backend as bk
+    from oracle.parity import build_pair, run_both
+    from oracle.parity import FP32_STATE_REL
+    dims = dict(layers=2, channels=64 * 2 * world, ffn=256 * world, vocab=64 * world, rank_w=32, rank_a=32, rank_v=16, rank_g=64)
+    ok, worst = True, [0.0, 0.0]
+    for wkv32 in (False, True):
+        box = [bk.tp_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(box, src=0)
+        d, om, gm = build_pair(orc.FMT_F16, wkv32, dims=dims, tp_rank=rank, tp_size=world, tp_unique_id=box[0])
+        for B, chunks, n_decode in ((2, (24, 7), 2), (1, (3,), 2)):
+            w, ids_ok, (shift, wkv, elapsed), st = run_both(d, om, gm, wkv32, B, chunks, n_decode)
+            worst[int(wkv32)] = max(worst[int(wkv32)], float(w))
+            Hl = d.heads // world
+            mine = wkv.astype(np.float32)[:, :, rank * Hl:(rank + 1) * Hl]
+            got = st.wkv_state.cpu().numpy().astype(np.float32)
+            ok = ok and ids_ok and w < (FP32_STATE_REL if wkv32 else 2e-2) and \
+                bool(np.abs(got - mine).max() <= 2e-2 * max(1.0, np.abs(mine).max()))
+        gm.close()
+    flag = torch.tensor([0.0 if ok else 1.0, worst[0], worst[1]], device="cuda", dtype=torch.float64)
+    dist.all_reduce(flag, op=dist.ReduceOp.MAX)
+    return bool(flag[0].item() == 0.0), float(flag[1].item()), float(flag[2].item())
+
+
+def run_ours(args, rank, world, local_rank):
+    hbm_peak, tf_peak, peak_kind = measured_peaks()
+    d, gm, fmt = build_model(args.model, args.fmt, args.wkv32, local_rank, seed=rank, layers=args.layers, vocab=args.vocab)
+    B = args.batch
+    check = correctness_check(gm, d, args.model, args.wkv32) if (rank == 0 and fmt == 0 and not (args.layers or args.vocab)) else None
+    sampler = ClockSampler(local_rank)
+    t = time_decode(gm, d, B, args.steps, args.warmup, world, rank)
+    clocks = sampler.stop()
+    ms, e2e_ms, greedy_ms = max_over_ranks([t["ms"], t["e2e_ms"], t["greedy_ms"]], world)
     abytes, wbytes, sbytes = algorithmic_bytes(d, B, bool(args.wkv32), fmt)
     achieved = abytes / (ms * 1e-3) / 1e9
-    # DRAM traffic of the dominant kernel (gemv_tma_kernel) per algorithmic byte, from the ncu capture summarised in
-    # profiles/gemv_tma_16384x4096_ncu_full.md: 134.28 MB read + 3.58 MB written for 134.26 MB; scaled to the step
+    # DRAM traffic of the dominant kernel (gemv_tma_kernel) per algorithmic byte, from an ncu capture of one launch
+    # (16384 x 4096 fp16): 134.28 MB read + 3.58 MB written for 134.26 MB of weights; scaled to the step
     traffic = abytes * (137.86 / 134.26) if (fmt == 0 and B == 1) else None
     line = {
         "metric": "decode_tokens_per_s", "value": whole_job_rate(world, B, ms), "unit": "tok/s", "n_gpus": world,
@@ -228,21 +368,67 @@ def run_ours(args, rank, world, local_rank):
         "config": {"reduced": {"layers": args.layers, "vocab": args.vocab} if (args.layers or args.vocab) else None,
                    "workload": f"RWKV-7 {args.model} random-init, decode, batch {B} per GPU, {'fp32' if args.wkv32 else 'fp16'} WKV state, weights {args.fmt}",
                    "batch_per_gpu": B, "parallelism": f"replicas x{world} (batch-sharded, no collective)",
-                   "l2": "inputs larger than L2 (every step streams all weights)"},
+                   "l2": "inputs larger than L2 (every step streams all weights)",
+                   "quantised_parity": None if fmt == 0 else "unpinned against the reference (it has no quantised weights); format and kernels checked against this repository's oracle"},
         "clocks": clocks,
         "e2e": {"value": whole_job_rate(world, B, e2e_ms), "unit": "tok/s", "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": B * 8, "d2h_bytes_per_step": B * d.vocab * 4},
         "e2e_greedy": {"value": whole_job_rate(world, B, greedy_ms), "unit": "tok/s", "ms_per_step": greedy_ms,
                        "what": "decode steps + greedy token choice on the device, one host call for all steps",
-                       "h2d_bytes_per_call": B * 8, "d2h_bytes_per_call": args.steps * B * 4, "gpu_launches": int(launches_g)},
-        "gpu_launches": int(launches),
+                       "h2d_bytes_per_call": B * 8, "d2h_bytes_per_call": args.steps * B * 4, "gpu_launches": int(t["greedy_launches"])},
+        "gpu_launches": int(t["launches"]),
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
                      "traffic": traffic, "peak_kind": peak_kind, "frac_of_nominal_8000": achieved / 8000.0,
                      "algorithmic_bytes_per_step": abytes, "weight_bytes": wbytes, "state_bytes_per_seq": sbytes,
                      "scope": "whole decode step (weight-streaming GEMV kernels dominate)"},
+        "check": check,
     }
+    extras = args.only == "all" and not (args.layers or args.vocab) and args.model == "7.2B" and fmt == 0 and B == 1
+    if extras:
+        steps2, warm2 = max(8, args.steps // 2), 3
+        # the other half of the metric: 256 sequences per GPU on the same model, fp16 state
+        t256 = time_decode(gm, d, 256, steps2, warm2, world, rank)
+        t256["ms"], t256["e2e_ms"], t256["greedy_ms"] = max_over_ranks([t256["ms"], t256["e2e_ms"], t256["greedy_ms"]], world)
+        line["b256"] = decode_entry(d, fmt, 256, 0, t256, world, hbm_peak, tf_peak)
+        gm.close()
+        torch.cuda.empty_cache()
+        if world == 1:
+            # long prompt on one GPU: 16384 tokens in chunks of 128, fp32 state (the configuration's prefill half)
+            d2, gm2, _ = build_model("7.2B", "f16", 1, local_rank, seed=0)
+            ms_p, launches_p = time_prefill(gm2, d2, 1, 128, 128, 3, world, rank, same_tokens=True)
+            line["prefill_16k"] = prefill_entry(d2, 1, 128, 128, ms_p, launches_p, 1, 1, tf_peak)
+            gm2.close()
+            torch.cuda.empty_cache()
+            d3, gm3, f3 = build_model("1.5B", "w8a16", 0, local_rank, seed=0)
+            sweep = {}
+            for b in (1, 8, 32, 64):
+                tb = time_decode(gm3, d3, b, steps2, warm2, world, rank, e2e=False, greedy=False)
+                sweep[f"b{b}"] = decode_entry(d3, f3, b, 0, tb, world, hbm_peak, tf_peak)
+            line["w8a16_1p5B"] = sweep
+            gm3.close()
+            torch.cuda.empty_cache()
+            d4, gm4, f4 = build_model("2.9B", "w4a16", 0, local_rank, seed=0)
+            tb = time_decode(gm4, d4, 256, steps2, warm2, world, rank, e2e=False, greedy=False)
+            line["w4a16_2p9B_b256"] = decode_entry(d4, f4, 256, 0, tb, world, hbm_peak, tf_peak)
+            gm4.close()
+            torch.cuda.empty_cache()
+            line["quantised_parity"] = "unpinned against the reference (it has no quantised weights); format and kernels checked against this repository's oracle"
+        else:
+            # the one path with a collective: all ranks as ONE head-sharded group on one 2048-token prompt
+            ok, w16, w32 = tp_parity(rank, world)
+            d2, gm2, _ = build_model("7.2B", "f16", 1, local_rank, seed=0, tp_rank=rank, tp_size=world)
+            ms_p, launches_p = time_prefill(gm2, d2, 1, 128, 16, 3, world, rank, same_tokens=True)
+            (ms_p,) = max_over_ranks([ms_p], world)
+            e = prefill_entry(d2, 1, 128, 16, ms_p, launches_p, 1, world, tf_peak)
+            e.update({"scaling": "strong", "parallelism": f"tp{world}: heads sharded, fp32 all-reduce after att.output and ffn.value",
+                      "parity_vs_oracle": {"ok": ok, "worst_logit_err_fp16_state": w16, "worst_rel_logit_err_fp32_state": w32}})
+            line["tp_prefill"] = e
+            gm2.close()
+            torch.cuda.empty_cache()
+    if rank != 0:
+        return
     if world == 1 and not args.no_cpu_baseline:
-        line["cpu_baseline"] = cpu_baseline(args)
+        line["cpu_baseline"] = cpu_baseline(args.model, args.wkv32)
     print(json.dumps(line))
 
 
@@ -250,53 +436,22 @@ def run_prefill(args, rank, world, local_rank):
     """Secondary line (not the headline metric): chunked prefill of one long prompt.  With --tp the ranks form one
     head-sharded tensor-parallel group working on the same prompt (strong scaling); without it every rank prefills
     its own prompt (weak scaling)."""
-    from rwkv_lightning_cuda_b200 import backend as bk
+    _, tf_peak, kind = measured_peaks()
     tp = world if args.tp else 1
     seed = 0 if tp > 1 else rank           # tensor-parallel ranks must draw the same checkpoint
-    d, gm, fmt = build_model(args, local_rank, seed, tp_rank=rank if tp > 1 else 0, tp_size=tp)
+    d, gm, fmt = build_model(args.model, args.fmt, args.wkv32, local_rank, seed, tp_rank=rank if tp > 1 else 0, tp_size=tp,
+                             layers=args.layers, vocab=args.vocab)
     B, T, n_chunks = args.batch, args.chunk, args.prefill // args.chunk
-    st = gm.create_state(B)
-    lg = bk.DeviceLogits()
-    rng = np.random.default_rng(99 if tp > 1 else 99 + rank)
-    toks = torch.from_numpy(rng.integers(0, d.vocab, (n_chunks, B, T)))
-    stream = torch.cuda.Stream()
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    with torch.cuda.stream(stream):
-        for i in range(min(args.warmup, n_chunks)):
-            gm._forward(toks[i], st, lg, sync=False)
-        barrier()
-        sampler = ClockSampler(local_rank)
-        launches0 = gm.kernel_launches()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record(stream)
-        for i in range(n_chunks):
-            gm._forward(toks[i], st, lg, sync=False)
-        e1.record(stream)
-        barrier()
-        ms = e0.elapsed_time(e1)
-        launches = gm.kernel_launches() - launches0
-        clocks = sampler.stop()
-    (ms,) = max_over_ranks([ms], world, "cuda")
+    sampler = ClockSampler(local_rank)
+    ms, launches = time_prefill(gm, d, B, T, n_chunks, args.warmup, world, rank, same_tokens=tp > 1)
+    clocks = sampler.stop()
+    (ms,) = max_over_ranks([ms], world)
     if rank != 0:
         return
     prompts = B * (1 if tp > 1 else world)
-    tokens = prompts * n_chunks * T
-    C, F, L_ = d.channels, d.ffn, d.layers
-    p_layer = 4 * C * C + 2 * C * F + 2 * C * (d.rank_w + d.rank_a + d.rank_g + d.rank_v)
-    flops = 2.0 * (p_layer * L_ * tokens + d.vocab * C * prompts * n_chunks)      # the head runs on each chunk's last row
-    try:
-        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as fh:
-            tf_peak, kind = float(json.load(fh)["bf16_tflops_sustained"]), "measured (sustained)"
-    except Exception:
-        tf_peak, kind = 1400.0, "fallback"
-    achieved = flops / (ms * 1e-3) / 1e12 / world
+    e = prefill_entry(d, B, T, n_chunks, ms, launches, prompts, tp if tp > 1 else world, tf_peak)
     print(json.dumps({
-        "metric": "prefill_tokens_per_s", "value": tokens / (ms * 1e-3), "unit": "tok/s", "n_gpus": world, "steps": n_chunks,
+        "metric": "prefill_tokens_per_s", "value": e["value"], "unit": "tok/s", "n_gpus": world, "steps": n_chunks,
         "warmup": min(args.warmup, n_chunks), "ms_per_step": ms / n_chunks, "higher_is_better": True,
         "scaling": "strong" if tp > 1 else "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
         "config": {"reduced": {"layers": args.layers, "vocab": args.vocab} if (args.layers or args.vocab) else None,
@@ -305,93 +460,14 @@ def run_prefill(args, rank, world, local_rank):
                    "parallelism": f"tp{tp} (head-sharded, fp32 all-reduce after att.output and ffn.value)" if tp > 1 else f"replicas x{world}",
                    "l2": "inputs larger than L2 (every chunk streams all weights)"},
         "clocks": clocks, "gpu_launches": int(launches),
-        "roofline": {"bound": "tensor", "achieved": achieved, "peak": tf_peak, "unit": "TFLOP/s", "frac": achieved / tf_peak,
-                     "traffic": None, "peak_kind": kind, "scope": "whole prefill, per GPU"},
+        "roofline": {"bound": "tensor", "achieved": e["tensor_tflops_per_gpu"], "peak": tf_peak, "unit": "TFLOP/s", "frac": e["tensor_frac"],
+                     "traffic": None, "peak_kind": kind + " (sustained)", "scope": "whole prefill, per GPU"},
     }))
 
 
-def micro_gemv(args):
-    """Isolated GEMV timing (not the benchmark line): y = x W^T for the 7.2B layer shapes on rotating weight
-    copies larger than L2, replayed from a CUDA graph so that launches are back to back.  `--micro gemv-small`
-    runs a handful of eager launches of the 16384x4096 case only (the command the ncu captures use)."""
-    from rwkv_lightning_cuda_b200 import ops
-    if args.micro.startswith("gemm"):
-        return micro_gemm(args)
-    small = args.micro == "gemv-small"
-    shapes = [(16384, 4096)] if small else [(4096, 4096), (13120, 4096), (16384, 4096), (4096, 16384), (65536, 4096)]
-    for N, K in shapes:
-        copies = max(2, min(6, int(2e9 // (N * K * 2))))
-        Ws = [torch.randn(N, K, device="cuda", dtype=torch.float16) * 0.02 for _ in range(copies)]
-        x = torch.randn(1, K, device="cuda", dtype=torch.float16)
-        s = torch.cuda.Stream()
-        with torch.cuda.stream(s):
-            for W in Ws:
-                ops.linear_f16_orig(x, W)
-            torch.cuda.synchronize()
-            if small:
-                for i in range(4):
-                    ops.linear_f16_orig(x, Ws[i % copies])
-                torch.cuda.synchronize()
-                print(json.dumps({"micro": "gemv-small", "N": N, "K": K, "launches": copies + 4}))
-                continue
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g, stream=s):
-                for _ in range(4):
-                    for W in Ws:
-                        ops.linear_f16_orig(x, W)
-            g.replay()
-            torch.cuda.synchronize()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record(s)
-            for _ in range(5):
-                g.replay()
-            e1.record(s)
-        torch.cuda.synchronize()
-        us = e0.elapsed_time(e1) * 1e3 / (5 * 4 * copies)
-        print(json.dumps({"micro": "gemv", "N": N, "K": K, "us_per_launch": us, "GB_per_s": N * K * 2 / us / 1e3}))
-
-
-def micro_gemm(args):
-    """Isolated tensor-core GEMM timing: y[M,N] = x[M,K] W[N,K]^T for batched-decode / prefill shapes of the 7.2B
-    model, graph-replayed on rotating weights.  `--micro gemm-small` runs a few eager launches of two shapes."""
-    from rwkv_lightning_cuda_b200 import ops
-    small = args.micro == "gemm-small"
-    shapes = [(256, 4096, 16384), (128, 4096, 16384)] if small else \
-        [(256, 128, 4096), (256, 4096, 128), (256, 4096, 4096), (256, 4096, 16384), (256, 16384, 4096), (128, 4096, 4096), (2048, 4096, 4096)]
-    for M, K, N in shapes:
-        copies = max(2, min(6, int(1e9 // (N * K * 2))))
-        Ws = [torch.randn(N, K, device="cuda", dtype=torch.float16) * 0.02 for _ in range(copies)]
-        x = torch.randn(M, K, device="cuda", dtype=torch.float16)
-        s = torch.cuda.Stream()
-        with torch.cuda.stream(s):
-            for W in Ws:
-                ops.linear_f16_orig(x, W)
-            torch.cuda.synchronize()
-            if small:
-                continue
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g, stream=s):
-                for _ in range(4):
-                    for W in Ws:
-                        ops.linear_f16_orig(x, W)
-            g.replay()
-            torch.cuda.synchronize()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record(s)
-            for _ in range(5):
-                g.replay()
-            e1.record(s)
-        torch.cuda.synchronize()
-        us = e0.elapsed_time(e1) * 1e3 / (5 * 4 * copies)
-        print(json.dumps({"micro": "gemm", "M": M, "K": K, "N": N, "us_per_launch": us, "TFLOP_per_s": 2.0 * M * N * K / us / 1e6,
-                          "weight_GB_per_s": N * K * 2 / us / 1e3}))
-    if small:
-        print(json.dumps({"micro": "gemm-small", "shapes": shapes}))
-
-
-def write_reference_checkpoint(args, path):
+def write_reference_checkpoint(model, path):
     from rwkv_lightning_cuda_b200 import synthetic
-    d = synthetic.CONFIGS[args.model]
+    d = synthetic.CONFIGS[model]
     gen = torch.Generator(device="cuda")
     gen.manual_seed(0)
     sd = {}
@@ -401,12 +477,57 @@ def write_reference_checkpoint(args, path):
     return d
 
 
+def reference_kernel_times(lib):
+    """CUDA-event time of two of the reference's own kernels alone (no host work, no allocation): its one-row GEMV on
+    a 16384 x 4096 fp16 matrix (cuda/rwkv7_v3a_ops.cu:464-560) and its fp16-state WKV step for 256 sequences x 64 heads
+    (cuda/rwkv7_wkv_fp16_v2.cu:676-742), with the same two shapes through this repository's kernels beside them.
+    Weights rotate over copies larger than L2."""
+    import ctypes as C
+    from rwkv_lightning_cuda_b200 import ops
+    p = lambda t: C.c_void_p(t.data_ptr())
+    N, K = 16384, 4096
+    Ws = [torch.randn(N, K, device="cuda", dtype=torch.float16) * 0.02 for _ in range(3)]
+    x = torch.randn(1, K, device="cuda", dtype=torch.float16)
+    y = torch.empty(1, N, device="cuda", dtype=torch.float16)
+    B, Cc, H = 256, 4096, 64
+    state = torch.zeros(B, H, 64, 64, device="cuda", dtype=torch.float16)
+    r, w, k, v, a, b = (torch.randn(B, Cc, device="cuda", dtype=torch.float16) * 0.1 for _ in range(6))
+    yy = torch.empty(B, Cc, device="cuda", dtype=torch.float16)
+    elapsed = torch.zeros(B, device="cuda", dtype=torch.int32)
+
+    def timed(fn, reps):
+        fn(0); torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(reps):
+            fn(i)
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) * 1e3 / reps
+
+    lib.ref_set_sync(0)
+    out = {}
+    try:
+        us = timed(lambda i: lib.ref_linear_orig(1, K, N, p(x), p(Ws[i % 3]), p(y), 1), 30)
+        out["ref_linear_orig_1x4096x16384"] = {"us": us, "GB_per_s": N * K * 2 / us / 1e3}
+        us = timed(lambda i: lib.ref_wkv_fp16_seq(B, 1, Cc, H, p(state), p(r), p(w), p(k), p(v), p(a), p(b), p(yy), p(elapsed)), 30)
+        out["ref_wkv_fp16_seq_b256"] = {"us": us, "GB_per_s": 2 * state.numel() * 2 / us / 1e3}
+    finally:
+        lib.ref_set_sync(1)
+    us = timed(lambda i: ops.linear_f16_orig(x, Ws[i % 3]), 30)
+    out["ours_linear_1x4096x16384"] = {"us": us, "GB_per_s": N * K * 2 / us / 1e3}
+    us = timed(lambda i: ops.wkv_fp16_seq(B, 1, state, r, w, k, v, a, b, elapsed), 30)
+    out["ours_wkv_fp16_seq_b256"] = {"us": us, "GB_per_s": 2 * state.numel() * 2 / us / 1e3}
+    out["note"] = "back-to-back eager launches on one stream, CUDA events around 30 of them"
+    return out
+
+
 def run_reference(args, rank, world):
     """The reference's own CUDA backend (built unmodified into oracle/_ref) on the same workload."""
     if rank != 0:
         return
     import ctypes as C
-    from tests.helpers import ref_lib
+    from oracle.oracle import ref_lib
     lib = ref_lib()
     if lib is None:
         print(json.dumps({"impl": "reference", "unavailable": "oracle/_ref/libref_rwkv7.so was not built (reference tree absent at build time)"}))
@@ -414,7 +535,7 @@ def run_reference(args, rank, world):
     tmpdir = tempfile.mkdtemp(prefix="rwkv7_ref_")
     path = os.path.join(tmpdir, "model.pth")
     try:
-        d = write_reference_checkpoint(args, path)
+        d = write_reference_checkpoint(args.model, path)
         be = lib.ref_backend_create(path.encode(), int(args.wkv32))
     finally:
         if os.path.exists(path):
@@ -424,10 +545,21 @@ def run_reference(args, rank, world):
         print(json.dumps({"impl": "reference", "unavailable": "reference backend failed to load: " + lib.ref_last_error().decode()}))
         return
     B = args.batch
+    out = np.empty((B, d.vocab), np.float32)
+    # the fixed short run whose logits the other arm compares its own with
+    st1 = lib.ref_state_create(be, 1)
+    one = np.empty((1, d.vocab), np.float32)
+    prompt = np.array([[t % d.vocab for t in CHECK_PROMPT]], dtype=np.int64)
+    nxt = np.array([[CHECK_NEXT % d.vocab]], dtype=np.int64)
+    lib.ref_forward(be, st1, prompt.ctypes.data_as(C.c_void_p), 1, prompt.shape[1], None)
+    rc = lib.ref_forward(be, st1, nxt.ctypes.data_as(C.c_void_p), 1, 1, one.ctypes.data_as(C.c_void_p))
+    lib.ref_state_destroy(st1)
+    if rc == 0:
+        os.makedirs(HANDOFF, exist_ok=True)
+        np.save(os.path.join(HANDOFF, f"ref_logits_{args.model}_{int(bool(args.wkv32))}.npy"), one[0])
     st = lib.ref_state_create(be, B)
     rng = np.random.default_rng(1234)
     toks = rng.integers(0, d.vocab, (args.warmup + args.steps + 1, B)).astype(np.int64)
-    out = np.empty((B, d.vocab), np.float32)
     prompt = np.ascontiguousarray(np.repeat(toks[0][:, None], 4, axis=1))
     lib.ref_forward(be, st, prompt.ctypes.data_as(C.c_void_p), B, 4, None)
     for i in range(args.warmup):
@@ -442,15 +574,21 @@ def run_reference(args, rank, world):
     ms = (time.perf_counter() - t0) * 1e3 / args.steps
     clocks = sampler.stop()
     v = B / (ms * 1e-3)
+    try:
+        kernels = reference_kernel_times(lib)
+    except Exception as e:      # the headline of this arm does not depend on it
+        kernels = {"unavailable": repr(e)[:200]}
     print(json.dumps({
         "impl": "reference", "metric": "decode_tokens_per_s", "value": v, "unit": "tok/s", "n_gpus": 1, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f16", "data": "synthetic",
-        "config": {"workload": f"RWKV-7 {args.model} random-init, decode, batch {B}, {'fp32' if args.wkv32 else 'fp16'} WKV state, weights f16",
+        "config": {"workload": f"RWKV-7 {args.model} random-init, decode, batch {B} per GPU, {'fp32' if args.wkv32 else 'fp16'} WKV state, weights f16",
                    "note": "the reference's own CUDA ModelBackend (it has no CPU implementation of this path), host token ids in, logits copied to host; wall clock including its per-call allocation and synchronisation"},
         "clocks": clocks,
         "cpu_baseline": {"value": v, "unit": "tok/s", "cores": 1, "kind": "reference", "sample": f"{args.steps} decode steps of the reference CUDA backend driven by one host thread"},
-        "e2e": {"value": v, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "e2e": {"value": v, "unit": "tok/s", "h2d_bytes_per_step": B * d.channels * 2, "d2h_bytes_per_step": B * d.vocab * 4,
+                "note": "the reference gathers embedding rows on the host and copies them in; its logits are copied back every step"},
+        "kernel_only": kernels,
     }))
 
 
@@ -465,21 +603,18 @@ def main():
     ap.add_argument("--fmt", default="f16", choices=["f16", "w8a16", "w4a16"])
     ap.add_argument("--wkv32", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--only", default="all", choices=["all", "headline"], help="headline: skip the secondary workloads of the line")
     ap.add_argument("--prefill", type=int, default=0, help="secondary line: prefill this many tokens in chunks instead of decoding")
     ap.add_argument("--chunk", type=int, default=128)
     ap.add_argument("--layers", type=int, default=0, help="timing aid: override the depth (the line then says so)")
     ap.add_argument("--vocab", type=int, default=0, help="timing aid: override the vocabulary size")
     ap.add_argument("--tp", action="store_true", help="with --prefill: the ranks form one head-sharded tensor-parallel group")
-    ap.add_argument("--micro", default="", choices=["", "gemv", "gemv-small", "gemm", "gemm-small"], help="kernel micro-benchmark instead of the bench line")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local_rank)
-    if args.micro:
-        micro_gemv(args)
-        return
     if args.impl == "reference":
         run_reference(args, rank, world)
         return

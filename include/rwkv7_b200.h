@@ -31,7 +31,7 @@ extern "C" {
 #define RWKV7_B200_PRECISION 3   /* state precision does not match the model (fp16 vs fp32 WKV state) */
 #define RWKV7_B200_CUDA 4
 #define RWKV7_B200_NCCL 5
-#define RWKV7_B200_TIMEOUT 6
+#define RWKV7_B200_TIMEOUT 6     /* a bounded wait inside a kernel ran out: see rwkv7_b200_timeout_flags */
 #define RWKV7_B200_NOT_READY 7   /* model not finalised / tensor missing */
 
 /* weight formats of the large matrices (att r/k/v/o, ffn key/value, head) */
@@ -125,12 +125,19 @@ int rwkv7_b200_state_init(const rwkv7_b200_model* m, int B, void* shift, void* w
  * 1402-1419).  tokens_host is [B][T] row-major on the host (decode: T = 1); the state is updated
  * in place; logits receives fp32 [B][vocab] of the last token of every sequence.  Token ids are
  * validated on the host before anything is enqueued (BAD_ARG, state untouched).  Asynchronous:
- * the logits are valid once `stream` has completed; tokens_host may be reused on return. */
+ * the logits are valid once `stream` has completed; tokens_host may be reused on return.
+ * Threading: calls may come from any thread.  A model owns ONE set of activation buffers (grown to the
+ * largest B*T seen, never per shape), so calls on the same model are serialised on the host (a mutex around the
+ * enqueue) and on the device (a call on another stream than the previous call's first waits for that call's
+ * work).  Concurrent sequences belong in one batch, or in separate models.  A call that has to grow the
+ * buffers synchronises the device first. */
 int rwkv7_b200_forward(rwkv7_b200_model* m, const int64_t* tokens_host, int B, int T, void* shift, void* wkv,
                        int* elapsed, float* logits, void* stream);
 
 /* Same call for a host program that keeps no device buffers for the result: additionally copies
- * the logits to logits_host (pinned memory recommended) and synchronises `stream`. */
+ * the logits to logits_host (pinned memory recommended) and synchronises `stream`.  Because it synchronises,
+ * it also reads the device's failure word: RWKV7_B200_TIMEOUT means a kernel gave up on a bounded wait and
+ * the logits and the state of this call are not to be trusted (the word is reset, later calls run normally). */
 int rwkv7_b200_forward_to_host(rwkv7_b200_model* m, const int64_t* tokens_host, int B, int T, void* shift,
                                void* wkv, int* elapsed, float* logits, float* logits_host, void* stream);
 
@@ -167,6 +174,36 @@ int rwkv7_b200_query_capacity(const rwkv7_b200_model* m, int prefill_chunk_size,
 
 /* Number of kernels enqueued by forward calls since the model was created (for benchmarks). */
 long long rwkv7_b200_kernel_launches(const rwkv7_b200_model* m);
+/* Device bytes the model's activation workspace holds now (it replaces the reference's per-call arena +
+ * 128 MiB workspace, src/rwkv7_fast_v4.cu:1087-1096; grow-only, sized by the largest call so far). */
+int rwkv7_b200_model_workspace_bytes(const rwkv7_b200_model* m, size_t* out);
+
+/* ------------------------------------------------------------------------------------------
+ * Failure word and options (no counterpart in the reference, whose kernels have no bounded waits and
+ * whose CUDA errors end the process, include/rwkv7_fast_v4_common.hpp:57-62)
+ * ---------------------------------------------------------------------------------------- */
+
+/* Every wait on a copy-completion barrier inside this library's kernels has a poll limit.  A kernel whose
+ * limit runs out sets a bit in a per-device word and returns instead of hanging.  The calls that synchronise
+ * (rwkv7_b200_forward_to_host, rwkv7_b200_decode_greedy with out_tokens_host) report it as
+ * RWKV7_B200_TIMEOUT; callers of the asynchronous entry points read it here after synchronising their
+ * stream.  *flags: 1 weight-streaming GEMV, 2 tensor-core GEMM, 4 time-mix core, 8 wait probe, 16 chunked WKV.
+ * clear != 0 resets the word.  Blocking (a 4-byte device-to-host copy on the current device). */
+int rwkv7_b200_timeout_flags(int clear, int* flags);
+/* Test aid: enqueues a one-thread kernel that polls a barrier nothing will ever complete `polls` times
+ * (<= 2^20), then sets bit 8 of the failure word and returns.  No copy is in flight, nothing hangs. */
+int rwkv7_b200_debug_wait_probe(void* stream, unsigned polls);
+/* Test aid: the largest K split among the products of the calling thread's most recent tensor-core GEMM launch
+ * (1: no fp32 partial sums were written; > 1: the split-K scratch was used).  Returns the count, not a status. */
+int rwkv7_b200_debug_last_gemm_splits(void);
+/* Process-wide switches for measurements and tests, read when a call is enqueued:
+ *   "gemm_cta_pair" 0|1     tensor-core GEMM as CTA pairs (cta_group::2); default 0 (measured equal)
+ *   "expanded_weights" 0|1  quantised models may keep fp16 copies for the tensor-core path; default 1
+ *   "quant_tc_rows" n       row count from which quantised weights take the tensor-core path; 0 = built-in
+ *   "fp16_tc_rows" n        the same for fp16 weights; 0 = built-in
+ *   "decode_graphs" 0|1     decode steps replay a CUDA graph; default 1
+ * BAD_ARG for an unknown name or a value out of range. */
+int rwkv7_b200_set_option(const char* name, int value);
 
 /* ------------------------------------------------------------------------------------------
  * Op-level entry points (replace launchers of cuda/rwkv7_fast_v4_kernels.cuh)
@@ -245,7 +282,9 @@ int rwkv7_b200_linear_f16_orig(void* stream, int M, int K, int N, const uint16_t
  * keeps that room in a fixed 16 MiB device array inside the library image (held by every GPU that loads the
  * library until the process exits) and calls no cudaMalloc/cudaFree or allocating library routine.
  * Limits: M > 4, N % 4 == 0, M*N <= 2,097,152 (SHAPE otherwise).  The first call on a device looks the array's
- * device address up (cudaGetSymbolAddress) and should therefore be made before any stream capture.  All calls
+ * device address up (cudaGetSymbolAddress) and makes the driver load the kernel and map the array; make one warm-up
+ * call per device before the host closes its allocator or freezes its memory budget, and before any stream
+ * capture.  All calls
  * share the array: nothing in it has to be cleared (every partial sum that is read is written by the same call), but
  * two calls whose kernels overlap on the GPU (different streams) race on it. */
 int rwkv7_b200_linear_f16_orig_static(void* stream, int M, int K, int N, const uint16_t* x, const uint16_t* weight,

@@ -31,6 +31,31 @@ def build() -> str:
     return so
 
 
+def reference_dir() -> str:
+    """Where the reference project's checkout is looked for when the oracle is built against it:
+    $RWKV7_REFERENCE_DIR, else a directory named ``reference`` beside this repository."""
+    return os.environ.get("RWKV7_REFERENCE_DIR") or os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")
+
+
+def ref_lib():
+    """The reference's own kernels and backend, built unmodified under oracle/_ref/ by ``make -C oracle ref``
+    (None when that build is absent).  A checker and a timed baseline, never part of the product path."""
+    path = os.path.join(_HERE, "_ref", "libref_rwkv7.so")
+    if not os.path.exists(path):
+        return None
+    r = C.CDLL(path)
+    r.ref_last_error.restype = C.c_char_p
+    r.ref_backend_create.restype = C.c_void_p
+    r.ref_state_create.restype = C.c_void_p
+    r.ref_backend_create.argtypes = [C.c_char_p, C.c_int]
+    r.ref_backend_destroy.argtypes = [C.c_void_p]
+    r.ref_state_create.argtypes = [C.c_void_p, C.c_int]
+    r.ref_state_destroy.argtypes = [C.c_void_p]
+    r.ref_forward.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p]
+    r.ref_state_read.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
+    return r
+
+
 def lib() -> C.CDLL:
     global _LIB
     if _LIB is None:

@@ -19,9 +19,10 @@ namespace {
 thread_local std::string g_err;
 inline const half* H(const uint16_t* p) { return reinterpret_cast<const half*>(p); }
 inline half* H(uint16_t* p) { return reinterpret_cast<half*>(p); }
+bool g_sync = true;  // op-level calls wait for their kernel unless a timing loop switches that off
 int done(cudaStream_t s) {
   cudaError_t e = cudaGetLastError();
-  if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+  if (e == cudaSuccess && g_sync) e = cudaStreamSynchronize(s);
   if (e != cudaSuccess) {
     g_err = cudaGetErrorString(e);
     return 1;
@@ -37,6 +38,8 @@ struct RefState {
 extern "C" {
 
 const char* ref_last_error() { return g_err.c_str(); }
+// on = 0: the op-level calls below only enqueue (kernel-only timing with events around a run of them)
+void ref_set_sync(int on) { g_sync = on != 0; }
 
 int ref_wkv_fp16_seq(int B, int T, int C, int Hh, uint16_t* state, const uint16_t* r, const uint16_t* w, const uint16_t* k,
                      const uint16_t* v, const uint16_t* a, const uint16_t* b, uint16_t* y, const int* elapsed) {

@@ -88,6 +88,10 @@ void B200ModelBackend::run(const int64_t* tokens, int B, int T, GenerationState&
   check(rwkv7_b200_forward(model_, tokens, B, T, state.shift.p, wkv, state.elapsed.p, logits.values.p, stream_));
   // synchronous on return, like the reference (src/rwkv7_fast_v4.cu:1343): callers use stream 0 next
   if (cudaStreamSynchronize(stream_) != cudaSuccess) throw std::runtime_error("sync backend stream");
+  // a kernel that gave up on a bounded wait left this call's logits and state incomplete: report it like any other error
+  int flags = 0;
+  check(rwkv7_b200_timeout_flags(1, &flags));
+  if (flags) throw std::runtime_error("rwkv7_b200: a bounded wait inside a kernel ran out (flags " + std::to_string(flags) + ")");
 }
 
 void B200ModelBackend::forward_prefill(const std::vector<std::vector<int64_t>>& token_batches, GenerationState& state,

@@ -10,6 +10,7 @@
 namespace rk {
 const char* last_error();
 int gemm_tc_static_scratch(cudaStream_t stream, const LinearArgs& a);
+int gemm_last_max_splits();
 }
 
 using rk::kBadArg;
@@ -98,8 +99,9 @@ int rwkv7_b200_forward_to_host(rwkv7_b200_model* m, const int64_t* tokens_host, 
   if (s != kOk) return s;
   RK_CUDA(cudaMemcpyAsync(logits_host, logits, static_cast<size_t>(B) * m->impl.cfg().vocab * sizeof(float),
                           cudaMemcpyDeviceToHost, st(stream)));
+  if ((s = m->impl.enqueue_timeout_read(st(stream))) != kOk) return s;
   RK_CUDA(cudaStreamSynchronize(st(stream)));
-  return kOk;
+  return m->impl.timeout_result();
 }
 
 int rwkv7_b200_decode_greedy(rwkv7_b200_model* m, const int64_t* first_tokens_host, int B, int steps, void* shift, void* wkv,
@@ -111,8 +113,9 @@ int rwkv7_b200_decode_greedy(rwkv7_b200_model* m, const int64_t* first_tokens_ho
   if (s != kOk || !out_tokens_host) return s;
   RK_CUDA(cudaMemcpyAsync(out_tokens_host, out_tokens, static_cast<size_t>(B) * steps * sizeof(int), cudaMemcpyDeviceToHost,
                           st(stream)));
+  if ((s = m->impl.enqueue_timeout_read(st(stream))) != kOk) return s;
   RK_CUDA(cudaStreamSynchronize(st(stream)));
-  return kOk;
+  return m->impl.timeout_result();
 }
 
 int rwkv7_b200_greedy_pick(void* stream, int B, int V, const float* logits, float* penalties, float presence_penalty,
@@ -135,6 +138,20 @@ int rwkv7_b200_query_capacity(const rwkv7_b200_model* m, int chunk, rwkv7_b200_c
 }
 
 long long rwkv7_b200_kernel_launches(const rwkv7_b200_model* m) { return m ? m->impl.launches() : 0; }
+
+int rwkv7_b200_model_workspace_bytes(const rwkv7_b200_model* m, size_t* out) {
+  RK_REQUIRE(m && out, kBadArg, "workspace_bytes: null argument");
+  *out = m->impl.workspace_bytes();
+  return kOk;
+}
+
+int rwkv7_b200_timeout_flags(int clear, int* flags) {
+  RK_REQUIRE(flags, kBadArg, "timeout_flags: null output");
+  return rk::timeout_read(flags, clear != 0);
+}
+int rwkv7_b200_debug_last_gemm_splits(void) { return rk::gemm_last_max_splits(); }
+int rwkv7_b200_debug_wait_probe(void* stream, unsigned polls) { return rk::wait_probe(st(stream), polls); }
+int rwkv7_b200_set_option(const char* name, int value) { return rk::set_option(name, value); }
 
 // ---------------------------------------------------------------- op level
 

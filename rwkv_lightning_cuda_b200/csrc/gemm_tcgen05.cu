@@ -22,7 +22,6 @@
 #include <cuda.h>
 
 #include <algorithm>
-#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <string>
@@ -46,8 +45,6 @@ constexpr int kEpiLd = kBM + 4;          // padded row of the transposition tile
 constexpr int kEpiBytes = kEpiRows * kEpiLd * 4;
 constexpr int kMaxStages = 8;
 
-__device__ int g_gemm_timeout = 0;
-
 struct Prob {
   int M, N, K, epi;
   int tiles_n;               // ceil(N / 128)
@@ -66,6 +63,7 @@ struct GroupDev {
   int n_prob, total_units, Nt, stages, tiles_m, red_blocks;
   int bm;         // output channels per work unit: 128, or 256 for the CTA-pair kernel
   int w_dynamic;  // the weights may have been written by the previous kernel: wait for it before reading them
+  int* timeout;   // the device's failure word: a bounded wait that runs out ORs kTimeoutGemm into it
   Prob prob[kMaxProb];
 };
 
@@ -470,7 +468,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_group_kernel(const __grid_co
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
-  if (threadIdx.x == 0 && failed) atomicExch(&g_gemm_timeout, 1);
+  if (threadIdx.x == 0 && failed && g.timeout) atomicOr(g.timeout, kTimeoutGemm);
   __syncwarp();
   if (kPair) cluster_sync_all();  // neither CTA leaves while its partner may still signal its barriers or read its tiles
   if (warp == 1) {
@@ -637,16 +635,11 @@ Plan make_plan_uncached(const LinearArgs* a, int n, size_t scratch_bytes, int sm
     if (M > 64) nts[n_nt++] = 64;
   }
   static const int targets[] = {1 << 30, 128, 96, 64, 48, 32, 24, 16, 12, 8, 6, 4};
-  // tuning aids: force the row-tile width / the K blocks per unit
-  static const int force_nt = [] { const char* e = getenv("RWKV7_B200_GEMM_NT"); return e ? atoi(e) : 0; }();
-  static const int force_target = [] { const char* e = getenv("RWKV7_B200_GEMM_TARGET"); return e ? atoi(e) : 0; }();
   Plan best;
   std::vector<double> load(static_cast<size_t>(sms));
   for (int ni = 0; ni < n_nt; ++ni) {
     const int Nt = nts[ni], tiles_m = (M + Nt - 1) / Nt;
-    if (force_nt && Nt != force_nt && !(ni == 0 && force_nt > Nt)) continue;
     for (int target : targets) {
-      if (force_target && target != force_target) continue;
       Plan p;
       p.Nt = Nt;
       p.tiles_m = tiles_m;
@@ -693,6 +686,12 @@ bool problem_ok(const LinearArgs& a) {
 
 bool gemm_tc_supported(const LinearArgs& a) { return problem_ok(a); }
 
+namespace {
+thread_local int g_last_max_splits = 0;
+}
+// Largest K split of the products of this thread's most recent tensor-core launch (1 = no partial sums were used).
+int gemm_last_max_splits() { return g_last_max_splits; }
+
 // Up to eight products with the same row count in one launch (plus one reduction launch if any K is split).
 // Split-K needs scratch (taken from the first product's args); without it every product runs unsplit.
 int gemm_group(cudaStream_t stream, const LinearArgs* a, int n) {
@@ -705,7 +704,7 @@ int gemm_group(cudaStream_t stream, const LinearArgs* a, int n) {
   const int sms = sm_count();
   // CTA pairs (cta_group::2: each CTA stages half of the activation tile) are opt-in: on the shapes of this model
   // they measured equal to single CTAs (M = 256 .. 2048), so the simpler kernel is the default.
-  static const int pair_mode = [] { const char* e = getenv("RWKV7_B200_GEMM_PAIR"); return e ? atoi(e) : 0; }();
+  const int pair_mode = options().gemm_cta_pair;
   static std::mutex mu;
   static int pairs_dev[64] = {0};  // co-resident CTA pairs per device; -1 = cluster launch not available
   int dev = 0;
@@ -738,6 +737,7 @@ int gemm_group(cudaStream_t stream, const LinearArgs* a, int n) {
   const int bm = pair ? 2 * kBM : kBM;
   const Plan plan = make_plan(a, n, a[0].scratch ? a[0].scratch_bytes : 0, walkers, bm);
   RK_REQUIRE(plan.Nt > 0 && plan.total_units > 0, kShape, "gemm_group: no launch plan");
+  g_last_max_splits = *std::max_element(plan.splits, plan.splits + n);
 
   static MapPack maps;  // filled and consumed under the lock: kernel parameters are copied at launch
   GroupDev g = {};
@@ -755,6 +755,7 @@ int gemm_group(cudaStream_t stream, const LinearArgs* a, int n) {
   const size_t smem = (w_bytes + x_bytes) * g.stages + kEpiBytes + 1024;
   g.w_dynamic = 0;
   for (int i = 0; i < n; ++i) g.w_dynamic |= a[i].w_dynamic ? 1 : 0;
+  g.timeout = timeout_word_or_null();
 
   std::lock_guard<std::mutex> lock(mu);
   float* scratch = a[0].scratch;
@@ -848,12 +849,6 @@ int gemm_tc_static_scratch(cudaStream_t stream, const LinearArgs& a) {
   b.scratch = ptr;
   b.scratch_bytes = kStaticScratchFloats * sizeof(float);
   return gemm_tc(stream, b);
-}
-
-int gemm_timeout_flag() {
-  int v = 0;
-  if (cudaMemcpyFromSymbol(&v, g_gemm_timeout, sizeof(int)) != cudaSuccess) return -1;
-  return v;
 }
 
 }  // namespace rk

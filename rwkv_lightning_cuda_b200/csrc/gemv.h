@@ -40,23 +40,12 @@ struct GemvSeg {
   int copy_n;
 };
 
-// L2 prefetch of what the NEXT kernel in the stream will read first: `count` blocks of `depth` bytes,
-// `stride` bytes apart, starting at `base`.  Issued by warps that have requested their last own piece,
-// so the HBM is kept busy while this kernel drains and the next one starts.
-constexpr int kMaxPrefetch = 6;
-struct GemvPrefetch {
-  const char* base;
-  long long stride;
-  int depth, count;
-};
-
 bool gemv_tma_fits(int M, int K);  // gemv_tma.cu
 
 struct GemvBatch {
   int n_seg;
   GemvSeg seg[kMaxSeg];
-  int n_pf;
-  GemvPrefetch pf[kMaxPrefetch];
+  int* timeout;  // the device's failure word (kernels.h): a bounded wait that runs out ORs kTimeoutGemv into it
 };
 
 #ifdef __CUDACC__
@@ -243,8 +232,6 @@ __device__ __forceinline__ void stage_ln_mix(const GemvSeg& sg, float* xs, float
 
 // gemv_tma.cu: fp16 weights fetched with per-warp rings of bulk copies (cp.async.bulk + mbarrier).
 bool gemv_tma_plan(GemvBatch& b, int M, size_t* smem_bytes, int* grid, int* n_slots, int* slot_stride, int* n_warps);
-// Prefetch pattern matching how gemv_tma_plan would spread a launch of `launch_rows` rows in total over warps.
-GemvPrefetch gemv_tma_prefetch_of(const void* w, int N, int K, int launch_rows);
 int gemv_tma_launch(cudaStream_t stream, const GemvBatch& b, int M, size_t smem_bytes, int grid, int n_slots, int slot_stride,
                     int n_warps);
 

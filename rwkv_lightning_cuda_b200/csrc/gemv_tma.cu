@@ -2,12 +2,11 @@
 // weights staged through shared memory by the bulk-copy engine: every warp owns a ring of kSlots buffers, one lane requests the next piece of
 // the warp's contiguous weight stream with cp.async.bulk (completion on an mbarrier), the warp
 // consumes pieces in order with 128-bit shared-memory loads and re-arms the slot it has just read.
-// About kSlots * 4 KiB per warp (96 KiB per CTA) are in flight without holding registers, which is
+// Two 4 KiB slots per warp (128 KiB per CTA of 16 warps) are in flight without holding registers, which is
 // what it takes to keep HBM3e busy from 148 SMs; the first kSlots pieces are requested before the
 // programmatic-dependency wait, so a kernel's weight stream starts while its predecessor drains.
 // Same arithmetic and rounding as the register-staged kernel in linear.cu.
 #include <algorithm>
-#include <cstdlib>
 
 #include "gemv.h"
 #include "kernels.h"
@@ -18,8 +17,6 @@ namespace {
 constexpr int kMaxWarps = 16;
 constexpr int kMaxSlots = 6;
 constexpr int kPieceCap = 4096;  // bytes
-
-__device__ int g_gemv_timeout = 0;  // set when a bounded mbarrier wait gives up
 
 // One 16-byte weight chunk (8 halves) against 8 fp32 activations from shared memory.
 __device__ __forceinline__ void fma_chunk(const uint4& q, const float* x, float& a0, float& a1) {
@@ -85,22 +82,8 @@ __global__ void __launch_bounds__(kW * 32, 1) gemv_tma_kernel(const GemvBatch p,
     if (++q_pp == parts) q_pp = 0;
     if (q_pp == rot) ++q_row;
   };
-  // Once this warp has requested its last piece it asks the L2 for its share of the next kernel's
-  // first reads (fire and forget).
-  auto prefetch_next = [&]() {
-    if (lane != 0) return;
-    const int gw = blockIdx.x * kW + warp, n_gw = gridDim.x * kW;
-    int e0 = 0;
-    for (int i = 0; i < p.n_pf; ++i) {
-      const GemvPrefetch& f = p.pf[i];
-      for (int e = ((gw - e0) % n_gw + n_gw) % n_gw; e < f.count; e += n_gw)
-          asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(f.base + static_cast<long long>(e) * f.stride), "r"(f.depth) : "memory");
-      e0 += f.count;
-    }
-  };
   // weights do not depend on the previous kernel: fill the ring before waiting for it
   for (int i = 0; i < n_slots && q_left > 0; ++i) issue();
-  if (q_left == 0) prefetch_next();
 
   LnPrefetch pf;
   if (sg.ln_w) ln_prefetch<kW * 32>(sg, pf);
@@ -147,7 +130,7 @@ __global__ void __launch_bounds__(kW * 32, 1) gemv_tma_kernel(const GemvBatch p,
     }
     const uint32_t bar = smem_u32(&bars[warp][slot]);
     if (!mbar_try_wait(bar, phase) && !mbar_wait(bar, phase)) {
-      if (lane == 0) atomicExch(&g_gemv_timeout, 1);
+      if (lane == 0 && p.timeout) atomicOr(p.timeout, kTimeoutGemv);
       return;
     }
     const uint4* wsm = reinterpret_cast<const uint4*>(ring + slot * slot_stride) + lane;
@@ -226,10 +209,7 @@ __global__ void __launch_bounds__(kW * 32, 1) gemv_tma_kernel(const GemvBatch p,
       }
     }
     __syncwarp();  // every lane has read the slot: it may be overwritten
-    if (q_left > 0) {
-      issue();
-      if (q_left == 0) prefetch_next();
-    }
+    if (q_left > 0) issue();
     if (kQuant && fmt == 2) { sz_cur[0] = sz_next[0]; sz_cur[1] = sz_next[1]; }
     if (++slot == n_slots) { slot = 0; phase ^= 1; }
     if (++pp == parts) pp = 0;
@@ -270,24 +250,15 @@ bool gemv_tma_plan(GemvBatch& b, int M, size_t* smem_bytes, int* grid, int* n_sl
     total_bytes += static_cast<double>(g.N) * row_bytes;
   }
   x_bytes = (x_bytes + 127) & ~static_cast<size_t>(127);
-  int cap = kPieceCap;
+  const int cap = kPieceCap;
   // measured best on B200: one CTA of 16 warps per SM, two 4 KiB slots per warp (128 KiB in flight)
-  int per_sm = 1, slots = 2, kWarps = 16;
-  static const int env_warps = getenv("RWKV7_B200_GEMV_WARPS") ? atoi(getenv("RWKV7_B200_GEMV_WARPS")) : 0;
-  static const int env_slots = getenv("RWKV7_B200_GEMV_SLOTS") ? atoi(getenv("RWKV7_B200_GEMV_SLOTS")) : 0;  // tuning aids
-  static const int env_per_sm = getenv("RWKV7_B200_GEMV_PER_SM") ? atoi(getenv("RWKV7_B200_GEMV_PER_SM")) : 0;
-  static const int env_cap = getenv("RWKV7_B200_GEMV_PIECE") ? atoi(getenv("RWKV7_B200_GEMV_PIECE")) : 0;
-  if (env_cap >= 512 && env_cap <= kPieceCap) cap = env_cap;
+  int slots = 2, kWarps = 16;
   if (x_bytes + static_cast<size_t>(kWarps) * slots * cap > 200 * 1024) {
     kWarps = 8;  // very large activation rows: fewer warps, whatever ring depth still fits
     slots = static_cast<int>((200 * 1024 - x_bytes) / (static_cast<size_t>(kWarps) * cap));
     slots = std::min(slots, kMaxSlots);
     if (slots < 2) return false;
   }
-  if (env_per_sm > 0) per_sm = env_per_sm;
-  if (env_warps == 8 || env_warps == 16) kWarps = env_warps;
-  if (env_slots > 0) slots = std::min(env_slots, kMaxSlots);
-  if (x_bytes + static_cast<size_t>(kWarps) * slots * cap > 200 * 1024) return false;
   for (int i = 0; i < b.n_seg; ++i) {
     GemvSeg& g = b.seg[i];
     const int row_bytes = g.fmt == 0 ? g.K * 2 : g.fmt == 1 ? g.K : g.K / 2;
@@ -302,7 +273,7 @@ bool gemv_tma_plan(GemvBatch& b, int M, size_t* smem_bytes, int* grid, int* n_sl
   // CTAs are shared out by weight bytes: every problem starts with its rounded-down share (at least one CTA), the
   // rest go one at a time to whichever problem has the most bytes per CTA, so that all SMs finish together.  (Rows
   // per CTA need not be a multiple of the warp count: 4096 rows on 148 SMs are 28 rows each, not 32 on 128 SMs.)
-  const int budget = 148 * per_sm;
+  const int budget = 148;
   int n_cta[kMaxSeg];
   int used = 0;
   for (int i = 0; i < b.n_seg; ++i) {
@@ -354,20 +325,6 @@ bool gemv_tma_fits(int M, int K) {
   return x_bytes + static_cast<size_t>(8) * 2 * kPieceCap <= 200 * 1024;
 }
 
-GemvPrefetch gemv_tma_prefetch_of(const void* w, int N, int K, int launch_rows) {
-  GemvPrefetch f;
-  const int rpw = std::max(1, (launch_rows + 148 * 16 - 1) / (148 * 16));
-  const long long row_bytes = static_cast<long long>(K) * 2;
-  f.base = static_cast<const char*>(w);
-  f.stride = rpw * row_bytes;
-  static const int env_depth = getenv("RWKV7_B200_PREFETCH_BYTES") ? atoi(getenv("RWKV7_B200_PREFETCH_BYTES")) : 0;  // off: measured no gain at 4-8 KiB, a loss at 32 KiB
-  f.depth = static_cast<int>(std::min<long long>(f.stride, env_depth)) & ~15;
-  f.count = f.depth > 0 ? (N + rpw - 1) / rpw : 0;
-  // the last block must not run past the matrix
-  if (static_cast<long long>(f.count - 1) * f.stride + f.depth > static_cast<long long>(N) * row_bytes) --f.count;
-  return f;
-}
-
 int gemv_tma_launch(cudaStream_t stream, const GemvBatch& b, int M, size_t smem_bytes, int grid, int n_slots, int slot_stride,
                     int kWarps) {
   const int x_bytes = static_cast<int>(smem_bytes - static_cast<size_t>(kWarps) * n_slots * slot_stride);
@@ -413,13 +370,6 @@ int gemv_tma_launch(cudaStream_t stream, const GemvBatch& b, int M, size_t smem_
   if (s != kOk) return s;
   RK_LAUNCH_CHECK("gemv_tma launch");
   return kOk;
-}
-
-// Non-zero when a bounded wait inside a bulk-copy kernel has timed out since the last call.
-int gemv_timeout_flag() {
-  int v = 0;
-  if (cudaMemcpyFromSymbol(&v, g_gemv_timeout, sizeof(int)) != cudaSuccess) return -1;
-  return v;
 }
 
 }  // namespace rk

@@ -11,6 +11,27 @@
 
 namespace rk {
 
+// ---- status.cu : the device-side failure word and the library's run-time options
+// Bits of the failure word: which kind of kernel gave up on a bounded wait.
+enum TimeoutBit : int { kTimeoutGemv = 1, kTimeoutGemm = 2, kTimeoutTmix = 4, kTimeoutProbe = 8, kTimeoutWkv = 16 };
+int timeout_word(int** device_ptr);           // address of the word on the current device (looked up once per device)
+int* timeout_word_or_null();                  // the same for launchers: nullptr when the lookup fails
+int timeout_read(int* flags, bool clear);     // blocking read (and reset) of the current device's word
+int timeout_status(int flags);                // kOk, or kTimeout with the message set
+int wait_probe(cudaStream_t stream, unsigned polls);  // a kernel whose bounded wait runs out by construction (tests)
+
+// The few switches that exist for measurements and tests; rwkv7_b200_set_option() sets them by name.  Process-wide,
+// read when a call is enqueued.
+struct Options {
+  int gemm_cta_pair = 0;     // 1: the tensor-core GEMM runs as CTA pairs (cta_group::2); measured equal, off by default
+  int expanded_weights = 1;  // 0: quantised models never keep fp16 copies for the tensor-core path
+  int quant_tc_rows = 0;     // > 1: row count from which quantised weights take the tensor-core path (0: built-in)
+  int fp16_tc_rows = 0;      // > 1: the same for fp16 weights
+  int decode_graphs = 1;     // 0: decode steps are enqueued kernel by kernel instead of replaying a CUDA graph
+};
+Options& options();
+int set_option(const char* name, int value);
+
 // ---- wkv7.cu
 int wkv7_fp16(cudaStream_t stream, int B, int T, int C, int H, half* state, const half* r, const half* w,
               const half* w0, int w_mode, const half* k, const half* v, const half* a, const half* b,
@@ -112,11 +133,6 @@ struct LinearArgs {
   const half* copy_src = nullptr;
   half* copy_dst = nullptr;
   int copy_n = 0;
-  // optional hint (first problem of a batch only): fp16 matrices the next GEMV launch in the stream will
-  // read, prefetched into L2 while this launch drains.  pf_launch_rows = total output rows of that launch.
-  const void* pf_w[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
-  int pf_n[6] = {0, 0, 0, 0, 0, 0}, pf_k[6] = {0, 0, 0, 0, 0, 0};
-  int pf_launch_rows = 0;
 };
 int linear(cudaStream_t stream, const LinearArgs& args);
 // Up to 8 independent problems sharing M <= 4 in a single launch.

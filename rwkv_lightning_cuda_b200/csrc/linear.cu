@@ -228,14 +228,7 @@ int linear_batch(cudaStream_t stream, const LinearArgs* args, int n) {
     max_fmt = std::max(max_fmt, a.fmt);
   }
   for (int i = n; i < kMaxSeg; ++i) b.seg[i] = b.seg[0];
-  b.n_pf = 0;
-  for (int i = 0; i < kMaxPrefetch; ++i) {
-    b.pf[i] = GemvPrefetch{nullptr, 0, 0, 0};
-    if (args[0].pf_w[i] && args[0].pf_launch_rows > 0) {
-      const GemvPrefetch f = gemv_tma_prefetch_of(args[0].pf_w[i], args[0].pf_n[i], args[0].pf_k[i], args[0].pf_launch_rows);
-      if (f.count > 0) b.pf[b.n_pf++] = f;
-    }
-  }
+  b.timeout = timeout_word_or_null();
 
   // bulk-copy kernel (shared-memory rings fed by the copy engine); the register-staged kernel below takes what it
   // cannot (row sizes that do not cut into 16-byte pieces, activations too large for shared memory)

@@ -46,12 +46,6 @@ void DevBuf::release() {
   p = nullptr;
   bytes = 0;
 }
-Workspace::~Workspace() {
-  for (int i = 0; i < kSlots; ++i) {
-    if (tokens_pinned[i]) cudaFreeHost(tokens_pinned[i]);
-    if (tokens_copied[i]) cudaEventDestroy(tokens_copied[i]);
-  }
-}
 
 // ------------------------------------------------------------------ model
 Model::Model(const rwkv7_b200_config& cfg) : cfg_(cfg) {
@@ -61,8 +55,19 @@ Model::Model(const rwkv7_b200_config& cfg) : cfg_(cfg) {
   layers_.resize(static_cast<size_t>(cfg.layers));
 }
 Model::~Model() {
+  drop_graphs();
+  for (int i = 0; i < kSlots; ++i) {
+    if (tokens_pinned_[i]) cudaFreeHost(tokens_pinned_[i]);
+    if (tokens_copied_[i]) cudaEventDestroy(tokens_copied_[i]);
+  }
+  if (last_done_) cudaEventDestroy(last_done_);
+  if (timeout_host_) cudaFreeHost(timeout_host_);
+}
+
+void Model::drop_graphs() {
   for (auto& kv : graphs_)
     if (kv.second.exec) cudaGraphExecDestroy(kv.second.exec);
+  graphs_.clear();
 }
 
 int Model::use_device() const {
@@ -282,15 +287,34 @@ int Model::finalize() {
   RK_CUDA(cudaDeviceSynchronize());
   lora_raw_.clear();
   if ((s = quantize(head_)) != kOk) return s;
+  // everything a forward call needs that is not a plain stream operation is set up here, outside any stream capture
+  if ((s = timeout_word(&timeout_dev_)) != kOk) return s;
+  RK_CUDA(cudaMallocHost(reinterpret_cast<void**>(&timeout_host_), sizeof(int)));
+  *timeout_host_ = 0;
+  RK_CUDA(cudaEventCreateWithFlags(&last_done_, cudaEventDisableTiming));
+  for (int i = 0; i < kSlots; ++i) RK_CUDA(cudaEventCreateWithFlags(&tokens_copied_[i], cudaEventDisableTiming));
   finalized_ = true;
   return kOk;
+}
+
+int Model::enqueue_timeout_read(cudaStream_t stream) {
+  RK_REQUIRE(timeout_dev_ && timeout_host_, kNotReady, "model not finalised");
+  RK_CUDA(cudaMemcpyAsync(timeout_host_, timeout_dev_, sizeof(int), cudaMemcpyDeviceToHost, stream));
+  return kOk;
+}
+
+int Model::timeout_result() {
+  const int flags = *timeout_host_;
+  if (!flags) return kOk;
+  *timeout_host_ = 0;
+  cudaMemset(timeout_dev_, 0, sizeof(int));
+  return timeout_status(flags);
 }
 
 int Model::ensure_expanded() {
   if (expanded_state_ != 0 || cfg_.weight_format == RWKV7_B200_FMT_F16) return kOk;
   expanded_state_ = -1;
-  const char* env = getenv("RWKV7_B200_EXPANDED_WEIGHTS");
-  if (env && atoi(env) == 0) return kOk;
+  if (!options().expanded_weights) return kOk;
   std::vector<Matrix*> all;
   for (LayerWeights& L : layers_)
     for (Matrix* m : {&L.Wr, &L.Wk, &L.Wv, &L.Wo, &L.Wkey, &L.Wval}) all.push_back(m);
@@ -381,64 +405,94 @@ int Model::query_capacity(int chunk, rwkv7_b200_capacity* out) const {
   RK_CUDA(cudaMemGetInfo(&out->free_vram_bytes, &out->total_vram_bytes));
   const size_t L = cfg_.layers, C = cfg_.channels;
   const size_t state = L * 2 * C * 2 + L * (H_ / tp_size_) * kHead * kHead * (cfg_.wkv32 ? 4 : 2) + sizeof(int);
+  // per sequence: its state, its rows of the activation arena, its split-K partial sums and its logits
   const size_t arena = workspace_halves(cfg_, static_cast<size_t>(chunk), 1) * 2 + static_cast<size_t>(chunk) * 8;
-  out->bytes_per_batch = state + arena + static_cast<size_t>(cfg_.vocab) * 4;
-  out->reserve_vram_bytes = std::max<size_t>(static_cast<size_t>(512) << 20, out->free_vram_bytes / 10);
+  const size_t splitk = static_cast<size_t>(chunk) * C * sizeof(float) * 24;
+  out->bytes_per_batch = state + arena + splitk + static_cast<size_t>(cfg_.vocab) * 4;
+  // beside the reference's reserve: what the workspace may still have to grow by that does not scale with the batch
+  // (the cap of the split-K scratch, one expanded matrix of a quantised model), less what it holds already
+  size_t fixed = static_cast<size_t>(512) << 20;
+  if (cfg_.weight_format != RWKV7_B200_FMT_F16 && expanded_state_ != 1)
+    fixed += std::max(static_cast<size_t>(cfg_.vocab) * C, static_cast<size_t>(cfg_.ffn) * C) * sizeof(half);
+  const size_t held = workspace_bytes();
+  fixed = fixed > held ? fixed - held : 0;
+  out->reserve_vram_bytes = std::max<size_t>(static_cast<size_t>(512) << 20, out->free_vram_bytes / 10) + fixed;
   const size_t usable = out->free_vram_bytes > out->reserve_vram_bytes ? out->free_vram_bytes - out->reserve_vram_bytes : 0;
-  out->max_batch_size = static_cast<int>(std::min<size_t>(usable / out->bytes_per_batch, std::numeric_limits<int>::max()));
+  // the split-K scratch stops growing at its cap: do not count it beyond that
+  size_t n = usable / out->bytes_per_batch;
+  if (n * splitk > (static_cast<size_t>(512) << 20)) {
+    const size_t per = out->bytes_per_batch - splitk;
+    const size_t rest = usable > (static_cast<size_t>(512) << 20) ? usable - (static_cast<size_t>(512) << 20) : 0;
+    n = std::max(rest / per, (static_cast<size_t>(512) << 20) / splitk);
+  }
+  out->max_batch_size = static_cast<int>(std::min<size_t>(n, std::numeric_limits<int>::max()));
   return kOk;
 }
 
-Workspace* Model::workspace(int B, int T) {
-  auto key = std::make_pair(B, T);
-  auto it = workspaces_.find(key);
-  if (it != workspaces_.end()) return it->second.get();
-  auto ws = std::make_unique<Workspace>();
+// Points ws_ at buffers for a forward of B sequences x T tokens.  The buffers only ever grow; growing waits for the
+// device (earlier calls may still be using the old ones) and drops the captured decode graphs, which hold their
+// addresses.  Must not be called while a stream is being captured.
+int Model::prepare(int B, int T, cudaStream_t stream) {
   const size_t rows = static_cast<size_t>(B) * T, C = cfg_.channels, F = cfg_.ffn;
-  ws->rows = static_cast<int>(rows);
-  ws->B = B;
-  const size_t halves = workspace_halves(cfg_, rows, B);
-  if (ws->arena.alloc(halves * 2 + rows * 8 + 256) != kOk) return nullptr;
-  half* p = ws->arena.as<half>();
-  auto take = [&](size_t n) { half* q = p; p += (n + 7) & ~static_cast<size_t>(7); return q; };
-  const size_t RC = rows * C;
-  ws->xA = take(RC); ws->xB = take(RC);
-  for (int i = 0; i < 6; ++i) ws->xm[i] = take(RC);
-  ws->r = take(RC); ws->k = take(RC); ws->v = take(RC); ws->vfirst = take(RC); ws->vout = take(RC);
-  ws->w12 = take(RC); ws->a12 = take(RC); ws->g = take(RC); ws->k2 = take(RC); ws->nkk = take(RC); ws->kka = take(RC);
-  ws->y = take(RC); ws->y2 = take(RC); ws->att = take(RC); ws->mixed = take(RC); ws->ffn = take(RC);
-  ws->hid = take(rows * F);
-  for (int i = 0; i < 4; ++i) ws->l1[i] = take(rows * 512);
-  ws->xf = take(static_cast<size_t>(B) * C);
-  ws->n1 = take(RC); ws->n2 = take(RC);
-  ws->tokens = reinterpret_cast<int64_t*>(take(rows * 4 + 8));
-  if (tp_size_ > 1) {
-    const size_t n = std::max(rows * C, static_cast<size_t>(B) * cfg_.vocab * 2);
-    if (ws->part32.alloc(n * sizeof(float)) != kOk) return nullptr;
-  }
+  const size_t arena_bytes = workspace_halves(cfg_, rows, B) * 2 + rows * 8 + 256;
+  size_t scratch_bytes = 0, wq_bytes = 0, part_bytes = 0;
   if (rows >= 2) {
-    const size_t want = std::min<size_t>(static_cast<size_t>(512) << 20, rows * C * sizeof(float) * 24);
-    if (ws->gemm_scratch.alloc(want) != kOk) return nullptr;
-    if (cfg_.weight_format != RWKV7_B200_FMT_F16 && expanded_state_ != 1) {
-      const size_t big = std::max(static_cast<size_t>(cfg_.vocab) * C, F * C) * sizeof(half);
-      if (ws->wq_scratch.alloc(big) != kOk) return nullptr;
+    scratch_bytes = std::min<size_t>(static_cast<size_t>(512) << 20, rows * C * sizeof(float) * 24);
+    if (cfg_.weight_format != RWKV7_B200_FMT_F16 && expanded_state_ != 1)
+      wq_bytes = std::max(static_cast<size_t>(cfg_.vocab) * C, F * C) * sizeof(half);
+  }
+  if (tp_size_ > 1) part_bytes = std::max(rows * C, static_cast<size_t>(B) * cfg_.vocab * 2) * sizeof(float);
+  const bool grow = arena_bytes > arena_.bytes || scratch_bytes > gemm_scratch_.bytes || wq_bytes > wq_scratch_.bytes ||
+                    part_bytes > part32_.bytes || rows > pinned_rows_;
+  if (grow) {
+    RK_CUDA(cudaDeviceSynchronize());
+    drop_graphs();
+    int s;
+    if (arena_bytes > arena_.bytes && (s = arena_.alloc(arena_bytes)) != kOk) return s;
+    if (scratch_bytes > gemm_scratch_.bytes && (s = gemm_scratch_.alloc(scratch_bytes)) != kOk) return s;
+    if (wq_bytes > wq_scratch_.bytes && (s = wq_scratch_.alloc(wq_bytes)) != kOk) return s;
+    if (part_bytes > part32_.bytes && (s = part32_.alloc(part_bytes)) != kOk) return s;
+    if (rows > pinned_rows_) {
+      for (int i = 0; i < kSlots; ++i) {
+        if (tokens_pinned_[i]) cudaFreeHost(tokens_pinned_[i]);
+        tokens_pinned_[i] = nullptr;
+      }
+      pinned_rows_ = 0;
+      for (int i = 0; i < kSlots; ++i) RK_CUDA(cudaMallocHost(reinterpret_cast<void**>(&tokens_pinned_[i]), rows * sizeof(int64_t)));
+      pinned_rows_ = rows;
     }
   }
-  for (int i = 0; i < Workspace::kSlots; ++i) {
-    if (cudaMallocHost(&ws->tokens_pinned[i], rows * sizeof(int64_t)) != cudaSuccess) return nullptr;
-    if (cudaEventCreateWithFlags(&ws->tokens_copied[i], cudaEventDisableTiming) != cudaSuccess) return nullptr;
-  }
-  Workspace* raw = ws.get();
-  workspaces_[key] = std::move(ws);
-  return raw;
+  Workspace& ws = ws_;
+  ws.rows = static_cast<int>(rows);
+  ws.B = B;
+  half* p = arena_.as<half>();
+  auto take = [&](size_t n) { half* q = p; p += (n + 7) & ~static_cast<size_t>(7); return q; };
+  const size_t RC = rows * C;
+  ws.xA = take(RC); ws.xB = take(RC);
+  for (int i = 0; i < 6; ++i) ws.xm[i] = take(RC);
+  ws.r = take(RC); ws.k = take(RC); ws.v = take(RC); ws.vfirst = take(RC); ws.vout = take(RC);
+  ws.w12 = take(RC); ws.a12 = take(RC); ws.g = take(RC); ws.k2 = take(RC); ws.nkk = take(RC); ws.kka = take(RC);
+  ws.y = take(RC); ws.y2 = take(RC); ws.att = take(RC); ws.mixed = take(RC); ws.ffn = take(RC);
+  ws.hid = take(rows * F);
+  for (int i = 0; i < 4; ++i) ws.l1[i] = take(rows * 512);
+  ws.xf = take(static_cast<size_t>(B) * C);
+  ws.n1 = take(RC); ws.n2 = take(RC);
+  ws.tokens = reinterpret_cast<int64_t*>(take(rows * 4 + 8));
+  ws.gemm_scratch = rows >= 2 ? gemm_scratch_.as<float>() : nullptr;
+  ws.gemm_scratch_bytes = rows >= 2 ? gemm_scratch_.bytes : 0;
+  ws.wq_scratch = wq_bytes ? wq_scratch_.as<half>() : nullptr;
+  ws.wq_scratch_bytes = wq_bytes ? wq_scratch_.bytes : 0;
+  ws.part32 = part32_.as<float>();
+  // the buffers are shared by every call: work enqueued on another stream must be over before this call's begins
+  if (have_last_ && last_stream_ != stream) RK_CUDA(cudaStreamWaitEvent(stream, last_done_, 0));
+  return kOk;
 }
 
 // Row count from which quantised weights take the tensor-core route through their fp16 copies (below it: the GEMV
 // kernels on the packed weights, whose time grows with the row count).  Measured cross-over: 3 rows for W8A16
 // (1.5B: 1.61 vs 1.73 ms per step), 2 rows for W4A16 (2.9B: 2.45 vs 2.97 ms), whose dequantisation costs more per row.
 static int quant_tc_rows(int fmt) {
-  static const int env = [] { const char* e = getenv("RWKV7_B200_QUANT_TC_ROWS"); return e ? atoi(e) : 0; }();
-  if (env >= 2) return env;
+  if (options().quant_tc_rows >= 2) return options().quant_tc_rows;
   return fmt == RWKV7_B200_FMT_W4A16 ? 2 : 3;
 }
 
@@ -453,8 +507,8 @@ int Model::lin(cudaStream_t s, int M, const Matrix& W, const half* x, void* y, i
   a.w_dynamic = false;  // resident weights
   a.prefer_tc = true;   // 2..4 rows of a large matrix: tensor cores (the GEMV's time grows with the row count)
   if (cur_) {
-    a.scratch = cur_->gemm_scratch.as<float>(); a.scratch_bytes = cur_->gemm_scratch.bytes;
-    a.wq_scratch = cur_->wq_scratch.as<half>(); a.wq_scratch_bytes = cur_->wq_scratch.bytes;
+    a.scratch = cur_->gemm_scratch; a.scratch_bytes = cur_->gemm_scratch_bytes;
+    a.wq_scratch = cur_->wq_scratch; a.wq_scratch_bytes = cur_->wq_scratch_bytes;
   }
   return linear(s, a);
 }
@@ -464,7 +518,7 @@ int Model::lin16(cudaStream_t s, int M, int K, int N, const half* x, const half*
   LinearArgs a;
   a.M = M; a.K = K; a.N = N; a.x = x; a.w = w; a.fmt = RWKV7_B200_FMT_F16; a.in_act = in_act; a.epi = epi; a.ea = ea; a.y = y;
   a.w_dynamic = false;
-  if (cur_) { a.scratch = cur_->gemm_scratch.as<float>(); a.scratch_bytes = cur_->gemm_scratch.bytes; }
+  if (cur_) { a.scratch = cur_->gemm_scratch; a.scratch_bytes = cur_->gemm_scratch_bytes; }
   return linear(s, a);
 }
 
@@ -518,14 +572,6 @@ int Model::enqueue_decode(Workspace& ws, int B, half* shift, void* wkv, int* ela
       }
       seg[0].x_out = ws.xA; seg[0].n_out = ws.n1;
     }
-    {  // while this launch drains: the LoRA up matrices of the fused head kernel and the start of att.output
-      const DevBuf* ups[4] = {&W.w2t, &W.a2t, &W.g2t, &W.v2t};
-      const int rk[4] = {cfg_.rank_w, cfg_.rank_a, cfg_.rank_g, cfg_.rank_v};
-      int np = 0;
-      for (int i = 0; i < (li == 0 ? 3 : 4); ++i) { seg[0].pf_w[np] = ups[i]->p; seg[0].pf_n[np] = C; seg[0].pf_k[np] = rk[i]; ++np; }
-      seg[0].pf_w[np] = W.Wo.w.p; seg[0].pf_n[np] = C; seg[0].pf_k[np] = C;
-      seg[0].pf_launch_rows = C;
-    }
     RK_TRY(linear_batch(st, seg, li == 0 ? 6 : 7));
     TmixDecodeArgs ta;
     ta.B = B; ta.C = C; ta.layer0 = li == 0; ta.wkv32 = cfg_.wkv32 != 0;
@@ -542,24 +588,14 @@ int Model::enqueue_decode(Workspace& ws, int B, half* shift, void* wkv, int* ela
     if (li > 0) { ta.shift_src = ws.n1; ta.shift_dst = shift0; }
     RK_TRY(tmix_decode(st, ta));
     LinearArgs wo = mat(W.Wo, ws.y2, ws.att, kEpiNone);
-    wo.pf_w[0] = W.Wkey.w.p; wo.pf_n[0] = W.Wkey.N; wo.pf_k[0] = W.Wkey.K; wo.pf_launch_rows = W.Wkey.N;
     RK_TRY(linear_batch(st, &wo, 1));
     // channel mix: x <- xA + att, LN2, token shift, ffn.key with relu^2
     LinearArgs key = mat(W.Wkey, ws.xA, ws.hid, kEpiRelu2);
     key.res = ws.att; key.ln_w = W.ln2_w.as<half>(); key.ln_b = W.ln2_b.as<half>(); key.shift = shift1;
     key.mix = W.ffn_x_k.as<half>(); key.x_out = ws.xB; key.n_out = ws.n2;
-    key.pf_w[0] = W.Wval.w.p; key.pf_n[0] = W.Wval.N; key.pf_k[0] = W.Wval.K; key.pf_launch_rows = W.Wval.N;
     RK_TRY(linear_batch(st, &key, 1));
     LinearArgs val = mat(W.Wval, ws.hid, ws.ffn, kEpiNone);
     val.copy_src = ws.n2; val.copy_dst = shift1; val.copy_n = B * C;
-    if (li + 1 < L) {
-      const LayerWeights& Nx = layers_[static_cast<size_t>(li) + 1];
-      const Matrix* nm[3] = {&Nx.Wr, &Nx.Wk, &Nx.Wv};
-      for (int i = 0; i < 3; ++i) { val.pf_w[i] = nm[i]->w.p; val.pf_n[i] = C; val.pf_k[i] = C; }
-      val.pf_launch_rows = 3 * C + cfg_.rank_w + cfg_.rank_a + cfg_.rank_g + cfg_.rank_v;
-    } else {
-      val.pf_w[0] = head_.w.p; val.pf_n[0] = head_.N; val.pf_k[0] = head_.K; val.pf_launch_rows = head_.N;
-    }
     RK_TRY(linear_batch(st, &val, 1));
   }
   RK_TRY(advance_i32(st, elapsed, 1, B));
@@ -584,8 +620,7 @@ int Model::enqueue(Workspace& ws, int B, int T, half* shift, void* wkv, int* ela
     const bool quant_tc = cfg_.weight_format != RWKV7_B200_FMT_F16 && expanded_state_ == 1 && rows >= quant_tc_rows(cfg_.weight_format);
     // measured cross-over for fp16 weights: 2 rows from the 1.5B layer width up (1.5B: 1.51 vs 1.53 ms at 2 rows, 1.58 vs
     // 2.18 at 3), 4 rows for narrow models, whose steps are launch-bound (0.1B: 0.42 ms on the GEMV route vs 0.54 at 2 rows)
-    static const int fp16_tc_env = [] { const char* e = getenv("RWKV7_B200_FP16_TC_ROWS"); return e ? atoi(e) : 0; }();
-    const int fp16_tc_rows = fp16_tc_env >= 2 ? fp16_tc_env : (C < 1536 ? 4 : 2);
+    const int fp16_tc_rows = options().fp16_tc_rows >= 2 ? options().fp16_tc_rows : (C < 1536 ? 4 : 2);
     const bool gemv_rows = rows == 1 || (cfg_.weight_format != RWKV7_B200_FMT_F16 && !quant_tc) ||
                            (cfg_.weight_format == RWKV7_B200_FMT_F16 && rows < fp16_tc_rows);
     // (the fused path stages a step's activations in shared memory: B rows of ffn inputs must fit)
@@ -638,7 +673,7 @@ int Model::enqueue(Workspace& ws, int B, int T, half* shift, void* wkv, int* ela
         // 2..4 rows: the three C x C projections as one tensor-core launch, the small LoRA down-projections as one GEMV
         for (int i = 0; i < 3; ++i) {
           seg[i].prefer_tc = true; seg[i].w_dynamic = false;
-          seg[i].scratch = ws.gemm_scratch.as<float>(); seg[i].scratch_bytes = ws.gemm_scratch.bytes;
+          seg[i].scratch = ws.gemm_scratch; seg[i].scratch_bytes = ws.gemm_scratch_bytes;
         }
         RK_TRY(linear_group(st, seg, 3));
         RK_TRY(linear_batch(st, seg + 3, li == 0 ? 3 : 4));
@@ -668,13 +703,13 @@ int Model::enqueue(Workspace& ws, int B, int T, half* shift, void* wkv, int* ela
             a.w = Wm.w16.p; a.fmt = RWKV7_B200_FMT_F16;
             a.out_scale = Wm.fmt == RWKV7_B200_FMT_W8A16 ? Wm.scale.as<half>() : nullptr;
           }
-          a.scratch = ws.gemm_scratch.as<float>(); a.scratch_bytes = ws.gemm_scratch.bytes;
+          a.scratch = ws.gemm_scratch; a.scratch_bytes = ws.gemm_scratch_bytes;
           return a;
         };
         auto low = [&](const DevBuf& w, int K, int N, const half* x, half* y, int epi) {
           LinearArgs a;
           a.M = rows; a.K = K; a.N = N; a.x = x; a.w = w.p; a.fmt = RWKV7_B200_FMT_F16; a.epi = epi; a.y = y; a.w_dynamic = false;
-          a.scratch = ws.gemm_scratch.as<float>(); a.scratch_bytes = ws.gemm_scratch.bytes;
+          a.scratch = ws.gemm_scratch; a.scratch_bytes = ws.gemm_scratch_bytes;
           return a;
         };
         LinearArgs grp[7];
@@ -765,14 +800,14 @@ int Model::enqueue(Workspace& ws, int B, int T, half* shift, void* wkv, int* ela
     if (G == 1) {
       RK_TRY(lin(st, rows, W.Wo, ws.y2, ws.att, kEpiNone));
     } else {
-      RK_TRY(lin(st, rows, W.Wo, ws.y2, ws.part32.p, kEpiRawF32));
-      RK_TRY(tp_.all_reduce_sum(ws.part32.as<float>(), static_cast<size_t>(rows) * C, st));
+      RK_TRY(lin(st, rows, W.Wo, ws.y2, ws.part32, kEpiRawF32));
+      RK_TRY(tp_.all_reduce_sum(ws.part32, static_cast<size_t>(rows) * C, st));
     }
     {
       RowOpArgs a;
       a.B = B; a.T = T; a.C = C; a.x = ws.xA; a.x_out = ws.xB;
       if (G == 1) a.residual = ws.att;
-      else a.residual_f32 = ws.part32.as<float>();
+      else a.residual_f32 = ws.part32;
       a.ln_w = W.ln2_w.as<half>(); a.ln_b = W.ln2_b.as<half>(); a.shift = shift1; a.n_mix = 1;
       a.mix[0] = W.ffn_x_k.as<half>(); a.mix_out[0] = ws.mixed;
       RK_TRY(row_op(st, a));
@@ -784,9 +819,9 @@ int Model::enqueue(Workspace& ws, int B, int T, half* shift, void* wkv, int* ela
       RK_TRY(lin(st, rows, W.Wval, ws.hid, ws.ffn, kEpiNone));
       a.residual = ws.ffn;
     } else {
-      RK_TRY(lin(st, rows, W.Wval, ws.hid, ws.part32.p, kEpiRawF32));
-      RK_TRY(tp_.all_reduce_sum(ws.part32.as<float>(), static_cast<size_t>(rows) * C, st));
-      a.residual_f32 = ws.part32.as<float>();
+      RK_TRY(lin(st, rows, W.Wval, ws.hid, ws.part32, kEpiRawF32));
+      RK_TRY(tp_.all_reduce_sum(ws.part32, static_cast<size_t>(rows) * C, st));
+      a.residual_f32 = ws.part32;
     }
     if (li + 1 < L) {
       const LayerWeights& Nx = layers_[static_cast<size_t>(li) + 1];
@@ -804,7 +839,7 @@ int Model::enqueue(Workspace& ws, int B, int T, half* shift, void* wkv, int* ela
   } else {
     // every rank computes its slice of the vocabulary; gather [G][B][V/G] and interleave to [B][V]
     const int Vl = cfg_.vocab / G;
-    float* loc = ws.part32.as<float>();
+    float* loc = ws.part32;
     float* all = loc + static_cast<size_t>(B) * Vl;
     RK_TRY(lin(st, B, head_, ws.xf, loc, kEpiF32));
     RK_TRY(tp_.all_gather(loc, all, static_cast<size_t>(B) * Vl, st));
@@ -825,34 +860,42 @@ int Model::forward(const int64_t* tokens_host, int B, int T, void* shift, void* 
   int s = use_device();
   if (s != kOk) return s;
   std::lock_guard<std::mutex> lock(mu_);
-  return step(tokens_host, B, T, shift, wkv, elapsed, logits, stream, nullptr);
+  return step(tokens_host, B, T, shift, wkv, elapsed, logits, stream);
 }
 
 // One forward with mu_ held.  tokens_host == nullptr: the ids are in the workspace's device buffer already (written
 // by the greedy pick of the previous step).
 int Model::step(const int64_t* tokens_host, int B, int T, void* shift, void* wkv, int* elapsed, float* logits,
-                cudaStream_t stream, Workspace** ws_out) {
+                cudaStream_t stream) {
   const long long rows = static_cast<long long>(B) * T;
   int s = kOk;
   if (cfg_.weight_format != RWKV7_B200_FMT_F16 && rows >= quant_tc_rows(cfg_.weight_format) && expanded_state_ == 0) {
     s = ensure_expanded();  // before any stream capture: it allocates
     if (s != kOk) return s;
   }
-  Workspace* ws = workspace(B, T);
-  RK_REQUIRE(ws, kCuda, "forward: workspace allocation failed for B=%d T=%d", B, T);
-  if (ws_out) *ws_out = ws;
+  if ((s = prepare(B, T, stream)) != kOk) return s;
+  Workspace* ws = &ws_;
   if (tokens_host) {
-    const int slot = ws->slot;
-    ws->slot = (slot + 1) % Workspace::kSlots;
-    RK_CUDA(cudaEventSynchronize(ws->tokens_copied[slot]));  // the copy that last read this slot is done
-    std::memcpy(ws->tokens_pinned[slot], tokens_host, static_cast<size_t>(rows) * sizeof(int64_t));
-    RK_CUDA(cudaMemcpyAsync(ws->tokens, ws->tokens_pinned[slot], static_cast<size_t>(rows) * sizeof(int64_t), cudaMemcpyHostToDevice, stream));
-    RK_CUDA(cudaEventRecord(ws->tokens_copied[slot], stream));
+    const int slot = slot_;
+    slot_ = (slot + 1) % kSlots;
+    RK_CUDA(cudaEventSynchronize(tokens_copied_[slot]));  // the copy that last read this slot is done
+    std::memcpy(tokens_pinned_[slot], tokens_host, static_cast<size_t>(rows) * sizeof(int64_t));
+    RK_CUDA(cudaMemcpyAsync(ws->tokens, tokens_pinned_[slot], static_cast<size_t>(rows) * sizeof(int64_t), cudaMemcpyHostToDevice, stream));
+    RK_CUDA(cudaEventRecord(tokens_copied_[slot], stream));
   }
+  s = run(*ws, B, T, shift, wkv, elapsed, logits, stream);
+  if (s != kOk) return s;
+  RK_CUDA(cudaEventRecord(last_done_, stream));
+  last_stream_ = stream;
+  have_last_ = true;
+  return kOk;
+}
 
-  // tensor-parallel steps are enqueued directly: their collectives are not recorded into graphs here
-  static const bool no_graph = [] { const char* e = getenv("RWKV7_B200_NO_GRAPH"); return e && atoi(e) != 0; }();  // tuning aid
-  if (T != 1 || stream == nullptr || tp_size_ > 1 || no_graph) {
+int Model::run(Workspace& wsr, int B, int T, void* shift, void* wkv, int* elapsed, float* logits, cudaStream_t stream) {
+  Workspace* ws = &wsr;
+  int s = kOk;
+  // prefill chunks and tensor-parallel steps (whose collectives are not recorded into graphs here) are enqueued directly
+  if (T != 1 || stream == nullptr || tp_size_ > 1 || !options().decode_graphs) {
     const long long before = launch_counter();
     s = enqueue(*ws, B, T, static_cast<half*>(shift), wkv, elapsed, logits, stream);
     launches_ += launch_counter() - before;
@@ -910,14 +953,15 @@ int Model::decode_greedy(const int64_t* first_tokens_host, int B, int steps, voi
   if (s != kOk) return s;
   std::lock_guard<std::mutex> lock(mu_);
   for (int i = 0; i < steps; ++i) {
-    Workspace* ws = nullptr;
-    s = step(i == 0 ? first_tokens_host : nullptr, B, 1, shift, wkv, elapsed, logits, stream, &ws);
+    s = step(i == 0 ? first_tokens_host : nullptr, B, 1, shift, wkv, elapsed, logits, stream);
     if (s != kOk) return s;
+    Workspace* ws = &ws_;
     const long long before = launch_counter();
     s = greedy_pick(stream, B, cfg_.vocab, logits, penalties, presence, repetition, decay, out_tokens + static_cast<size_t>(i) * B,
                     ws->tokens);
     launches_ += launch_counter() - before;
     if (s != kOk) return s;
+    RK_CUDA(cudaEventRecord(last_done_, stream));  // the pick wrote the token buffer after the step's own record
   }
   return kOk;
 }

@@ -53,23 +53,17 @@ struct LayerWeights {
   DevBuf k_k, k_a, r_k, lnx_w, lnx_b, ffn_x_k;
 };
 
-// Activation buffers for one forward of `rows` = B*T rows.
+// Activation buffers of one forward of `rows` = B*T rows: pointers into the model's arena (see Model::prepare).
 struct Workspace {
   int rows = 0, B = 0;
-  DevBuf arena;
   half *xA, *xB, *xm[6], *r, *k, *v, *vfirst, *vout, *w12, *a12, *g, *k2, *nkk, *kka, *y, *y2, *att, *mixed, *ffn;
   half *hid, *l1[4], *xf, *n1, *n2;
   int64_t* tokens;
-  DevBuf gemm_scratch;  // split-K partial sums of the tensor-core GEMM (rows > 4)
-  DevBuf wq_scratch;    // one dequantised fp16 matrix (quantised weights, rows > 4)
-  DevBuf part32;        // tensor parallel: fp32 partial sums [rows, C] / gathered logits
-  // ring of pinned host staging slots for the token ids; a slot is reused only after the copy
-  // that read it has completed, so callers may overwrite their token array as soon as forward returns
-  static constexpr int kSlots = 4;
-  int64_t* tokens_pinned[kSlots] = {nullptr, nullptr, nullptr, nullptr};
-  cudaEvent_t tokens_copied[kSlots] = {nullptr, nullptr, nullptr, nullptr};
-  int slot = 0;
-  ~Workspace();
+  float* gemm_scratch = nullptr;  // split-K partial sums of the tensor-core GEMM (rows >= 2)
+  size_t gemm_scratch_bytes = 0;
+  half* wq_scratch = nullptr;     // one dequantised fp16 matrix (quantised weights without resident fp16 copies)
+  size_t wq_scratch_bytes = 0;
+  float* part32 = nullptr;        // tensor parallel: fp32 partial sums [rows, C] / gathered logits
 };
 
 class Model {
@@ -89,8 +83,13 @@ class Model {
                        void* dst_shift, void* dst_wkv, int* dst_elapsed, int dst_B, int dst_off, int count,
                        cudaStream_t stream) const;
   int query_capacity(int chunk, rwkv7_b200_capacity* out) const;
-  int tp_init(const void* unique_id);
-  int ensure_expanded();  // see Matrix::w16  // joins the tensor-parallel group (collective over all ranks)
+  int tp_init(const void* unique_id);  // joins the tensor-parallel group (collective over all ranks)
+  int ensure_expanded();               // see Matrix::w16
+  // Reads (and resets) the device's failure word through this model's pinned slot; `stream` must have been
+  // given the copy by enqueue_timeout_read and be synchronised by the caller in between.
+  int enqueue_timeout_read(cudaStream_t stream);
+  int timeout_result();
+  size_t workspace_bytes() const { return arena_.bytes + gemm_scratch_.bytes + wq_scratch_.bytes + part32_.bytes; }
 
   const rwkv7_b200_config& cfg() const { return cfg_; }
   long long launches() const { return launches_; }
@@ -116,9 +115,10 @@ class Model {
                    int c0, int nc);
   int transpose_into(DevBuf& dst, const DevBuf& src, int rows, int cols);
   int quantize(Matrix& m);
-  Workspace* workspace(int B, int T);
-  int step(const int64_t* tokens_host, int B, int T, void* shift, void* wkv, int* elapsed, float* logits, cudaStream_t stream,
-           Workspace** ws_out);
+  int prepare(int B, int T, cudaStream_t stream);
+  void drop_graphs();
+  int step(const int64_t* tokens_host, int B, int T, void* shift, void* wkv, int* elapsed, float* logits, cudaStream_t stream);
+  int run(Workspace& ws, int B, int T, void* shift, void* wkv, int* elapsed, float* logits, cudaStream_t stream);
   int enqueue(Workspace& ws, int B, int T, half* shift, void* wkv, int* elapsed, float* logits, cudaStream_t s);
   int enqueue_decode(Workspace& ws, int B, half* shift, void* wkv, int* elapsed, float* logits, cudaStream_t s);
   int lin(cudaStream_t s, int M, const Matrix& W, const half* x, void* y, int epi);
@@ -139,8 +139,25 @@ class Model {
   int emb_dtype_ = -1;
   std::unordered_map<std::string, DevBuf> lora_raw_;  // checkpoint-orientation LoRA matrices
 
+  // One set of activation buffers per model, grown to the largest call seen and never per shape: a server that
+  // walks through many (batch, chunk) shapes holds the memory of the largest one only.  Calls are serialised on
+  // the device as well as on the host: mu_ guards the enqueue, and a call on another stream than the previous one
+  // first waits for that one's work (last_done_), because both would use these buffers.
   std::mutex mu_;
-  std::map<std::pair<int, int>, std::unique_ptr<Workspace>> workspaces_;
+  DevBuf arena_, gemm_scratch_, wq_scratch_, part32_;
+  Workspace ws_;
+  // ring of pinned host staging slots for the token ids; a slot is reused only after the copy that read it has
+  // completed, so callers may overwrite their token array as soon as forward returns
+  static constexpr int kSlots = 4;
+  int64_t* tokens_pinned_[kSlots] = {nullptr, nullptr, nullptr, nullptr};
+  cudaEvent_t tokens_copied_[kSlots] = {nullptr, nullptr, nullptr, nullptr};
+  size_t pinned_rows_ = 0;
+  int slot_ = 0;
+  cudaEvent_t last_done_ = nullptr;
+  cudaStream_t last_stream_ = nullptr;
+  bool have_last_ = false;
+  int* timeout_dev_ = nullptr;   // the device's failure word
+  int* timeout_host_ = nullptr;  // pinned slot it is copied to
   std::map<GraphKey, GraphEntry> graphs_;
   unsigned long long tick_ = 0;
   long long launches_ = 0;

@@ -20,8 +20,6 @@ constexpr float kTwoNeg41 = 4.547473508864641e-13f;
 constexpr float kNegExpHalfLog2e = -0.8750387749145276f;
 constexpr float kNegLog2e = -1.4426950408889634f;
 
-__device__ int g_tmix_timeout = 0;  // set when the bounded wait for the weight rows gives up
-
 struct TmixDev {
   int C, H, layer0, round_act;
   int R[4];               // ranks of w, a, g, v
@@ -34,6 +32,7 @@ struct TmixDev {
   half* y2;
   const half* shift_src;  // optional [B,C] rows to move into the time-mix shift state (this head's 64 channels)
   half* shift_dst;
+  int* timeout;           // the device's failure word: set when the bounded wait for the weight rows gives up
 };
 
 template <bool kWkv32>
@@ -150,7 +149,7 @@ __global__ void __launch_bounds__(256) tmix_decode_kernel(const TmixDev p) {
   cp_async_wait<0>();
   __syncthreads();
   if (!mbar_wait(smem_u32(&wbar), 0)) {  // uniform: every thread waits on the same barrier
-    if (tid == 0) atomicExch(&g_tmix_timeout, 1);
+    if (tid == 0 && p.timeout) atomicOr(p.timeout, kTimeoutTmix);
     return;
   }
 
@@ -355,6 +354,7 @@ int tmix_decode(cudaStream_t stream, const TmixDecodeArgs& a) {
   p.r = a.r; p.k = a.k; p.v = a.v; p.v_first = a.v_first;
   p.w0 = a.w0; p.a0 = a.a0; p.v0 = a.v0; p.k_k = a.k_k; p.k_a = a.k_a; p.r_k = a.r_k; p.lnx_w = a.lnx_w; p.lnx_b = a.lnx_b;
   p.state = a.state; p.elapsed = a.elapsed; p.y2 = a.y2; p.shift_src = a.shift_src; p.shift_dst = a.shift_dst;
+  p.timeout = timeout_word_or_null();
   const int sum_r = a.R[0] + a.R[1] + a.R[2] + (a.layer0 ? 0 : a.R[3]);
   const size_t smem = static_cast<size_t>(kHead) * (sum_r * 2 + 64) + (a.wkv32 ? 0 : 8192);
   const dim3 grid(a.B * p.H), block(256);

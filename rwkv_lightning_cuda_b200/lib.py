@@ -56,6 +56,11 @@ SIGNATURES = {
     "rwkv7_b200_copy_state_slice": [_vp, _vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _i, _vp],
     "rwkv7_b200_query_capacity": [_vp, _i, C.POINTER(Capacity)],
     "rwkv7_b200_kernel_launches": [_vp],
+    "rwkv7_b200_model_workspace_bytes": [_vp, C.POINTER(C.c_size_t)],
+    "rwkv7_b200_timeout_flags": [_i, C.POINTER(_i)],
+    "rwkv7_b200_debug_wait_probe": [_vp, C.c_uint],
+    "rwkv7_b200_debug_last_gemm_splits": [],
+    "rwkv7_b200_set_option": [C.c_char_p, _i],
     "rwkv7_b200_wkv_fp16_seq": [_vp, _i, _i, _i, _i] + [_vp] * 9,
     "rwkv7_b200_wkv_fp16_seq_w0": [_vp, _i, _i, _i, _i] + [_vp] * 10,
     "rwkv7_b200_wkv_fp32io16": [_vp, _i, _i, _i, _i] + [_vp] * 8,
@@ -105,6 +110,18 @@ def load_library() -> C.CDLL:
         fn.restype = _RESTYPES.get(name, C.c_int)
     _LIB = lib
     return lib
+
+
+def set_option(name: str, value: int) -> None:
+    """rwkv7_b200_set_option: process-wide switches for measurements and tests (see the header)."""
+    check(load_library().rwkv7_b200_set_option(name.encode(), int(value)))
+
+
+def timeout_flags(clear: bool = True) -> int:
+    """The current device's failure word (bits: 1 GEMV, 2 GEMM, 4 time-mix, 8 probe, 16 chunked WKV)."""
+    v = C.c_int(0)
+    check(load_library().rwkv7_b200_timeout_flags(int(clear), C.byref(v)))
+    return v.value
 
 
 def check(status: int) -> None:

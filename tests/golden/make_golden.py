@@ -22,6 +22,9 @@ from tests.helpers import h16, ref_lib, wkv_inputs  # noqa: E402
 # the smallest benchmark model's layer shape (the reference's kernels do not launch for much narrower layers), two layers
 # deep and with a short vocabulary so that the fixture stays small
 TINY = dict(layers=2, channels=768, ffn=3072, vocab=1024, rank_w=64, rank_a=64, rank_v=32, rank_g=128)
+# the widest benchmark model's layer shape: the reference has kernels of their own for exactly 4096 channels
+# (cuda/rwkv7_v3a_ops.cu:1353-1513,1637-1885), which no narrower fixture reaches
+WIDE = dict(layers=2, channels=4096, ffn=16384, vocab=1024, rank_w=128, rank_a=128, rank_v=96, rank_g=480)
 
 
 _KEEP = []   # device tensors stay alive until the script ends: a freed temporary's memory would be handed to the next one
@@ -139,13 +142,15 @@ def ops(ref, out):
     print("ref_ops.npz:", len(g), "arrays")
 
 
-def model(ref, out):
+def model(ref, out, dims=TINY, name="ref_model_tiny.npz", lengths=(5, 3), wkv_heads=None):
+    """Logits of every call and the final state of the reference's ModelBackend on the seeded checkpoint of `dims`.
+    wkv_heads: keep only the first so many heads of the WKV state (keeps a wide fixture small)."""
     from rwkv_lightning_cuda_b200 import backend as bk, synthetic
-    d = bk.ModelDims(**TINY)
+    d = bk.ModelDims(**dims)
     ck = synthetic.make_checkpoint(d, seed=0, device="cpu", dtype=torch.bfloat16)
     rng = np.random.default_rng(77)
     B = 1
-    chunks = [rng.integers(0, d.vocab, (B, 5)), rng.integers(0, d.vocab, (B, 3))]
+    chunks = [rng.integers(0, d.vocab, (B, n)) for n in lengths]
     g = {"B": B}
     with tempfile.TemporaryDirectory() as tmp:
         path = os.path.join(tmp, "tiny.pth")
@@ -181,11 +186,13 @@ def model(ref, out):
             for i, (t, lg) in enumerate(calls):
                 g[f"{tag}_tok{i}"] = t
                 g[f"{tag}_logits{i}"] = lg
+            if wkv_heads:
+                wkv = np.ascontiguousarray(wkv[:, :, :wkv_heads])
             g[tag + "_shift"] = shift; g[tag + "_wkv"] = wkv; g[tag + "_elapsed"] = el
             ref.ref_state_destroy(st)
             ref.ref_backend_destroy(be)
-    np.savez_compressed(os.path.join(out, "ref_model_tiny.npz"), **g)
-    print("ref_model_tiny.npz:", len(g), "arrays")
+    np.savez_compressed(os.path.join(out, name), **g)
+    print(name + ":", len(g), "arrays")
 
 
 def main():
@@ -194,9 +201,13 @@ def main():
     ref = ref_lib()
     if ref is None:
         raise SystemExit("oracle/_ref/libref_rwkv7.so is missing: run `make -C oracle ref` where the reference sources are")
+    if "--wide-only" in sys.argv:
+        model(ref, out, WIDE, "ref_model_c4096.npz", lengths=(5, 20), wkv_heads=4)
+        return
     if "--model-only" not in sys.argv:
         ops(ref, out)
     model(ref, out)
+    model(ref, out, WIDE, "ref_model_c4096.npz", lengths=(5, 20), wkv_heads=4)
 
 
 if __name__ == "__main__":

@@ -1,11 +1,13 @@
 """Shared input generators and comparison helpers for the parity tests."""
-import ctypes as C
 import os
+import sys
 
 import numpy as np
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 GOLDEN = os.path.join(ROOT, "tests", "golden")
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
 
 
 def h16(a):
@@ -46,19 +48,4 @@ def ulp_diff16(a, b):
     return np.abs(key(a) - key(b))
 
 
-def ref_lib():
-    """The reference's own kernels built under oracle/_ref/ (None when that build is absent)."""
-    path = os.path.join(ROOT, "oracle", "_ref", "libref_rwkv7.so")
-    if not os.path.exists(path):
-        return None
-    lib = C.CDLL(path)
-    lib.ref_last_error.restype = C.c_char_p
-    lib.ref_backend_create.restype = C.c_void_p
-    lib.ref_state_create.restype = C.c_void_p
-    lib.ref_backend_create.argtypes = [C.c_char_p, C.c_int]
-    lib.ref_backend_destroy.argtypes = [C.c_void_p]
-    lib.ref_state_create.argtypes = [C.c_void_p, C.c_int]
-    lib.ref_state_destroy.argtypes = [C.c_void_p]
-    lib.ref_forward.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p]
-    lib.ref_state_read.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
-    return lib
+from oracle.oracle import ref_lib  # noqa: E402,F401  (the reference's own kernels built under oracle/_ref/)

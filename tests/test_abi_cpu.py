@@ -68,7 +68,8 @@ def test_adapter_compiles_against_the_unmodified_reference_headers():
     """The C++ IModelBackend adapter must build against the reference's own headers (drop-in proof)."""
     import shutil
     import subprocess
-    ref = "/root/reference/include"
+    from oracle.oracle import reference_dir
+    ref = os.path.join(reference_dir(), "include")
     if not os.path.isdir(ref) or shutil.which("g++") is None:
         pytest.skip("reference tree or g++ not present")
     cmd = ["g++", "-std=c++17", "-fsyntax-only", "-I" + ref, "-I/usr/local/cuda/include", "-I" + os.path.join(ROOT, "include"),

@@ -89,8 +89,8 @@ def test_head_gates_and_linear_match_the_reference_kernels(g):
     close16(orc.linear_orig(g["lin_x"], g["lin_W"]), g["lin_y"], 1, 0.97, "linear_orig (reference GEMV)")
 
 
-def golden_model_calls(tag):
-    m = np.load(os.path.join(GOLDEN, "ref_model_tiny.npz"))
+def golden_model_calls(tag, name="ref_model_tiny.npz"):
+    m = np.load(os.path.join(GOLDEN, name))
     calls = [(m[f"{tag}_tok{i}"], m[f"{tag}_logits{i}"]) for i in range(int(m[tag + "_n"]))]
     return m, calls
 
@@ -110,15 +110,27 @@ def oracle_model(dims):
 
 
 GOLDEN_DIMS = dict(layers=2, channels=768, ffn=3072, vocab=1024, rank_w=64, rank_a=64, rank_v=32, rank_g=128)
+GOLDEN_WIDE_DIMS = dict(layers=2, channels=4096, ffn=16384, vocab=1024, rank_w=128, rank_a=128, rank_v=96, rank_g=480)
+# fixture file -> the dimensions its checkpoint was drawn with (seed 0)
+GOLDEN_MODELS = {"ref_model_tiny.npz": GOLDEN_DIMS, "ref_model_c4096.npz": GOLDEN_WIDE_DIMS}
+from oracle.parity import FP32_STATE_REL  # noqa: E402
 
 
+def available_golden_models():
+    return [n for n in GOLDEN_MODELS if os.path.exists(os.path.join(GOLDEN, n))]
+
+
+@pytest.mark.parametrize("name", list(GOLDEN_MODELS))
 @pytest.mark.parametrize("wkv32", [False, True])
-def test_whole_model_matches_the_reference_backend(wkv32):
-    """Prefill chunks of 5 and 3 tokens, then four greedy decode steps: the logits the reference's ModelBackend produced
-    (tolerance: 2e-2 abs for the fp16 state, 1e-4 x 50 of the largest logit for the fp32 state, greedy ids identical)."""
+def test_whole_model_matches_the_reference_backend(wkv32, name):
+    """Two prefill chunks, then four greedy decode steps: the logits the reference's ModelBackend produced
+    (tolerance: 2e-2 abs for the fp16 state, FP32_STATE_REL of the largest logit for the fp32 state, greedy ids
+    identical)."""
+    if name not in available_golden_models():
+        pytest.skip(name + " has not been recorded")
     tag = "s32" if wkv32 else "s16"
-    m, calls = golden_model_calls(tag)
-    d, om, _, _ = oracle_model(GOLDEN_DIMS)
+    m, calls = golden_model_calls(tag, name)
+    d, om, _, _ = oracle_model(GOLDEN_MODELS[name])
     B = int(m["B"])
     shift, wkv, elapsed = om.new_state(B, wkv32)
     worst = 0.0
@@ -127,11 +139,12 @@ def test_whole_model_matches_the_reference_backend(wkv32):
         worst = max(worst, float(np.abs(got - want).max() / (np.abs(want).max() if wkv32 else 1.0)))
         assert (got.argmax(-1) == want.argmax(-1)).all()
     print(f"[golden] oracle vs reference backend ({tag}): worst logit err {worst:.3e}")
-    assert worst < (1e-4 * 50 if wkv32 else 2e-2)
+    assert worst < (FP32_STATE_REL if wkv32 else 2e-2)
     assert (elapsed == m[tag + "_elapsed"]).all()
     assert np.abs(shift.astype(np.float32) - m[tag + "_shift"].astype(np.float32)).max() < 2e-2
     ref_wkv = m[tag + "_wkv"].astype(np.float32)
-    assert np.abs(wkv.astype(np.float32) - ref_wkv).max() <= 2e-2 * max(1.0, float(np.abs(ref_wkv).max()))
+    mine = wkv.astype(np.float32)[:, :, :ref_wkv.shape[2]]      # wide fixtures keep the first heads only
+    assert np.abs(mine - ref_wkv).max() <= 2e-2 * max(1.0, float(np.abs(ref_wkv).max()))
 
 
 def test_greedy_pick_reproduces_the_reference_sampler_tests_known_answers():

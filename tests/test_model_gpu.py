@@ -1,62 +1,16 @@
 """Whole-model parity: the C-ABI forward (prefill chunks + decode steps) against the CPU oracle
 on a small seeded random-init model, for fp16 / fp32 WKV state and the three weight formats.
-Tolerances are the benchmark definition's: logits within 2e-2 abs (fp16 state) and 1e-4 relative
-(fp32 state, relative to the largest logit), greedy token ids identical."""
+Tolerances: logits within 2e-2 abs (fp16 state, the benchmark definition's), within FP32_STATE_REL of the largest
+logit for the fp32 state (the benchmark's 1e-4 holds for the state recurrence, checked at op level; whole logits carry
+the fp16 rounding of every activation, see tests/test_golden_cpu.py), greedy token ids identical."""
 import numpy as np
 import pytest
 import torch
 
 from oracle import oracle as orc
-from tests.helpers import h16
+from oracle.parity import FP32_STATE_REL, TINY, build_pair, run_both  # noqa: F401
 
 pytestmark = pytest.mark.gpu
-
-TINY = dict(layers=3, channels=128, ffn=512, vocab=320, rank_w=32, rank_a=32, rank_v=16, rank_g=64)
-
-
-def build_pair(fmt, wkv32, seed=0, dims=TINY, **backend_kw):
-    from rwkv_lightning_cuda_b200 import backend as bk, synthetic
-    d = bk.ModelDims(**dims)
-    ck = synthetic.make_checkpoint(d, seed=seed, device="cpu", dtype=torch.float16)
-    ck16 = {k: v for k, v in ck.items()}
-    table = orc.emb_ln0(ck["emb.weight"].float().numpy(), ck["blocks.0.ln0.weight"].float().numpy(),
-                        ck["blocks.0.ln0.bias"].float().numpy())
-    om = orc.Model(d.layers, d.channels, d.ffn, d.vocab, d.rank_w, d.rank_a, d.rank_v, d.rank_g, fmt)
-    om.set("emb_ln0", table)
-    dev_tensors = {"emb_ln0": torch.from_numpy(table)}
-    for name, t in ck16.items():
-        if name in ("emb.weight", "blocks.0.ln0.weight", "blocks.0.ln0.bias"):
-            continue
-        om.set(name, t.numpy())
-        dev_tensors[name] = t
-    gm = bk.ModelBackend(d, dev_tensors, use_wkv32=wkv32, weight_format=fmt, **backend_kw)
-    return d, om, gm
-
-
-def run_both(d, om, gm, wkv32, B, chunks, n_decode, seed=1):
-    from rwkv_lightning_cuda_b200 import backend as bk
-    rng = np.random.default_rng(seed)
-    shift, wkv, elapsed = om.new_state(B, wkv32)
-    st = gm.create_state(B)
-    lg = bk.DeviceLogits()
-    worst = 0.0
-    for T in chunks:
-        toks = rng.integers(0, d.vocab, (B, T))
-        want = om.forward(toks, shift, wkv, elapsed, lora_round_act=int(B * T > 4))
-        gm.forward_prefill(toks.tolist(), st, lg)
-        got = lg.values.cpu().numpy()
-        worst = max(worst, np.abs(got - want).max() / (np.abs(want).max() if wkv32 else 1.0))
-    ids_o = want.argmax(-1); ids_g = got.argmax(-1)
-    agree = []
-    for _ in range(n_decode):
-        agree.append((ids_o == ids_g).all())
-        want = om.forward(ids_o[:, None], shift, wkv, elapsed, lora_round_act=int(B > 4))
-        gm.forward_decode(ids_o.tolist(), st, lg)
-        got = lg.values.cpu().numpy()
-        worst = max(worst, np.abs(got - want).max() / (np.abs(want).max() if wkv32 else 1.0))
-        ids_o = want.argmax(-1); ids_g = got.argmax(-1)
-    agree.append((ids_o == ids_g).all())
-    return worst, all(agree), (shift, wkv, elapsed), st
 
 
 @pytest.mark.parametrize("wkv32", [False, True])
@@ -65,7 +19,7 @@ def test_forward_matches_oracle_fp16_weights(wkv32, B, chunks, n_decode):
     d, om, gm = build_pair(orc.FMT_F16, wkv32)
     worst, ids_ok, (shift, wkv, elapsed), st = run_both(d, om, gm, wkv32, B, chunks, n_decode)
     print(f"[parity] model fp16 weights wkv32={wkv32} B={B} chunks={chunks}: worst logit err {worst:.3e}")
-    assert worst < (1e-4 * 50 if wkv32 else 2e-2)   # see module docstring; fp16 activations bound the fp32-state case
+    assert worst < (FP32_STATE_REL if wkv32 else 2e-2)   # fp16 activations bound the fp32-state case: see FP32_STATE_REL
     assert ids_ok
     assert (st.elapsed.cpu().numpy() == elapsed).all()
     g_shift = st.shift.cpu().numpy().astype(np.float32)
@@ -161,15 +115,19 @@ def test_full_size_0p1B_prefill_and_greedy_decode_match_the_oracle():
     assert (st.elapsed.cpu().numpy() == elapsed).all()
 
 
+@pytest.mark.parametrize("name", ["ref_model_tiny.npz", "ref_model_c4096.npz"])
 @pytest.mark.parametrize("wkv32", [False, True])
-def test_library_matches_the_reference_backend_golden(wkv32):
+def test_library_matches_the_reference_backend_golden(wkv32, name):
     """The library against what the reference's own ModelBackend produced on a B200 for the same checkpoint and tokens
-    (tests/golden/ref_model_tiny.npz): prefill chunks of 5 and 3 tokens, four greedy decode steps, final state."""
+    (tests/golden/ref_model_*.npz): two prefill chunks, four greedy decode steps, final state; at the 0.1B layer shape
+    and at the 7.2B layer shape (4096 channels, for which the reference has kernels of their own)."""
     from rwkv_lightning_cuda_b200 import backend as bk
-    from tests.test_golden_cpu import GOLDEN_DIMS, golden_model_calls
+    from tests.test_golden_cpu import FP32_STATE_REL, GOLDEN_MODELS, available_golden_models, golden_model_calls
+    if name not in available_golden_models():
+        pytest.skip(name + " has not been recorded")
     tag = "s32" if wkv32 else "s16"
-    m, calls = golden_model_calls(tag)
-    d, om, gm = build_pair(orc.FMT_F16, wkv32, dims=GOLDEN_DIMS)
+    m, calls = golden_model_calls(tag, name)
+    d, om, gm = build_pair(orc.FMT_F16, wkv32, dims=GOLDEN_MODELS[name], oracle_model=False)
     B = int(m["B"])
     st = gm.create_state(B); lg = bk.DeviceLogits()
     worst = 0.0
@@ -181,12 +139,13 @@ def test_library_matches_the_reference_backend_golden(wkv32):
         got = lg.values.cpu().numpy()
         worst = max(worst, float(np.abs(got - want).max() / (np.abs(want).max() if wkv32 else 1.0)))
         assert (got.argmax(-1) == want.argmax(-1)).all()
-    print(f"[parity] library vs reference backend ({tag}): worst logit err {worst:.3e}")
-    assert worst < (1e-4 * 50 if wkv32 else 2e-2)
+    print(f"[parity] library vs reference backend ({name}, {tag}): worst logit err {worst:.3e}")
+    assert worst < (FP32_STATE_REL if wkv32 else 2e-2)
     assert (st.elapsed.cpu().numpy() == m[tag + "_elapsed"]).all()
     assert np.abs(st.shift.cpu().numpy().astype(np.float32) - m[tag + "_shift"].astype(np.float32)).max() < 2e-2
     ref_wkv = m[tag + "_wkv"].astype(np.float32)
-    assert np.abs(st.wkv_state.cpu().numpy().astype(np.float32) - ref_wkv).max() <= 2e-2 * max(1.0, float(np.abs(ref_wkv).max()))
+    mine = st.wkv_state.cpu().numpy().astype(np.float32)[:, :, :ref_wkv.shape[2]]
+    assert np.abs(mine - ref_wkv).max() <= 2e-2 * max(1.0, float(np.abs(ref_wkv).max()))
 
 
 @pytest.mark.parametrize("use_stream", [False, True])     # default stream: eager launches; side stream: graph replay

@@ -251,8 +251,8 @@ def test_bad_arguments_return_status_not_abort(ops):
 
 
 def test_linear_fp16_cta_pair_kernel():
-    """The opt-in CTA-pair (cta_group::2) variant of the tensor-core GEMM gives the same results.  The switch is read
-    once per process, so the check runs in a child process."""
+    """The opt-in CTA-pair (cta_group::2) variant of the tensor-core GEMM gives the same results.  The switch is
+    process-wide, so the check runs in a child process."""
     import os
     import subprocess
     import sys
@@ -260,9 +260,10 @@ def test_linear_fp16_cta_pair_kernel():
     code = (
         "import numpy as np, torch\n"
         "from oracle import oracle as orc\n"
-        "from rwkv_lightning_cuda_b200 import ops\n"
+        "from rwkv_lightning_cuda_b200 import ops, lib\n"
         "from tests.helpers import h16\n"
         "from tests.test_ops_gpu import assert_close16\n"
+        "lib.set_option('gemm_cta_pair', 1)\n"
         "rng = np.random.default_rng(5)\n"
         "for M, K, N in ((256, 1024, 640), (40, 96, 130 * 2), (300, 512, 128)):\n"
         "    x = h16(rng.standard_normal((M, K))); W = h16(rng.standard_normal((N, K)) * 0.02)\n"
@@ -271,7 +272,7 @@ def test_linear_fp16_cta_pair_kernel():
         "    got = ops.linear_f16_orig_static(torch.from_numpy(x).cuda(), torch.from_numpy(W).cuda()).cpu().numpy()\n"
         "    assert_close16(got, orc.linear_orig(x, W), max_ulp=2, what='linear split-K (CTA pair)')\n"
         "print('pair ok')\n")
-    env = dict(os.environ, RWKV7_B200_GEMM_PAIR="1", PYTHONPATH=root)
+    env = dict(os.environ, PYTHONPATH=root)
     res = subprocess.run([sys.executable, "-c", code], cwd=root, env=env, capture_output=True, text=True, timeout=600)
     assert res.returncode == 0 and "pair ok" in res.stdout, res.stdout[-2000:] + res.stderr[-4000:]
 
