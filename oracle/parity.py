@@ -11,8 +11,18 @@ TINY = dict(layers=3, channels=128, ffn=512, vocab=320, rank_w=32, rank_a=32, ra
 # fp32 WKV state: worst |logit error| / max |logit| allowed between two implementations of the model.  The benchmark's
 # 1e-4 holds for the state recurrence itself (checked at op level) but not for whole logits: every activation between
 # two kernels is rounded to fp16 (relative half-ulp 4.9e-4) by the reference, the oracle and the library alike, each
-# with its own summation order.
-FP32_STATE_REL = 5e-3
+# with its own summation order.  Measured worst cases: 9.4e-4 oracle vs the reference's recorded logits (0.1B layer
+# shape), 1.14e-3 library vs oracle over the benchmark shapes (7.2B layer shape, 16 rows); the bound is about twice that.
+FP32_STATE_REL = 2.5e-3
+
+
+def fp32_state_bound_vs_reference(rows, ffn):
+    """The same bound against logits RECORDED FROM THE REFERENCE.  For calls of up to 12 rows the reference's FFN
+    down-projection accumulates in fp16 per slice of the hidden dimension and combines the slices with fp16 atomic adds
+    in arbitrary order (cuda/rwkv7_fast_ops_fp16.cu:618-679, launch :966-1008); with a 16384-wide FFN that path alone
+    moves its logits by 3e-3 of the largest one (measured: 2.4e-3 .. 3.4e-3 on such calls against 1.0e-3 on the 20-row
+    call of the same fixture, which takes its fp32-accumulating path).  The oracle and the library accumulate in fp32."""
+    return 2 * FP32_STATE_REL if (rows <= 12 and ffn >= 8192) else FP32_STATE_REL
 
 
 def build_pair(fmt, wkv32, seed=0, dims=TINY, oracle_model=True, **backend_kw):
@@ -37,27 +47,39 @@ def build_pair(fmt, wkv32, seed=0, dims=TINY, oracle_model=True, **backend_kw):
     return d, om, gm
 
 
+def _ids_agree(want, got):
+    """Greedy ids are compared where the oracle itself is decided: a row whose two largest logits lie closer together than
+    twice that row's logit error can legitimately resolve either way (with 64 or 256 random-init sequences per call such
+    near-ties do occur)."""
+    err = np.abs(got - want).max(-1)
+    top2 = np.sort(want, -1)[:, -2:]
+    decided = (top2[:, 1] - top2[:, 0]) > 2 * err
+    return bool((want.argmax(-1) == got.argmax(-1))[decided].all())
+
+
 def run_both(d, om, gm, wkv32, B, chunks, n_decode, seed=1):
+    """Drives the oracle model and the library model through the same prefill chunks and decode steps (both are fed the
+    ORACLE's greedy ids).  Returns (worst logit error -- relative to the largest logit for the fp32 state --, whether
+    the greedy ids agree, the oracle's final state, the library's final state)."""
     from rwkv_lightning_cuda_b200 import backend as bk
     rng = np.random.default_rng(seed)
     shift, wkv, elapsed = om.new_state(B, wkv32)
     st = gm.create_state(B)
     lg = bk.DeviceLogits()
     worst = 0.0
+    agree = []
     for T in chunks:
         toks = rng.integers(0, d.vocab, (B, T))
         want = om.forward(toks, shift, wkv, elapsed, lora_round_act=int(B * T > 4))
         gm.forward_prefill(toks.tolist(), st, lg)
         got = lg.values.cpu().numpy()
         worst = max(worst, np.abs(got - want).max() / (np.abs(want).max() if wkv32 else 1.0))
-    ids_o = want.argmax(-1); ids_g = got.argmax(-1)
-    agree = []
+        agree.append(_ids_agree(want, got))
     for _ in range(n_decode):
-        agree.append((ids_o == ids_g).all())
+        ids_o = want.argmax(-1)
         want = om.forward(ids_o[:, None], shift, wkv, elapsed, lora_round_act=int(B > 4))
         gm.forward_decode(ids_o.tolist(), st, lg)
         got = lg.values.cpu().numpy()
         worst = max(worst, np.abs(got - want).max() / (np.abs(want).max() if wkv32 else 1.0))
-        ids_o = want.argmax(-1); ids_g = got.argmax(-1)
-    agree.append((ids_o == ids_g).all())
+        agree.append(_ids_agree(want, got))
     return worst, all(agree), (shift, wkv, elapsed), st

@@ -37,9 +37,12 @@ def test_static_scratch_linear_matches_the_ordinary_entry_point_twice():
             splits = lib.rwkv7_b200_debug_last_gemm_splits()
             assert splits > 1 or not must_split, f"{(M, K, N)}: expected the K split (and so the built-in array) to be used"
             got = out.cpu().numpy()
+            # next to zero an fp16 ulp is far smaller than the rounding error of an fp32 sum over K products taken in
+            # another order (the K split), so differences below that error never count for more than one ulp
+            atol = 1e-5 * (K / 1024) ** 0.5 * 4
             for ref, name in ((want, "ordinary entry point"), (exact, "oracle")):
                 d = ulp_diff16(got, ref)
-                d = np.where(np.abs(got.astype(np.float32) - ref.astype(np.float32)) <= 1e-5, np.minimum(d, 1), d)
+                d = np.where(np.abs(got.astype(np.float32) - ref.astype(np.float32)) <= atol, np.minimum(d, 1), d)
                 assert d.max() <= 2, f"{(M, K, N)} call {call} vs {name}: max ulp {d.max()}"      # the tolerance of the other tensor-path tests
                 assert (d == 0).mean() >= 0.97
     # sizes beyond the built-in scratch are refused with a clear error, not truncated
