@@ -44,7 +44,7 @@ def test_static_scratch_linear_matches_the_ordinary_entry_point_twice():
                 d = ulp_diff16(got, ref)
                 d = np.where(np.abs(got.astype(np.float32) - ref.astype(np.float32)) <= atol, np.minimum(d, 1), d)
                 assert d.max() <= 2, f"{(M, K, N)} call {call} vs {name}: max ulp {d.max()}"      # the tolerance of the other tensor-path tests
-                assert (d == 0).mean() >= 0.97
+                assert (d == 0).mean() >= (0.95 if must_split else 0.97)      # 32 partial sums added in split order round a few more results the other way
     # sizes beyond the built-in scratch are refused with a clear error, not truncated
     x = torch.zeros((4096, 64), dtype=torch.float16, device="cuda")
     W = torch.zeros((1024, 64), dtype=torch.float16, device="cuda")
