@@ -198,7 +198,6 @@ int rwkv7_b200_debug_wait_probe(void* stream, unsigned polls);
 int rwkv7_b200_debug_last_gemm_splits(void);
 /* Process-wide switches for measurements and tests, read when a call is enqueued:
  *   "gemm_cta_pair" 0|1     tensor-core GEMM as CTA pairs (cta_group::2); default 0 (measured equal)
- *   "expanded_weights" 0|1  quantised models may keep fp16 copies for the tensor-core path; default 1
  *   "quant_tc_rows" n       row count from which quantised weights take the tensor-core path; 0 = built-in
  *   "fp16_tc_rows" n        the same for fp16 weights; 0 = built-in
  *   "decode_graphs" 0|1     decode steps replay a CUDA graph; default 1

@@ -17,6 +17,13 @@
 // Narrow products are split along K so that every SM has work; the fp32 partial sums go to scratch and
 // a second small kernel adds them in split order (the result does not depend on timing).
 //
+// W8A16 / W4A16 weights (kQuant instantiation): TMA brings the PACKED tile (128 rows x 64 int8, or x 32 bytes of
+// nibbles) into a raw staging area of the stage; four more warps -- one thread per weight row -- expand it in
+// registers to the fp16 values the format defines (W8A16: the integer code, the channel scale goes on the
+// accumulator in the epilogue; W4A16: half((q - zero) * scale) with the group's scale and zero) and write the
+// 128-byte-swizzled tile the MMA reads; a second barrier per stage tells the MMA issuer that the tile is ready.
+// HBM traffic is the packed bytes; no fp16 copy of a quantised matrix exists anywhere.
+//
 // Every mbarrier wait is bounded; on a time-out the kernel records it in a device flag, every role
 // leaves its loop, the CTA reaches its final barrier, frees its tensor memory and returns.
 #include <cuda.h>
@@ -39,6 +46,9 @@ constexpr int kBK = 64;   // halves per K block = one 128-byte swizzle row
 constexpr int kEpiThreads = 256;  // eight epilogue warps: two per scheduler, each pair shares a TMEM lane quadrant
 constexpr int kCtrlThreads = 64;   // TMA producer and MMA issuer (one lane of a warp each)
 constexpr int kThreads = kCtrlThreads + kEpiThreads;
+constexpr int kDequantThreads = 256;  // quantised weights only: two groups of 128 (one thread per weight row of a tile)
+                                      // that take alternate stages, so two tiles are being expanded at any time
+constexpr int kRawBytes = kBM * kBK;  // raw staging area of a stage: a packed int8 tile (an int4 tile takes half)
 constexpr int kMaxProb = 8;
 constexpr int kEpiRows = 32;             // activation rows transposed through shared memory at a time
 constexpr int kEpiLd = kBM + 4;          // padded row of the transposition tile (floats)
@@ -54,6 +64,9 @@ struct Prob {
   float* partial;            // [splits, M, N] fp32 partial sums, when splits > 1
   void* y;
   const half* scale;         // optional per-output-channel factor applied to the accumulator
+  int fmt;                   // weight format of this product (0 fp16, 1 W8A16, 2 W4A16)
+  const half* qscale;        // W4A16: [N, K/128] group scales and zeros
+  const half* qzero;
   const half* v;             // kEpiVres
   const half* v_first;
   const half* v0;
@@ -251,10 +264,12 @@ __device__ __forceinline__ Unit decode_unit(const GroupDev& g, int u) {
   return r;
 }
 
-template <bool kPair>
-__global__ void __launch_bounds__(kThreads, 1) gemm_group_kernel(const __grid_constant__ MapPack maps, const GroupDev g) {
+template <bool kPair, bool kQuant>
+__global__ void __launch_bounds__(kThreads + (kQuant ? kDequantThreads : 0), 1)
+    gemm_group_kernel(const __grid_constant__ MapPack maps, const GroupDev g) {
+  static_assert(!(kPair && kQuant), "the CTA-pair variant takes fp16 weights only");
   extern __shared__ __align__(1024) unsigned char smem_raw[];
-  __shared__ __align__(8) uint64_t full_bar[kMaxStages], empty_bar[kMaxStages];
+  __shared__ __align__(8) uint64_t full_bar[kMaxStages], empty_bar[kMaxStages], ready_bar[kMaxStages];
   __shared__ __align__(8) uint64_t acc_full[2], acc_empty[2];
   __shared__ uint32_t tmem_slot;
   __shared__ volatile int failed;
@@ -269,7 +284,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_group_kernel(const __grid_co
   const uint32_t x_bytes = x_rows * 128;
   // the dynamic window is 1024-byte aligned here (required by the 128-byte swizzle): weight ring, activation ring,
   // epilogue tile
-  const uint32_t stage_bytes = kWBytes + x_bytes;
+  const uint32_t stage_bytes = kWBytes + x_bytes + (kQuant ? kRawBytes : 0);  // [fp16 weights][activations][packed weights]
   const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
   float* const epi_tile = reinterpret_cast<float*>(smem_raw + (ring - smem_u32(smem_raw)) + g.stages * stage_bytes);
   constexpr uint32_t kTmemCols = 512;  // two accumulators of up to 256 columns; one CTA per SM
@@ -278,6 +293,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_group_kernel(const __grid_co
     for (int s = 0; s < g.stages; ++s) {
       mbar_init(smem_u32(&full_bar[s]), 1);
       mbar_init(smem_u32(&empty_bar[s]), 1);
+      mbar_init(smem_u32(&ready_bar[s]), kDequantThreads / 2);
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(smem_u32(&acc_full[a]), 1);
@@ -313,8 +329,12 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_group_kernel(const __grid_co
           if (rank == 0) mbar_expect_tx(bar, 2 * stage_bytes);
           tma_load_2d_pair(ring + s * stage_bytes, &maps.w[u.prob], map_to_rank(bar, 0), (u.kb_begin + kb) * kBK,
                            u.n0 + static_cast<int>(rank) * kBM);
+        } else if (kQuant && g.prob[u.prob].fmt != 0) {  // packed tile into the raw area: 64 or 32 bytes per row
+          const int row_bytes = g.prob[u.prob].fmt == 1 ? kBK : kBK / 2;
+          mbar_expect_tx(bar, static_cast<uint32_t>(kBM * row_bytes) + x_bytes);
+          tma_load_2d(ring + s * stage_bytes + kWBytes + x_bytes, &maps.w[u.prob], bar, (u.kb_begin + kb) * row_bytes, u.n0);
         } else {
-          mbar_expect_tx(bar, stage_bytes);
+          mbar_expect_tx(bar, kWBytes + x_bytes);
           tma_load_2d(ring + s * stage_bytes, &maps.w[u.prob], bar, (u.kb_begin + kb) * kBK, u.n0);
         }
       };
@@ -369,6 +389,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_group_kernel(const __grid_co
         for (int kb = 0; kb < u.kblocks; ++kb, ++it) {
           const int s = it % g.stages;
           ok = mbar_wait(smem_u32(&full_bar[s]), (it / g.stages) & 1);
+          if (kQuant && ok) ok = mbar_wait(smem_u32(&ready_bar[s]), (it / g.stages) & 1);  // the expanded tile is written
           if (!ok) break;
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const uint64_t da = smem_desc(ring + s * stage_bytes), db = smem_desc(ring + s * stage_bytes + kWBytes);
@@ -390,6 +411,84 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_group_kernel(const __grid_co
       }
       if (!ok) failed = 1;
     }
+  } else if (kQuant && threadIdx.x >= kThreads) {
+    // ---- dequantisation: thread r expands weight row r of every stage's packed tile into the swizzled fp16 tile.
+    // Row r of the tile is 128 bytes at r * 128; its 16-byte chunk c lives at chunk position c ^ (r & 7).
+    const int r = (static_cast<int>(threadIdx.x) - kThreads) & 127;
+    const int my_parity = (static_cast<int>(threadIdx.x) - kThreads) >> 7;  // this group's stages: it % 2 == my_parity
+    unsigned char* const ring_g = smem_raw + (ring - smem_u32(smem_raw));
+    bool ok = true;
+    int it = 0;
+    for (int ui = first_unit; ui < g.total_units && ok && !failed; ui += unit_stride) {
+      const Unit u = decode_unit(g, ui);
+      const Prob& p = g.prob[u.prob];
+      const int fmt = p.fmt, row = u.n0 + r, groups = p.K >> 7;
+      for (int kb = 0; kb < u.kblocks; ++kb, ++it) {
+        if ((it & 1) != my_parity) continue;
+        const int s = it % g.stages;
+        __half2 sc2 = __floats2half2_rn(0.f, 0.f), add2 = sc2;
+        if (fmt == 2 && row < p.N) {  // this K block's group parameters, requested before the wait for the tile
+          const size_t gi = static_cast<size_t>(row) * groups + (((u.kb_begin + kb) * kBK) >> 7);
+          const half sc = p.qscale[gi];
+          const float z = __half2float(p.qzero[gi]);
+          sc2 = __half2half2(sc);
+          // low nibble: (1024 + q) - (1024 + z); high nibble arrives as 1024 + 16 q: / 16 - (64 + z)
+          add2 = __halves2half2(__hneg(__float2half_rn(1024.f + z)), __hneg(__float2half_rn(64.f + z)));
+        }
+        ok = mbar_wait(smem_u32(&full_bar[s]), (it / g.stages) & 1);
+        if (!ok) break;
+        if (fmt != 0) {
+          unsigned char* stage = ring_g + static_cast<size_t>(s) * stage_bytes;
+          uint4* dst = reinterpret_cast<uint4*>(stage + r * 128);
+          if (fmt == 1) {
+            const uint4* src = reinterpret_cast<const uint4*>(stage + kWBytes + x_bytes + r * kBK);
+            const __half2 bias = __floats2half2_rn(1152.f, 1152.f);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {  // 16 codes -> two chunks of 8 halves
+              const uint4 q = src[c];
+              const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+              uint32_t h[8];
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const uint32_t t = w[i] ^ 0x80808080u;
+                uint32_t h01 = __byte_perm(t, 0x64646464u, 0x4140);
+                uint32_t h23 = __byte_perm(t, 0x64646464u, 0x4342);
+                const __half2 a = __hsub2(*reinterpret_cast<__half2*>(&h01), bias);
+                const __half2 b = __hsub2(*reinterpret_cast<__half2*>(&h23), bias);
+                h[2 * i] = *reinterpret_cast<const uint32_t*>(&a);
+                h[2 * i + 1] = *reinterpret_cast<const uint32_t*>(&b);
+              }
+              dst[(2 * c) ^ (r & 7)] = make_uint4(h[0], h[1], h[2], h[3]);
+              dst[(2 * c + 1) ^ (r & 7)] = make_uint4(h[4], h[5], h[6], h[7]);
+            }
+          } else {
+            const uint4* src = reinterpret_cast<const uint4*>(stage + kWBytes + x_bytes + r * (kBK / 2));
+            const __half2 mul = __floats2half2_rn(1.0f, 0.0625f);
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {  // 32 codes -> four chunks
+              const uint4 q = src[c];
+              const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {  // a word = 8 codes = one chunk; byte b holds codes 2b (low nibble), 2b + 1
+                uint32_t h[4];
+#pragma unroll
+                for (int b = 0; b < 4; ++b) {
+                  const uint32_t both = __byte_perm(w[i], 0u, 0x4040u + 0x0101u * b);  // the byte in both halves
+                  uint32_t pair = (both & 0x00f0000fu) | 0x64006400u;                  // (1024 + lo, 1024 + 16 hi)
+                  const __half2 v = __hmul2(__hfma2(*reinterpret_cast<__half2*>(&pair), mul, add2), sc2);
+                  h[b] = *reinterpret_cast<const uint32_t*>(&v);
+                }
+                dst[(4 * c + i) ^ (r & 7)] = make_uint4(h[0], h[1], h[2], h[3]);
+              }
+            }
+          }
+          // the tile was written through the generic proxy; the tensor core reads it through the async proxy
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        }
+        mbar_arrive(smem_u32(&ready_bar[s]));
+      }
+    }
+    if (!ok) failed = 1;
   } else {
     // ---- epilogue: warp w reads TMEM lanes 32*(w%4) .. +31 = output channels n0 + that
     pdl_wait();  // y and the partial sums may still be read by the previous kernel
@@ -534,7 +633,7 @@ EncodeFn encode_fn() {
 // hundred (pointer, shape) combinations on every call.
 struct MapKey {
   const void* base;
-  int rows, cols, ld, box_rows;
+  int rows, cols, ld, box_rows;  // box_rows < 0: a packed (byte) matrix, box of -box_rows bytes x 128 rows
   bool operator==(const MapKey& o) const {
     return base == o.base && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows;
   }
@@ -569,6 +668,36 @@ int make_map(CUtensorMap* map, const void* base, int rows, int cols, int ld, int
                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   RK_REQUIRE(r == CUDA_SUCCESS, kCuda, "gemm_tc: cuTensorMapEncodeTiled failed with %d (rows=%d cols=%d ld=%d)", static_cast<int>(r), rows, cols, ld);
+  std::lock_guard<std::mutex> lock(mu);
+  if (cache.size() > 8192) cache.clear();
+  cache.emplace(key, *map);
+  return kOk;
+}
+
+// Packed weights: 2-D byte tensor [rows, row_bytes], boxes of box_bytes x 128 rows, no swizzle, zero fill outside.
+int make_map_packed(CUtensorMap* map, const void* base, int rows, int row_bytes, int box_bytes) {
+  static std::mutex mu;
+  static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+  const MapKey key{base, rows, row_bytes, row_bytes, -box_bytes};
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) {
+      *map = it->second;
+      return kOk;
+    }
+  }
+  EncodeFn fn = encode_fn();
+  RK_REQUIRE(fn, kCuda, "gemm_tc: cuTensorMapEncodeTiled is not available from this driver");
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(row_bytes), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(row_bytes)};
+  const cuuint32_t box[2] = {static_cast<cuuint32_t>(box_bytes), static_cast<cuuint32_t>(kBM)};
+  const cuuint32_t elem[2] = {1, 1};
+  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, elem,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  RK_REQUIRE(r == CUDA_SUCCESS, kCuda, "gemm_tc: cuTensorMapEncodeTiled (packed weights) failed with %d (rows=%d row_bytes=%d)",
+             static_cast<int>(r), rows, row_bytes);
   std::lock_guard<std::mutex> lock(mu);
   if (cache.size() > 8192) cache.clear();
   cache.emplace(key, *map);
@@ -678,7 +807,9 @@ Plan make_plan_uncached(const LinearArgs* a, int n, size_t scratch_bytes, int sm
 
 bool problem_ok(const LinearArgs& a) {
   const int ldx = a.ldx ? a.ldx : a.K;
-  return a.fmt == 0 && a.in_act == kActNone && a.K % 8 == 0 && ldx % 8 == 0 && a.M >= 2 && a.N % 4 == 0 &&
+  if (a.fmt == 1 && (a.K % 16 != 0 || !a.scale)) return false;             // packed rows must be 16-byte multiples
+  if (a.fmt == 2 && (a.K % 128 != 0 || !a.scale || !a.zero)) return false;
+  return a.fmt >= 0 && a.fmt <= 2 && a.in_act == kActNone && a.K % 8 == 0 && ldx % 8 == 0 && a.M >= 2 && a.N % 4 == 0 &&
          (reinterpret_cast<uintptr_t>(a.x) & 15u) == 0 && (reinterpret_cast<uintptr_t>(a.w) & 15u) == 0;
 }
 
@@ -713,8 +844,9 @@ int gemm_group(cudaStream_t stream, const LinearArgs* a, int n) {
   {
     std::lock_guard<std::mutex> lock(mu);
     if (!pairs_dev[dev]) {
-      RK_CUDA(cudaFuncSetAttribute(gemm_group_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 225 * 1024));
-      RK_CUDA(cudaFuncSetAttribute(gemm_group_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 225 * 1024));
+      RK_CUDA(cudaFuncSetAttribute(gemm_group_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 225 * 1024));
+      RK_CUDA(cudaFuncSetAttribute(gemm_group_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 225 * 1024));
+      RK_CUDA(cudaFuncSetAttribute(gemm_group_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 225 * 1024));
       cudaLaunchConfig_t probe = {};
       probe.gridDim = dim3(static_cast<unsigned>(sms & ~1));
       probe.blockDim = dim3(kThreads);
@@ -725,14 +857,16 @@ int gemm_group(cudaStream_t stream, const LinearArgs* a, int n) {
       probe.attrs = at;
       probe.numAttrs = 1;
       int clusters = 0;
-      if (cudaOccupancyMaxActiveClusters(&clusters, gemm_group_kernel<true>, &probe) != cudaSuccess || clusters < 1) {
+      if (cudaOccupancyMaxActiveClusters(&clusters, gemm_group_kernel<true, false>, &probe) != cudaSuccess || clusters < 1) {
         cudaGetLastError();
         clusters = -1;
       }
       pairs_dev[dev] = clusters;
     }
   }
-  const bool pair = pair_mode == 1 && pairs_dev[dev] > 0;
+  bool quant = false;
+  for (int i = 0; i < n; ++i) quant = quant || a[i].fmt != 0;
+  const bool pair = pair_mode == 1 && pairs_dev[dev] > 0 && !quant;
   const int walkers = pair ? std::min(pairs_dev[dev], sms / 2) : sms;
   const int bm = pair ? 2 * kBM : kBM;
   const Plan plan = make_plan(a, n, a[0].scratch ? a[0].scratch_bytes : 0, walkers, bm);
@@ -751,8 +885,9 @@ int gemm_group(cudaStream_t stream, const LinearArgs* a, int n) {
   const int x_rows = pair ? g.Nt / 2 : g.Nt;
   const size_t x_bytes = static_cast<size_t>(x_rows) * 128, w_bytes = static_cast<size_t>(kBM) * 128;
   const size_t budget = 224 * 1024 - kEpiBytes;
-  g.stages = static_cast<int>(std::min<size_t>(kMaxStages, budget / (x_bytes + w_bytes)));
-  const size_t smem = (w_bytes + x_bytes) * g.stages + kEpiBytes + 1024;
+  const size_t stage_bytes = x_bytes + w_bytes + (quant ? kRawBytes : 0);
+  g.stages = static_cast<int>(std::min<size_t>(kMaxStages, budget / stage_bytes));
+  const size_t smem = stage_bytes * g.stages + kEpiBytes + 1024;
   g.w_dynamic = 0;
   for (int i = 0; i < n; ++i) g.w_dynamic |= a[i].w_dynamic ? 1 : 0;
   g.timeout = timeout_word_or_null();
@@ -763,6 +898,8 @@ int gemm_group(cudaStream_t stream, const LinearArgs* a, int n) {
   for (int i = 0; i < n; ++i) {
     Prob& p = g.prob[i];
     p.M = a[i].M; p.N = a[i].N; p.K = a[i].K; p.epi = a[i].epi; p.y = a[i].y; p.scale = a[i].out_scale;
+    p.fmt = a[i].fmt; p.qscale = a[i].scale; p.qzero = a[i].zero;
+    if (a[i].fmt == 1 && !p.scale) p.scale = a[i].scale;  // W8A16: one scale per output channel, applied to the accumulator
     p.v = a[i].ea.v; p.v_first = a[i].ea.v_first; p.v0 = a[i].ea.v0;
     p.tiles_n = (a[i].N + bm - 1) / bm;
     p.splits = plan.splits[i];
@@ -776,7 +913,10 @@ int gemm_group(cudaStream_t stream, const LinearArgs* a, int n) {
       scratch += static_cast<size_t>(p.splits) * p.M * p.N;
       red += static_cast<int>((static_cast<long long>(p.M) * (p.N / 4) + 255) / 256);
     }
-    int s = make_map(&maps.w[i], a[i].w, a[i].N, a[i].K, a[i].K, kBM);
+    int s;
+    if (a[i].fmt == 0) s = make_map(&maps.w[i], a[i].w, a[i].N, a[i].K, a[i].K, kBM);
+    else if (a[i].fmt == 1) s = make_map_packed(&maps.w[i], a[i].w, a[i].N, a[i].K, kBK);
+    else s = make_map_packed(&maps.w[i], a[i].w, a[i].N, a[i].K / 2, kBK / 2);
     if (s != kOk) return s;
     s = make_map(&maps.x[i], a[i].x, a[i].M, a[i].K, a[i].ldx ? a[i].ldx : a[i].K, x_rows);
     if (s != kOk) return s;
@@ -799,10 +939,13 @@ int gemm_group(cudaStream_t stream, const LinearArgs* a, int n) {
     at[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = at;
     cfg.numAttrs = 2;
-    RK_CUDA(cudaLaunchKernelEx(&cfg, gemm_group_kernel<true>, maps, g));
+    RK_CUDA(cudaLaunchKernelEx(&cfg, gemm_group_kernel<true, false>, maps, g));
+  } else if (quant) {
+    const dim3 grid(static_cast<unsigned>(std::min(walkers, g.total_units))), block(kThreads + kDequantThreads);
+    RK_CUDA(launch_pdl(gemm_group_kernel<false, true>, grid, block, smem, stream, maps, g));
   } else {
     const dim3 grid(static_cast<unsigned>(std::min(walkers, g.total_units))), block(kThreads);
-    RK_CUDA(launch_pdl(gemm_group_kernel<false>, grid, block, smem, stream, maps, g));
+    RK_CUDA(launch_pdl(gemm_group_kernel<false, false>, grid, block, smem, stream, maps, g));
   }
   RK_LAUNCH_CHECK("gemm_group launch");
   if (red > 0) {

@@ -24,7 +24,6 @@ int wait_probe(cudaStream_t stream, unsigned polls);  // a kernel whose bounded 
 // read when a call is enqueued.
 struct Options {
   int gemm_cta_pair = 0;     // 1: the tensor-core GEMM runs as CTA pairs (cta_group::2); measured equal, off by default
-  int expanded_weights = 1;  // 0: quantised models never keep fp16 copies for the tensor-core path
   int quant_tc_rows = 0;     // > 1: row count from which quantised weights take the tensor-core path (0: built-in)
   int fp16_tc_rows = 0;      // > 1: the same for fp16 weights
   int decode_graphs = 1;     // 0: decode steps are enqueued kernel by kernel instead of replaying a CUDA graph
@@ -110,10 +109,7 @@ struct LinearArgs {
   // calls sharing it must not overlap on the GPU
   float* scratch = nullptr;
   size_t scratch_bytes = 0;
-  // optional: room for one dequantised fp16 copy of a W8A16/W4A16 matrix, used when rows > 4 (the weights are
-  // expanded once per call and fed to the tensor-core GEMM); and a per-output-channel factor for the accumulator
-  half* wq_scratch = nullptr;
-  size_t wq_scratch_bytes = 0;
+  // optional per-output-channel factor for the accumulator (tensor-core path)
   const half* out_scale = nullptr;
   // tensor-core path: true when w may have been written by the kernel launched just before this call on the same
   // stream (then its tiles are not requested until that kernel has completed); a model's resident weights set false
@@ -168,7 +164,6 @@ int tmix_decode(cudaStream_t stream, const TmixDecodeArgs& args);
 // ---- quant.cu
 int quant_pack_w8(cudaStream_t stream, int N, int K, const half* W, int8_t* q, half* scale);
 int quant_unpack_w8(cudaStream_t stream, int N, int K, const int8_t* q, const half* scale, half* W);
-int quant_unpack_w8_raw(cudaStream_t stream, int N, int K, const int8_t* q, half* W);  // half(q), scale not applied
 int quant_pack_w4(cudaStream_t stream, int N, int K, const half* W, uint8_t* q, half* scale, half* zero);
 int quant_unpack_w4(cudaStream_t stream, int N, int K, const uint8_t* q, const half* scale, const half* zero, half* W);
 

@@ -276,24 +276,6 @@ int linear(cudaStream_t stream, const LinearArgs& a) {
   int s = check_args(a);
   if (s != kOk) return s;
   if ((a.M > 4 || (a.prefer_tc && a.M >= 2)) && gemm_tc_supported(a)) return gemm_tc(stream, a);
-  if (a.M > 4 && a.fmt != 0 && a.in_act == kActNone && a.wq_scratch &&
-      a.wq_scratch_bytes >= static_cast<size_t>(a.N) * a.K * sizeof(half)) {
-    // quantised weights, many rows: expand to fp16 once, then the tensor-core GEMM
-    LinearArgs b = a;
-    b.fmt = 0;
-    b.w = a.wq_scratch;
-    b.w_dynamic = true;  // written by the unpack kernel launched just below
-    b.scale = nullptr;
-    b.zero = nullptr;
-    if (a.fmt == 1) {
-      s = quant_unpack_w8_raw(stream, a.N, a.K, static_cast<const int8_t*>(a.w), a.wq_scratch);
-      b.out_scale = a.scale;
-    } else {
-      s = quant_unpack_w4(stream, a.N, a.K, static_cast<const uint8_t*>(a.w), a.scale, a.zero, a.wq_scratch);
-    }
-    if (s != kOk) return s;
-    if (gemm_tc_supported(b)) return gemm_tc(stream, b);
-  }
   const int ldx = a.ldx ? a.ldx : a.K;
   const size_t out_elem = (a.epi == kEpiF32 || a.epi == kEpiRawF32) ? sizeof(float) : sizeof(half);
   for (int m0 = 0; m0 < a.M; m0 += 4) {

@@ -311,35 +311,6 @@ int Model::timeout_result() {
   return timeout_status(flags);
 }
 
-int Model::ensure_expanded() {
-  if (expanded_state_ != 0 || cfg_.weight_format == RWKV7_B200_FMT_F16) return kOk;
-  expanded_state_ = -1;
-  if (!options().expanded_weights) return kOk;
-  std::vector<Matrix*> all;
-  for (LayerWeights& L : layers_)
-    for (Matrix* m : {&L.Wr, &L.Wk, &L.Wv, &L.Wo, &L.Wkey, &L.Wval}) all.push_back(m);
-  all.push_back(&head_);
-  size_t need = 0;
-  for (const Matrix* m : all) need += static_cast<size_t>(m->N) * m->K * sizeof(half);
-  size_t free_b = 0, total_b = 0;
-  RK_CUDA(cudaMemGetInfo(&free_b, &total_b));
-  if (need + total_b / 5 > free_b) return kOk;  // keep a fifth of the device free: fall back to expanding per call
-  for (Matrix* m : all) {
-    if (m->w16.alloc(static_cast<size_t>(m->N) * m->K * sizeof(half)) != kOk) {
-      for (Matrix* u : all) u->w16.release();
-      cudaGetLastError();
-      return kOk;
-    }
-    int s;
-    if (m->fmt == RWKV7_B200_FMT_W8A16) s = quant_unpack_w8_raw(nullptr, m->N, m->K, m->w.as<int8_t>(), m->w16.as<half>());
-    else s = quant_unpack_w4(nullptr, m->N, m->K, m->w.as<uint8_t>(), m->scale.as<half>(), m->zero.as<half>(), m->w16.as<half>());
-    if (s != kOk) return s;
-  }
-  RK_CUDA(cudaDeviceSynchronize());
-  expanded_state_ = 1;
-  return kOk;
-}
-
 int Model::tp_init(const void* unique_id) {
   RK_REQUIRE(tp_size_ > 1, kBadArg, "tp_init: the model was created with tp_size <= 1");
   int s = use_device();
@@ -410,10 +381,8 @@ int Model::query_capacity(int chunk, rwkv7_b200_capacity* out) const {
   const size_t splitk = static_cast<size_t>(chunk) * C * sizeof(float) * 24;
   out->bytes_per_batch = state + arena + splitk + static_cast<size_t>(cfg_.vocab) * 4;
   // beside the reference's reserve: what the workspace may still have to grow by that does not scale with the batch
-  // (the cap of the split-K scratch, one expanded matrix of a quantised model), less what it holds already
+  // (the cap of the split-K scratch), less what it holds already
   size_t fixed = static_cast<size_t>(512) << 20;
-  if (cfg_.weight_format != RWKV7_B200_FMT_F16 && expanded_state_ != 1)
-    fixed += std::max(static_cast<size_t>(cfg_.vocab) * C, static_cast<size_t>(cfg_.ffn) * C) * sizeof(half);
   const size_t held = workspace_bytes();
   fixed = fixed > held ? fixed - held : 0;
   out->reserve_vram_bytes = std::max<size_t>(static_cast<size_t>(512) << 20, out->free_vram_bytes / 10) + fixed;
@@ -435,22 +404,17 @@ int Model::query_capacity(int chunk, rwkv7_b200_capacity* out) const {
 int Model::prepare(int B, int T, cudaStream_t stream) {
   const size_t rows = static_cast<size_t>(B) * T, C = cfg_.channels, F = cfg_.ffn;
   const size_t arena_bytes = workspace_halves(cfg_, rows, B) * 2 + rows * 8 + 256;
-  size_t scratch_bytes = 0, wq_bytes = 0, part_bytes = 0;
-  if (rows >= 2) {
-    scratch_bytes = std::min<size_t>(static_cast<size_t>(512) << 20, rows * C * sizeof(float) * 24);
-    if (cfg_.weight_format != RWKV7_B200_FMT_F16 && expanded_state_ != 1)
-      wq_bytes = std::max(static_cast<size_t>(cfg_.vocab) * C, F * C) * sizeof(half);
-  }
+  size_t scratch_bytes = 0, part_bytes = 0;
+  if (rows >= 2) scratch_bytes = std::min<size_t>(static_cast<size_t>(512) << 20, rows * C * sizeof(float) * 24);
   if (tp_size_ > 1) part_bytes = std::max(rows * C, static_cast<size_t>(B) * cfg_.vocab * 2) * sizeof(float);
-  const bool grow = arena_bytes > arena_.bytes || scratch_bytes > gemm_scratch_.bytes || wq_bytes > wq_scratch_.bytes ||
-                    part_bytes > part32_.bytes || rows > pinned_rows_;
+  const bool grow = arena_bytes > arena_.bytes || scratch_bytes > gemm_scratch_.bytes || part_bytes > part32_.bytes ||
+                    rows > pinned_rows_;
   if (grow) {
     RK_CUDA(cudaDeviceSynchronize());
     drop_graphs();
     int s;
     if (arena_bytes > arena_.bytes && (s = arena_.alloc(arena_bytes)) != kOk) return s;
     if (scratch_bytes > gemm_scratch_.bytes && (s = gemm_scratch_.alloc(scratch_bytes)) != kOk) return s;
-    if (wq_bytes > wq_scratch_.bytes && (s = wq_scratch_.alloc(wq_bytes)) != kOk) return s;
     if (part_bytes > part32_.bytes && (s = part32_.alloc(part_bytes)) != kOk) return s;
     if (rows > pinned_rows_) {
       for (int i = 0; i < kSlots; ++i) {
@@ -480,17 +444,15 @@ int Model::prepare(int B, int T, cudaStream_t stream) {
   ws.tokens = reinterpret_cast<int64_t*>(take(rows * 4 + 8));
   ws.gemm_scratch = rows >= 2 ? gemm_scratch_.as<float>() : nullptr;
   ws.gemm_scratch_bytes = rows >= 2 ? gemm_scratch_.bytes : 0;
-  ws.wq_scratch = wq_bytes ? wq_scratch_.as<half>() : nullptr;
-  ws.wq_scratch_bytes = wq_bytes ? wq_scratch_.bytes : 0;
   ws.part32 = part32_.as<float>();
   // the buffers are shared by every call: work enqueued on another stream must be over before this call's begins
   if (have_last_ && last_stream_ != stream) RK_CUDA(cudaStreamWaitEvent(stream, last_done_, 0));
   return kOk;
 }
 
-// Row count from which quantised weights take the tensor-core route through their fp16 copies (below it: the GEMV
-// kernels on the packed weights, whose time grows with the row count).  Measured cross-over: 3 rows for W8A16
-// (1.5B: 1.61 vs 1.73 ms per step), 2 rows for W4A16 (2.9B: 2.45 vs 2.97 ms), whose dequantisation costs more per row.
+// Row count from which quantised weights take the tensor-core route (the GEMM that expands packed tiles in shared
+// memory); below it the GEMV kernels dequantise in registers, and their time grows with the row count.  Measured
+// cross-over: 3 rows for W8A16, 2 rows for W4A16, whose dequantisation costs more per row.
 static int quant_tc_rows(int fmt) {
   if (options().quant_tc_rows >= 2) return options().quant_tc_rows;
   return fmt == RWKV7_B200_FMT_W4A16 ? 2 : 3;
@@ -500,16 +462,10 @@ int Model::lin(cudaStream_t s, int M, const Matrix& W, const half* x, void* y, i
   LinearArgs a;
   a.M = M; a.K = W.K; a.N = W.N; a.x = x; a.w = W.w.p; a.fmt = W.fmt;
   a.scale = W.scale.as<half>(); a.zero = W.zero.as<half>(); a.epi = epi; a.y = y;
-  if (W.w16.p && M >= quant_tc_rows(W.fmt)) {  // expanded copy: straight to the tensor cores
-    a.w = W.w16.p; a.fmt = RWKV7_B200_FMT_F16; a.scale = nullptr; a.zero = nullptr;
-    a.out_scale = W.fmt == RWKV7_B200_FMT_W8A16 ? W.scale.as<half>() : nullptr;
-  }
   a.w_dynamic = false;  // resident weights
-  a.prefer_tc = true;   // 2..4 rows of a large matrix: tensor cores (the GEMV's time grows with the row count)
-  if (cur_) {
-    a.scratch = cur_->gemm_scratch; a.scratch_bytes = cur_->gemm_scratch_bytes;
-    a.wq_scratch = cur_->wq_scratch; a.wq_scratch_bytes = cur_->wq_scratch_bytes;
-  }
+  // 2..4 rows of a large matrix: tensor cores (the GEMV's time grows with the row count)
+  a.prefer_tc = W.fmt == RWKV7_B200_FMT_F16 || M >= quant_tc_rows(W.fmt);
+  if (cur_) { a.scratch = cur_->gemm_scratch; a.scratch_bytes = cur_->gemm_scratch_bytes; }
   return linear(s, a);
 }
 
@@ -617,7 +573,7 @@ int Model::enqueue(Workspace& ws, int B, int T, half* shift, void* wkv, int* ela
     const bool rows_ok = cfg_.weight_format == RWKV7_B200_FMT_F16 ? C % 8 == 0 : (C % 128 == 0 && cfg_.ffn % 128 == 0);
     // Which one-token steps of up to four rows take the five-launch GEMV path (enqueue_decode); the others go through
     // the general path below, with the large matrices on the tensor cores.
-    const bool quant_tc = cfg_.weight_format != RWKV7_B200_FMT_F16 && expanded_state_ == 1 && rows >= quant_tc_rows(cfg_.weight_format);
+    const bool quant_tc = cfg_.weight_format != RWKV7_B200_FMT_F16 && rows >= quant_tc_rows(cfg_.weight_format);
     // measured cross-over for fp16 weights: 2 rows from the 1.5B layer width up (1.5B: 1.51 vs 1.53 ms at 2 rows, 1.58 vs
     // 2.18 at 3), 4 rows for narrow models, whose steps are launch-bound (0.1B: 0.42 ms on the GEMV route vs 0.54 at 2 rows)
     const int fp16_tc_rows = options().fp16_tc_rows >= 2 ? options().fp16_tc_rows : (C < 1536 ? 4 : 2);
@@ -662,14 +618,7 @@ int Model::enqueue(Workspace& ws, int B, int T, half* shift, void* wkv, int* ela
       LinearArgs seg[7] = {mat(W.Wr, xr, ws.r), mat(W.Wk, xk, ws.k), mat(W.Wv, xv, v_lin),
                            low(W.w1t, cfg_.rank_w, xw, ws.l1[0]), low(W.a1t, cfg_.rank_a, xa, ws.l1[1]),
                            low(W.g1t, cfg_.rank_g, xg, ws.l1[2]), low(W.v1t, cfg_.rank_v, xv, ws.l1[3])};
-      if (rows >= 2 && (cfg_.weight_format == RWKV7_B200_FMT_F16 || (W.Wr.w16.p && rows >= quant_tc_rows(cfg_.weight_format)))) {
-        for (int i = 0; i < 3; ++i) {  // quantised: the fp16 copies
-          const Matrix* m3[3] = {&W.Wr, &W.Wk, &W.Wv};
-          if (m3[i]->w16.p) {
-            seg[i].w = m3[i]->w16.p; seg[i].fmt = RWKV7_B200_FMT_F16; seg[i].scale = nullptr; seg[i].zero = nullptr;
-            seg[i].out_scale = m3[i]->fmt == RWKV7_B200_FMT_W8A16 ? m3[i]->scale.as<half>() : nullptr;
-          }
-        }
+      if (rows >= 2 && (cfg_.weight_format == RWKV7_B200_FMT_F16 || rows >= quant_tc_rows(cfg_.weight_format))) {
         // 2..4 rows: the three C x C projections as one tensor-core launch, the small LoRA down-projections as one GEMV
         for (int i = 0; i < 3; ++i) {
           seg[i].prefer_tc = true; seg[i].w_dynamic = false;
@@ -699,10 +648,7 @@ int Model::enqueue(Workspace& ws, int B, int T, half* shift, void* wkv, int* ela
         auto dense = [&](const Matrix& Wm, const half* x, void* y) {
           LinearArgs a;
           a.M = rows; a.K = Wm.K; a.N = Wm.N; a.x = x; a.w = Wm.w.p; a.fmt = Wm.fmt; a.y = y; a.w_dynamic = false;
-          if (Wm.w16.p) {
-            a.w = Wm.w16.p; a.fmt = RWKV7_B200_FMT_F16;
-            a.out_scale = Wm.fmt == RWKV7_B200_FMT_W8A16 ? Wm.scale.as<half>() : nullptr;
-          }
+          a.scale = Wm.scale.as<half>(); a.zero = Wm.zero.as<half>();
           a.scratch = ws.gemm_scratch; a.scratch_bytes = ws.gemm_scratch_bytes;
           return a;
         };
@@ -714,13 +660,7 @@ int Model::enqueue(Workspace& ws, int B, int T, half* shift, void* wkv, int* ela
         };
         LinearArgs grp[7];
         int ng = 0;
-        if (cfg_.weight_format == RWKV7_B200_FMT_F16 || W.Wr.w16.p) {
-          grp[ng++] = dense(W.Wr, xr, ws.r); grp[ng++] = dense(W.Wk, xk, ws.k); grp[ng++] = dense(W.Wv, xv, v_lin);
-        } else {  // quantised matrices without an expanded copy: expanded one at a time through a shared scratch buffer
-          RK_TRY(lin(st, rows, W.Wr, xr, ws.r, kEpiNone));
-          RK_TRY(lin(st, rows, W.Wk, xk, ws.k, kEpiNone));
-          RK_TRY(lin(st, rows, W.Wv, xv, v_lin, kEpiNone));
-        }
+        grp[ng++] = dense(W.Wr, xr, ws.r); grp[ng++] = dense(W.Wk, xk, ws.k); grp[ng++] = dense(W.Wv, xv, v_lin);
         // A few sequences, one token each: the fused time-mix kernel (LoRA up + gates + WKV + GroupNorm, one CTA per
         // sequence and head) replaces five launches; it applies tanh / sigmoid itself, with the many-row rounding.
         TmixDecodeArgs tf;
@@ -869,10 +809,6 @@ int Model::step(const int64_t* tokens_host, int B, int T, void* shift, void* wkv
                 cudaStream_t stream) {
   const long long rows = static_cast<long long>(B) * T;
   int s = kOk;
-  if (cfg_.weight_format != RWKV7_B200_FMT_F16 && rows >= quant_tc_rows(cfg_.weight_format) && expanded_state_ == 0) {
-    s = ensure_expanded();  // before any stream capture: it allocates
-    if (s != kOk) return s;
-  }
   if ((s = prepare(B, T, stream)) != kOk) return s;
   Workspace* ws = &ws_;
   if (tokens_host) {
@@ -894,25 +830,35 @@ int Model::step(const int64_t* tokens_host, int B, int T, void* shift, void* wkv
 int Model::run(Workspace& wsr, int B, int T, void* shift, void* wkv, int* elapsed, float* logits, cudaStream_t stream) {
   Workspace* ws = &wsr;
   int s = kOk;
-  // prefill chunks and tensor-parallel steps (whose collectives are not recorded into graphs here) are enqueued directly
-  if (T != 1 || stream == nullptr || tp_size_ > 1 || !options().decode_graphs) {
+  auto direct = [&]() {
     const long long before = launch_counter();
-    s = enqueue(*ws, B, T, static_cast<half*>(shift), wkv, elapsed, logits, stream);
+    const int r = enqueue(*ws, B, T, static_cast<half*>(shift), wkv, elapsed, logits, stream);
     launches_ += launch_counter() - before;
-    return s;
-  }
-  // Decode step: replay a captured graph (key: batch and the caller's buffers).
-  const GraphKey key{B, shift, wkv, elapsed, logits};
+    return r;
+  };
+  if (stream == nullptr || !options().decode_graphs) return direct();
+  // A call that repeats (same shape, same buffers: decode steps, the chunks of a long prompt) replays a captured graph
+  // from its second occurrence on; the first one is enqueued directly (one-off shapes never pay for a capture, and
+  // libraries that set themselves up on first use -- NCCL -- have done so before anything is captured).
+  const GraphKey key{B, T, shift, wkv, elapsed, logits};
   auto it = graphs_.find(key);
   if (it == graphs_.end()) {
     if (graphs_.size() >= 16) {  // evict the least recently used
       auto victim = graphs_.begin();
       for (auto g = graphs_.begin(); g != graphs_.end(); ++g)
         if (g->second.last_use < victim->second.last_use) victim = g;
-      cudaGraphExecDestroy(victim->second.exec);
+      if (victim->second.exec) cudaGraphExecDestroy(victim->second.exec);
       graphs_.erase(victim);
     }
     GraphEntry e;
+    e.last_use = ++tick_;
+    graphs_.emplace(key, e);
+    return direct();
+  }
+  GraphEntry& e = it->second;
+  e.last_use = ++tick_;
+  if (e.failed) return direct();
+  if (!e.exec) {
     cudaGraph_t graph = nullptr;
     RK_CUDA(cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal));
     const long long before = launch_counter();
@@ -923,15 +869,20 @@ int Model::run(Workspace& wsr, int B, int T, void* shift, void* wkv, int* elapse
       if (graph) cudaGraphDestroy(graph);
       return s;
     }
-    RK_CUDA(ce);
-    const cudaError_t ie = cudaGraphInstantiate(&e.exec, graph, 0);
-    cudaGraphDestroy(graph);
-    RK_CUDA(ie);
-    it = graphs_.emplace(key, e).first;
+    cudaError_t ie = ce;
+    if (ce == cudaSuccess) {
+      ie = cudaGraphInstantiate(&e.exec, graph, 0);
+      cudaGraphDestroy(graph);
+    }
+    if (ie != cudaSuccess) {  // (a collective library that cannot be captured here, ...): nothing ran, enqueue directly
+      cudaGetLastError();
+      e.exec = nullptr;
+      e.failed = true;
+      return direct();
+    }
   }
-  it->second.last_use = ++tick_;
-  RK_CUDA(cudaGraphLaunch(it->second.exec, stream));
-  launches_ += it->second.launches;
+  RK_CUDA(cudaGraphLaunch(e.exec, stream));
+  launches_ += e.launches;
   return kOk;
 }
 

@@ -36,11 +36,7 @@ struct DevBuf {
 // One large matrix in its device format.
 struct Matrix {
   int N = 0, K = 0, fmt = RWKV7_B200_FMT_F16;
-  DevBuf w, scale, zero;
-  // Quantised formats only, optional: the matrix expanded to fp16 once (W8A16: the integer codes, the channel scale is
-  // applied to the accumulator; W4A16: the dequantised values) for calls with more than four rows, which run on the
-  // tensor cores.  Built at the first such call while memory allows; the packed copy keeps serving the GEMV path.
-  DevBuf w16;
+  DevBuf w, scale, zero;  // packed weights and their quantisation parameters (the only copy, whatever the row count)
 };
 
 struct LayerWeights {
@@ -61,8 +57,6 @@ struct Workspace {
   int64_t* tokens;
   float* gemm_scratch = nullptr;  // split-K partial sums of the tensor-core GEMM (rows >= 2)
   size_t gemm_scratch_bytes = 0;
-  half* wq_scratch = nullptr;     // one dequantised fp16 matrix (quantised weights without resident fp16 copies)
-  size_t wq_scratch_bytes = 0;
   float* part32 = nullptr;        // tensor parallel: fp32 partial sums [rows, C] / gathered logits
 };
 
@@ -84,28 +78,28 @@ class Model {
                        cudaStream_t stream) const;
   int query_capacity(int chunk, rwkv7_b200_capacity* out) const;
   int tp_init(const void* unique_id);  // joins the tensor-parallel group (collective over all ranks)
-  int ensure_expanded();               // see Matrix::w16
   // Reads (and resets) the device's failure word through this model's pinned slot; `stream` must have been
   // given the copy by enqueue_timeout_read and be synchronised by the caller in between.
   int enqueue_timeout_read(cudaStream_t stream);
   int timeout_result();
-  size_t workspace_bytes() const { return arena_.bytes + gemm_scratch_.bytes + wq_scratch_.bytes + part32_.bytes; }
+  size_t workspace_bytes() const { return arena_.bytes + gemm_scratch_.bytes + part32_.bytes; }
 
   const rwkv7_b200_config& cfg() const { return cfg_; }
   long long launches() const { return launches_; }
 
  private:
   struct GraphKey {
-    int B;
+    int B, T;
     const void *shift, *wkv, *elapsed, *logits;
     bool operator<(const GraphKey& o) const {
-      return std::tie(B, shift, wkv, elapsed, logits) < std::tie(o.B, o.shift, o.wkv, o.elapsed, o.logits);
+      return std::tie(B, T, shift, wkv, elapsed, logits) < std::tie(o.B, o.T, o.shift, o.wkv, o.elapsed, o.logits);
     }
   };
   struct GraphEntry {
-    cudaGraphExec_t exec = nullptr;
+    cudaGraphExec_t exec = nullptr;  // null until the call has been seen twice (the first one is enqueued directly)
     long long launches = 0;
     unsigned long long last_use = 0;
+    bool failed = false;             // capture did not work for this call: always enqueue directly
   };
 
   int use_device() const;
@@ -128,7 +122,6 @@ class Model {
   rwkv7_b200_config cfg_;
   int H_ = 0;
   int tp_size_ = 1, tp_rank_ = 0;
-  int expanded_state_ = 0;  // 0 not tried, 1 built, -1 unavailable (switched off or not enough memory)
   TpComm tp_;
   bool finalized_ = false;
   std::vector<LayerWeights> layers_;
@@ -144,7 +137,7 @@ class Model {
   // the device as well as on the host: mu_ guards the enqueue, and a call on another stream than the previous one
   // first waits for that one's work (last_done_), because both would use these buffers.
   std::mutex mu_;
-  DevBuf arena_, gemm_scratch_, wq_scratch_, part32_;
+  DevBuf arena_, gemm_scratch_, part32_;
   Workspace ws_;
   // ring of pinned host staging slots for the token ids; a slot is reused only after the copy that read it has
   // completed, so callers may overwrite their token array as soon as forward returns

@@ -46,19 +46,6 @@ __global__ void unpack_w8_kernel(int K, long long total, const int8_t* __restric
   W[i] = __float2half_rn(__fmul_rn(static_cast<float>(q[i]), __half2float(scale[i / K])));
 }
 
-// int8 -> the same integer as a half (exact: |q| <= 127); the tensor-core path multiplies by the
-// per-channel scale after the accumulation, as the W8A16 definition says.
-__global__ void unpack_w8_raw_kernel(long long total, const int8_t* __restrict__ q, half* __restrict__ W) {
-  const long long i = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) * 8;
-  if (i >= total) return;
-  const uint2 v = *reinterpret_cast<const uint2*>(q + i);
-  const int8_t* b = reinterpret_cast<const int8_t*>(&v);
-  __align__(16) half o[8];
-#pragma unroll
-  for (int j = 0; j < 8; ++j) o[j] = __int2half_rn(b[j]);
-  *reinterpret_cast<uint4*>(W + i) = *reinterpret_cast<const uint4*>(o);
-}
-
 // One warp per (row, group of 128): lane handles 4 consecutive weights = 2 packed bytes.
 __global__ void __launch_bounds__(128) pack_w4_kernel(int K, long long n_groups, const half* __restrict__ W,
                                                       uint8_t* __restrict__ q, half* __restrict__ scale,
@@ -124,14 +111,6 @@ int quant_unpack_w8(cudaStream_t stream, int N, int K, const int8_t* q, const ha
   const long long total = static_cast<long long>(N) * K;
   unpack_w8_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, stream>>>(K, total, q, scale, W);
   RK_LAUNCH_CHECK("quant_unpack_w8 launch");
-  return kOk;
-}
-
-int quant_unpack_w8_raw(cudaStream_t stream, int N, int K, const int8_t* q, half* W) {
-  RK_REQUIRE(N > 0 && K > 0 && K % 8 == 0 && W && q, kBadArg, "quant_unpack_w8_raw: bad argument");
-  const long long total = static_cast<long long>(N) * K;
-  unpack_w8_raw_kernel<<<static_cast<unsigned>((total / 8 + 255) / 256), 256, 0, stream>>>(total, q, W);
-  RK_LAUNCH_CHECK("quant_unpack_w8_raw launch");
   return kOk;
 }
 

@@ -84,7 +84,7 @@ int set_option(const char* name, int value) {
   struct Slot { const char* name; int* v; int lo, hi; };
   Options& o = g_options;
   const Slot slots[] = {
-      {"gemm_cta_pair", &o.gemm_cta_pair, 0, 1},         {"expanded_weights", &o.expanded_weights, 0, 1},
+      {"gemm_cta_pair", &o.gemm_cta_pair, 0, 1},
       {"quant_tc_rows", &o.quant_tc_rows, 0, 1 << 20},   {"fp16_tc_rows", &o.fp16_tc_rows, 0, 1 << 20},
       {"decode_graphs", &o.decode_graphs, 0, 1},
   };

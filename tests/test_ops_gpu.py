@@ -172,6 +172,27 @@ def test_quant_pack_bit_exact_and_linear(ops, N, K):
         assert_close16(host(ops.linear_w4a16(dev(x), q4, s4, z4)), orc.linear_w4a16(x, oq4, os4, oz4), max_ulp=1, what="linear_w4a16")
 
 
+@pytest.mark.parametrize("M,K,N", [(5, 256, 64), (64, 2048, 260), (256, 2560, 1024), (200, 1024, 132), (33, 8192, 128), (8, 128, 512)])
+def test_linear_quantised_on_the_tensor_cores(ops, M, K, N):
+    """More than four rows of W8A16 / W4A16 weights: the GEMM that expands the packed tiles in shared memory
+    (ragged N, K long enough for split-K, K blocks that end in the middle of a 128-wide quantisation group)."""
+    from rwkv_lightning_cuda_b200 import lib as L
+    rng = np.random.default_rng(M + K + N)
+    W = h16(rng.standard_normal((N, K)) * 0.02)
+    W[0, :128] = 0
+    W[N - 1, :] = np.float16(-0.015)
+    x = h16(rng.standard_normal((M, K)))
+    q8, s8 = orc.quant_pack_w8(W); q4, s4, z4 = orc.quant_pack_w4(W)
+    got8 = host(ops.linear_w8a16(dev(x), dev(q8), dev(s8)))
+    atol = 1e-5 * 4 * (K / 1024) ** 0.5     # near zero an fp16 ulp is smaller than the rounding of an fp32 sum of K products
+    assert_close16(got8, orc.linear_w8a16(x, q8, s8), max_ulp=2, min_exact=0.95, what="linear_w8a16, tensor cores", atol=atol)
+    got4 = host(ops.linear_w4a16(dev(x), dev(q4), dev(s4), dev(z4)))
+    assert_close16(got4, orc.linear_w4a16(x, q4, s4, z4), max_ulp=2, min_exact=0.95, what="linear_w4a16, tensor cores", atol=atol)
+    r4 = host(ops.linear_w4a16(dev(x), dev(q4), dev(s4), dev(z4), epilogue=L.EPI_RELU2))
+    assert_close16(r4, orc.linear_w4a16(x, q4, s4, z4, epi=orc.EPI_RELU2), max_ulp=4, min_exact=0.95, what="linear_w4a16 relu2", atol=atol)
+    assert L.timeout_flags(clear=True) == 0
+
+
 @pytest.mark.parametrize("B,T,H", [(1, 128, 12), (3, 1, 2), (2, 7, 3), (1, 1, 64)])
 def test_wkv_fp32(ops, B, T, H):
     r, w, k, v, a, b = wkv_inputs(B, T, H, seed=B * 10 + T)

@@ -84,4 +84,6 @@ def test_0p1B_prefill_512_then_256_greedy_steps_against_the_live_reference(tmp_p
     # token-exact wherever the reference itself is decided by more than the two runs' combined error
     decided = margin > 2 * max(err.max(), noise)
     assert same[decided].all()
-    assert same.mean() >= 0.99
+    # elsewhere (fp16 logits tie exactly now and then: the smallest margin is 0) no more disagreements than the
+    # reference has with itself, give or take a few
+    assert int((~same).sum()) <= 2 * flips + 3
