@@ -201,6 +201,7 @@ int rwkv7_b200_debug_last_gemm_splits(void);
  *   "quant_tc_rows" n       row count from which quantised weights take the tensor-core path; 0 = built-in
  *   "fp16_tc_rows" n        the same for fp16 weights; 0 = built-in
  *   "decode_graphs" 0|1     decode steps replay a CUDA graph; default 1
+ *   "wkv_chunked" 0|1       fp32-state WKV over 64 tokens or more runs in matrix form on the tensor cores; default 1
  * BAD_ARG for an unknown name or a value out of range. */
 int rwkv7_b200_set_option(const char* name, int value);
 

@@ -27,6 +27,7 @@ struct Options {
   int quant_tc_rows = 0;     // > 1: row count from which quantised weights take the tensor-core path (0: built-in)
   int fp16_tc_rows = 0;      // > 1: the same for fp16 weights
   int decode_graphs = 1;     // 0: decode steps are enqueued kernel by kernel instead of replaying a CUDA graph
+  int wkv_chunked = 1;       // 0: fp32-state WKV over a chunk runs the per-token scan instead of the matrix form
 };
 Options& options();
 int set_option(const char* name, int value);
@@ -38,6 +39,11 @@ int wkv7_fp16(cudaStream_t stream, int B, int T, int C, int H, half* state, cons
                                                                // tensor-parallel rank's slice starts later): phase of the decay dither
 int wkv7_fp32(cudaStream_t stream, int B, int T, int C, int H, float* state, const half* r, const half* w,
               const half* w0, const half* k, const half* v, const half* a, const half* b, half* y);
+// wkv7_chunk.cu: the same recurrence over a chunk of tokens in matrix form on the tensor cores (wkv7_fp32 dispatches
+// to it for chunks of 64 tokens and more)
+bool wkv7_fp32_chunked_applies(int T);
+int wkv7_fp32_chunked(cudaStream_t stream, int B, int T, int C, int H, float* state, const half* r, const half* w,
+                      const half* w0, const half* k, const half* v, const half* a, const half* b, half* y);
 
 // ---- rowops.cu : LayerNorm / residual / token-shift fusions, one CTA per activation row
 struct RowOpArgs {

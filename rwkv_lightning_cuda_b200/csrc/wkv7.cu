@@ -366,6 +366,7 @@ int wkv7_fp32(cudaStream_t stream, int B, int T, int C, int H, float* state, con
   RK_REQUIRE(state && r && w && k && v && a && b && y, kBadArg, "wkv7_fp32: null pointer");
   RK_REQUIRE(aligned16(state) && aligned16(r) && aligned16(w) && aligned16(k) && aligned16(a) && aligned16(b),
              kBadArg, "wkv7_fp32: tensors must be 16-byte aligned");
+  if (wkv7_fp32_chunked_applies(T) && options().wkv_chunked) return wkv7_fp32_chunked(stream, B, T, C, H, state, r, w, w0, k, v, a, b, y);
   const dim3 grid(B * H), block(256);
   if (T == 1) {
     if (w0) wkv7_fp32_decode_kernel<true><<<grid, block, 0, stream>>>(C, H, state, r, w, w0, k, v, a, b, y);

@@ -14,7 +14,8 @@ pytestmark = pytest.mark.gpu
 
 
 @pytest.mark.parametrize("wkv32", [False, True])
-@pytest.mark.parametrize("B,chunks,n_decode", [(1, (5, 3), 6), (2, (4,), 4), (1, (20,), 2), (6, (2,), 3)])   # last: 5..16 one-token rows
+@pytest.mark.parametrize("B,chunks,n_decode", [(1, (5, 3), 6), (2, (4,), 4), (1, (20,), 2), (6, (2,), 3),   # 5..16 one-token rows
+                                               (2, (70, 64), 2)])   # chunks of 64 tokens and more: the matrix-form WKV for the fp32 state
 def test_forward_matches_oracle_fp16_weights(wkv32, B, chunks, n_decode):
     d, om, gm = build_pair(orc.FMT_F16, wkv32)
     worst, ids_ok, (shift, wkv, elapsed), st = run_both(d, om, gm, wkv32, B, chunks, n_decode)

@@ -34,10 +34,11 @@ def check(tag, dims, fmt, wkv32, B, chunks, n_decode, pair=None):
 
 
 @pytest.mark.parametrize("wkv32", [False, True])
-@pytest.mark.parametrize("B,chunks,n_decode", [(1, (4,), 3), (1, (48,), 1), (4, (1,), 2), (16, (1,), 1)])
+@pytest.mark.parametrize("B,chunks,n_decode", [(1, (4,), 3), (1, (48,), 1), (4, (1,), 2), (16, (1,), 1), (1, (128,), 1)])
 def test_7p2B_layer_shape(wkv32, B, chunks, n_decode):
     """B=1: the five-launch decode path the headline number times (after a 4-row prompt on the same path);
-    a 48-token chunk and 16 one-token rows: the tensor-core path; B=4: four GEMV rows."""
+    a 48-token chunk and 16 one-token rows: the tensor-core path; B=4: four GEMV rows; a 128-token chunk: the prefill
+    configuration's chunk (with the fp32 state: the matrix-form WKV)."""
     check("7.2B shape", D72, orc.FMT_F16, wkv32, B, chunks, n_decode)
 
 
