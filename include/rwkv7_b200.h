@@ -187,7 +187,7 @@ int rwkv7_b200_model_workspace_bytes(const rwkv7_b200_model* m, size_t* out);
  * limit runs out sets a bit in a per-device word and returns instead of hanging.  The calls that synchronise
  * (rwkv7_b200_forward_to_host, rwkv7_b200_decode_greedy with out_tokens_host) report it as
  * RWKV7_B200_TIMEOUT; callers of the asynchronous entry points read it here after synchronising their
- * stream.  *flags: 1 weight-streaming GEMV, 2 tensor-core GEMM, 4 time-mix core, 8 wait probe, 16 chunked WKV.
+ * stream.  *flags: 1 weight-streaming GEMV, 2 tensor-core GEMM, 4 time-mix core, 8 wait probe, 16 all-reduce through peer memory (a rank of the tensor-parallel group did not show up).
  * clear != 0 resets the word.  Blocking (a 4-byte device-to-host copy on the current device). */
 int rwkv7_b200_timeout_flags(int clear, int* flags);
 /* Test aid: enqueues a one-thread kernel that polls a barrier nothing will ever complete `polls` times

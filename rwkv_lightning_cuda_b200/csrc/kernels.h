@@ -13,7 +13,7 @@ namespace rk {
 
 // ---- status.cu : the device-side failure word and the library's run-time options
 // Bits of the failure word: which kind of kernel gave up on a bounded wait.
-enum TimeoutBit : int { kTimeoutGemv = 1, kTimeoutGemm = 2, kTimeoutTmix = 4, kTimeoutProbe = 8, kTimeoutWkv = 16 };
+enum TimeoutBit : int { kTimeoutGemv = 1, kTimeoutGemm = 2, kTimeoutTmix = 4, kTimeoutProbe = 8, kTimeoutPeer = 16 };
 int timeout_word(int** device_ptr);           // address of the word on the current device (looked up once per device)
 int* timeout_word_or_null();                  // the same for launchers: nullptr when the lookup fails
 int timeout_read(int* flags, bool clear);     // blocking read (and reset) of the current device's word

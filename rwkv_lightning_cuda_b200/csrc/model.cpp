@@ -426,6 +426,10 @@ int Model::prepare(int B, int T, cudaStream_t stream) {
       pinned_rows_ = rows;
     }
   }
+  if (tp_size_ > 1) {  // room for this call's partial sums in the region the other ranks have mapped (a collective)
+    const int s = tp_.ensure_peer(rows * C);
+    if (s != kOk) return s;
+  }
   Workspace& ws = ws_;
   ws.rows = static_cast<int>(rows);
   ws.B = B;
@@ -739,6 +743,9 @@ int Model::enqueue(Workspace& ws, int B, int T, half* shift, void* wkv, int* ela
     // partial sums that are added across ranks (NCCL) and rounded to half once, like the single-GPU layer.
     if (G == 1) {
       RK_TRY(lin(st, rows, W.Wo, ws.y2, ws.att, kEpiNone));
+    } else if (tp_.peer_ready()) {  // partial sums into the peer-mapped buffer, summed by one kernel over NVLink
+      RK_TRY(lin(st, rows, W.Wo, ws.y2, tp_.peer_partial(0), kEpiRawF32));
+      RK_TRY(tp_.all_reduce_peer(0, static_cast<size_t>(rows) * C, ws.part32, timeout_dev_, st));
     } else {
       RK_TRY(lin(st, rows, W.Wo, ws.y2, ws.part32, kEpiRawF32));
       RK_TRY(tp_.all_reduce_sum(ws.part32, static_cast<size_t>(rows) * C, st));
@@ -758,6 +765,10 @@ int Model::enqueue(Workspace& ws, int B, int T, half* shift, void* wkv, int* ela
     if (G == 1) {
       RK_TRY(lin(st, rows, W.Wval, ws.hid, ws.ffn, kEpiNone));
       a.residual = ws.ffn;
+    } else if (tp_.peer_ready()) {  // (the two all-reduces of a layer alternate between the two partial buffers)
+      RK_TRY(lin(st, rows, W.Wval, ws.hid, tp_.peer_partial(1), kEpiRawF32));
+      RK_TRY(tp_.all_reduce_peer(1, static_cast<size_t>(rows) * C, ws.part32, timeout_dev_, st));
+      a.residual_f32 = ws.part32;
     } else {
       RK_TRY(lin(st, rows, W.Wval, ws.hid, ws.part32, kEpiRawF32));
       RK_TRY(tp_.all_reduce_sum(ws.part32, static_cast<size_t>(rows) * C, st));

@@ -63,7 +63,7 @@ int timeout_status(int flags) {
   if (!flags) return kOk;
   set_error("a bounded wait inside a kernel ran out (flags 0x%x:%s%s%s%s); the results of that call are incomplete", flags,
             (flags & kTimeoutGemv) ? " weight-streaming GEMV" : "", (flags & kTimeoutGemm) ? " tensor-core GEMM" : "",
-            (flags & kTimeoutTmix) ? " time-mix core" : "", (flags & kTimeoutProbe) ? " wait probe" : "");
+            (flags & kTimeoutTmix) ? " time-mix core" : "", (flags & (kTimeoutProbe | kTimeoutPeer)) ? " wait probe / peer all-reduce" : "");
   return kTimeout;
 }
 

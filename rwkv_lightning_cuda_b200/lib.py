@@ -118,7 +118,7 @@ def set_option(name: str, value: int) -> None:
 
 
 def timeout_flags(clear: bool = True) -> int:
-    """The current device's failure word (bits: 1 GEMV, 2 GEMM, 4 time-mix, 8 probe, 16 chunked WKV)."""
+    """The current device's failure word (bits: 1 GEMV, 2 GEMM, 4 time-mix, 8 probe, 16 peer all-reduce)."""
     v = C.c_int(0)
     check(load_library().rwkv7_b200_timeout_flags(int(clear), C.byref(v)))
     return v.value
