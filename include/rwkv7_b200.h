@@ -156,6 +156,28 @@ int rwkv7_b200_decode_greedy(rwkv7_b200_model* m, const int64_t* first_tokens_ho
                              void* wkv, int* elapsed, float* logits, float* penalties, float presence_penalty,
                              float repetition_penalty, float penalty_decay, int* out_tokens, int* out_tokens_host,
                              void* stream);
+/* The same loop with the sampler's general case -- temperature, top-k, top-p -- instead of the greedy choice
+ * (src/utils/sampling.cu:205-471 with the argument rules of :492-512: top_k <= 0 or > vocab means no limit, top_p outside
+ * [0, 1] means 1, top_p == 0 means greedy, temperature must lie in [0.001, 1000]).  Random numbers are Philox-4x32-10
+ * words keyed by `seed` with the counter (offset + step, sequence): a run is reproducible from (seed, offset), where the
+ * reference's cuRAND states are seeded from the clock (src/rwkv_sampler.cpp:14-19,39-42).  Step i uses offset + i; pass
+ * offset + steps to the next call to continue the stream. */
+typedef struct {
+  float temperature;
+  int top_k;
+  float top_p;
+  unsigned long long seed, offset;
+} rwkv7_b200_sampling;
+int rwkv7_b200_decode_sample(rwkv7_b200_model* m, const int64_t* first_tokens_host, int B, int steps, void* shift,
+                             void* wkv, int* elapsed, float* logits, float* penalties, float presence_penalty,
+                             float repetition_penalty, float penalty_decay, const rwkv7_b200_sampling* sampling,
+                             int* out_tokens, int* out_tokens_host, void* stream);
+/* One draw per row for a caller that runs its own loop (batch_sampling_repetition_temperature_topk_topp_raw,
+ * src/utils/sampling.cu:474-541; penalties NULL: batch_sampling_temperature_topk_topp_raw).  probs is scratch, fp32
+ * [B][V] on the device; out[b] and next_tokens[b] (int64, may be NULL) receive the token. */
+int rwkv7_b200_sample(void* stream, int B, int V, const float* logits, float* penalties, float* probs,
+                      float presence_penalty, float repetition_penalty, float penalty_decay,
+                      const rwkv7_b200_sampling* sampling, int* out, int64_t* next_tokens);
 /* The choice alone, for a caller that runs its own loop: out[b] = argmax_i (logits[b][i] - penalties[b][i]) with the
  * penalty update above; next_tokens (int64 [B], may be NULL) receives the same ids. */
 int rwkv7_b200_greedy_pick(void* stream, int B, int V, const float* logits, float* penalties, float presence_penalty,

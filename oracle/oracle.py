@@ -297,3 +297,74 @@ class Model:
             lib().orc_model_destroy(self.h)
         except Exception:
             pass
+
+
+def philox4x32_first(c0, c1, c2, c3, k0, k1):
+    """First output word of Philox-4x32-10 (Salmon et al. 2011), plain Python integers."""
+    M = 0xFFFFFFFF
+    for _ in range(10):
+        p0, p1 = 0xD2511F53 * c0, 0xCD9E8D57 * c2
+        c0, c1, c2, c3 = ((p1 >> 32) ^ c1 ^ k0) & M, p1 & M, ((p0 >> 32) ^ c3 ^ k1) & M, p0 & M
+        k0, k1 = (k0 + 0x9E3779B9) & M, (k1 + 0xBB67AE85) & M
+    return c0
+
+
+def sample_weights(logits, penalties=None, temperature=1.0, top_k=0, top_p=1.0):
+    """What the sampler keeps of every token's probability, [B, V] float64: the reference's rule
+    (src/utils/sampling.cu:205-399, argument rules :504-512) restated -- softmax of (finite(logit) - penalty) / T, the
+    smallest threshold t whose strictly-greater tokens stay strictly inside both budgets, tokens on the threshold scaled to fill them."""
+    lg = np.asarray(logits, dtype=np.float32)
+    B, V = lg.shape
+    if top_k <= 0 or top_k > V:
+        top_k = V
+    if not (0.0 <= top_p <= 1.0):
+        top_p = 1.0
+    if top_p == 0.0:
+        top_k, top_p = 1, 1.0
+    big = np.float32(np.finfo(np.float32).max)
+    fin = lambda x: np.clip(np.nan_to_num(x, nan=0.0, posinf=big, neginf=-big), -big, big)
+    pen = np.zeros_like(lg) if penalties is None else np.asarray(penalties, dtype=np.float32)
+    z = fin((fin(lg) - pen).astype(np.float32) * np.float32(1.4426950408889634 / temperature)).astype(np.float64)
+    p = np.exp2(z - z.max(-1, keepdims=True))
+    p /= p.sum(-1, keepdims=True)
+    w = np.zeros_like(p)
+    for b in range(B):
+        vals = np.unique(p[b])[::-1]                     # distinct values, descending
+        thr = vals[-1]
+        for v in vals:                                   # the first value at which a budget is reached: everything
+            keep = p[b] >= v                             # strictly above it is still strictly inside both budgets
+            if keep.sum() >= top_k or p[b][keep].sum() >= top_p:
+                thr = v
+                break
+        above, on = p[b] > thr, p[b] == thr
+        n = on.sum()
+        comp = 1.0
+        if n:
+            comp = min(comp, (top_p - p[b][above].sum()) / (thr * n), (top_k - above.sum()) / n)
+            comp = max(comp, 0.0)
+        w[b] = np.where(above, p[b], np.where(on, p[b] * comp, 0.0))
+    return w
+
+
+def sample(logits, penalties=None, presence=0.0, repetition=0.0, decay=1.0, temperature=1.0, top_k=0, top_p=1.0, seed=0, offset=0):
+    """Tokens [B] drawn with the counter-based uniform number of (seed, offset, row): the first token whose cumulative kept
+    weight reaches u * total.  `penalties` ([B, V] float32) is updated in place like greedy_pick does."""
+    w = sample_weights(logits, penalties, temperature, top_k, top_p)
+    B, V = w.shape
+    out = np.zeros(B, dtype=np.int64)
+    for b in range(B):
+        bits = philox4x32_first(offset & 0xFFFFFFFF, (offset >> 32) & 0xFFFFFFFF, b, 0, seed & 0xFFFFFFFF, (seed >> 32) & 0xFFFFFFFF)
+        u = ((bits >> 8) + 0.5) / 16777216.0
+        cum = np.cumsum(w[b])
+        idx = int(np.searchsorted(cum, u * cum[-1], side="left"))
+        idx = min(idx, V - 1)
+        while w[b][idx] == 0.0 and idx > 0:              # (cannot happen for side="left" unless rounding: stay on a kept token)
+            idx -= 1
+        out[b] = idx
+    if penalties is not None:
+        for b in range(B):
+            hit = penalties[b, out[b]]
+            add = np.float32(presence if hit == 0 else repetition)
+            penalties[b] = (penalties[b].astype(np.float32) * np.float32(decay)).astype(np.float32)
+            penalties[b, out[b]] = np.float32(np.float32(hit) * np.float32(decay) + add)
+    return out

@@ -256,6 +256,34 @@ class ModelBackend:
             C.c_void_p(out_host.data_ptr()) if out_host is not None else None, C.c_void_p(stream)))
         return out
 
+    def decode_sample(self, first_tokens: Sequence[int], steps: int, state: GenerationState, logits: DeviceLogits,
+                      temperature: float = 1.0, top_k: int = 0, top_p: float = 1.0, seed: int = 0, offset: int = 0,
+                      penalties: Optional[torch.Tensor] = None, presence_penalty: float = 0.0, repetition_penalty: float = 0.0,
+                      penalty_decay: float = 1.0, out_host: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """decode_greedy with the sampler's general case (temperature / top-k / top-p; src/utils/sampling.cu:205-512): step i
+        draws with the counter-based random number of (seed, offset + i, sequence).  Returns the ids, int32 [steps, B]."""
+        t = first_tokens.to(dtype=torch.int64, device="cpu").contiguous() if isinstance(first_tokens, torch.Tensor) \
+            else torch.tensor(list(first_tokens), dtype=torch.int64)
+        B = t.numel()
+        if B == 0:
+            raise L.Rwkv7B200Error(1, "token_batches must not be empty")
+        if state.batch_size != B:
+            raise L.Rwkv7B200Error(1, "state batch size mismatch")
+        if state.wkv32 != self.use_wkv32:
+            raise L.Rwkv7B200Error(3, "state wkv precision mismatch")
+        dev = torch.device("cuda", self.device)
+        if logits.values is None or logits.values.numel() < B * self.dims.vocab:
+            logits.values = torch.empty((B, self.dims.vocab), dtype=torch.float32, device=dev)
+        logits.rows, logits.vocab_size = B, self.dims.vocab
+        out = torch.empty((max(steps, 0), B), dtype=torch.int32, device=dev)
+        sp = L.Sampling(temperature, top_k, top_p, seed, offset)
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        L.check(self._lib.rwkv7_b200_decode_sample(
+            self._h, C.c_void_p(t.data_ptr()), B, steps, _ptr(state.shift), _ptr(state.wkv_state), _ptr(state.elapsed),
+            _ptr(logits.values), _ptr(penalties), presence_penalty, repetition_penalty, penalty_decay, C.byref(sp), _ptr(out),
+            C.c_void_p(out_host.data_ptr()) if out_host is not None else None, C.c_void_p(stream)))
+        return out
+
     def copy_state_slice(self, src: GenerationState, src_offset: int, dst: GenerationState, dst_offset: int, count: int) -> None:
         if src.wkv32 != dst.wkv32 or src.wkv32 != self.use_wkv32:
             raise L.Rwkv7B200Error(3, "state slice wkv precision mismatch")

@@ -118,6 +118,29 @@ int rwkv7_b200_decode_greedy(rwkv7_b200_model* m, const int64_t* first_tokens_ho
   return m->impl.timeout_result();
 }
 
+int rwkv7_b200_decode_sample(rwkv7_b200_model* m, const int64_t* first_tokens_host, int B, int steps, void* shift, void* wkv,
+                             int* elapsed, float* logits, float* penalties, float presence_penalty, float repetition_penalty,
+                             float penalty_decay, const rwkv7_b200_sampling* sampling, int* out_tokens, int* out_tokens_host,
+                             void* stream) {
+  RK_REQUIRE(m && sampling, kBadArg, "decode_sample: null argument");
+  int s = m->impl.decode_greedy(first_tokens_host, B, steps, shift, wkv, elapsed, logits, penalties, presence_penalty,
+                                repetition_penalty, penalty_decay, out_tokens, st(stream), sampling);
+  if (s != kOk || !out_tokens_host) return s;
+  RK_CUDA(cudaMemcpyAsync(out_tokens_host, out_tokens, static_cast<size_t>(B) * steps * sizeof(int), cudaMemcpyDeviceToHost,
+                          st(stream)));
+  if ((s = m->impl.enqueue_timeout_read(st(stream))) != kOk) return s;
+  RK_CUDA(cudaStreamSynchronize(st(stream)));
+  return m->impl.timeout_result();
+}
+
+int rwkv7_b200_sample(void* stream, int B, int V, const float* logits, float* penalties, float* probs, float presence_penalty,
+                      float repetition_penalty, float penalty_decay, const rwkv7_b200_sampling* sampling, int* out,
+                      int64_t* next_tokens) {
+  RK_REQUIRE(sampling, kBadArg, "sample: null sampling parameters");
+  return rk::sample_tokens(st(stream), B, V, logits, penalties, probs, presence_penalty, repetition_penalty, penalty_decay,
+                           sampling->temperature, sampling->top_k, sampling->top_p, sampling->seed, sampling->offset, out, next_tokens);
+}
+
 int rwkv7_b200_greedy_pick(void* stream, int B, int V, const float* logits, float* penalties, float presence_penalty,
                            float repetition_penalty, float penalty_decay, int* out, int64_t* next_tokens) {
   return rk::greedy_pick(st(stream), B, V, logits, penalties, presence_penalty, repetition_penalty, penalty_decay, out,

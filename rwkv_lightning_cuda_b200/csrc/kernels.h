@@ -89,6 +89,11 @@ int advance_i32(cudaStream_t stream, int* x, int amount, int n);
 // goes to out[b] and, when next_tokens is given, to next_tokens[b] (the next decode step's input).  See greedy.cu.
 int greedy_pick(cudaStream_t stream, int B, int V, const float* logits, float* penalties, float presence, float repetition,
                 float decay, int* out, int64_t* next_tokens);
+// Temperature / top-k / top-p sampling with penalties (sampler.cu): out[b] is drawn from the filtered distribution of
+// row b with the counter-based random number of (seed, offset, b); probs is scratch, fp32 [B, V].
+int sample_tokens(cudaStream_t stream, int B, int V, const float* logits, float* penalties, float* probs, float presence,
+                  float repetition, float decay, float temperature, int top_k, float top_p, unsigned long long seed,
+                  unsigned long long offset, int* out, int64_t* next_tokens);
 // src [G][B][Vl] (one block per rank, as an all-gather leaves it) -> dst [B][G*Vl]
 int interleave_gathered(cudaStream_t stream, const float* src, float* dst, int G, int B, int Vl);
 int relu_square(cudaStream_t stream, const half* x, half* out, long long n);

@@ -903,7 +903,7 @@ int Model::run(Workspace& wsr, int B, int T, void* shift, void* wkv, int* elapse
 // (src/rwkv_sampler.cpp:47-111, src/utils/sampling.cu:205-471,507-512).
 int Model::decode_greedy(const int64_t* first_tokens_host, int B, int steps, void* shift, void* wkv, int* elapsed,
                          float* logits, float* penalties, float presence, float repetition, float decay, int* out_tokens,
-                         cudaStream_t stream) {
+                         cudaStream_t stream, const rwkv7_b200_sampling* sampling) {
   RK_REQUIRE(finalized_, kNotReady, "decode_greedy: model not finalised");
   RK_REQUIRE(B > 0, kBadArg, "token_batches must not be empty");
   RK_REQUIRE(steps > 0, kBadArg, "decode_greedy: steps must be positive");
@@ -914,13 +914,25 @@ int Model::decode_greedy(const int64_t* first_tokens_host, int B, int steps, voi
   int s = use_device();
   if (s != kOk) return s;
   std::lock_guard<std::mutex> lock(mu_);
+  if (sampling) {
+    RK_REQUIRE(sampling->temperature >= 0.001f && sampling->temperature <= 1000.f, kBadArg, "decode_sample: temperature outside [0.001, 1000]");
+    const size_t need = static_cast<size_t>(B) * cfg_.vocab * sizeof(float);
+    if (need > probs_.bytes) {
+      RK_CUDA(cudaDeviceSynchronize());
+      if ((s = probs_.alloc(need)) != kOk) return s;
+    }
+  }
   for (int i = 0; i < steps; ++i) {
     s = step(i == 0 ? first_tokens_host : nullptr, B, 1, shift, wkv, elapsed, logits, stream);
     if (s != kOk) return s;
     Workspace* ws = &ws_;
     const long long before = launch_counter();
-    s = greedy_pick(stream, B, cfg_.vocab, logits, penalties, presence, repetition, decay, out_tokens + static_cast<size_t>(i) * B,
-                    ws->tokens);
+    int* out_i = out_tokens + static_cast<size_t>(i) * B;
+    if (sampling)
+      s = sample_tokens(stream, B, cfg_.vocab, logits, penalties, probs_.as<float>(), presence, repetition, decay, sampling->temperature,
+                        sampling->top_k, sampling->top_p, sampling->seed, sampling->offset + static_cast<unsigned long long>(i), out_i, ws->tokens);
+    else
+      s = greedy_pick(stream, B, cfg_.vocab, logits, penalties, presence, repetition, decay, out_i, ws->tokens);
     launches_ += launch_counter() - before;
     if (s != kOk) return s;
     RK_CUDA(cudaEventRecord(last_done_, stream));  // the pick wrote the token buffer after the step's own record

@@ -69,8 +69,10 @@ class Model {
   int finalize();
   int forward(const int64_t* tokens_host, int B, int T, void* shift, void* wkv, int* elapsed, float* logits,
               cudaStream_t stream);
+  // sampling == nullptr: greedy choice
   int decode_greedy(const int64_t* first_tokens_host, int B, int steps, void* shift, void* wkv, int* elapsed, float* logits,
-                    float* penalties, float presence, float repetition, float decay, int* out_tokens, cudaStream_t stream);
+                    float* penalties, float presence, float repetition, float decay, int* out_tokens, cudaStream_t stream,
+                    const rwkv7_b200_sampling* sampling = nullptr);
   int state_sizes(int B, size_t* shift_elems, size_t* wkv_elems, size_t* elapsed_elems) const;
   int state_init(int B, void* shift, void* wkv, int* elapsed, cudaStream_t stream) const;
   int copy_state_slice(const void* src_shift, const void* src_wkv, const int* src_elapsed, int src_B, int src_off,
@@ -137,7 +139,7 @@ class Model {
   // the device as well as on the host: mu_ guards the enqueue, and a call on another stream than the previous one
   // first waits for that one's work (last_done_), because both would use these buffers.
   std::mutex mu_;
-  DevBuf arena_, gemm_scratch_, part32_;
+  DevBuf arena_, gemm_scratch_, part32_, probs_;  // probs_: the sampler's scratch, [B, vocab] fp32
   Workspace ws_;
   // ring of pinned host staging slots for the token ids; a slot is reused only after the copy that read it has
   // completed, so callers may overwrite their token array as soon as forward returns

@@ -29,6 +29,10 @@ class Config(C.Structure):
         "weight_format", "wkv32", "device", "tp_rank", "tp_size")]
 
 
+class Sampling(C.Structure):
+    _fields_ = [("temperature", C.c_float), ("top_k", C.c_int), ("top_p", C.c_float), ("seed", C.c_ulonglong), ("offset", C.c_ulonglong)]
+
+
 class Capacity(C.Structure):
     _fields_ = [("free_vram_bytes", C.c_size_t), ("total_vram_bytes", C.c_size_t), ("reserve_vram_bytes", C.c_size_t),
                 ("bytes_per_batch", C.c_size_t), ("max_batch_size", C.c_int)]
@@ -53,6 +57,8 @@ SIGNATURES = {
     "rwkv7_b200_forward_to_host": [_vp, _vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp],
     "rwkv7_b200_decode_greedy": [_vp, _vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _f, _f, _f, _vp, _vp, _vp],
     "rwkv7_b200_greedy_pick": [_vp, _i, _i, _vp, _vp, _f, _f, _f, _vp, _vp],
+    "rwkv7_b200_decode_sample": [_vp, _vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _f, _f, _f, C.POINTER(Sampling), _vp, _vp, _vp],
+    "rwkv7_b200_sample": [_vp, _i, _i, _vp, _vp, _vp, _f, _f, _f, C.POINTER(Sampling), _vp, _vp],
     "rwkv7_b200_copy_state_slice": [_vp, _vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _i, _vp],
     "rwkv7_b200_query_capacity": [_vp, _i, C.POINTER(Capacity)],
     "rwkv7_b200_kernel_launches": [_vp],

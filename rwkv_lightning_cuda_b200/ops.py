@@ -192,3 +192,17 @@ def quant_unpack_w4(q, s, z):
     W = torch.empty((N, K), dtype=torch.float16, device=q.device)
     L.check(L.load_library().rwkv7_b200_quant_unpack_w4(_s(), N, K, _p(q), _p(s), _p(z), _p(W)))
     return W
+
+
+def sample(logits, penalties=None, presence=0.0, repetition=0.0, decay=1.0, temperature=1.0, top_k=0, top_p=1.0, seed=0, offset=0,
+           next_tokens=None):
+    """One token per row of fp32 logits [B, V] with the sampler's rule (temperature, top-k, top-p, penalties updated in
+    place); the draw is a function of (seed, offset, row).  Returns int32 [B] on the device."""
+    B, V = logits.shape
+    out = torch.empty((B,), dtype=torch.int32, device=logits.device)
+    probs = torch.empty((B, V), dtype=torch.float32, device=logits.device)
+    sp = L.Sampling(temperature, top_k, top_p, seed, offset)
+    import ctypes as C
+    L.check(L.load_library().rwkv7_b200_sample(_s(), B, V, _p(logits), _p(penalties), _p(probs), presence, repetition, decay,
+                                                C.byref(sp), _p(out), _p(next_tokens)))
+    return out

@@ -175,3 +175,22 @@ def test_greedy_pick_edge_values():
     pen[2, 1] = 0.5
     assert orc.greedy_pick(logits, pen, 1.0, 2.0, 0.5).tolist() == [0, 1, 2, 0]
     assert pen[2].tolist() == [0.0, 0.25, 1.0, 0.0] and pen[3, 0] == 1.0 and pen[3, 1] == inf
+
+
+def test_sampler_oracle_known_answers():
+    """The counter-based generator against the published known answer of Philox-4x32-10 (counter 0, key 0 -> first word
+    0x6627e8d5), and the filtering rule on a case small enough to check by hand."""
+    assert orc.philox4x32_first(0, 0, 0, 0, 0, 0) == 0x6627E8D5
+    assert orc.philox4x32_first(0xFFFFFFFF, 0xFFFFFFFF, 0xFFFFFFFF, 0xFFFFFFFF, 0xFFFFFFFF, 0xFFFFFFFF) == 0x408F276D
+    lg = np.log(np.array([[0.4, 0.3, 0.2, 0.1]], dtype=np.float64)).astype(np.float32)
+    np.testing.assert_allclose(orc.sample_weights(lg)[0], [0.4, 0.3, 0.2, 0.1], rtol=1e-6)
+    np.testing.assert_allclose(orc.sample_weights(lg, top_k=2)[0], [0.4, 0.3, 0.0, 0.0], rtol=1e-6, atol=1e-9)
+    # top_p = 0.6: 0.4 stays, the token on the threshold (0.3) is scaled so that the kept mass is exactly 0.6
+    np.testing.assert_allclose(orc.sample_weights(lg, top_p=0.6)[0], [0.4, 0.2, 0.0, 0.0], rtol=1e-5, atol=1e-9)
+    # ties on the threshold share what is left: two tokens of 0.25 under top_k = 3 after 0.5 keep one token's worth together
+    lt = np.log(np.array([[0.5, 0.25, 0.25]], dtype=np.float64)).astype(np.float32)
+    np.testing.assert_allclose(orc.sample_weights(lt, top_k=2)[0], [0.5, 0.125, 0.125], rtol=1e-5)
+    assert orc.sample_weights(lg, top_p=0.0)[0].tolist() == orc.sample_weights(lg, top_k=1)[0].tolist()      # both greedy
+    toks = [int(orc.sample(lg, seed=1, offset=i)[0]) for i in range(2000)]
+    freq = np.bincount(toks, minlength=4) / 2000.0
+    assert np.abs(freq - [0.4, 0.3, 0.2, 0.1]).max() < 0.04

@@ -233,3 +233,36 @@ def test_from_pth_loads_a_bf16_checkpoint_like_the_reference_constructor(tmp_pat
         m.forward_decode([11, 12], st, lg)
         outs.append(lg.values.clone())
     assert torch.isfinite(outs[0]).all() and torch.equal(outs[0], outs[1])
+
+
+def test_decode_sample_equals_the_step_by_step_loop():
+    """The on-device sampling loop against the same library driven step by step (forward_decode, then the sampler entry
+    point with offset + step): identical ids, penalties and state; and the ids are a function of the seed."""
+    from rwkv_lightning_cuda_b200 import backend as bk, ops
+    d, om, gm = build_pair(orc.FMT_F16, False)
+    B, steps = 3, 6
+    first, prompt = [7, 11, 200], [[5, 6, 7], [8, 9, 10], [3, 2, 1]]
+    kw = dict(temperature=0.9, top_k=50, top_p=0.9)
+    s = torch.cuda.Stream()
+    with torch.cuda.stream(s):
+        st_a = gm.create_state(B); lg_a = bk.DeviceLogits()
+        gm.forward_prefill(prompt, st_a, lg_a)
+        pen_a = torch.zeros((B, d.vocab), dtype=torch.float32, device="cuda")
+        host_ids = torch.empty((steps, B), dtype=torch.int32).pin_memory()
+        ids_a = gm.decode_sample(first, steps, st_a, lg_a, seed=42, offset=10, penalties=pen_a, presence_penalty=0.4,
+                                 repetition_penalty=0.3, penalty_decay=0.9, out_host=host_ids, **kw)
+        st_b = gm.create_state(B); lg_b = bk.DeviceLogits()
+        gm.forward_prefill(prompt, st_b, lg_b)
+        pen_b = torch.zeros((B, d.vocab), dtype=torch.float32, device="cuda")
+        cur, ids_b = list(first), []
+        for i in range(steps):
+            gm.forward_decode(cur, st_b, lg_b)
+            cur = ops.sample(lg_b.values, pen_b, 0.4, 0.3, 0.9, seed=42, offset=10 + i, **kw).cpu().tolist()
+            ids_b.append(cur)
+        st_c = gm.create_state(B); lg_c = bk.DeviceLogits()
+        gm.forward_prefill(prompt, st_c, lg_c)
+        ids_c = gm.decode_sample(first, steps, st_c, lg_c, seed=43, offset=10, **kw)
+    torch.cuda.synchronize()
+    assert host_ids.tolist() == ids_b and ids_a.cpu().tolist() == ids_b
+    assert torch.equal(pen_a, pen_b) and torch.equal(st_a.wkv_state, st_b.wkv_state) and torch.equal(st_a.elapsed, st_b.elapsed)
+    assert ids_c.cpu().tolist() != ids_b          # another seed, another sequence

@@ -371,3 +371,55 @@ def test_greedy_pick_matches_the_oracle(V):
         assert got.cpu().tolist() == want.tolist() and nxt.cpu().tolist() == want.tolist()
         assert np.array_equal(pen_g.cpu().numpy(), pen, equal_nan=True)
     assert ops.greedy_pick(lg).cpu().tolist() == orc.greedy_pick(logits).tolist()
+
+
+def test_sampler_temperature_topk_topp_against_the_oracle(ops):
+    """The sampler's general case: what is kept (top-k / top-p with ties sharing what is left of the budgets), the draw
+    as a function of (seed, offset, row), the penalty update, the greedy limit, and the frequencies of many draws."""
+    rng = np.random.default_rng(3)
+    B, V = 3, 512
+    lg = (rng.standard_normal((B, V)) * 2.5).astype(np.float32)
+    lg[1, 100:110] = lg[1, 100]                       # a run of exactly tied logits
+    lg[2, 7] = np.inf; lg[2, 9] = np.nan              # clamped / zeroed like the reference does
+    dl = dev(lg)
+    # (1) top_p == 0 and top_k == 1 are the greedy choice (no tie at the top here)
+    for kw in (dict(top_p=0.0), dict(top_k=1)):
+        got = host(ops.sample(dl, temperature=0.7, seed=1, offset=0, **kw))
+        assert got.tolist() == orc.greedy_pick(lg).tolist()
+    # (2) the draw equals the oracle's for the same (seed, offset); penalties are updated the same way
+    agree = total = 0
+    for temperature, top_k, top_p in ((1.0, 0, 1.0), (0.8, 20, 1.0), (1.3, 0, 0.6), (0.5, 8, 0.9), (2.0, 200, 0.95)):
+        pen_g = torch.zeros((B, V), dtype=torch.float32, device="cuda"); pen_o = np.zeros((B, V), dtype=np.float32)
+        pen_o[0, 5] = 1.5; pen_g[0, 5] = 1.5
+        for off in range(40):
+            got = host(ops.sample(dl, pen_g, 0.4, 0.3, 0.9, temperature, top_k, top_p, seed=99, offset=off))
+            want = orc.sample(lg, pen_o, 0.4, 0.3, 0.9, temperature, top_k, top_p, seed=99, offset=off)
+            same = got == want
+            agree += int(same.sum()); total += B
+            if not same.all():                        # a draw on the boundary between two tokens (fp32 vs float64 sums): re-align
+                pen_g.copy_(torch.from_numpy(pen_o))
+            else:
+                assert np.allclose(host(pen_g), pen_o, rtol=1e-6, atol=1e-7)
+            kept = orc.sample_weights(lg, None, temperature, top_k, top_p)        # (penalties move little here)
+    print(f"[parity] sampler draws equal to the oracle's: {agree}/{total}")
+    assert agree >= 0.98 * total
+    # (3) every drawn token lies in the kept set, and frequencies follow the kept weights
+    small = (rng.standard_normal((1, 64)) * 1.5).astype(np.float32)
+    w = orc.sample_weights(small, None, 0.9, 10, 0.85)[0]
+    counts = np.zeros(64)
+    n_draws = 6000
+    ds = dev(np.repeat(small, 8, axis=0))             # eight rows per launch, each with its own counter
+    for off in range(n_draws // 8):
+        for tok in host(ops.sample(ds, temperature=0.9, top_k=10, top_p=0.85, seed=5, offset=off)):
+            counts[tok] += 1
+    assert (counts[w == 0] == 0).all()
+    expect = w / w.sum() * n_draws
+    chi2 = (((counts - expect) ** 2) / np.maximum(expect, 1e-9))[w > 0].sum()
+    print(f"[parity] sampler frequencies over {n_draws} draws: chi2 {chi2:.1f} with {int((w > 0).sum()) - 1} degrees of freedom")
+    assert chi2 < 5 * max(1, int((w > 0).sum()))
+    # (4) same (seed, offset) -> same token; argument errors
+    a = host(ops.sample(dl, temperature=1.0, seed=11, offset=4)); b = host(ops.sample(dl, temperature=1.0, seed=11, offset=4))
+    assert (a == b).all()
+    from rwkv_lightning_cuda_b200 import lib as L
+    with pytest.raises(L.Rwkv7B200Error, match="temperature"):
+        ops.sample(dl, temperature=0.0)
