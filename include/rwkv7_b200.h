@@ -191,6 +191,25 @@ int rwkv7_b200_copy_state_slice(const rwkv7_b200_model* m, const void* src_shift
                                 void* dst_wkv, int* dst_elapsed, int dst_B, int dst_offset, int count,
                                 void* stream);
 
+/* Session records: one sequence's state as the three blobs the reference's state cache stores per session
+ * (src/rwkv_state_cache.cpp:268-292: shift_blob = half [layers][2][channels], wkv_blob = half or float
+ * [layers][heads][64][64], elapsed_blob = int32 [1]; same bytes, so records are interchangeable).  The reference
+ * fills a batch-1 GenerationState with copy_state_slice and then copies buffer by buffer with blocking cudaMemcpy
+ * (:132-223); these two calls gather / scatter sequence `index` of a batch state directly, as three asynchronous
+ * strided copies on `stream` (pinned host memory makes them overlap with compute).  The blobs are valid / may be
+ * reused once `stream` has completed. */
+int rwkv7_b200_state_blob_sizes(const rwkv7_b200_model* m, size_t* shift_bytes, size_t* wkv_bytes,
+                                size_t* elapsed_bytes);
+int rwkv7_b200_state_export(const rwkv7_b200_model* m, const void* shift, const void* wkv, const int* elapsed, int B,
+                            int index, void* shift_blob_host, void* wkv_blob_host, int* elapsed_blob_host, void* stream);
+int rwkv7_b200_state_import(const rwkv7_b200_model* m, const void* shift_blob_host, const void* wkv_blob_host,
+                            const int* elapsed_blob_host, void* shift, void* wkv, int* elapsed, int B, int index,
+                            void* stream);
+/* A WKV state (or blob on the device) from one precision to the other, for a session saved under one setting of the
+ * reference's --wkv32 switch and resumed under the other (the reference refuses such a session,
+ * src/rwkv_state_cache.cpp:180-187): half -> float is exact, float -> half rounds to nearest.  elems % 8 == 0. */
+int rwkv7_b200_state_convert_wkv(void* stream, const void* src, void* dst, long long elems, int src_is_fp32);
+
 /* Replaces ModelBackend::query_prefill_capacity (src/rwkv7_fast_v4.cu:1534-1580). */
 int rwkv7_b200_query_capacity(const rwkv7_b200_model* m, int prefill_chunk_size, rwkv7_b200_capacity* out);
 

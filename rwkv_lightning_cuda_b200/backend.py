@@ -294,6 +294,30 @@ class ModelBackend:
             _ptr(dst.shift), _ptr(dst.wkv_state), _ptr(dst.elapsed), dst.batch_size, dst_offset, count, C.c_void_p(stream)))
         torch.cuda.current_stream(dev).synchronize()
 
+    def export_sequence(self, state: GenerationState, index: int):
+        """One sequence's state as the reference's session record (src/rwkv_state_cache.cpp:268-292): pinned host tensors
+        (shift half [L, 2, C], wkv half|float [L, H, 64, 64], elapsed int32 [1]), filled by asynchronous copies; synchronised
+        on return."""
+        d = self.dims
+        shift = torch.empty((d.layers, 2, d.channels), dtype=torch.float16).pin_memory()
+        wkv = torch.empty((d.layers, d.heads // self.tp_size, 64, 64), dtype=torch.float32 if self.use_wkv32 else torch.float16).pin_memory()
+        elapsed = torch.empty((1,), dtype=torch.int32).pin_memory()
+        dev = torch.device("cuda", self.device)
+        stream = torch.cuda.current_stream(dev)
+        L.check(self._lib.rwkv7_b200_state_export(self._h, _ptr(state.shift), _ptr(state.wkv_state), _ptr(state.elapsed), state.batch_size,
+                                                  index, _ptr(shift), _ptr(wkv), _ptr(elapsed), C.c_void_p(stream.cuda_stream)))
+        stream.synchronize()
+        return shift, wkv, elapsed
+
+    def import_sequence(self, blobs, state: GenerationState, index: int) -> None:
+        """The inverse of export_sequence: writes a session record into sequence `index` of `state`."""
+        shift, wkv, elapsed = (t.contiguous() for t in blobs)
+        dev = torch.device("cuda", self.device)
+        stream = torch.cuda.current_stream(dev)
+        L.check(self._lib.rwkv7_b200_state_import(self._h, _ptr(shift), _ptr(wkv), _ptr(elapsed), _ptr(state.shift), _ptr(state.wkv_state),
+                                                  _ptr(state.elapsed), state.batch_size, index, C.c_void_p(stream.cuda_stream)))
+        stream.synchronize()
+
     def copy_logits_slice(self, src: DeviceLogits, src_offset: int, dst: DeviceLogits, dst_offset: int, count: int) -> None:
         if src_offset < 0 or dst_offset < 0 or count <= 0:
             raise L.Rwkv7B200Error(1, "invalid backend logits slice range")

@@ -155,6 +155,30 @@ int rwkv7_b200_copy_state_slice(const rwkv7_b200_model* m, const void* src_shift
                                   dst_offset, count, st(stream));
 }
 
+int rwkv7_b200_state_blob_sizes(const rwkv7_b200_model* m, size_t* shift_bytes, size_t* wkv_bytes, size_t* elapsed_bytes) {
+  RK_REQUIRE(m, kBadArg, "null model");
+  size_t ns = 0, nw = 0, ne = 0;
+  int s = m->impl.state_sizes(1, &ns, &nw, &ne);
+  if (s != kOk) return s;
+  if (shift_bytes) *shift_bytes = ns * 2;
+  if (wkv_bytes) *wkv_bytes = nw * (m->impl.cfg().wkv32 ? 4 : 2);
+  if (elapsed_bytes) *elapsed_bytes = ne * sizeof(int);
+  return kOk;
+}
+int rwkv7_b200_state_export(const rwkv7_b200_model* m, const void* shift, const void* wkv, const int* elapsed, int B, int index,
+                            void* shift_blob_host, void* wkv_blob_host, int* elapsed_blob_host, void* stream) {
+  RK_REQUIRE(m, kBadArg, "null model");
+  return m->impl.state_export(shift, wkv, elapsed, B, index, shift_blob_host, wkv_blob_host, elapsed_blob_host, st(stream));
+}
+int rwkv7_b200_state_import(const rwkv7_b200_model* m, const void* shift_blob_host, const void* wkv_blob_host,
+                            const int* elapsed_blob_host, void* shift, void* wkv, int* elapsed, int B, int index, void* stream) {
+  RK_REQUIRE(m, kBadArg, "null model");
+  return m->impl.state_import(shift_blob_host, wkv_blob_host, elapsed_blob_host, shift, wkv, elapsed, B, index, st(stream));
+}
+int rwkv7_b200_state_convert_wkv(void* stream, const void* src, void* dst, long long elems, int src_is_fp32) {
+  return rk::wkv_state_convert(st(stream), src, dst, elems, src_is_fp32);
+}
+
 int rwkv7_b200_query_capacity(const rwkv7_b200_model* m, int chunk, rwkv7_b200_capacity* out) {
   RK_REQUIRE(m, kBadArg, "null model");
   return m->impl.query_capacity(chunk, out);

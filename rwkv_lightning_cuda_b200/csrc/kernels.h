@@ -84,6 +84,7 @@ int tmix_lnx_rkvres_xg(cudaStream_t stream, int rows, int C, const half* y, cons
 int tmix_vres_gate(cudaStream_t stream, int rows, int C, const half* v, const half* v_first, const half* v0,
                    const half* v12, half* out);
 int advance_i32(cudaStream_t stream, int* x, int amount, int n);
+int wkv_state_convert(cudaStream_t stream, const void* src, void* dst, long long elems, int src_is_fp32);  // half <-> float
 
 // Greedy token choice per sequence over fp32 logits [B, V] with optional penalties [B, V] (updated in place); the token
 // goes to out[b] and, when next_tokens is given, to next_tokens[b] (the next decode step's input).  See greedy.cu.

@@ -361,6 +361,43 @@ int Model::copy_state_slice(const void* src_shift, const void* src_wkv, const in
   return kOk;
 }
 
+// Session records.  The reference's state cache keeps a paused sequence as three blobs -- shift [L][2][C] halves, wkv
+// [L][H][64][64] halves or floats, elapsed [1] int -- copied with blocking cudaMemcpy calls out of / into a batch-1
+// GenerationState that copy_state_slice filled first (src/rwkv_state_cache.cpp:132-223, blobs :268-333).  Here the blobs
+// are gathered straight from / scattered straight into sequence `index` of a batch state by three strided asynchronous
+// copies on the caller's stream (use pinned host memory for real overlap); same bytes, no staging state, no blocking.
+int Model::state_export(const void* shift, const void* wkv, const int* elapsed, int B, int index, void* shift_blob, void* wkv_blob,
+                        int* elapsed_blob, cudaStream_t stream) const {
+  RK_REQUIRE(B > 0 && index >= 0 && index < B, kBadArg, "state slice range exceeds batch size");
+  RK_REQUIRE(shift && wkv && elapsed && shift_blob && wkv_blob && elapsed_blob, kBadArg, "state_export: null buffer");
+  int s = use_device();
+  if (s != kOk) return s;
+  const size_t C = static_cast<size_t>(cfg_.channels);
+  const size_t lane = static_cast<size_t>(H_ / tp_size_) * kHead * kHead * (cfg_.wkv32 ? 4 : 2);
+  RK_CUDA(cudaMemcpy2DAsync(shift_blob, C * 2, static_cast<const char*>(shift) + static_cast<size_t>(index) * C * 2, static_cast<size_t>(B) * C * 2,
+                            C * 2, static_cast<size_t>(cfg_.layers) * 2, cudaMemcpyDeviceToHost, stream));
+  RK_CUDA(cudaMemcpy2DAsync(wkv_blob, lane, static_cast<const char*>(wkv) + static_cast<size_t>(index) * lane, static_cast<size_t>(B) * lane, lane,
+                            static_cast<size_t>(cfg_.layers), cudaMemcpyDeviceToHost, stream));
+  RK_CUDA(cudaMemcpyAsync(elapsed_blob, elapsed + index, sizeof(int), cudaMemcpyDeviceToHost, stream));
+  return kOk;
+}
+
+int Model::state_import(const void* shift_blob, const void* wkv_blob, const int* elapsed_blob, void* shift, void* wkv, int* elapsed, int B,
+                        int index, cudaStream_t stream) const {
+  RK_REQUIRE(B > 0 && index >= 0 && index < B, kBadArg, "state slice range exceeds batch size");
+  RK_REQUIRE(shift && wkv && elapsed && shift_blob && wkv_blob && elapsed_blob, kBadArg, "state_import: null buffer");
+  int s = use_device();
+  if (s != kOk) return s;
+  const size_t C = static_cast<size_t>(cfg_.channels);
+  const size_t lane = static_cast<size_t>(H_ / tp_size_) * kHead * kHead * (cfg_.wkv32 ? 4 : 2);
+  RK_CUDA(cudaMemcpy2DAsync(static_cast<char*>(shift) + static_cast<size_t>(index) * C * 2, static_cast<size_t>(B) * C * 2, shift_blob, C * 2, C * 2,
+                            static_cast<size_t>(cfg_.layers) * 2, cudaMemcpyHostToDevice, stream));
+  RK_CUDA(cudaMemcpy2DAsync(static_cast<char*>(wkv) + static_cast<size_t>(index) * lane, static_cast<size_t>(B) * lane, wkv_blob, lane, lane,
+                            static_cast<size_t>(cfg_.layers), cudaMemcpyHostToDevice, stream));
+  RK_CUDA(cudaMemcpyAsync(elapsed + index, elapsed_blob, sizeof(int), cudaMemcpyHostToDevice, stream));
+  return kOk;
+}
+
 namespace {
 size_t workspace_halves(const rwkv7_b200_config& c, size_t rows, size_t B) {
   const size_t C = c.channels;

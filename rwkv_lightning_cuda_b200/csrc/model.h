@@ -78,6 +78,11 @@ class Model {
   int copy_state_slice(const void* src_shift, const void* src_wkv, const int* src_elapsed, int src_B, int src_off,
                        void* dst_shift, void* dst_wkv, int* dst_elapsed, int dst_B, int dst_off, int count,
                        cudaStream_t stream) const;
+  // One sequence's state <-> three contiguous host blobs (the reference's session record: shift, wkv, elapsed)
+  int state_export(const void* shift, const void* wkv, const int* elapsed, int B, int index, void* shift_blob, void* wkv_blob,
+                   int* elapsed_blob, cudaStream_t stream) const;
+  int state_import(const void* shift_blob, const void* wkv_blob, const int* elapsed_blob, void* shift, void* wkv, int* elapsed, int B,
+                   int index, cudaStream_t stream) const;
   int query_capacity(int chunk, rwkv7_b200_capacity* out) const;
   int tp_init(const void* unique_id);  // joins the tensor-parallel group (collective over all ranks)
   // Reads (and resets) the device's failure word through this model's pinned slot; `stream` must have been

@@ -619,6 +619,38 @@ int interleave_gathered(cudaStream_t stream, const float* src, float* dst, int G
   return kOk;
 }
 
+namespace {
+// WKV state between its two precisions (a session paused under one setting of the reference's --wkv32 switch and
+// resumed under the other): fp16 -> fp32 is exact, fp32 -> fp16 rounds to nearest even.
+__global__ void wkv_state_convert_kernel(long long n8, const void* __restrict__ src, void* __restrict__ dst, int src_is_fp32) {
+  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= n8) return;
+  if (src_is_fp32) {
+    const float4 a = reinterpret_cast<const float4*>(src)[2 * i], b = reinterpret_cast<const float4*>(src)[2 * i + 1];
+    const __half2 h0 = __floats2half2_rn(a.x, a.y), h1 = __floats2half2_rn(a.z, a.w), h2 = __floats2half2_rn(b.x, b.y), h3 = __floats2half2_rn(b.z, b.w);
+    uint4 o;
+    o.x = *reinterpret_cast<const uint32_t*>(&h0); o.y = *reinterpret_cast<const uint32_t*>(&h1);
+    o.z = *reinterpret_cast<const uint32_t*>(&h2); o.w = *reinterpret_cast<const uint32_t*>(&h3);
+    reinterpret_cast<uint4*>(dst)[i] = o;
+  } else {
+    const uint4 q = reinterpret_cast<const uint4*>(src)[i];
+    const float2 f0 = h2f2(q.x), f1 = h2f2(q.y), f2 = h2f2(q.z), f3 = h2f2(q.w);
+    reinterpret_cast<float4*>(dst)[2 * i] = make_float4(f0.x, f0.y, f1.x, f1.y);
+    reinterpret_cast<float4*>(dst)[2 * i + 1] = make_float4(f2.x, f2.y, f3.x, f3.y);
+  }
+}
+}  // namespace
+
+int wkv_state_convert(cudaStream_t stream, const void* src, void* dst, long long elems, int src_is_fp32) {
+  RK_REQUIRE(src && dst && elems > 0 && elems % 8 == 0, kBadArg, "wkv_state_convert: need a positive multiple of 8 elements");
+  RK_REQUIRE((reinterpret_cast<uintptr_t>(src) & 15u) == 0 && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0, kBadArg,
+             "wkv_state_convert: buffers must be 16-byte aligned");
+  const long long n8 = elems / 8;
+  wkv_state_convert_kernel<<<static_cast<unsigned>((n8 + 255) / 256), 256, 0, stream>>>(n8, src, dst, src_is_fp32);
+  RK_LAUNCH_CHECK("wkv_state_convert launch");
+  return kOk;
+}
+
 int advance_i32(cudaStream_t stream, int* x, int amount, int n) {
   RK_REQUIRE(x && n > 0, kBadArg, "advance_i32: bad argument");
   advance_i32_kernel<<<(n + 255) / 256, 256, 0, stream>>>(x, amount, n);

@@ -60,6 +60,10 @@ SIGNATURES = {
     "rwkv7_b200_decode_sample": [_vp, _vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _f, _f, _f, C.POINTER(Sampling), _vp, _vp, _vp],
     "rwkv7_b200_sample": [_vp, _i, _i, _vp, _vp, _vp, _f, _f, _f, C.POINTER(Sampling), _vp, _vp],
     "rwkv7_b200_copy_state_slice": [_vp, _vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _i, _vp],
+    "rwkv7_b200_state_blob_sizes": [_vp, C.POINTER(C.c_size_t), C.POINTER(C.c_size_t), C.POINTER(C.c_size_t)],
+    "rwkv7_b200_state_export": [_vp, _vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _vp],
+    "rwkv7_b200_state_import": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp],
+    "rwkv7_b200_state_convert_wkv": [_vp, _vp, _vp, _ll, _i],
     "rwkv7_b200_query_capacity": [_vp, _i, C.POINTER(Capacity)],
     "rwkv7_b200_kernel_launches": [_vp],
     "rwkv7_b200_model_workspace_bytes": [_vp, C.POINTER(C.c_size_t)],

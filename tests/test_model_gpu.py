@@ -266,3 +266,38 @@ def test_decode_sample_equals_the_step_by_step_loop():
     assert host_ids.tolist() == ids_b and ids_a.cpu().tolist() == ids_b
     assert torch.equal(pen_a, pen_b) and torch.equal(st_a.wkv_state, st_b.wkv_state) and torch.equal(st_a.elapsed, st_b.elapsed)
     assert ids_c.cpu().tolist() != ids_b          # another seed, another sequence
+
+
+@pytest.mark.parametrize("wkv32", [False, True])
+def test_session_records_round_trip_and_match_the_reference_blob_layout(wkv32):
+    """A sequence exported from one batch and imported into another place of another batch continues with identical
+    logits; the blobs are the reference's session record (the sequence's slices of the three state buffers, contiguous);
+    the WKV state converts between its two precisions as torch does."""
+    from rwkv_lightning_cuda_b200 import backend as bk, lib as L
+    import ctypes as C
+    d, om, gm = build_pair(orc.FMT_F16, wkv32)
+    lib = L.load_library()
+    src = gm.create_state(3); lg = bk.DeviceLogits()
+    gm.forward_prefill([[1, 2, 3, 4], [5, 6, 7, 8], [9, 10, 11, 12]], src, lg)
+    blobs = gm.export_sequence(src, 1)
+    assert torch.equal(blobs[0], src.shift[:, :, 1].cpu()) and torch.equal(blobs[1], src.wkv_state[:, 1].cpu())
+    assert blobs[2].tolist() == [4]
+    sizes = [C.c_size_t() for _ in range(3)]
+    L.check(lib.rwkv7_b200_state_blob_sizes(gm._h, *[C.byref(s) for s in sizes]))
+    assert [s.value for s in sizes] == [b.numel() * b.element_size() for b in blobs]
+    dst = gm.create_state(2)
+    gm.forward_prefill([[20, 21], [22, 23]], dst, bk.DeviceLogits())
+    gm.import_sequence(blobs, dst, 0)
+    la, lb = bk.DeviceLogits(), bk.DeviceLogits()
+    gm.forward_decode([30, 31, 32], src, la)
+    gm.forward_decode([31, 40], dst, lb)
+    assert torch.equal(la.values[1], lb.values[0])
+    with pytest.raises(L.Rwkv7B200Error, match="exceeds batch size"):
+        gm.export_sequence(src, 3)
+    # precision conversion of a WKV state
+    w = src.wkv_state
+    other = torch.empty_like(w, dtype=torch.float16 if wkv32 else torch.float32)
+    s = torch.cuda.current_stream().cuda_stream
+    L.check(lib.rwkv7_b200_state_convert_wkv(C.c_void_p(s), C.c_void_p(w.data_ptr()), C.c_void_p(other.data_ptr()), w.numel(), int(wkv32)))
+    torch.cuda.synchronize()
+    assert torch.equal(other, w.to(other.dtype))
