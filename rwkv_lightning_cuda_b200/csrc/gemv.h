@@ -173,8 +173,9 @@ __device__ __forceinline__ void ln_prefetch(const GemvSeg& sg, LnPrefetch& pf) {
   }
 }
 
-template <int kM, int kThreads>
-__device__ __forceinline__ void stage_ln_mix(const GemvSeg& sg, float* xs, float* scratch, bool writer, const LnPrefetch& pf) {
+// `put(m, k, v)` receives the two activations (k, k + 1) of row m; both are exact halves.
+template <int kM, int kThreads, class Put>
+__device__ __forceinline__ void stage_ln_mix(const GemvSeg& sg, Put put, float* scratch, bool writer, const LnPrefetch& pf) {
   const int K = sg.K, pairs = K >> 1;
 #pragma unroll
   for (int m = 0; m < kM; ++m) {
@@ -208,7 +209,6 @@ __device__ __forceinline__ void stage_ln_mix(const GemvSeg& sg, float* xs, float
       }
     }
     const float rstd = rsqrtf(block_sum<kThreads>(sv, scratch) * inv_k + sg.eps);
-    float* row = xs + static_cast<size_t>(m) * K;
 #pragma unroll
     for (int i = 0; i < kLnPairs; ++i) {
       const int q = threadIdx.x + kThreads * i;
@@ -224,11 +224,21 @@ __device__ __forceinline__ void stage_ln_mix(const GemvSeg& sg, float* xs, float
         const float2 p = __half22float2(sh[i]), c = __half22float2(pf.mix[i]);
         n = __half22float2(__floats2half2_rn(n.x + (p.x - n.x) * c.x, n.y + (p.y - n.y) * c.y));
       }
-      *reinterpret_cast<float2*>(row + 2 * q) = n;
+      put(m, 2 * q, n);
     }
   }
 }
 #endif
+
+// gemv_mma.cu: 2..4 rows of any format and one row of quantised weights: 16-row weight tiles (2-D TMA, 128-byte
+// swizzle) against the activations on mma.sync, so that the weights are dequantised in half2 arithmetic once per
+// tile instead of once per row of activations.  plan() returns false for shapes it does not take.
+struct GemvMmaPlan {
+  size_t smem_bytes;
+  int grid, n_slots, x_pitch;  // x_pitch: bytes between rows of activations in shared memory
+};
+bool gemv_mma_plan(GemvBatch& b, int M, GemvMmaPlan* plan);
+int gemv_mma_launch(cudaStream_t stream, const GemvBatch& b, int M, const GemvMmaPlan& plan);
 
 // gemv_tma.cu: fp16 weights fetched with per-warp rings of bulk copies (cp.async.bulk + mbarrier).
 bool gemv_tma_plan(GemvBatch& b, int M, size_t* smem_bytes, int* grid, int* n_slots, int* slot_stride, int* n_warps);

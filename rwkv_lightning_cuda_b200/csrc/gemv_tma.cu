@@ -93,7 +93,9 @@ __global__ void __launch_bounds__(kW * 32, 1) gemv_tma_kernel(const GemvBatch p,
   if (first_cta && sg.copy_src)
     for (int i = threadIdx.x; i < (sg.copy_n >> 1); i += kW * 32)
       reinterpret_cast<__half2*>(sg.copy_dst)[i] = reinterpret_cast<const __half2*>(sg.copy_src)[i];
-  if (sg.ln_w) stage_ln_mix<kM, kW * 32>(sg, xs, red_scratch, first_cta, pf);
+  if (sg.ln_w)
+    stage_ln_mix<kM, kW * 32>(sg, [&](int m, int k, float2 v) { *reinterpret_cast<float2*>(xs + static_cast<size_t>(m) * K + k) = v; },
+                              red_scratch, first_cta, pf);
   else stage_activations<kM, kW * 32>(sg, nullptr, xs);
   __syncthreads();
 

@@ -28,6 +28,8 @@ struct Options {
   int fp16_tc_rows = 0;      // > 1: the same for fp16 weights
   int decode_graphs = 1;     // 0: decode steps are enqueued kernel by kernel instead of replaying a CUDA graph
   int wkv_chunked = 1;       // 0: fp32-state WKV over a chunk runs the per-token scan instead of the matrix form
+  int gemv_mma = 2;          // 1..4 rows: 0 = scalar weight-streaming kernels only, 1 = the tensor-core-instruction kernel for
+                             // quantised weights, 2 = also for 2..4 rows of fp16 weights
 };
 Options& options();
 int set_option(const char* name, int value);
@@ -146,6 +148,7 @@ int linear(cudaStream_t stream, const LinearArgs& args);
 // Up to 8 independent problems sharing M <= 4 in a single launch.
 int linear_batch(cudaStream_t stream, const LinearArgs* args, int n);
 // Whether linear_batch can run M rows of K inputs with the fused prologue (bulk-copy kernel: activations in shared memory).
+bool gemv_mma_fits(int M, int K);  // gemv_mma.cu: M rows of K activations leave room for a ring of weight boxes
 bool linear_batch_fused_fits(int M, int K);
 // Up to eight products with the same M > 4: one tensor-core launch when every product has fp16 weights and no
 // input activation (split-K scratch is taken from args[0]); otherwise one linear() call per product.

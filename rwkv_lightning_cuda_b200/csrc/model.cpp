@@ -496,6 +496,7 @@ int Model::prepare(int B, int T, cudaStream_t stream) {
 // cross-over: 3 rows for W8A16, 2 rows for W4A16, whose dequantisation costs more per row.
 static int quant_tc_rows(int fmt) {
   if (options().quant_tc_rows >= 2) return options().quant_tc_rows;
+  if (options().gemv_mma >= 1) return 5;  // the 16-channel-tile kernel (gemv_mma.cu) costs the same for 1..4 rows
   return fmt == RWKV7_B200_FMT_W4A16 ? 2 : 3;
 }
 
@@ -505,7 +506,7 @@ int Model::lin(cudaStream_t s, int M, const Matrix& W, const half* x, void* y, i
   a.scale = W.scale.as<half>(); a.zero = W.zero.as<half>(); a.epi = epi; a.y = y;
   a.w_dynamic = false;  // resident weights
   // 2..4 rows of a large matrix: tensor cores (the GEMV's time grows with the row count)
-  a.prefer_tc = W.fmt == RWKV7_B200_FMT_F16 || M >= quant_tc_rows(W.fmt);
+  a.prefer_tc = W.fmt == RWKV7_B200_FMT_F16 ? options().gemv_mma < 2 : M >= quant_tc_rows(W.fmt);
   if (cur_) { a.scratch = cur_->gemm_scratch; a.scratch_bytes = cur_->gemm_scratch_bytes; }
   return linear(s, a);
 }
@@ -617,12 +618,19 @@ int Model::enqueue(Workspace& ws, int B, int T, half* shift, void* wkv, int* ela
     const bool quant_tc = cfg_.weight_format != RWKV7_B200_FMT_F16 && rows >= quant_tc_rows(cfg_.weight_format);
     // measured cross-over for fp16 weights: 2 rows from the 1.5B layer width up (1.5B: 1.51 vs 1.53 ms at 2 rows, 1.58 vs
     // 2.18 at 3), 4 rows for narrow models, whose steps are launch-bound (0.1B: 0.42 ms on the GEMV route vs 0.54 at 2 rows)
-    const int fp16_tc_rows = options().fp16_tc_rows >= 2 ? options().fp16_tc_rows : (C < 1536 ? 4 : 2);
+    // Dimensions the 16-channel-tile kernel takes (whole 128-byte boxes per weight row, channel counts in fours): with
+    // it 2..4 rows cost what one row costs, so nothing up to four rows goes to the tensor-core GEMM.
+    const bool mma_dims = C % 256 == 0 && cfg_.ffn % 256 == 0 && cfg_.vocab % 4 == 0 && cfg_.rank_w % 4 == 0 &&
+                          cfg_.rank_a % 4 == 0 && cfg_.rank_g % 4 == 0 && cfg_.rank_v % 4 == 0;
+    const bool mma_fp16 = mma_dims && options().gemv_mma >= 2 && rows >= 2 && cfg_.weight_format == RWKV7_B200_FMT_F16;
+    const bool mma_quant = mma_dims && options().gemv_mma >= 1 && cfg_.weight_format != RWKV7_B200_FMT_F16;
+    const int fp16_tc_rows = options().fp16_tc_rows >= 2 ? options().fp16_tc_rows : mma_fp16 ? 5 : (C < 1536 ? 4 : 2);
     const bool gemv_rows = rows == 1 || (cfg_.weight_format != RWKV7_B200_FMT_F16 && !quant_tc) ||
                            (cfg_.weight_format == RWKV7_B200_FMT_F16 && rows < fp16_tc_rows);
     // (the fused path stages a step's activations in shared memory: B rows of ffn inputs must fit)
     if (G == 1 && T == 1 && rows <= 4 && gemv_rows && tmix_decode_supported(probe) && C <= 4096 && rows_ok &&
-        linear_batch_fused_fits(rows, cfg_.ffn) && linear_batch_fused_fits(rows, C))
+        ((mma_fp16 || mma_quant) ? gemv_mma_fits(rows, std::max(C, cfg_.ffn))
+                                 : (linear_batch_fused_fits(rows, cfg_.ffn) && linear_batch_fused_fits(rows, C))))
       return enqueue_decode(ws, B, shift, wkv, elapsed, logits, st);
   }
   {
@@ -659,7 +667,7 @@ int Model::enqueue(Workspace& ws, int B, int T, half* shift, void* wkv, int* ela
       LinearArgs seg[7] = {mat(W.Wr, xr, ws.r), mat(W.Wk, xk, ws.k), mat(W.Wv, xv, v_lin),
                            low(W.w1t, cfg_.rank_w, xw, ws.l1[0]), low(W.a1t, cfg_.rank_a, xa, ws.l1[1]),
                            low(W.g1t, cfg_.rank_g, xg, ws.l1[2]), low(W.v1t, cfg_.rank_v, xv, ws.l1[3])};
-      if (rows >= 2 && (cfg_.weight_format == RWKV7_B200_FMT_F16 || rows >= quant_tc_rows(cfg_.weight_format))) {
+      if (rows >= 2 && (cfg_.weight_format == RWKV7_B200_FMT_F16 ? options().gemv_mma < 2 : rows >= quant_tc_rows(cfg_.weight_format))) {
         // 2..4 rows: the three C x C projections as one tensor-core launch, the small LoRA down-projections as one GEMV
         for (int i = 0; i < 3; ++i) {
           seg[i].prefer_tc = true; seg[i].w_dynamic = false;

@@ -193,6 +193,44 @@ def test_linear_quantised_on_the_tensor_cores(ops, M, K, N):
     assert L.timeout_flags(clear=True) == 0
 
 
+@pytest.mark.parametrize("M,K,N", [(1, 4096, 4100), (4, 4096, 1000), (2, 16384, 256), (3, 2560, 132), (1, 768, 64), (4, 10240, 48),
+                                   (2, 256, 16), (1, 2048, 20)])
+def test_linear_one_to_four_rows_on_the_warp_level_tensor_core_instruction(ops, M, K, N):
+    """1..4 rows: 16-channel weight tiles (2-D tensor copies, 128-byte swizzle) against the activations with
+    mma.sync -- W8A16 and W4A16 always, fp16 by option.  Channel counts that leave ragged tiles of 4, 8 and 12
+    channels per CTA, K from one 128-byte box per row to many per warp, all epilogues the decode path uses."""
+    from rwkv_lightning_cuda_b200 import lib as L
+    rng = np.random.default_rng(M + K + N)
+    W = h16(rng.standard_normal((N, K)) * 0.02)
+    W[0, :128] = 0
+    W[N - 1, :] = np.float16(-0.015)
+    x = h16(rng.standard_normal((M, K)))
+    q8, s8 = orc.quant_pack_w8(W); q4, s4, z4 = orc.quant_pack_w4(W)
+    atol = 1e-5 * 4 * (K / 1024) ** 0.5
+    got8 = host(ops.linear_w8a16(dev(x), dev(q8), dev(s8)))
+    assert_close16(got8, orc.linear_w8a16(x, q8, s8), max_ulp=2, min_exact=0.97, what="linear_w8a16, mma", atol=atol)
+    got4 = host(ops.linear_w4a16(dev(x), dev(q4), dev(s4), dev(z4)))
+    assert_close16(got4, orc.linear_w4a16(x, q4, s4, z4), max_ulp=2, min_exact=0.97, what="linear_w4a16, mma", atol=atol)
+    r4 = host(ops.linear_w4a16(dev(x), dev(q4), dev(s4), dev(z4), epilogue=L.EPI_RELU2))
+    assert_close16(r4, orc.linear_w4a16(x, q4, s4, z4, epi=orc.EPI_RELU2), max_ulp=4, min_exact=0.95, what="linear_w4a16 relu2, mma", atol=atol)
+    L.set_option("gemv_mma", 2)
+    try:
+        got = host(ops.linear_f16_orig(dev(x), dev(W)))
+        lg = host(ops.linear_f16_orig(dev(x), dev(W), epilogue=L.EPI_F32))
+    finally:
+        L.set_option("gemv_mma", 2)
+    assert_close16(got, orc.linear_orig(x, W), max_ulp=2, min_exact=0.97, what="linear fp16, mma", atol=atol)
+    assert (lg.astype(np.float16).view(np.uint16) == got.view(np.uint16)).all()
+    # the scalar kernels give the same values up to the order of the fp32 sums
+    L.set_option("gemv_mma", 0)
+    try:
+        old8 = host(ops.linear_w8a16(dev(x), dev(q8), dev(s8)))
+    finally:
+        L.set_option("gemv_mma", 2)
+    assert_close16(got8, old8, max_ulp=2, min_exact=0.95, what="mma vs scalar kernel", atol=atol)
+    assert L.timeout_flags(clear=True) == 0
+
+
 @pytest.mark.parametrize("B,T,H", [(1, 128, 12), (3, 1, 2), (2, 7, 3), (1, 1, 64),
                                    # 64 tokens and more: the matrix form on the tensor cores (ragged ends, several blocks)
                                    (1, 128, 64), (2, 100, 3), (1, 65, 2), (1, 256, 4), (3, 64, 2)])
