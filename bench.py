@@ -10,7 +10,7 @@ figure is weak scaling (batch per GPU fixed).  Prints ONE JSON line on rank 0.
 
 The headline (`value`, `e2e`, `roofline`) is the 7.2B fp16 model at B=1.  The same line carries, timed in the
 same run, the other workloads of the benchmark definition under their own keys: `b256` (7.2B, 256 sequences),
-`w8a16_1p5B` (B = 1, 8, 32, 64), `w4a16_2p9B_b256`, `prefill_16k` (7.2B, 16384 tokens in chunks of 128, fp32
+`b2` / `b4`, `w8a16_1p5B` (B = 1, 8, 32, 64), `w4a16_2p9B_b256`, `w4a16_7p2B` (B = 1, 2, 4), `prefill_16k` (7.2B, 16384 tokens in chunks of 128, fp32
 state) and, with N > 1, `tp_prefill` (the ranks as one head-sharded group, with a parity check of that path against
 the CPU oracle on a small model first).  `--only headline` skips them.  `check` compares a fixed short run's logits
 with what the reference arm (`--impl reference`, run before on the same machine) left for it.
@@ -394,6 +394,10 @@ def run_ours(args, rank, world, local_rank):
         t256 = time_decode(gm, d, 256, steps2, warm2, world, rank)
         t256["ms"], t256["e2e_ms"], t256["greedy_ms"] = max_over_ranks([t256["ms"], t256["e2e_ms"], t256["greedy_ms"]], world)
         line["b256"] = decode_entry(d, fmt, 256, 0, t256, world, hbm_peak, tf_peak)
+        if world == 1:
+            for b in (2, 4):   # a few sequences: the same weight stream as one sequence
+                tb = time_decode(gm, d, b, steps2, warm2, world, rank, e2e=False, greedy=False)
+                line[f"b{b}"] = decode_entry(d, fmt, b, 0, tb, world, hbm_peak, tf_peak)
         gm.close()
         torch.cuda.empty_cache()
         if world == 1:
@@ -415,6 +419,15 @@ def run_ours(args, rank, world, local_rank):
             tb = time_decode(gm4, d4, 256, steps2, warm2, world, rank, e2e=False, greedy=False)
             line["w4a16_2p9B_b256"] = decode_entry(d4, f4, 256, 0, tb, world, hbm_peak, tf_peak)
             gm4.close()
+            torch.cuda.empty_cache()
+            # the quantised row of the headline model: 7.2B W4A16 at 1, 2 and 4 sequences
+            d5, gm5, f5 = build_model("7.2B", "w4a16", 0, local_rank, seed=0)
+            sweep = {}
+            for b in (1, 2, 4):
+                tb = time_decode(gm5, d5, b, steps2, warm2, world, rank, e2e=False, greedy=False)
+                sweep[f"b{b}"] = decode_entry(d5, f5, b, 0, tb, world, hbm_peak, tf_peak)
+            line["w4a16_7p2B"] = sweep
+            gm5.close()
             torch.cuda.empty_cache()
             line["quantised_parity"] = "unpinned against the reference (it has no quantised weights); format and kernels checked against this repository's oracle"
         else:

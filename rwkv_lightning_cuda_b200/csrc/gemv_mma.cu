@@ -70,6 +70,12 @@ __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1
 __device__ __forceinline__ void mbar_arrive_cta(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
+// (a & b) | c in one instruction.
+__device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t b, uint32_t c) {
+  uint32_t d;
+  asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
 __device__ __forceinline__ uint32_t h2u(__half2 h) { return *reinterpret_cast<uint32_t*>(&h); }
 __device__ __forceinline__ __half2 u2h(uint32_t u) { return *reinterpret_cast<__half2*>(&u); }
 
@@ -327,10 +333,10 @@ __global__ void __launch_bounds__(kWarps * 32, 1)
         const __half2 sixteenth = __floats2half2_rn(0.0625f, 0.0625f);
         auto dq = [&](uint32_t u, const __half2 sc, const __half2 zlo, const __half2 zhi, uint32_t (&o)[4]) {
           const uint32_t v = u >> 8;
-          o[0] = h2u(__hmul2(__hsub2(u2h((u & 0x000f000fu) | 0x64006400u), zlo), sc));
-          o[1] = h2u(__hmul2(__hfma2(u2h((u & 0x00f000f0u) | 0x64006400u), sixteenth, zhi), sc));
-          o[2] = h2u(__hmul2(__hsub2(u2h((v & 0x000f000fu) | 0x64006400u), zlo), sc));
-          o[3] = h2u(__hmul2(__hfma2(u2h((v & 0x00f000f0u) | 0x64006400u), sixteenth, zhi), sc));
+          o[0] = h2u(__hmul2(__hsub2(u2h(and_or(u, 0x000f000fu, 0x64006400u)), zlo), sc));
+          o[1] = h2u(__hmul2(__hfma2(u2h(and_or(u, 0x00f000f0u, 0x64006400u)), sixteenth, zhi), sc));
+          o[2] = h2u(__hmul2(__hsub2(u2h(and_or(v, 0x000f000fu, 0x64006400u)), zlo), sc));
+          o[3] = h2u(__hmul2(__hfma2(u2h(and_or(v, 0x00f000f0u, 0x64006400u)), sixteenth, zhi), sc));
         };
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
