@@ -446,6 +446,9 @@ def run_ours(args, rank, world, local_rank):
         return
     if world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline(args.model, args.wkv32)
+    # bounded waits inside the kernels that ran out during any of the timed work (0 = none; bits as in the header)
+    from rwkv_lightning_cuda_b200 import lib as _L
+    line["timeout_flags"] = int(_L.timeout_flags(clear=True))
     print(json.dumps(line))
 
 

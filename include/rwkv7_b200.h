@@ -231,6 +231,11 @@ int rwkv7_b200_model_workspace_bytes(const rwkv7_b200_model* m, size_t* out);
  * stream.  *flags: 1 weight-streaming GEMV, 2 tensor-core GEMM, 4 time-mix core, 8 wait probe, 16 all-reduce through peer memory (a rank of the tensor-parallel group did not show up).
  * clear != 0 resets the word.  Blocking (a 4-byte device-to-host copy on the current device). */
 int rwkv7_b200_timeout_flags(int clear, int* flags);
+/* Diagnostic (no counterpart in the reference): the record the tensor-core GEMM leaves when one of its bounded waits
+ * runs out for the first time since the record was cleared: {1, role (1 producer, 20/21/22 MMA thread waiting for an
+ * accumulator / a stage / a dequantised tile, 3 dequantisation, 4 epilogue), CTA, work unit, K-block counter, stages,
+ * units, product, M, N, K, format, row tile, K splits, 0}; all zero when nothing expired. */
+int rwkv7_b200_debug_timeout_detail(int* out15, int clear);
 /* Test aid: enqueues a one-thread kernel that polls a barrier nothing will ever complete `polls` times
  * (<= 2^20), then sets bit 8 of the failure word and returns.  No copy is in flight, nothing hangs. */
 int rwkv7_b200_debug_wait_probe(void* stream, unsigned polls);

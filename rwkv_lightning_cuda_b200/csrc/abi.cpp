@@ -197,6 +197,7 @@ int rwkv7_b200_timeout_flags(int clear, int* flags) {
   return rk::timeout_read(flags, clear != 0);
 }
 int rwkv7_b200_debug_last_gemm_splits(void) { return rk::gemm_last_max_splits(); }
+int rwkv7_b200_debug_timeout_detail(int* out15, int clear) { return rk::timeout_detail(out15, clear != 0); }
 int rwkv7_b200_debug_wait_probe(void* stream, unsigned polls) { return rk::wait_probe(st(stream), polls); }
 int rwkv7_b200_set_option(const char* name, int value) { return rk::set_option(name, value); }
 

@@ -94,6 +94,13 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
+// First expired wait of the device since the record was last cleared: who waited, and on what (status.cu).
+__device__ __forceinline__ void note_timeout(int* word, int role, int unit, int it, int stages, int total, int prob, int M, int N,
+                                             int K, int fmt, int Nt, int splits) {
+  if (!word || atomicCAS(word + 1, 0, 1) != 0) return;
+  const int v[13] = {role, static_cast<int>(blockIdx.x), unit, it, stages, total, prob, M, N, K, fmt, Nt, splits};
+  for (int i = 0; i < 13; ++i) word[2 + i] = v[i];
+}
 
 // ---- CTA-pair (cta_group::2) forms: two CTAs of a cluster work on one 256-channel tile.  Each loads its own 128
 // weight rows and HALF of the activation tile; the leader (cluster rank 0) issues the MMAs for both.
@@ -361,7 +368,11 @@ __global__ void __launch_bounds__(kThreads + (kQuant ? kDequantThreads : 0), 1)
         for (int kb = 0; kb < u.kblocks; ++kb, ++it) {
           const int s = it % g.stages;
           if (it >= pre) {
-            if (it >= g.stages && !mbar_wait(smem_u32(&empty_bar[s]), ((it / g.stages) - 1) & 1)) { ok = false; break; }
+            if (it >= g.stages && !mbar_wait(smem_u32(&empty_bar[s]), ((it / g.stages) - 1) & 1)) {
+              note_timeout(g.timeout, 1, ui, it, g.stages, g.total_units, u.prob, g.prob[u.prob].M, g.prob[u.prob].N, g.prob[u.prob].K, g.prob[u.prob].fmt, g.Nt, g.prob[u.prob].splits);
+              ok = false;
+              break;
+            }
             load_w(u, kb, s);
           }
           load_x(u, kb, s);
@@ -382,14 +393,21 @@ __global__ void __launch_bounds__(kThreads + (kQuant ? kDequantThreads : 0), 1)
         const int acc = n_unit & 1;
         if (n_unit >= 2) {  // the epilogue of the unit that used this accumulator two units ago has drained it
           ok = mbar_wait(smem_u32(&acc_empty[acc]), ((n_unit >> 1) - 1) & 1);
-          if (!ok) break;
+          if (!ok) {
+            note_timeout(g.timeout, 20, ui, it, g.stages, g.total_units, u.prob, g.prob[u.prob].M, g.prob[u.prob].N, g.prob[u.prob].K, g.prob[u.prob].fmt, g.Nt, g.prob[u.prob].splits);
+            break;
+          }
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         }
         const uint32_t tmem_acc = tmem_base + static_cast<uint32_t>(acc * g.Nt);
         for (int kb = 0; kb < u.kblocks; ++kb, ++it) {
           const int s = it % g.stages;
           ok = mbar_wait(smem_u32(&full_bar[s]), (it / g.stages) & 1);
-          if (kQuant && ok) ok = mbar_wait(smem_u32(&ready_bar[s]), (it / g.stages) & 1);  // the expanded tile is written
+          if (!ok) note_timeout(g.timeout, 21, ui, it, g.stages, g.total_units, u.prob, g.prob[u.prob].M, g.prob[u.prob].N, g.prob[u.prob].K, g.prob[u.prob].fmt, g.Nt, g.prob[u.prob].splits);
+          if (kQuant && ok) {
+            ok = mbar_wait(smem_u32(&ready_bar[s]), (it / g.stages) & 1);  // the expanded tile is written
+            if (!ok) note_timeout(g.timeout, 22, ui, it, g.stages, g.total_units, u.prob, g.prob[u.prob].M, g.prob[u.prob].N, g.prob[u.prob].K, g.prob[u.prob].fmt, g.Nt, g.prob[u.prob].splits);
+          }
           if (!ok) break;
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const uint64_t da = smem_desc(ring + s * stage_bytes), db = smem_desc(ring + s * stage_bytes + kWBytes);
@@ -424,10 +442,10 @@ __global__ void __launch_bounds__(kThreads + (kQuant ? kDequantThreads : 0), 1)
       const Prob& p = g.prob[u.prob];
       const int fmt = p.fmt, row = u.n0 + r, groups = p.K >> 7;
       for (int kb = 0; kb < u.kblocks; ++kb, ++it) {
-        if ((it & 1) != my_parity) continue;
         const int s = it % g.stages;
+        const bool mine = (it & 1) == my_parity;
         __half2 sc2 = __floats2half2_rn(0.f, 0.f), add2 = sc2;
-        if (fmt == 2 && row < p.N) {  // this K block's group parameters, requested before the wait for the tile
+        if (mine && fmt == 2 && row < p.N) {  // this K block's group parameters, requested before the wait for the tile
           const size_t gi = static_cast<size_t>(row) * groups + (((u.kb_begin + kb) * kBK) >> 7);
           const half sc = p.qscale[gi];
           const float z = __half2float(p.qzero[gi]);
@@ -436,7 +454,15 @@ __global__ void __launch_bounds__(kThreads + (kQuant ? kDequantThreads : 0), 1)
           add2 = __halves2half2(__hneg(__float2half_rn(1024.f + z)), __hneg(__float2half_rn(64.f + z)));
         }
         ok = mbar_wait(smem_u32(&full_bar[s]), (it / g.stages) & 1);
-        if (!ok) break;
+        // Every thread watches EVERY fill of every stage, also those the other group expands: a waiter that skipped a
+        // phase of a barrier would find the parity of the phase after it "already complete" while the one in between
+        // is still pending (the parity test cannot tell phase n + 2 from phase n), and expand a tile that has not
+        // landed -- seen as expired waits on launches where a later stage's tile arrived before an earlier one's.
+        if (ok && !mine) continue;
+        if (!ok) {
+          if (r == 0) note_timeout(g.timeout, 3, ui, it, g.stages, g.total_units, u.prob, g.prob[u.prob].M, g.prob[u.prob].N, g.prob[u.prob].K, g.prob[u.prob].fmt, g.Nt, g.prob[u.prob].splits);
+          break;
+        }
         if (fmt != 0) {
           unsigned char* stage = ring_g + static_cast<size_t>(s) * stage_bytes;
           uint4* dst = reinterpret_cast<uint4*>(stage + r * 128);
@@ -505,7 +531,10 @@ __global__ void __launch_bounds__(kThreads + (kQuant ? kDequantThreads : 0), 1)
       // the four warps must agree, or the named barriers below would not match up
       ok = epi_all(ok);
       if (!ok) {
-        if (t == 0) failed = 1;
+        if (t == 0) {
+          if (!failed) note_timeout(g.timeout, 4, ui, n_unit, g.stages, g.total_units, u.prob, g.prob[u.prob].M, g.prob[u.prob].N, g.prob[u.prob].K, g.prob[u.prob].fmt, g.Nt, g.prob[u.prob].splits);
+          failed = 1;
+        }
         break;
       }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");

@@ -16,6 +16,7 @@ namespace rk {
 enum TimeoutBit : int { kTimeoutGemv = 1, kTimeoutGemm = 2, kTimeoutTmix = 4, kTimeoutProbe = 8, kTimeoutPeer = 16 };
 int timeout_word(int** device_ptr);           // address of the word on the current device (looked up once per device)
 int* timeout_word_or_null();                  // the same for launchers: nullptr when the lookup fails
+int timeout_detail(int* out15, bool clear);   // status.cu: the first expired GEMM wait of the current device
 int timeout_read(int* flags, bool clear);     // blocking read (and reset) of the current device's word
 int timeout_status(int flags);                // kOk, or kTimeout with the message set
 int wait_probe(cudaStream_t stream, unsigned polls);  // a kernel whose bounded wait runs out by construction (tests)

@@ -12,7 +12,8 @@
 namespace rk {
 namespace {
 
-__device__ int g_timeout_word = 0;
+// word 0: the failure bits; words 1..15: where the first tensor-core GEMM wait ran out (a diagnostic, see timeout_detail)
+__device__ int g_timeout_word[16] = {0};
 
 std::mutex g_mu;
 int* g_word_ptr[64] = {nullptr};
@@ -56,6 +57,17 @@ int timeout_read(int* flags, bool clear) {
   if (s != kOk) return s;
   RK_CUDA(cudaMemcpy(flags, p, sizeof(int), cudaMemcpyDeviceToHost));
   if (clear && *flags) RK_CUDA(cudaMemset(p, 0, sizeof(int)));
+  return kOk;
+}
+
+// The record a GEMM kernel leaves with its first expired wait: {1, role (1 producer, 2 MMA, 3 dequantisation, 4
+// epilogue), CTA, work unit, K-block counter, stages, total units, product index, M, N, K, format, row tile, splits, 0}.
+int timeout_detail(int* out15, bool clear) {
+  int* p = nullptr;
+  int s = timeout_word(&p);
+  if (s != kOk) return s;
+  RK_CUDA(cudaMemcpy(out15, p + 1, 15 * sizeof(int), cudaMemcpyDeviceToHost));
+  if (clear) RK_CUDA(cudaMemset(p + 1, 0, 15 * sizeof(int)));
   return kOk;
 }
 

@@ -69,6 +69,7 @@ SIGNATURES = {
     "rwkv7_b200_model_workspace_bytes": [_vp, C.POINTER(C.c_size_t)],
     "rwkv7_b200_timeout_flags": [_i, C.POINTER(_i)],
     "rwkv7_b200_debug_wait_probe": [_vp, C.c_uint],
+    "rwkv7_b200_debug_timeout_detail": [C.POINTER(_i), _i],
     "rwkv7_b200_debug_last_gemm_splits": [],
     "rwkv7_b200_set_option": [C.c_char_p, _i],
     "rwkv7_b200_wkv_fp16_seq": [_vp, _i, _i, _i, _i] + [_vp] * 9,
@@ -125,6 +126,13 @@ def load_library() -> C.CDLL:
 def set_option(name: str, value: int) -> None:
     """rwkv7_b200_set_option: process-wide switches for measurements and tests (see the header)."""
     check(load_library().rwkv7_b200_set_option(name.encode(), int(value)))
+
+
+def timeout_detail(clear: bool = True):
+    """The record of the first expired GEMM wait (see the header); a list of 15 ints, all zero when nothing expired."""
+    buf = (C.c_int * 15)()
+    check(load_library().rwkv7_b200_debug_timeout_detail(buf, int(clear)))
+    return list(buf)
 
 
 def timeout_flags(clear: bool = True) -> int:

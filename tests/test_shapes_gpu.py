@@ -59,3 +59,33 @@ def test_1p5B_w8a16_fp32_state():
 @pytest.mark.parametrize("B,wkv32", [(256, False), (1, False), (8, True)])
 def test_2p9B_w4a16(B, wkv32):
     check("2.9B shape W4A16", D29, orc.FMT_W4A16, wkv32, B, (1,), 1 if B == 256 else 2)
+
+
+def test_2p9B_w4a16_many_rows_repeated_calls_never_expire_a_wait():
+    """The grouped launch that mixes packed (r, k, v) and fp16 (LoRA) products at 256 rows, 40 times over with fresh
+    state and logits buffers and other allocations moved in between (tile arrival order varies with where things
+    live): the device's failure word stays clear and all runs give the same logits.  (A dequantisation thread that
+    waited on only every other fill of a stage could take a tile for landed that had not.)"""
+    import torch
+    from rwkv_lightning_cuda_b200 import backend as bk, lib as L
+    d, _, gm = build_pair(orc.FMT_W4A16, False, dims=D29, oracle_model=False)
+    rng = np.random.default_rng(0)
+    toks = torch.from_numpy(rng.integers(0, d.vocab, (3, 256, 1)))
+    keep, first = [], None
+    L.timeout_flags(clear=True)
+    stream = torch.cuda.Stream()          # a stream of its own: the second and third step replay a CUDA graph
+    for call in range(40):
+        keep.append(torch.empty(int(rng.integers(1, 64)) * 1024 * 513, dtype=torch.uint8, device="cuda"))
+        st, lg = gm.create_state(256), bk.DeviceLogits()
+        torch.cuda.synchronize()
+        with torch.cuda.stream(stream):
+            for i in range(3):
+                gm.forward_decode(toks[i], st, lg, sync=False)
+        torch.cuda.synchronize()
+        assert L.timeout_flags(clear=True) == 0, (call, L.timeout_detail())
+        out = lg.values.cpu().numpy()
+        if first is None:
+            first = out
+        assert np.array_equal(out, first), call
+        del st, lg
+    gm.close()
