@@ -371,6 +371,7 @@ def run_ours(args, rank, world, local_rank):
         "vs_baseline": None, "dtype": "f16" if fmt == 0 else args.fmt, "data": "synthetic",
         "config": {"reduced": {"layers": args.layers, "vocab": args.vocab} if (args.layers or args.vocab) else None,
                    "workload": f"RWKV-7 {args.model} random-init, decode, batch {B} per GPU, {'fp32' if args.wkv32 else 'fp16'} WKV state, weights {args.fmt}",
+                   "options": args.option or None,
                    "batch_per_gpu": B, "parallelism": f"replicas x{world} (batch-sharded, no collective)",
                    "l2": "inputs larger than L2 (every step streams all weights)",
                    "quantised_parity": None if fmt == 0 else "unpinned against the reference (it has no quantised weights); format and kernels checked against this repository's oracle"},
@@ -475,6 +476,7 @@ def run_prefill(args, rank, world, local_rank):
         "warmup": min(args.warmup, n_chunks), "ms_per_step": ms / n_chunks, "higher_is_better": True,
         "scaling": "strong" if tp > 1 else "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
         "config": {"reduced": {"layers": args.layers, "vocab": args.vocab} if (args.layers or args.vocab) else None,
+                   "options": args.option or None,
                    "workload": f"RWKV-7 {args.model} random-init, prefill {n_chunks * T} tokens x {B} prompt(s) in chunks of {T}, "
                                f"{'fp32' if args.wkv32 else 'fp16'} WKV state, weights {args.fmt}",
                    "parallelism": f"tp{tp} (head-sharded, fp32 all-reduce after att.output and ffn.value)" if tp > 1 else f"replicas x{world}",
@@ -634,6 +636,8 @@ def main():
     ap.add_argument("--chunk", type=int, default=128)
     ap.add_argument("--layers", type=int, default=0, help="timing aid: override the depth (the line then says so)")
     ap.add_argument("--vocab", type=int, default=0, help="timing aid: override the vocabulary size")
+    ap.add_argument("--option", action="append", default=[], metavar="NAME=VALUE",
+                    help="measurement aid: a switch of rwkv7_b200_set_option (the line then lists it under config.options)")
     ap.add_argument("--tp", action="store_true", help="with --prefill: the ranks form one head-sharded tensor-parallel group")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
@@ -644,6 +648,11 @@ def main():
     if args.impl == "reference":
         run_reference(args, rank, world)
         return
+    if args.option:
+        from rwkv_lightning_cuda_b200 import lib as _L
+        for item in args.option:
+            name, _, value = item.partition("=")
+            _L.set_option(name, int(value))
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
