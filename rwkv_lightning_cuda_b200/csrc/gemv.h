@@ -236,6 +236,7 @@ __device__ __forceinline__ void stage_ln_mix(const GemvSeg& sg, Put put, float* 
 struct GemvMmaPlan {
   size_t smem_bytes;
   int grid, n_slots, x_pitch;  // x_pitch: bytes between rows of activations in shared memory
+  int blocks;                  // 16-channel blocks per tile (1, or 2 for quantised weights where shared memory allows)
 };
 bool gemv_mma_plan(GemvBatch& b, int M, GemvMmaPlan* plan);
 int gemv_mma_launch(cudaStream_t stream, const GemvBatch& b, int M, const GemvMmaPlan& plan);

@@ -119,6 +119,7 @@ def main():
     a.add_argument("--iters", type=int, default=40)
     a.add_argument("--launches", type=int, default=0)
     a.add_argument("--gemv-mma", type=int, default=None, help="the library's gemv_mma option (0, 1, 2)")
+    a.add_argument("--option", action="append", default=[], metavar="NAME=VALUE", help="any switch of rwkv7_b200_set_option")
     b = sub.add_parser("wkv")
     b.add_argument("--batch", type=int, default=1)
     b.add_argument("--tokens", type=int, default=128)
@@ -131,6 +132,9 @@ def main():
     torch.cuda.set_device(0)
     if getattr(args, "gemv_mma", None) is not None:
         L.set_option("gemv_mma", args.gemv_mma)
+    for item in getattr(args, "option", []):
+        name, _, value = item.partition("=")
+        L.set_option(name, int(value))
     print(json.dumps(linear(args) if args.op == "linear" else wkv(args)))
 
 

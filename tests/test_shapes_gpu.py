@@ -89,3 +89,32 @@ def test_2p9B_w4a16_many_rows_repeated_calls_never_expire_a_wait():
         assert np.array_equal(out, first), call
         del st, lg
     gm.close()
+
+
+@pytest.mark.parametrize("fmt,B", [(orc.FMT_W4A16, 1), (orc.FMT_W4A16, 4), (orc.FMT_W8A16, 2), (orc.FMT_F16, 2), (orc.FMT_F16, 1)])
+def test_7p2B_shape_small_batches_repeated_calls_are_identical(fmt, B):
+    """The five-launch decode path (weight boxes through per-warp rings, partial sums handed over between warps through
+    mbarriers) 30 times over with fresh buffers at shifting addresses: identical logits every time, no expired wait."""
+    import torch
+    from rwkv_lightning_cuda_b200 import backend as bk, lib as L
+    d, _, gm = build_pair(fmt, False, dims=D72, oracle_model=False)
+    rng = np.random.default_rng(1)
+    toks = torch.from_numpy(rng.integers(0, d.vocab, (4, B, 1)))
+    keep, first = [], None
+    L.timeout_flags(clear=True)
+    stream = torch.cuda.Stream()
+    for call in range(30):
+        keep.append(torch.empty(int(rng.integers(1, 64)) * 1024 * 513, dtype=torch.uint8, device="cuda"))
+        st, lg = gm.create_state(B), bk.DeviceLogits()
+        torch.cuda.synchronize()
+        with torch.cuda.stream(stream):
+            for i in range(4):
+                gm.forward_decode(toks[i], st, lg, sync=False)
+        torch.cuda.synchronize()
+        assert L.timeout_flags(clear=True) == 0, call
+        out = lg.values.cpu().numpy()
+        if first is None:
+            first = out
+        assert np.array_equal(out, first), call
+        del st, lg
+    gm.close()
