@@ -498,8 +498,8 @@ bool gemv_mma_plan(GemvBatch& b, int M, GemvMmaPlan* plan) {
   for (int i = 0; i < b.n_seg; ++i) quant = quant || b.seg[i].fmt != 0;
   // Quantised weights, one row of activations: tiles of 32 channels (two 4 KiB slots per warp) where the activations
   // leave room for them.  (Measured on the 7.2B W4A16 model: 2.03 -> 1.90 ms per step at one row, but 2.29 -> 2.54 ms at
-  // two rows and 2.96 -> 3.39 ms at four, although single matrices gain at any row count -- the launch that mixes
-  // packed projections with the fp16 LoRA matrices loses more than the others win.)
+  // two rows and 2.96 -> 3.39 ms at four, although large single matrices gain at any row count; which launch of the
+  // step loses was not isolated.)
   int blk = 1, slots = kMaxSlots;
   size_t fixed = 1024 + kPartialBytes + kSzBytes + static_cast<size_t>(M) * x_pitch;
   const size_t fixed_tall = 1024 + 2 * (kPartialBytes + kSzBytes) + static_cast<size_t>(M) * x_pitch;
