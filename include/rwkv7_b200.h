@@ -248,7 +248,8 @@ int rwkv7_b200_debug_last_gemm_splits(void);
  *   "fp16_tc_rows" n        the same for fp16 weights; 0 = built-in
  *   "decode_graphs" 0|1     decode steps replay a CUDA graph; default 1
  *   "wkv_chunked" 0|1       fp32-state WKV over 64 tokens or more runs in matrix form on the tensor cores; default 1
- *   "gemv_mma_tall" 0|1     the mma.sync kernel walks quantised weights in tiles of 32 channels for one row of activations; default 1
+ *   "gemv_mma_tall" 0|1|2   the mma.sync kernel walks quantised weights in tiles of 32 channels: 1 for one row of activations
+ *                           (default), 2 for 1..4 rows
  *   "tp_peer_ranks" n       tensor-parallel groups of up to n ranks all-reduce in the library's own kernel over peer-mapped
  *                           memory, larger ones through NCCL; default 2 (set before the first forward call)
  *   "gemv_mma" 0|1|2        linear layers of 1..4 rows: 0 scalar weight-streaming kernels only, 1 the mma.sync kernel (16-channel

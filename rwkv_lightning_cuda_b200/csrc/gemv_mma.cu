@@ -503,7 +503,7 @@ bool gemv_mma_plan(GemvBatch& b, int M, GemvMmaPlan* plan) {
   int blk = 1, slots = kMaxSlots;
   size_t fixed = 1024 + kPartialBytes + kSzBytes + static_cast<size_t>(M) * x_pitch;
   const size_t fixed_tall = 1024 + 2 * (kPartialBytes + kSzBytes) + static_cast<size_t>(M) * x_pitch;
-  if (quant && M == 1 && options().gemv_mma_tall && fixed_tall + static_cast<size_t>(kWarps) * 2 * 2 * kSlotBytes <= static_cast<size_t>(kSmemLimit)) {
+  if (quant && (M == 1 ? options().gemv_mma_tall >= 1 : options().gemv_mma_tall >= 2) && fixed_tall + static_cast<size_t>(kWarps) * 2 * 2 * kSlotBytes <= static_cast<size_t>(kSmemLimit)) {
     blk = 2;
     slots = 2;
     fixed = fixed_tall;

@@ -31,7 +31,7 @@ struct Options {
   int wkv_chunked = 1;       // 0: fp32-state WKV over a chunk runs the per-token scan instead of the matrix form
   int tp_peer_ranks = 2;     // tensor parallelism: largest group whose all-reduce runs in the library's kernel over peer-mapped
                              // memory (larger groups use NCCL); read when a model first needs its peer region
-  int gemv_mma_tall = 1;     // quantised weights on the mma.sync kernel: tiles of 32 channels where they fit (0: always 16)
+  int gemv_mma_tall = 1;     // quantised weights on the mma.sync kernel: tiles of 32 channels for one row (1) or for 1..4 rows (2) of activations
   int gemv_mma = 2;          // 1..4 rows: 0 = scalar weight-streaming kernels only, 1 = the tensor-core-instruction kernel for
                              // quantised weights, 2 = also for 2..4 rows of fp16 weights
 };

@@ -101,7 +101,7 @@ int set_option(const char* name, int value) {
       {"decode_graphs", &o.decode_graphs, 0, 1},         {"wkv_chunked", &o.wkv_chunked, 0, 1},
       {"gemv_mma", &o.gemv_mma, 0, 2},
       {"tp_peer_ranks", &o.tp_peer_ranks, 0, 64},
-      {"gemv_mma_tall", &o.gemv_mma_tall, 0, 1},
+      {"gemv_mma_tall", &o.gemv_mma_tall, 0, 2},
   };
   for (const Slot& s : slots) {
     if (std::strcmp(name, s.name) != 0) continue;
