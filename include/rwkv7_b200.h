@@ -248,12 +248,15 @@ int rwkv7_b200_debug_last_gemm_splits(void);
  *   "fp16_tc_rows" n        the same for fp16 weights; 0 = built-in
  *   "decode_graphs" 0|1     decode steps replay a CUDA graph; default 1
  *   "wkv_chunked" 0|1       fp32-state WKV over 64 tokens or more runs in matrix form on the tensor cores; default 1
- *   "gemv_mma_tall" 0|1|2   the mma.sync kernel walks quantised weights in tiles of 32 channels: 1 for one row of activations
- *                           (default), 2 for 1..4 rows
+ *   "gemv_mma_tall" 0..3    the mma.sync linear kernel walks the weights in tiles of 32 instead of 16 channels: 0 never, 1 one
+ *                           row of quantised weights, 2 one row of any format and up to three rows of fp16 (default), 3 wherever
+ *                           shared memory allows
  *   "tp_peer_ranks" n       tensor-parallel groups of up to n ranks all-reduce in the library's own kernel over peer-mapped
  *                           memory, larger ones through NCCL; default 2 (set before the first forward call)
- *   "gemv_mma" 0|1|2        linear layers of 1..4 rows: 0 scalar weight-streaming kernels only, 1 the mma.sync kernel (16-channel
- *                           weight tiles, dequantised once for all rows) for W8A16 / W4A16, 2 also for 2..4 rows of fp16; default 2
+ *   "gemv_mma" 0..4         linear layers of 1..4 rows: 0 scalar weight-streaming kernels only, 1 the mma.sync kernel (weight
+ *                           tiles by 2-D tensor copies, dequantised once for all rows) for W4A16 and for 2..4 rows of W8A16,
+ *                           2 also for 2..4 rows of fp16, 3 also for one row of fp16 / W8A16 in launches of 24 MB and more
+ *                           (default), 4 for every launch the kernel accepts
  * BAD_ARG for an unknown name or a value out of range. */
 int rwkv7_b200_set_option(const char* name, int value);
 

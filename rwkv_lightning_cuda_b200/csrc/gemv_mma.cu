@@ -496,14 +496,17 @@ bool gemv_mma_plan(GemvBatch& b, int M, GemvMmaPlan* plan) {
   const int x_pitch = max_k * 2 + 64;  // rows 64 bytes apart modulo 128: two rows of activations share no bank
   bool quant = false;
   for (int i = 0; i < b.n_seg; ++i) quant = quant || b.seg[i].fmt != 0;
-  // Quantised weights, one row of activations: tiles of 32 channels (two 4 KiB slots per warp) where the activations
-  // leave room for them.  (Measured on the 7.2B W4A16 model: 2.03 -> 1.90 ms per step at one row, but 2.29 -> 2.54 ms at
-  // two rows and 2.96 -> 3.39 ms at four, although large single matrices gain at any row count; which launch of the
-  // step loses was not isolated.)
+  // Tiles of 32 channels (two 4 KiB slots per warp) halve the per-box bookkeeping.  Measured per decode step of the 7.2B
+  // model: fp16 2.85 -> 2.59 ms at one row, 3.43 -> 3.25 at two, 3.72 -> 3.65 at three, but 4.01 -> 4.21 at four;
+  // W4A16 2.03 -> 1.90 ms at one row, but 2.29 -> 2.54 at two and 2.96 -> 3.39 at four (large single matrices gain at
+  // any row count; which launch of the step loses was not isolated).  Hence, by default (gemv_mma_tall = 2): one row of
+  // any format, and up to three rows of fp16.  1: one row of quantised weights only; 3: wherever they fit; 0: never.
+  const int tall_mode = options().gemv_mma_tall;
+  const bool want_tall = tall_mode >= 3 || (tall_mode == 2 && (M == 1 || (!quant && M <= 3))) || (tall_mode == 1 && quant && M == 1);
   int blk = 1, slots = kMaxSlots;
   size_t fixed = 1024 + kPartialBytes + kSzBytes + static_cast<size_t>(M) * x_pitch;
   const size_t fixed_tall = 1024 + 2 * (kPartialBytes + kSzBytes) + static_cast<size_t>(M) * x_pitch;
-  if (quant && (M == 1 ? options().gemv_mma_tall >= 1 : options().gemv_mma_tall >= 2) && fixed_tall + static_cast<size_t>(kWarps) * 2 * 2 * kSlotBytes <= static_cast<size_t>(kSmemLimit)) {
+  if (want_tall && fixed_tall + static_cast<size_t>(kWarps) * 2 * 2 * kSlotBytes <= static_cast<size_t>(kSmemLimit)) {
     blk = 2;
     slots = 2;
     fixed = fixed_tall;
@@ -592,6 +595,13 @@ int gemv_mma_launch(cudaStream_t stream, const GemvBatch& b, int M, const GemvMm
       case 2: s = launch(gemv_mma_kernel<2, true, 1>); break;
       case 3: s = launch(gemv_mma_kernel<3, true, 1>); break;
       default: s = launch(gemv_mma_kernel<4, true, 1>); break;
+    }
+  } else if (plan.blocks == 2) {
+    switch (M) {
+      case 1: s = launch(gemv_mma_kernel<1, false, 2>); break;
+      case 2: s = launch(gemv_mma_kernel<2, false, 2>); break;
+      case 3: s = launch(gemv_mma_kernel<3, false, 2>); break;
+      default: s = launch(gemv_mma_kernel<4, false, 2>); break;
     }
   } else {
     switch (M) {

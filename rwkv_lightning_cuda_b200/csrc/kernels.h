@@ -31,9 +31,11 @@ struct Options {
   int wkv_chunked = 1;       // 0: fp32-state WKV over a chunk runs the per-token scan instead of the matrix form
   int tp_peer_ranks = 2;     // tensor parallelism: largest group whose all-reduce runs in the library's kernel over peer-mapped
                              // memory (larger groups use NCCL); read when a model first needs its peer region
-  int gemv_mma_tall = 1;     // quantised weights on the mma.sync kernel: tiles of 32 channels for one row (1) or for 1..4 rows (2) of activations
-  int gemv_mma = 2;          // 1..4 rows: 0 = scalar weight-streaming kernels only, 1 = the tensor-core-instruction kernel for
-                             // quantised weights, 2 = also for 2..4 rows of fp16 weights
+  int gemv_mma_tall = 2;     // the mma.sync linear kernel walks the weights in tiles of 32 channels: 0 never, 1 one row of
+                             // quantised weights, 2 one row of any format and up to three rows of fp16, 3 wherever they fit
+  int gemv_mma = 3;          // 1..4 rows: 0 = scalar weight-streaming kernels only, 1 = the mma.sync kernel for quantised
+                             // weights, 2 = also for 2..4 rows of fp16, 3 = also for one row of fp16 / W8A16 in launches of
+                             // 24 MB and more, 4 = for every launch it accepts
 };
 Options& options();
 int set_option(const char* name, int value);

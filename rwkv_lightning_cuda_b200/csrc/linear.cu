@@ -230,11 +230,18 @@ int linear_batch(cudaStream_t stream, const LinearArgs* args, int n) {
   for (int i = n; i < kMaxSeg; ++i) b.seg[i] = b.seg[0];
   b.timeout = timeout_word_or_null();
 
-  // quantised weights and 2..4 rows of fp16 weights: 16-channel tiles on the warp-level tensor-core instruction
+  // The kernel built on the warp-level tensor-core instruction (gemv_mma.cu) takes, by default (option gemv_mma = 3):
+  // W4A16 at any row count; 2..4 rows of W8A16 and fp16; and ONE row of fp16 / W8A16 when the launch streams at least
+  // 24 MB -- there its 2-D tensor copies and lock-stepped warps stream faster than the per-warp bulk-copy rings below
+  // (7.2B fp16 decode 2.85 -> 2.59 ms per step, W8A16 2.12 -> 1.96 ms), while the launches of narrower models are
+  // latency-bound and stay on the scalar kernel (1.5B W8A16 0.81 against 0.84 ms, 0.1B 0.25 against 0.26 ms).
   const int mma_mode = options().gemv_mma;
-  // (one row of W8A16 stays on the scalar kernel: 7.2B decode 2.13 ms against 2.16-2.20 ms)
-  const bool w8_one = M == 1 && max_fmt == 1;
-  if (((mma_mode >= 1 && max_fmt > 0) || (mma_mode >= 2 && M >= 2)) && !w8_one) {
+  double launch_bytes = 0;
+  for (int i = 0; i < n; ++i) launch_bytes += static_cast<double>(args[i].N) * args[i].K * (args[i].fmt == 0 ? 2.0 : args[i].fmt == 1 ? 1.0 : 0.5);
+  const bool one_row_scalar = M == 1 && max_fmt <= 1;   // one row of fp16 / W8A16: the scalar kernel's home ground
+  const bool use_mma = mma_mode >= 4 || (one_row_scalar ? (mma_mode >= 3 && launch_bytes >= 24e6)
+                                                        : ((mma_mode >= 1 && max_fmt > 0) || (mma_mode >= 2 && M >= 2)));
+  if (use_mma) {
     GemvMmaPlan mp;
     if (gemv_mma_plan(b, M, &mp)) return gemv_mma_launch(stream, b, M, mp);
   }

@@ -99,9 +99,9 @@ int set_option(const char* name, int value) {
       {"gemm_cta_pair", &o.gemm_cta_pair, 0, 1},
       {"quant_tc_rows", &o.quant_tc_rows, 0, 1 << 20},   {"fp16_tc_rows", &o.fp16_tc_rows, 0, 1 << 20},
       {"decode_graphs", &o.decode_graphs, 0, 1},         {"wkv_chunked", &o.wkv_chunked, 0, 1},
-      {"gemv_mma", &o.gemv_mma, 0, 2},
+      {"gemv_mma", &o.gemv_mma, 0, 4},
       {"tp_peer_ranks", &o.tp_peer_ranks, 0, 64},
-      {"gemv_mma_tall", &o.gemv_mma_tall, 0, 2},
+      {"gemv_mma_tall", &o.gemv_mma_tall, 0, 3},
   };
   for (const Slot& s : slots) {
     if (std::strcmp(name, s.name) != 0) continue;

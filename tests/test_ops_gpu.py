@@ -213,21 +213,36 @@ def test_linear_one_to_four_rows_on_the_warp_level_tensor_core_instruction(ops, 
     assert_close16(got4, orc.linear_w4a16(x, q4, s4, z4), max_ulp=2, min_exact=0.97, what="linear_w4a16, mma", atol=atol)
     r4 = host(ops.linear_w4a16(dev(x), dev(q4), dev(s4), dev(z4), epilogue=L.EPI_RELU2))
     assert_close16(r4, orc.linear_w4a16(x, q4, s4, z4, epi=orc.EPI_RELU2), max_ulp=4, min_exact=0.95, what="linear_w4a16 relu2, mma", atol=atol)
-    L.set_option("gemv_mma", 2)
+    L.set_option("gemv_mma", 4)          # every launch the kernel accepts, whatever its size (fp16 and one row included)
     try:
         got = host(ops.linear_f16_orig(dev(x), dev(W)))
         lg = host(ops.linear_f16_orig(dev(x), dev(W), epilogue=L.EPI_F32))
+        got8b = host(ops.linear_w8a16(dev(x), dev(q8), dev(s8)))
+        L.set_option("gemv_mma_tall", 0)  # tiles of 16 channels
+        got16 = host(ops.linear_f16_orig(dev(x), dev(W)))
+        got4_16 = host(ops.linear_w4a16(dev(x), dev(q4), dev(s4), dev(z4)))
+        L.set_option("gemv_mma_tall", 3)
+        got4_32 = host(ops.linear_w4a16(dev(x), dev(q4), dev(s4), dev(z4)))
+        got32 = host(ops.linear_f16_orig(dev(x), dev(W)))
     finally:
-        L.set_option("gemv_mma", 2)
+        L.set_option("gemv_mma", 3)
+        L.set_option("gemv_mma_tall", 2)
     assert_close16(got, orc.linear_orig(x, W), max_ulp=2, min_exact=0.97, what="linear fp16, mma", atol=atol)
     assert (lg.astype(np.float16).view(np.uint16) == got.view(np.uint16)).all()
+    assert_close16(got8b, orc.linear_w8a16(x, q8, s8), max_ulp=2, min_exact=0.97, what="linear_w8a16, mma, any size", atol=atol)
+    # (the same sums in the same order when a row has a multiple of 16 boxes; otherwise the boxes fall to other warps)
+    exact = (K * 2) % 2048 == 0
+    assert_close16(got32, got16, max_ulp=0 if exact else 2, min_exact=1.0 if exact else 0.95, what="fp16, tiles of 32 vs 16", atol=0 if exact else atol)
+    exact4 = (K // 2) % 2048 == 0
+    assert_close16(got4_32, got4_16, max_ulp=0 if exact4 else 2, min_exact=1.0 if exact4 else 0.95, what="W4A16, tiles of 32 vs 16", atol=0 if exact4 else atol)
+    assert_close16(got4_32, orc.linear_w4a16(x, q4, s4, z4), max_ulp=2, min_exact=0.97, what="linear_w4a16, mma, tiles of 32", atol=atol)
     # the scalar kernels give the same values up to the order of the fp32 sums
     L.set_option("gemv_mma", 0)
     try:
         old8 = host(ops.linear_w8a16(dev(x), dev(q8), dev(s8)))
     finally:
-        L.set_option("gemv_mma", 2)
-    assert_close16(got8, old8, max_ulp=2, min_exact=0.95, what="mma vs scalar kernel", atol=atol)
+        L.set_option("gemv_mma", 3)
+    assert_close16(got8b, old8, max_ulp=2, min_exact=0.95, what="mma vs scalar kernel", atol=atol)
     assert L.timeout_flags(clear=True) == 0
 
 
