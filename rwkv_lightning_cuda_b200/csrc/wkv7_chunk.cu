@@ -138,12 +138,6 @@ __device__ __forceinline__ void fold(float (&acc)[NT][4], float (&lo)[NT][4]) {
     for (int e = 0; e < 4; ++e) { acc[nt][e] += lo[nt][e]; lo[nt][e] = 0.f; }
 }
 
-#ifdef RK_WKV_TRACE
-__device__ long long g_wkv_trace[64];
-#define RK_STAMP(i) do { if (blockIdx.x == 0 && tid == 0 && tb == 0) g_wkv_trace[i] = clock64(); } while (0)
-#else
-#define RK_STAMP(i) do { } while (0)
-#endif
 
 template <bool kAddW0>
 __global__ void __launch_bounds__(kThreadsChunk) wkv7_fp32_chunk_kernel(
@@ -182,7 +176,6 @@ __global__ void __launch_bounds__(kThreadsChunk) wkv7_fp32_chunk_kernel(
 
   for (int tb = 0; tb < T; tb += kBlock) {
     const int n_tok = min(kBlock, T - tb);
-    RK_STAMP(0);
     // the block's other token vectors are requested now (twenty 16-byte loads per thread) and used in step A3, after
     // the decays and their running products: their latency hides behind those two steps
     uint4 q[4][5];
@@ -230,7 +223,6 @@ __global__ void __launch_bounds__(kThreadsChunk) wkv7_fp32_chunk_kernel(
       }
     }
     __syncthreads();
-    RK_STAMP(1);
     // ---- A2: running products per column inside every sub-chunk: Kh <- P_t, Ah <- P_{t-1}
     for (int idx = tid; idx < kSub * kHead; idx += kThreadsChunk) {
       const int c = idx >> 6, j = idx & 63;
@@ -245,7 +237,6 @@ __global__ void __launch_bounds__(kThreadsChunk) wkv7_fp32_chunk_kernel(
       PL[c * kHead + j] = p;
     }
     __syncthreads();
-    RK_STAMP(2);
     // ---- A3: the scaled token vectors
     {
       const int j0 = (tid & 7) * 8;
@@ -294,7 +285,6 @@ __global__ void __launch_bounds__(kThreadsChunk) wkv7_fp32_chunk_kernel(
       }
     }
     __syncthreads();
-    RK_STAMP(3);
     // ---- B: the 16 x 16 matrices of sub-chunk `warp`: rows s (tokens of B^ / K^), columns t (tokens of A^ / R^)
     {
       const int c = warp;
@@ -328,7 +318,6 @@ __global__ void __launch_bounds__(kThreadsChunk) wkv7_fp32_chunk_kernel(
         }
       }
       __syncwarp();
-      RK_STAMP(4);
       // (I - N_ab)^-1, column by column: T[s][t] = [s == t] + sum_{m > s} N[s][m] T[m][t] (T is upper triangular, so the
       // terms with m > t vanish by themselves).  Lane t < 16 keeps column t in registers and walks s downwards; the
       // rows of N are read from shared memory (the same address for every lane).
@@ -347,7 +336,6 @@ __global__ void __launch_bounds__(kThreadsChunk) wkv7_fp32_chunk_kernel(
       }
     }
     __syncthreads();
-    RK_STAMP(5);
     // ---- C: the sequential part, sub-chunk after sub-chunk, every warp on its own 16 rows
     for (int c = 0; c < kSub; ++c) {
       const float* Ya = Ah + c * kL * kPitch;
@@ -364,12 +352,10 @@ __global__ void __launch_bounds__(kThreadsChunk) wkv7_fp32_chunk_kernel(
       mm_acc_a<2, 8>(X, lo, S, Ya, kPlaneTok, 1, kPitch, g, t4);
       mm_smem_a<2, 2, true>(X, lo, Vc, 0, 1, kPitch, m_nka, kPlaneMat, kMatPitch, 1, g, t4);
       fold(X, lo);
-      if (c == 0) RK_STAMP(8);
       // U = X (I - N_ab)^-1
       float U[2][4] = {};
       mm_acc_a<2, 2>(U, lo, X, m_t, kPlaneMat, kMatPitch, 1, g, t4);
       fold(U, lo);
-      if (c == 0) RK_STAMP(9);
       // Y = S R^^T + U M_br + V M_kr   (rows i, columns t)
       float Y[2][4] = {};
       mm_acc_a<2, 8>(Y, lo, S, Yr, kPlaneTok, 1, kPitch, g, t4);
@@ -384,7 +370,6 @@ __global__ void __launch_bounds__(kThreadsChunk) wkv7_fp32_chunk_kernel(
           Ysm[tt * kYPitch + i] = __float2half_rn(Y[nt][e]);
         }
       }
-      if (c == 0) RK_STAMP(10);
       // S = (S + U B^ + V K^) diag(P_L)     B(s, j) = B^[s][j], K^[s][j]   (eight column tiles: the cross terms go
       // straight into S, consecutive MMAs already hit different tiles)
       mm_acc_a<8, 2>(S, S, U, Xb, kPlaneTok, kPitch, 1, g, t4);
@@ -394,10 +379,8 @@ __global__ void __launch_bounds__(kThreadsChunk) wkv7_fp32_chunk_kernel(
         const float2 pl = *reinterpret_cast<const float2*>(PL + c * kHead + nt * 8 + 2 * t4);
         S[nt][0] *= pl.x; S[nt][1] *= pl.y; S[nt][2] *= pl.x; S[nt][3] *= pl.y;
       }
-      if (c == 0) RK_STAMP(11);
     }
     __syncthreads();
-    RK_STAMP(6);
     // ---- D: this block's outputs, coalesced
     for (int idx = tid; idx < kBlock * 8; idx += kThreadsChunk) {
       const int tl = idx >> 3, c8 = (idx & 7) * 8;
@@ -405,7 +388,6 @@ __global__ void __launch_bounds__(kThreadsChunk) wkv7_fp32_chunk_kernel(
         *reinterpret_cast<uint4*>(y + tok0 + static_cast<size_t>(tb + tl) * C + c8) = *reinterpret_cast<const uint4*>(Ysm + tl * kYPitch + c8);
     }
     __syncthreads();
-    RK_STAMP(7);
   }
 #pragma unroll
   for (int nt = 0; nt < 8; ++nt) {
@@ -418,11 +400,6 @@ constexpr size_t kChunkSmem = (9 * kPlaneTok + 8 * kPlaneMat + kSub * kHead) * s
 
 }  // namespace
 
-#ifdef RK_WKV_TRACE
-extern "C" int rwkv7_b200_debug_wkv_trace(long long* out) {
-  return cudaMemcpyFromSymbol(out, g_wkv_trace, sizeof(long long) * 64) == cudaSuccess ? 0 : 4;
-}
-#endif
 
 // Chunks of at least this many tokens take the matrix form (below it the per-token scan is faster: the matrix form
 // stages and prepares a block of 64 tokens at a time).
