@@ -128,8 +128,12 @@ __global__ void __launch_bounds__(kWarps * 32, 1)
   const uint32_t base = (dyn + 1023u) & ~1023u;  // the swizzle pattern is a function of the address: slots at 1 KiB
   const uint32_t ring = base + warp * n_slots * kSlot;
   const uint32_t part = base + kWarps * n_slots * kSlot;
-  const uint32_t szs = part + kPartialBytes * kBlk + warp * kMaxSlots * kSzSlot;
-  const uint32_t xs = part + (kPartialBytes + kSzBytes) * kBlk;
+  // (fp16-only launches meet at a CTA barrier per tile: two buffers of partial sums are enough, and there are no
+  // quantisation parameters to stage -- the room goes to the activations, so that more shapes fit tiles of 32 channels)
+  constexpr int kBufs = kQuant ? kPartBufs : 2;
+  constexpr uint32_t kPartBytes = kBufs * kWarps * 256 * kBlk;
+  const uint32_t szs = part + kPartBytes + warp * kMaxSlots * kSzSlot;
+  const uint32_t xs = part + kPartBytes + (kQuant ? kSzBytes * kBlk : 0);
   unsigned char* xs_ptr = smem_dyn + (xs - dyn);
 
   if (lane == 0) {
@@ -243,7 +247,7 @@ __global__ void __launch_bounds__(kWarps * 32, 1)
   // instead of 4.2 TB/s on a 65536 x 4096 matrix).
   constexpr bool kLockstep = !kQuant;
   auto reduce_tile = [&](int t) {
-    const int buf = t & (kPartBufs - 1);
+    const int buf = t & (kBufs - 1);
     if (!kLockstep && !dead && !wait_phase(smem_u32(&part_full[buf]), (t / kPartBufs) & 1)) give_up();
     if (!dead && tq < 2) {
 #pragma unroll
@@ -280,7 +284,7 @@ __global__ void __launch_bounds__(kWarps * 32, 1)
     // partial sums and goes on; the warp whose turn it is adds the PREVIOUS tile's sums, which by then are complete
     // as a rule, so that no warp waits for the others at a boundary.
     for (const int upto = min(c_tile, n_tiles); cur_tile < upto; ++cur_tile) {
-      const int buf = cur_tile & (kPartBufs - 1);
+      const int buf = cur_tile & (kBufs - 1);
       if (!kLockstep && cur_tile >= kPartBufs && !dead && !wait_phase(smem_u32(&part_free[buf]), (cur_tile / kPartBufs - 1) & 1)) give_up();
 #pragma unroll
       for (int b = 0; b < kBlk; ++b) {
@@ -504,8 +508,12 @@ bool gemv_mma_plan(GemvBatch& b, int M, GemvMmaPlan* plan) {
   const int tall_mode = options().gemv_mma_tall;
   const bool want_tall = tall_mode >= 3 || (tall_mode == 2 && (M == 1 || (!quant && M <= 3))) || (tall_mode == 1 && quant && M == 1);
   int blk = 1, slots = kMaxSlots;
-  size_t fixed = 1024 + kPartialBytes + kSzBytes + static_cast<size_t>(M) * x_pitch;
-  const size_t fixed_tall = 1024 + 2 * (kPartialBytes + kSzBytes) + static_cast<size_t>(M) * x_pitch;
+  auto fixed_bytes = [&](int blocks) {  // alignment slack + partial sums + quantisation parameters + activations
+    const size_t part = static_cast<size_t>(quant ? kPartBufs : 2) * kWarps * 256 * blocks;
+    return 1024 + part + (quant ? static_cast<size_t>(kSzBytes) * blocks : 0) + static_cast<size_t>(M) * x_pitch;
+  };
+  size_t fixed = fixed_bytes(1);
+  const size_t fixed_tall = fixed_bytes(2);
   if (want_tall && fixed_tall + static_cast<size_t>(kWarps) * 2 * 2 * kSlotBytes <= static_cast<size_t>(kSmemLimit)) {
     blk = 2;
     slots = 2;
@@ -551,7 +559,7 @@ bool gemv_mma_plan(GemvBatch& b, int M, GemvMmaPlan* plan) {
   return true;
 }
 
-bool gemv_mma_fits(int M, int K) {
+bool gemv_mma_fits(int M, int K) {  // (the quantised layout, which is the larger one)
   return M >= 1 && M <= 4 && 1024 + kPartialBytes + kSzBytes + static_cast<size_t>(M) * (K * 2 + 64) + static_cast<size_t>(kWarps) * 2 * kSlotBytes <=
                                  static_cast<size_t>(kSmemLimit);
 }
