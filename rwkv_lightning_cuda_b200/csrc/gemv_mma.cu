@@ -1,20 +1,23 @@
 // Weight-streaming linear layers for 1..4 rows of activations on the warp-level tensor-core instruction
 // (mma.sync m16n8k16, fp32 accumulation): 16 output channels of weights are the M side of the instruction, the rows
-// of activations (at most 4 of its 8 columns are used) the N side.  What this buys over one fused multiply-add per
-// weight and row (gemv_tma.cu): int8 / int4 weights are turned into halves with a few half2 operations per 32-bit
-// word, ONCE for all rows, and the multiply-adds cost one instruction per 16 x 16 weights, so that the kernel stays
-// bound by the weight stream for W8A16 / W4A16 and for 2..4 rows of any format.  The arithmetic is exact in the same
-// sense as the scalar kernels: products of halves accumulated in fp32, int8 as exact integers with the channel scale
-// on the sum, int4 as half((q - zero) * scale).
+// of activations (at most 4 of its 8 columns are used) the N side.  This is the kernel of the decode step: every
+// linear layer of a 7.2B step at 1..4 sequences runs here (fp16: 5.9 TB/s on a 134 MB matrix, 6.9 TB/s on the 537 MB
+// lm-head at one row); linear.cu says which launches go to the scalar kernel of gemv_tma.cu instead (one row of
+// fp16 / W8A16 in small launches).  What it buys over one fused multiply-add per weight and row: int8 / int4 weights
+// are turned into halves with a few half2 operations per 32-bit word ONCE for all rows, the multiply-adds cost one
+// instruction per 16 x 16 weights, the activations are halves (one 16-byte load per 16 bytes of fp16 weights), and the
+// 16 warps of a CTA work on the same weight rows at the same time.  The arithmetic is exact in the same sense as the
+// scalar kernels: products of halves accumulated in fp32, int8 as exact integers with the channel scale on the sum,
+// int4 as half((q - zero) * scale).
 //
 // Data movement: one 16-warp CTA per SM owns a contiguous range of output channels (a multiple of 4) and walks it in
-// tiles of 16 channels; the K extent of a tile is cut into boxes of 128 bytes, box b going to warp b mod 16.  A box
-// (16 channels x 128 bytes, 2 KiB) is fetched by ONE 2-D tensor copy with the 128-byte swizzle into the warp's own
-// ring (four slots, 128 KiB per CTA in flight; completion on an mbarrier), so a lane's 16-byte reads of the rows g and
-// g + 8 of the fragment layout are free of bank conflicts; a tile with fewer than 16 valid channels is fetched as
-// boxes of 4 channels, so no byte of another CTA's range is read.  The activations are staged once per CTA as halves
-// in the order the fragments want them (a lane's operands of one or two instructions are 16 contiguous bytes).  At
-// the end of a tile the warps leave their partial sums in shared memory and one warp adds them in warp order:
+// tiles of 16 or 32 channels; the K extent of a tile is cut into boxes of 128 bytes, box b going to warp b mod 16.  A
+// box (16 or 32 channels x 128 bytes, 2 or 4 KiB) is fetched by ONE 2-D tensor copy with the 128-byte swizzle into the
+// warp's own ring (8 KiB per warp, 128 KiB per CTA in flight; completion on an mbarrier), so a lane's 16-byte reads of
+// the rows g and g + 8 of the fragment layout are free of bank conflicts; a tile with fewer valid channels is fetched
+// as boxes of 4 channels, so no byte of another CTA's range is read.  The activations are staged once per CTA as
+// halves in the order the fragments want them (a lane's operands of one or two instructions are 16 contiguous bytes).
+// At the end of a tile the warps leave their partial sums in shared memory and one warp adds them in warp order:
 // results do not depend on timing.  W4A16: the scales and zeros of a box travel with it (4-byte asynchronous copies
 // into the slot, counted by the same mbarrier).  The ring fill is issued before the programmatic-dependency wait.
 #include <cuda.h>

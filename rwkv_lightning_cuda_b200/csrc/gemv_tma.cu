@@ -1,4 +1,5 @@
-// Weight-streaming GEMV (M <= 4; fp16, W8A16 or W4A16 weights, dequantised in registers) with the
+// Scalar weight-streaming GEMV (M <= 4; fp16, W8A16 or W4A16 weights, dequantised in registers; since gemv_mma.cu the
+// route of one-row launches that are small or whose shapes that kernel refuses -- linear.cu decides) with the
 // weights staged through shared memory by the bulk-copy engine: every warp owns a ring of kSlots buffers, one lane requests the next piece of
 // the warp's contiguous weight stream with cp.async.bulk (completion on an mbarrier), the warp
 // consumes pieces in order with 128-bit shared-memory loads and re-arms the slot it has just read.
