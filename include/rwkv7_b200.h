@@ -255,7 +255,7 @@ int rwkv7_b200_debug_last_gemm_splits(void);
  *                           memory, larger ones through NCCL; default 2 (set before the first forward call)
  *   "gemv_mma" 0..4         linear layers of 1..4 rows: 0 scalar weight-streaming kernels only, 1 the mma.sync kernel (weight
  *                           tiles by 2-D tensor copies, dequantised once for all rows) for W4A16 and for 2..4 rows of W8A16,
- *                           2 also for 2..4 rows of fp16, 3 also for one row of fp16 / W8A16 in large launches (8 / 24 MB and more)
+ *                           2 also for 2..4 rows of fp16, 3 also for one row of fp16 / W8A16 in large launches (8 MB and more, rows of 2 / 4 KiB and more)
  *                           (default), 4 for every launch the kernel accepts
  * BAD_ARG for an unknown name or a value out of range. */
 int rwkv7_b200_set_option(const char* name, int value);

@@ -35,7 +35,7 @@ struct Options {
                              // quantised weights, 2 one row of any format and up to three rows of fp16, 3 wherever they fit
   int gemv_mma = 3;          // 1..4 rows: 0 = scalar weight-streaming kernels only, 1 = the mma.sync kernel for quantised
                              // weights, 2 = also for 2..4 rows of fp16, 3 = also for one row of fp16 / W8A16 in large
-                             // launches (8 / 24 MB and more), 4 = for every launch it accepts
+                             // launches (8 MB and more, rows of 2 / 4 KiB and more), 4 = for every launch it accepts
 };
 Options& options();
 int set_option(const char* name, int value);

@@ -231,11 +231,12 @@ int linear_batch(cudaStream_t stream, const LinearArgs* args, int n) {
   b.timeout = timeout_word_or_null();
 
   // The kernel built on the warp-level tensor-core instruction (gemv_mma.cu) takes, by default (option gemv_mma = 3):
-  // W4A16 at any row count; 2..4 rows of W8A16 and fp16; and ONE row of fp16 / W8A16 when every weight row fills the 16
-  // warps of a CTA (2 KiB and more) and the launch streams at least 8 MB (fp16) or 24 MB (with W8A16) -- there its 2-D
-  // tensor copies and lock-stepped warps stream faster than the per-warp bulk-copy rings below (decode step of 7.2B fp16
-  // 2.85 -> 2.59 ms, 7.2B W8A16 2.12 -> 1.96 ms, 2.9B fp16 1.68 -> 1.54 ms, 1.5B fp16 0.94 -> 0.91 ms), while smaller
-  // launches are latency-bound and stay on the scalar kernel (1.5B W8A16 0.81 against 0.84 ms, 0.1B 0.25 against 0.26 ms).
+  // W4A16 at any row count; 2..4 rows of W8A16 and fp16; and ONE row of fp16 / W8A16 when the launch streams at least
+  // 8 MB and every weight row gives each of the 16 warps of a CTA a box (fp16: rows of 2 KiB and more) or two (W8A16:
+  // 4 KiB and more) -- there its 2-D tensor copies and warps working on the same rows stream faster than the per-warp
+  // bulk-copy rings below (decode step of 7.2B fp16 2.85 -> 2.59 ms, 7.2B W8A16 2.12 -> 1.96 ms, 2.9B fp16 1.68 -> 1.54 ms,
+  // 1.5B fp16 0.94 -> 0.91 ms), while smaller launches are latency-bound and stay on the scalar kernel (1.5B W8A16 0.81
+  // against 0.84 ms, 0.1B 0.25 against 0.26 ms).
   const int mma_mode = options().gemv_mma;
   double launch_bytes = 0;
   int min_row_bytes = 1 << 30;
@@ -245,7 +246,10 @@ int linear_batch(cudaStream_t stream, const LinearArgs* args, int n) {
     min_row_bytes = std::min(min_row_bytes, rb);
   }
   const bool one_row_scalar = M == 1 && max_fmt <= 1;   // one row of fp16 / W8A16: the scalar kernel's home ground
-  const bool large = min_row_bytes >= 2048 && launch_bytes >= (max_fmt == 0 ? 8e6 : 24e6);
+  long long launch_rows = 0;
+  for (int i = 0; i < n; ++i) launch_rows += args[i].N;
+  // (W8A16 also wants about a 32-channel tile per CTA: the 2048 x 8192 ffn.value of the 1.5B model is faster on the scalar kernel)
+  const bool large = launch_bytes >= 8e6 && min_row_bytes >= (max_fmt == 0 ? 2048 : 4096) && (max_fmt == 0 || launch_rows >= 4096);
   const bool use_mma = mma_mode >= 4 || (one_row_scalar ? (mma_mode >= 3 && large)
                                                         : ((mma_mode >= 1 && max_fmt > 0) || (mma_mode >= 2 && M >= 2)));
   if (use_mma) {
