@@ -111,7 +111,7 @@ int TpComm::ensure_peer(size_t count) {
   RK_REQUIRE(comm_, kNotReady, "tensor-parallel model used before rwkv7_b200_model_tp_init");
   // One-shot all-reduce: every rank reads every other rank's plane, (G - 1) x the message over NVLink per rank.  At
   // two ranks that is the minimum and beats NCCL (7.2B prefill chunk 5.81 -> 5.46 ms); at eight it moves four times
-  // what a reduce-scatter + all-gather moves and loses (6.75 against 5.9 ms), so from `tp_peer_ranks` + 1 ranks on the
+  // what a reduce-scatter + all-gather moves and loses (6.75 against 5.32 ms), so from `tp_peer_ranks` + 1 ranks on the
   // all-reduce stays with NCCL.
   if (peer_failed_ || size_ > kTpMaxRanks || size_ > options().tp_peer_ranks) return kOk;
   count = (count + 3) & ~static_cast<size_t>(3);
