@@ -37,6 +37,7 @@
 
 #include "common.cuh"
 #include "kernels.h"
+#include "tensormap.h"
 
 namespace rk {
 namespace {
@@ -641,21 +642,8 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const GroupDev g) {
 // ---------------------------------------------------------------------------------- host side
 namespace {
 
-using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                              const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeFn encode_fn() {
-  static EncodeFn fn = [] {
-    void* sym = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) != cudaSuccess ||
-        q != cudaDriverEntryPointSuccess)
-      return static_cast<EncodeFn>(nullptr);
-    return reinterpret_cast<EncodeFn>(sym);
-  }();
-  return fn;
-}
+using EncodeFn = TensorMapEncodeFn;
+inline EncodeFn encode_fn() { return tensor_map_encode_fn(); }
 
 // 2-D fp16 tensor [rows, cols] with row stride ld (elements), boxes of 64 columns x box_rows rows,
 // 128-byte swizzle, zero fill outside the tensor.  Encoded maps are kept: a model asks for the same few

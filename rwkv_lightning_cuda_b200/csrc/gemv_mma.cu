@@ -28,6 +28,7 @@
 
 #include "gemv.h"
 #include "kernels.h"
+#include "tensormap.h"
 
 namespace rk {
 namespace {
@@ -422,21 +423,8 @@ __global__ void __launch_bounds__(kWarps * 32, 1)
 }
 
 // ---------------------------------------------------------------------------------- host side
-using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                              const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeFn encode_fn() {
-  static EncodeFn fn = [] {
-    void* sym = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) != cudaSuccess ||
-        q != cudaDriverEntryPointSuccess)
-      return static_cast<EncodeFn>(nullptr);
-    return reinterpret_cast<EncodeFn>(sym);
-  }();
-  return fn;
-}
+using EncodeFn = TensorMapEncodeFn;
+inline EncodeFn encode_fn() { return tensor_map_encode_fn(); }
 
 struct MapKey {
   const void* base;
