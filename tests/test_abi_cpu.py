@@ -56,6 +56,25 @@ def test_bad_config_is_rejected_without_a_gpu(lib):
     assert lib.rwkv7_b200_model_destroy(h) == 0
 
 
+def test_options_are_named_ranged_and_documented(lib):
+    """rwkv7_b200_set_option: every switch the header documents is accepted at its documented default, values outside
+    its range and unknown names are refused with BAD_ARG (no GPU involved: the switches are host-side state)."""
+    import re
+    text = open(os.path.join(ROOT, "include", "rwkv7_b200.h")).read()
+    end = text.index("int rwkv7_b200_set_option")
+    block = text[text.rindex("/*", 0, end):end]
+    documented = re.findall(r'^ \*   "([a-z0-9_]+)"', block, flags=re.M)
+    defaults = dict(gemm_cta_pair=0, quant_tc_rows=0, fp16_tc_rows=0, decode_graphs=1, wkv_chunked=1, tp_peer_ranks=2,
+                    gemv_mma_tall=2, gemv_mma=3)
+    assert sorted(documented) == sorted(defaults), (documented, "header and test disagree about the options")
+    for name, value in defaults.items():
+        assert lib.rwkv7_b200_set_option(name.encode(), value) == 0, name
+    assert lib.rwkv7_b200_set_option(b"gemv_mma", 5) == 1 and b"gemv_mma" in lib.rwkv7_b200_last_error()
+    assert lib.rwkv7_b200_set_option(b"decode_graphs", -1) == 1
+    assert lib.rwkv7_b200_set_option(b"no_such_option", 0) == 1
+    assert lib.rwkv7_b200_set_option(None, 0) == 1
+
+
 def test_missing_library_fails_loudly(monkeypatch, tmp_path):
     from rwkv_lightning_cuda_b200 import lib as L
     monkeypatch.setattr(L, "_LIB", None)
